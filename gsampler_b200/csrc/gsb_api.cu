@@ -1,0 +1,100 @@
+// Library-level entry points: version, status strings, and the multi-layer
+// GraphSAGE sampler that chains the per-stage launches on one stream without
+// any host synchronisation (all intermediate sizes stay on the device).
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+static thread_local const char* g_last_cuda_error = "";
+
+__global__ void record_counts_kernel(const i64* seeds_ptr, const i64* unique_ptr, int B,
+                                     i64* counts /* {S, E, U}; E already written */) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    counts[0] = seeds_ptr[B];
+    counts[2] = unique_ptr[B];
+  }
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" int gsb_abi_version(void) { return 1; }
+
+extern "C" const char* gsb_status_string(int status) {
+  switch (status) {
+    case GSB_OK: return "ok";
+    case GSB_ERR_INVALID: return "invalid argument";
+    case GSB_ERR_UNSUPPORTED: return "request outside the supported range";
+    case GSB_ERR_WORKSPACE: return "workspace missing or too small";
+    case GSB_ERR_CUDA: return "CUDA runtime error";
+    default: return "unknown status";
+  }
+}
+
+extern "C" const char* gsb_last_cuda_error(void) {
+  cudaError_t e = cudaPeekAtLastError();
+  if (e != cudaSuccess) g_last_cuda_error = cudaGetErrorString(e);
+  return g_last_cuda_error;
+}
+
+static size_t align256(size_t x) { return (x + 255) & ~(size_t)255; }
+
+extern "C" size_t gsb_graphsage_workspace_bytes(int64_t B, int num_layers,
+                                                const gsb_layer_buffers* layers,
+                                                const int64_t* fanouts) {
+  if (!layers || !fanouts || num_layers < 1 || B < 1) return 0;
+  size_t need = 0;
+  for (int l = 0; l < num_layers; ++l) {
+    size_t a = align256(gsb_sample_cols_workspace_bytes(layers[l].S_cap, fanouts[l]));
+    size_t b = align256(gsb_batch_relabel_workspace_bytes(layers[l].S_cap, layers[l].E_cap, B));
+    if (a + b > need) need = a + b;
+  }
+  return need;
+}
+
+extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, int indices_dtype,
+                                    int64_t id_bound, const int64_t* seeds,
+                                    const int64_t* seeds_ptr, int64_t B, int64_t S0,
+                                    int num_layers, const int64_t* fanouts, uint64_t seed,
+                                    const gsb_layer_buffers* layers, int64_t* d_counts,
+                                    void* workspace, size_t workspace_bytes, int* d_err,
+                                    void* cuda_stream) {
+  if (!indptr || !indices || !seeds_ptr || !layers || !fanouts || !d_counts || num_layers < 1 ||
+      B < 1 || S0 < 0 || (S0 > 0 && !seeds))
+    return GSB_ERR_INVALID;
+  if (workspace_bytes < gsb_graphsage_workspace_bytes(B, num_layers, layers, fanouts) || !workspace)
+    return GSB_ERR_WORKSPACE;
+  // capacity chain: the node lists of layer l are the seeds of layer l+1
+  if (layers[0].S_cap < S0) return GSB_ERR_INVALID;
+  for (int l = 0; l + 1 < num_layers; ++l)
+    if (layers[l + 1].S_cap < layers[l].S_cap + layers[l].E_cap) return GSB_ERR_INVALID;
+
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  const int64_t* cur_seeds = seeds;
+  const int64_t* cur_ptr = seeds_ptr;
+  const int64_t* d_S = nullptr;
+  for (int l = 0; l < num_layers; ++l) {
+    const gsb_layer_buffers& L = layers[l];
+    const int64_t S_max = l == 0 ? S0 : L.S_cap;
+    const size_t ws_a = align256(gsb_sample_cols_workspace_bytes(L.S_cap, fanouts[l]));
+    int rc = gsb_sample_cols(indptr, indices, indices_dtype, cur_seeds, S_max, d_S, fanouts[l], 0,
+                             seed, (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
+                             d_counts + 3 * l + 1, workspace, ws_a, d_err, cuda_stream);
+    if (rc != GSB_OK) return rc;
+    rc = gsb_gather_i64(L.sub_indptr, cur_ptr, B + 1, L.edge_ptr, cuda_stream);
+    if (rc != GSB_OK) return rc;
+    rc = gsb_batch_relabel(cur_seeds, cur_ptr, B, S_max, L.rows, L.cols, L.edge_ptr, L.E_cap,
+                           id_bound, L.unique, L.S_cap + L.E_cap, L.unique_ptr, L.block_row,
+                           L.block_col, (char*)workspace + ws_a, workspace_bytes - ws_a, d_err,
+                           cuda_stream);
+    if (rc != GSB_OK) return rc;
+    record_counts_kernel<<<1, 32, 0, st>>>((const i64*)cur_ptr, (const i64*)L.unique_ptr, (int)B,
+                                           (i64*)d_counts + 3 * l);
+    cur_seeds = L.unique;
+    cur_ptr = L.unique_ptr;
+    d_S = L.unique_ptr + B;
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

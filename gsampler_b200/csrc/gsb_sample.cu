@@ -1,0 +1,200 @@
+// Per-column fanout sampling fused with column slicing (uniform).
+//
+// One CTA owns a tile of consecutive column slots.  Phase 1 (thread per
+// column) reads the seed and its indptr pair and derives the pick count; a
+// block scan plus the chained tile prefix turns the counts into global output
+// offsets in the same pass (no separate degree/scan kernels, no host read of
+// the edge count).  Phase 2 (thread per column) chooses the in-column
+// positions into shared memory.  Phase 3 (thread per OUTPUT edge) gathers the
+// row ids and writes the three output arrays fully coalesced: consecutive
+// threads write consecutive output elements, whatever the degree skew.
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+constexpr int SAMPLE_THREADS = 256;
+constexpr int SAMPLE_MAX_TILE_EDGES = 8192;  // picks staged in shared memory per tile
+
+struct SampleParams {
+  const i64* indptr;
+  const void* indices;
+  const i64* seeds;  // nullable
+  i64 S_max;
+  const i64* d_S;    // nullable
+  int K;
+  int replace;
+  u64 seed;
+  u32 stream;
+  i64* sub_indptr;
+  i64* out_rows;
+  i64* out_cols;  // nullable
+  i64* out_sel;
+  i64 E_cap;
+  i64* d_num_edges;  // nullable
+  u64* status;       // chained-prefix words, zeroed
+  int* ticket;       // tile ticket counter, zeroed
+  int* err;
+  int tile_cols;
+};
+
+template <typename IndexT>
+__global__ void __launch_bounds__(SAMPLE_THREADS)
+sample_tile_kernel(const SampleParams p) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int tc = p.tile_cols;
+  const int K = p.K;
+  // shared layout: in_start[tc] i64 | scan scratch[33] i64 | picks[tc*K] u32 |
+  //                 tmp[tc*K] u32 | owner[tc*K] u8
+  i64* s_in_start = reinterpret_cast<i64*>(smem_raw);
+  i64* s_scan = s_in_start + tc;
+  u32* s_pick = reinterpret_cast<u32*>(s_scan + 34);
+  u32* s_tmp = s_pick + (size_t)tc * K;
+  unsigned char* s_owner = reinterpret_cast<unsigned char*>(s_tmp + (size_t)tc * K);
+  __shared__ int s_tile;
+  __shared__ i64 s_base;
+
+  if (threadIdx.x == 0) s_tile = atomicAdd(p.ticket, 1);
+  __syncthreads();
+  const int tile = s_tile;
+  i64 S = p.S_max;
+  if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
+  const i64 num_tiles = S == 0 ? 1 : (S + tc - 1) / tc;
+  if (tile >= num_tiles) return;
+
+  const int lc = threadIdx.x;
+  const i64 slot = (i64)tile * tc + lc;
+  const bool valid = lc < tc && slot < S;
+  i64 in_start = 0;
+  u32 deg = 0;
+  int cnt = 0;
+  if (valid) {
+    const i64 c = p.seeds ? p.seeds[slot] : slot;
+    in_start = __ldg(p.indptr + c);
+    const i64 d = __ldg(p.indptr + c + 1) - in_start;
+    deg = (u32)d;
+    cnt = p.replace ? (d == 0 ? 0 : K) : (d < (i64)K ? (int)d : K);
+    s_in_start[lc] = in_start;
+  }
+  i64 total;
+  const i64 loff = block_exclusive_scan((i64)cnt, s_scan, &total);
+  if (threadIdx.x < 32) {
+    i64 base = chained_exclusive_prefix(p.status, tile, total, p.err);
+    if (threadIdx.x == 0) s_base = base;
+  }
+  // Phase 2: choose positions inside the column (thread per column).
+  if (valid && cnt > 0) {
+    const int o = (int)loff;
+    if (p.replace) {
+      Philox4 blk;
+      for (int k = 0; k < K; ++k) {
+        if ((k & 3) == 0) blk = stream_block(p.seed, p.stream, (u64)slot, (u32)k >> 2);
+        s_pick[o + k] = __umulhi(pick_word(blk, k), deg);
+        s_owner[o + k] = (unsigned char)lc;
+      }
+    } else if (deg <= (u32)K) {
+      for (int k = 0; k < cnt; ++k) {
+        s_pick[o + k] = (u32)k;
+        s_owner[o + k] = (unsigned char)lc;
+      }
+    } else {
+      // Floyd's subset selection: pick k is a uniform draw from [0, deg-K+k],
+      // replaced by deg-K+k itself when that value was already taken.  The
+      // running set lives in a transposed shared array (bank = column).
+      Philox4 blk;
+      for (int k = 0; k < K; ++k) {
+        if ((k & 3) == 0) blk = stream_block(p.seed, p.stream, (u64)slot, (u32)k >> 2);
+        const u32 j = deg - (u32)K + (u32)k;
+        const u32 t = __umulhi(pick_word(blk, k), j + 1u);
+        bool dup = false;
+        for (int m = 0; m < k; ++m) dup |= (s_tmp[m * tc + lc] == t);
+        const u32 v = dup ? j : t;
+        s_tmp[k * tc + lc] = v;
+        s_pick[o + k] = v;
+        s_owner[o + k] = (unsigned char)lc;
+      }
+    }
+  }
+  __syncthreads();
+  const i64 base = s_base;
+  if (valid) p.sub_indptr[slot] = base + loff;
+  if (tile == num_tiles - 1 && threadIdx.x == 0) {
+    p.sub_indptr[S] = base + total;
+    if (p.d_num_edges) *p.d_num_edges = base + total;
+  }
+  if (base + total > p.E_cap) {
+    if (threadIdx.x == 0) raise(p.err, ERRBIT_CAPACITY);
+    return;
+  }
+  // Phase 3: thread per output edge, coalesced stores.
+  const i64 col0 = (i64)tile * tc;
+  for (int o = threadIdx.x; o < (int)total; o += SAMPLE_THREADS) {
+    const int c = s_owner[o];
+    const i64 pos = s_in_start[c] + (i64)s_pick[o];
+    const i64 row = load_index<IndexT>(p.indices, pos);
+    p.out_rows[base + o] = row;
+    p.out_sel[base + o] = pos;
+    if (p.out_cols) p.out_cols[base + o] = col0 + c;
+  }
+}
+
+static int sample_tile_cols(i64 K) {
+  i64 tc = SAMPLE_MAX_TILE_EDGES / K;
+  if (tc > SAMPLE_THREADS) tc = SAMPLE_THREADS;
+  if (tc < 1) tc = 1;
+  return (int)tc;
+}
+
+static size_t sample_smem_bytes(int tc, i64 K) {
+  return sizeof(i64) * (size_t)(tc + 34) + (size_t)tc * K * (4 + 4 + 1) + 16;
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" size_t gsb_sample_cols_workspace_bytes(int64_t S_max, int64_t K) {
+  if (S_max < 0 || K < 1) return 0;
+  int tc = sample_tile_cols(K);
+  size_t tiles = (size_t)((S_max + tc - 1) / tc) + 1;
+  return 256 + tiles * sizeof(u64);
+}
+
+extern "C" int gsb_sample_cols(const int64_t* indptr, const void* indices, int indices_dtype,
+                               const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K,
+                               int replace, uint64_t seed, uint32_t stream, int64_t* sub_indptr,
+                               int64_t* out_rows, int64_t* out_cols, int64_t* out_sel,
+                               int64_t E_cap, int64_t* d_num_edges, void* workspace,
+                               size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (!indptr || !indices || !sub_indptr || S_max < 0 || E_cap < 0) return GSB_ERR_INVALID;
+  if (E_cap > 0 && (!out_rows || !out_sel)) return GSB_ERR_INVALID;
+  if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
+  if (K < 1) return GSB_ERR_INVALID;
+  if (K > SAMPLE_MAX_TILE_EDGES) return GSB_ERR_UNSUPPORTED;
+  if (workspace_bytes < gsb_sample_cols_workspace_bytes(S_max, K) || !workspace)
+    return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  const int tc = sample_tile_cols(K);
+  const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, tc);
+  GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
+  SampleParams p;
+  p.indptr = (const i64*)indptr; p.indices = indices; p.seeds = (const i64*)seeds;
+  p.S_max = S_max; p.d_S = (const i64*)d_S; p.K = (int)K; p.replace = replace ? 1 : 0;
+  p.seed = seed; p.stream = stream; p.sub_indptr = (i64*)sub_indptr; p.out_rows = (i64*)out_rows;
+  p.out_cols = (i64*)out_cols; p.out_sel = (i64*)out_sel; p.E_cap = E_cap;
+  p.d_num_edges = (i64*)d_num_edges;
+  p.ticket = (int*)workspace;
+  p.status = (u64*)((char*)workspace + 256);
+  p.err = d_err; p.tile_cols = tc;
+  const size_t smem = sample_smem_bytes(tc, K);
+  if (indices_dtype == GSB_I32) {
+    GSB_CUDA_OK(cudaFuncSetAttribute(sample_tile_kernel<int>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sample_tile_kernel<int><<<tiles, SAMPLE_THREADS, smem, st>>>(p);
+  } else {
+    GSB_CUDA_OK(cudaFuncSetAttribute(sample_tile_kernel<i64>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    sample_tile_kernel<i64><<<tiles, SAMPLE_THREADS, smem, st>>>(p);
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

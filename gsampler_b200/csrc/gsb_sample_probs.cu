@@ -1,0 +1,292 @@
+// Weighted per-column sampling.
+//
+// Without replacement: every edge e of a column gets the key log2(u_e)/p_e
+// (the logarithm of the A-Res key u^(1/p)); the K largest keys win.  A warp
+// owns a column.  Keys are never stored: u_e is draw e of the column slot's
+// counter-based stream, so each pass simply recomputes them.  The K-th largest
+// key is found by a 4-pass radix select (8 bits per pass, per-warp histogram in
+// shared memory); a last pass writes the winners in column order, ties on the
+// threshold key going to the lowest positions.  No scratch proportional to the
+// degrees, no sort, no limit of 32 on K.
+//
+// With replacement: K independent draws from the column's distribution by
+// streaming the running sum through the warp (no materialised CDF).
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+constexpr int WP_WARPS = 4;
+constexpr int WP_THREADS = WP_WARPS * 32;
+constexpr int WP_MAX_K = 1024;
+
+struct ProbParams {
+  const i64* indptr;
+  const void* indices;
+  const float* probs;
+  const i64* seeds;
+  i64 S_max;
+  const i64* d_S;
+  int K;
+  int replace;
+  u64 seed;
+  u32 stream;
+  const i64* sub_indptr;
+  i64* out_rows;
+  i64* out_cols;
+  i64* out_sel;
+  i64 E_cap;
+  int* err;
+};
+
+__device__ __forceinline__ u32 orderable(float f) {
+  u32 b = __float_as_uint(f);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
+
+// key of edge e (position inside the column) of column slot `slot`
+__device__ __forceinline__ u32 ares_key(u32 draw, float p) {
+  if (!(p > 0.f)) return 0u;  // never preferred; below every finite key
+  const float u = ((float)draw + 1.0f) * 2.3283064365386963e-10f;  // (0,1]
+  const float k = __log2f(u) / p;
+  const u32 o = orderable(k);
+  return o == 0u ? 1u : o;
+}
+
+template <typename IndexT>
+__global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbParams p) {
+  extern __shared__ u32 s_dyn[];
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  u32* hist = s_dyn + wid * 256;
+  float* targets = reinterpret_cast<float*>(s_dyn + WP_WARPS * 256) + wid * p.K;
+  i64 S = p.S_max;
+  if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
+  const int K = p.K;
+  for (i64 slot = (i64)blockIdx.x * WP_WARPS + wid; slot < S; slot += (i64)gridDim.x * WP_WARPS) {
+    const i64 c = p.seeds ? p.seeds[slot] : slot;
+    const i64 in_start = __ldg(p.indptr + c);
+    const i64 deg = __ldg(p.indptr + c + 1) - in_start;
+    const i64 out_start = p.sub_indptr[slot];
+    const i64 cnt = p.sub_indptr[slot + 1] - out_start;
+    if (cnt == 0) continue;
+    if (out_start + cnt > p.E_cap) { if (lane == 0) raise(p.err, ERRBIT_CAPACITY); continue; }
+    const float* pr = p.probs + in_start;
+    if (!p.replace && deg <= K) {
+      for (i64 k = lane; k < deg; k += 32) {
+        p.out_rows[out_start + k] = load_index<IndexT>(p.indices, in_start + k);
+        p.out_sel[out_start + k] = in_start + k;
+        if (p.out_cols) p.out_cols[out_start + k] = slot;
+      }
+      continue;
+    }
+    if (!p.replace) {
+      // ---- radix select of the K-th largest key
+      u32 prefix = 0, prefix_mask = 0;
+      u32 remaining = (u32)K;  // rank (1 = largest) still to locate inside the prefix class
+      for (int shift = 24; shift >= 0; shift -= 8) {
+        for (int i = lane; i < 256; i += 32) hist[i] = 0;
+        __syncwarp();
+        for (i64 e0 = (i64)lane * 4; e0 < deg; e0 += 128) {
+          const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (e0 + j < deg) {
+              const u32 key = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
+              if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            }
+          }
+        }
+        __syncwarp();
+        // walk the buckets from the top: lane owns 8 buckets
+        u32 mine = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mine += hist[255 - (lane * 8 + j)];
+        u32 inc = mine;  // inclusive scan over lanes (lane 0 = top buckets)
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          u32 t = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += t;
+        }
+        const u32 exc = inc - mine;
+        const unsigned hit = __ballot_sync(0xffffffffu, inc >= remaining);
+        const int owner = __ffs(hit) - 1;
+        u32 digit = 0, above = 0;
+        if (lane == owner) {
+          u32 run = exc;
+          for (int j = 0; j < 8; ++j) {
+            const u32 h = hist[255 - (lane * 8 + j)];
+            if (run + h >= remaining) { digit = 255u - (u32)(lane * 8 + j); above = run; break; }
+            run += h;
+          }
+        }
+        digit = __shfl_sync(0xffffffffu, digit, owner);
+        above = __shfl_sync(0xffffffffu, above, owner);
+        remaining -= above;
+        prefix |= digit << shift;
+        prefix_mask |= 255u << shift;
+        __syncwarp();
+      }
+      // prefix = threshold key; `remaining` = how many keys equal to it are taken
+      const u32 thr = prefix;
+      u32 ties_left = remaining;
+      i64 written = 0;
+      for (i64 base = 0; base < deg; base += 128) {
+        const i64 e0 = base + (i64)lane * 4;
+        u32 keys[4];
+        int ntie = 0;
+        if (e0 < deg) {
+          const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            keys[j] = e0 + j < deg ? ares_key(pick_word(blk, j), __ldg(pr + e0 + j)) : 0u;
+            if (e0 + j < deg && keys[j] == thr) ++ntie;
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) keys[j] = 0u;
+        }
+        // rank of this lane's ties among the warp's ties of this chunk
+        u32 tinc = (u32)ntie;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          u32 t = __shfl_up_sync(0xffffffffu, tinc, d);
+          if (lane >= d) tinc += t;
+        }
+        u32 tie_rank = tinc - (u32)ntie;
+        const u32 chunk_ties = __shfl_sync(0xffffffffu, tinc, 31);
+        bool take[4];
+        int ntake = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          take[j] = false;
+          if (e0 + j < deg) {
+            if (keys[j] > thr) take[j] = true;
+            else if (keys[j] == thr) { take[j] = tie_rank < ties_left; ++tie_rank; }
+          }
+          ntake += take[j] ? 1 : 0;
+        }
+        u32 sinc = (u32)ntake;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          u32 t = __shfl_up_sync(0xffffffffu, sinc, d);
+          if (lane >= d) sinc += t;
+        }
+        i64 o = out_start + written + (sinc - (u32)ntake);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (take[j]) {
+            p.out_rows[o] = load_index<IndexT>(p.indices, in_start + e0 + j);
+            p.out_sel[o] = in_start + e0 + j;
+            if (p.out_cols) p.out_cols[o] = slot;
+            ++o;
+          }
+        }
+        written += __shfl_sync(0xffffffffu, sinc, 31);
+        ties_left -= chunk_ties < ties_left ? chunk_ties : ties_left;
+      }
+      continue;
+    }
+    // ---- with replacement: K draws by streaming the running sum
+    float tot = 0.f;
+    for (i64 e = lane; e < deg; e += 32) tot += fmaxf(__ldg(pr + e), 0.f);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) tot += __shfl_xor_sync(0xffffffffu, tot, d);
+    for (int k = lane; k < K; k += 32) {
+      const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)k >> 2);
+      const float u = ((float)pick_word(blk, k) + 1.0f) * 2.3283064365386963e-10f;
+      targets[k] = u * tot;
+      p.out_sel[out_start + k] = -1;
+    }
+    __syncwarp();
+    float run = 0.f;
+    for (i64 base = 0; base < deg; base += 32) {
+      const i64 e = base + lane;
+      const float v = e < deg ? fmaxf(__ldg(pr + e), 0.f) : 0.f;
+      float inc = v;
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        float t = __shfl_up_sync(0xffffffffu, inc, d);
+        if (lane >= d) inc += t;
+      }
+      const float hi = run + __shfl_sync(0xffffffffu, inc, 31);
+      const bool last_chunk = base + 32 >= deg;
+      for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        const float t = k < K ? targets[k] : -1.f;
+        const bool mine = k < K && t > run && (t <= hi || last_chunk) && p.out_sel[out_start + k] < 0;
+        unsigned pending = __ballot_sync(0xffffffffu, mine);
+        while (pending) {
+          const int src = __ffs(pending) - 1;
+          pending &= pending - 1;
+          const float tt = __shfl_sync(0xffffffffu, t, src);
+          const unsigned ge = __ballot_sync(0xffffffffu, e < deg && run + inc >= tt);
+          i64 pick = ge ? base + (__ffs(ge) - 1) : deg - 1;
+          if (lane == 0) {
+            const int kk = k0 + src;
+            p.out_sel[out_start + kk] = in_start + pick;
+            p.out_rows[out_start + kk] = load_index<IndexT>(p.indices, in_start + pick);
+            if (p.out_cols) p.out_cols[out_start + kk] = slot;
+          }
+        }
+        __syncwarp();
+      }
+      run = hi;
+    }
+    // draws that fell past the accumulated total (rounding) or columns whose
+    // weights are all zero: fall back to the last / a uniform position
+    for (int k = lane; k < K; k += 32) {
+      if (p.out_sel[out_start + k] < 0) {
+        const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)k >> 2);
+        const i64 pick = tot > 0.f ? deg - 1 : (i64)__umulhi(pick_word(blk, k), (u32)deg);
+        p.out_sel[out_start + k] = in_start + pick;
+        p.out_rows[out_start + k] = load_index<IndexT>(p.indices, in_start + pick);
+        if (p.out_cols) p.out_cols[out_start + k] = slot;
+      }
+    }
+    __syncwarp();
+  }
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" size_t gsb_sample_cols_probs_workspace_bytes(int64_t S_max, int64_t K) {
+  if (S_max < 0 || K < 1) return 0;
+  return count_workspace_bytes(S_max);
+}
+
+extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices, int indices_dtype,
+                                     const float* probs, const int64_t* seeds, int64_t S_max,
+                                     const int64_t* d_S, int64_t K, int replace, uint64_t seed,
+                                     uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
+                                     int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
+                                     int64_t* d_num_edges, void* workspace, size_t workspace_bytes,
+                                     int* d_err, void* cuda_stream) {
+  if (!indptr || !indices || !probs || !sub_indptr || S_max < 0 || E_cap < 0 || K < 1)
+    return GSB_ERR_INVALID;
+  if (E_cap > 0 && (!out_rows || !out_sel)) return GSB_ERR_INVALID;
+  if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
+  if (K > WP_MAX_K) return GSB_ERR_UNSUPPORTED;
+  if (!workspace || workspace_bytes < gsb_sample_cols_probs_workspace_bytes(S_max, K))
+    return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  int rc = launch_count((const i64*)indptr, (const i64*)seeds, S_max, (const i64*)d_S, K,
+                        replace ? 1 : 0, (i64*)sub_indptr, (i64*)d_num_edges, workspace, d_err, st);
+  if (rc != GSB_OK) return rc;
+  if (S_max == 0) return GSB_OK;
+  ProbParams p;
+  p.indptr = (const i64*)indptr; p.indices = indices; p.probs = probs; p.seeds = (const i64*)seeds;
+  p.S_max = S_max; p.d_S = (const i64*)d_S; p.K = (int)K; p.replace = replace ? 1 : 0;
+  p.seed = seed; p.stream = stream; p.sub_indptr = (const i64*)sub_indptr;
+  p.out_rows = (i64*)out_rows; p.out_cols = (i64*)out_cols; p.out_sel = (i64*)out_sel;
+  p.E_cap = E_cap; p.err = d_err;
+  i64 blocks = (S_max + WP_WARPS - 1) / WP_WARPS;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  const size_t smem = sizeof(u32) * WP_WARPS * 256 + sizeof(float) * WP_WARPS * (size_t)K;
+  if (indices_dtype == GSB_I32)
+    sample_probs_kernel<int><<<(int)blocks, WP_THREADS, smem, st>>>(p);
+  else
+    sample_probs_kernel<i64><<<(int)blocks, WP_THREADS, smem, st>>>(p);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

@@ -1,0 +1,202 @@
+// Column slicing A[:, seeds] (all edges of the chosen columns) and small
+// gather utilities.
+//
+// count: thread per seed, degree -> block scan -> chained tile prefix, so the
+//        offsets come out of one pass.
+// fill : thread per OUTPUT edge; the owning column is found by a binary search
+//        in the (L2-resident) offset array, which keeps loads and stores
+//        coalesced however skewed the degrees are.
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+constexpr int SLICE_THREADS = 256;
+
+// Pick count of one column: K == 0 -> the whole column; otherwise min(deg, K)
+// without replacement, K (0 for an empty column) with replacement.
+__global__ void __launch_bounds__(SLICE_THREADS)
+count_kernel(const i64* __restrict__ indptr, const i64* __restrict__ seeds, i64 S_max,
+             const i64* __restrict__ d_S, i64 K, int replace, i64* __restrict__ sub_indptr,
+             i64* __restrict__ d_total, u64* status, int* ticket, int* err) {
+  __shared__ i64 s_scan[34];
+  __shared__ int s_tile;
+  __shared__ i64 s_base;
+  if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
+  __syncthreads();
+  const int tile = s_tile;
+  i64 S = S_max;
+  if (d_S) { i64 live = *d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
+  const i64 tiles = S == 0 ? 1 : (S + SLICE_THREADS - 1) / SLICE_THREADS;
+  if (tile >= tiles) return;
+  const i64 slot = (i64)tile * SLICE_THREADS + threadIdx.x;
+  i64 cnt = 0;
+  if (slot < S) {
+    const i64 c = seeds ? seeds[slot] : slot;
+    const i64 deg = __ldg(indptr + c + 1) - __ldg(indptr + c);
+    cnt = K == 0 ? deg : (replace ? (deg == 0 ? 0 : K) : (deg < K ? deg : K));
+  }
+  i64 total;
+  const i64 loff = block_exclusive_scan(cnt, s_scan, &total);
+  if (threadIdx.x < 32) {
+    i64 base = chained_exclusive_prefix(status, tile, total, err);
+    if (threadIdx.x == 0) s_base = base;
+  }
+  __syncthreads();
+  if (slot < S) sub_indptr[slot] = s_base + loff;
+  if (tile == tiles - 1 && threadIdx.x == 0) {
+    sub_indptr[S] = s_base + total;
+    if (d_total) *d_total = s_base + total;
+  }
+}
+
+size_t count_workspace_bytes(i64 S_max) {
+  return 256 + (size_t)((S_max + SLICE_THREADS - 1) / SLICE_THREADS + 1) * sizeof(u64);
+}
+
+int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
+                 int replace, i64* sub_indptr, i64* d_total, void* workspace, int* d_err,
+                 cudaStream_t st) {
+  const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, SLICE_THREADS);
+  GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
+  count_kernel<<<tiles, SLICE_THREADS, 0, st>>>(indptr, seeds, S_max, d_S, K, replace, sub_indptr,
+                                                d_total, (u64*)((char*)workspace + 256),
+                                                (int*)workspace, d_err);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+template <typename IndexT>
+__global__ void __launch_bounds__(SLICE_THREADS)
+slice_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices,
+                  const i64* __restrict__ seeds, i64 S, const i64* __restrict__ sub_indptr, i64 E,
+                  i64* __restrict__ out_rows, i64* __restrict__ out_cols,
+                  i64* __restrict__ out_sel, const i64* __restrict__ col_bptr, int B,
+                  i64 encoding_size) {
+  for (i64 e = (i64)blockIdx.x * SLICE_THREADS + threadIdx.x; e < E;
+       e += (i64)gridDim.x * SLICE_THREADS) {
+    // column slot = last i with sub_indptr[i] <= e
+    i64 lo = 0, hi = S;
+    while (hi - lo > 1) {
+      i64 mid = (lo + hi) >> 1;
+      if (__ldg(sub_indptr + mid) <= e) lo = mid; else hi = mid;
+    }
+    const i64 c = seeds[lo];
+    const i64 pos = __ldg(indptr + c) + (e - __ldg(sub_indptr + lo));
+    i64 row = load_index<IndexT>(indices, pos);
+    if (encoding_size > 0 && col_bptr) row += (i64)find_segment(col_bptr, B, lo) * encoding_size;
+    out_rows[e] = row;
+    out_sel[e] = pos;
+    if (out_cols) out_cols[e] = lo;
+  }
+}
+
+__global__ void gather_i64_kernel(const i64* __restrict__ src, const i64* __restrict__ idx, i64 n,
+                                  i64* __restrict__ out) {
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (i64)gridDim.x * blockDim.x)
+    out[i] = src[idx[i]];
+}
+
+// out[e] = segment (column) that owns position e of a CSC/CSR offset array
+__global__ void expand_indptr_kernel(const i64* __restrict__ indptr, i64 nseg, i64 nnz,
+                                     i64* __restrict__ out) {
+  for (i64 e = (i64)blockIdx.x * blockDim.x + threadIdx.x; e < nnz;
+       e += (i64)gridDim.x * blockDim.x) {
+    i64 lo = 0, hi = nseg;
+    while (hi - lo > 1) {
+      i64 mid = (lo + hi) >> 1;
+      if (__ldg(indptr + mid) <= e) lo = mid; else hi = mid;
+    }
+    out[e] = lo;
+  }
+}
+
+// indptr[k] = number of keys < k, for k in [0, nkeys]; keys sorted ascending
+__global__ void indptr_from_sorted_kernel(const i64* __restrict__ keys, i64 nnz, i64 nkeys,
+                                          i64* __restrict__ indptr) {
+  for (i64 k = (i64)blockIdx.x * blockDim.x + threadIdx.x; k <= nkeys;
+       k += (i64)gridDim.x * blockDim.x) {
+    i64 lo = 0, hi = nnz;  // first position with keys[pos] >= k
+    while (lo < hi) {
+      i64 mid = (lo + hi) >> 1;
+      if (__ldg(keys + mid) < k) lo = mid + 1; else hi = mid;
+    }
+    indptr[k] = lo;
+  }
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nnz, int64_t* out,
+                                 void* cuda_stream) {
+  if (nnz == 0) return GSB_OK;
+  if (!indptr || !out || nseg <= 0 || nnz < 0) return GSB_ERR_INVALID;
+  i64 blocks = (nnz + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  expand_indptr_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
+      (const i64*)indptr, nseg, nnz, (i64*)out);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nkeys,
+                                      int64_t* indptr, void* cuda_stream) {
+  if (!indptr || nkeys < 0 || nnz < 0 || (nnz > 0 && !keys)) return GSB_ERR_INVALID;
+  i64 blocks = (nkeys + 1 + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  indptr_from_sorted_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
+      (const i64*)keys, nnz, nkeys, (i64*)indptr);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" size_t gsb_slice_cols_workspace_bytes(int64_t S) {
+  if (S < 0) return 0;
+  return count_workspace_bytes(S);
+}
+
+extern "C" int gsb_slice_cols_count(const int64_t* indptr, const int64_t* seeds, int64_t S,
+                                    int64_t* sub_indptr, void* workspace, size_t workspace_bytes,
+                                    int* d_err, void* cuda_stream) {
+  if (!indptr || !sub_indptr || S < 0 || (S > 0 && !seeds)) return GSB_ERR_INVALID;
+  if (!workspace || workspace_bytes < gsb_slice_cols_workspace_bytes(S)) return GSB_ERR_WORKSPACE;
+  return launch_count((const i64*)indptr, (const i64*)seeds, S, nullptr, 0, 0, (i64*)sub_indptr,
+                      nullptr, workspace, d_err, (cudaStream_t)cuda_stream);
+}
+
+extern "C" int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, int indices_dtype,
+                                   const int64_t* seeds, int64_t S, const int64_t* sub_indptr,
+                                   int64_t E, int64_t* out_rows, int64_t* out_cols,
+                                   int64_t* out_sel, const int64_t* col_bptr, int64_t B,
+                                   int64_t encoding_size, void* cuda_stream) {
+  if (E == 0) return GSB_OK;
+  if (!indptr || !indices || !seeds || !sub_indptr || !out_rows || !out_sel || S <= 0 || E < 0)
+    return GSB_ERR_INVALID;
+  if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  i64 blocks = (E + SLICE_THREADS - 1) / SLICE_THREADS;
+  if (blocks > 148 * 64) blocks = 148 * 64;
+  if (indices_dtype == GSB_I32)
+    slice_fill_kernel<int><<<(int)blocks, SLICE_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, (const i64*)seeds, S, (const i64*)sub_indptr, E,
+        (i64*)out_rows, (i64*)out_cols, (i64*)out_sel, (const i64*)col_bptr, (int)B, encoding_size);
+  else
+    slice_fill_kernel<i64><<<(int)blocks, SLICE_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, (const i64*)seeds, S, (const i64*)sub_indptr, E,
+        (i64*)out_rows, (i64*)out_cols, (i64*)out_sel, (const i64*)col_bptr, (int)B, encoding_size);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_gather_i64(const int64_t* src, const int64_t* idx, int64_t n, int64_t* out,
+                              void* cuda_stream) {
+  if (n == 0) return GSB_OK;
+  if (!src || !idx || !out || n < 0) return GSB_ERR_INVALID;
+  i64 blocks = (n + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  gather_i64_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
+      (const i64*)src, (const i64*)idx, n, (i64*)out);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

@@ -1,0 +1,206 @@
+"""``BatchMatrix``: super-batch flavour of :class:`Matrix` (mirror of
+python/gs/matrix_api/batch_matrix.py:39-263 in gSampler).  Slices are written
+``A[:, seeds::seeds_ptr]``: ``seeds`` concatenates the minibatches and ``seeds_ptr`` holds
+their offsets.
+
+Differences from the reference: blocks are :class:`Block` objects; with ``encoding=False``
+the column slice is lazy and fuses with a following ``individual_sampling`` (the reference
+obtains this through ``batch_fuse_slicing_and_sampling``, python/gs/jit/optimize.py:280-325);
+``individual_sampling`` with probabilities calls the registered
+``_CAPI_BatchRowSamplingProbs`` (the reference calls an unregistered name,
+batch_matrix.py:183-184); ``all_nodes`` + ``to_dgl_block`` share one relabel pass.
+"""
+import torch
+
+from ..format import _COO, _CSC, _CSR
+from ..ops import gsddmm, gspmm
+from ..utils import create_block_from_coo
+from .matrix import Matrix, data_index
+
+
+def batch_gen_block(frontier_list, coo_row_list, coo_col_list, coo_eids, coo_ptr, edata, col_counts):
+    edata_list = {}
+    if coo_eids is not None:
+        edata_list["_ID"] = torch.ops.gs_ops._CAPI_BatchSplitByOffset(coo_eids, coo_ptr)
+    for key, value in edata.items():
+        edata_list[key] = torch.ops.gs_ops._CAPI_BatchSplitByOffset(value, coo_ptr)
+    block_list = []
+    for i in range(len(frontier_list)):
+        block = create_block_from_coo(coo_row_list[i], coo_col_list[i], frontier_list[i].numel(),
+                                      col_counts[i])
+        block.srcdata["_ID"] = frontier_list[i]
+        for key, value in edata_list.items():
+            block.edata[key] = value[i]
+        block_list.append(block)
+    return block_list
+
+
+class BatchMatrix(Matrix):
+
+    def __init__(self, graph=None, row_ndata=None, col_ndata=None, edata=None, encoding=True):
+        super().__init__(graph, row_ndata, col_ndata, edata, False)
+        self.encoding = encoding
+        self._pending_ptr = None
+
+    def _new(self):
+        return BatchMatrix(encoding=self.encoding)
+
+    def load_from_matrix(self, matrix, encoding=True):
+        self.__init__(matrix._graph, matrix.row_ndata, matrix.col_ndata, matrix.edata)
+        self.encoding = encoding
+
+    def _materialize(self):
+        if self._pending is not None:
+            parent, seeds, pedata = self._pending
+            ptr = self._pending_ptr
+            self._pending = None
+            graph, edge_index = parent._CAPI_BatchColSlicing(seeds, ptr, False)
+            self._g = graph
+            for key, value in pedata.items():
+                self._edata[key] = data_index(value, edge_index)
+
+    def __getitem__(self, data):
+        assert len(data) == 2
+        r, c = data
+        assert isinstance(r, slice) and isinstance(c, slice)
+        r_slice, r_ptr, c_slice, c_ptr = r.start, r.step, c.start, c.step
+        has_r = r_slice is not None and r_ptr is not None
+        has_c = c_slice is not None and c_ptr is not None
+        ret = self._new()
+
+        if has_r and has_c:
+            graph, edge_index = self._graph._CAPI_BatchColRowSlcing(c_slice, c_ptr, r_slice, r_ptr)
+            if "_ID" in self.row_ndata or "_ID" in self.col_ndata:
+                raise NotImplementedError
+            ret._graph = graph
+            ret.row_ndata["_ID"] = r_slice
+            ret.col_ndata["_ID"] = c_slice
+            for key, value in self.edata.items():
+                ret._edata[key] = data_index(value, edge_index)
+            for key, value in self.row_ndata.items():
+                ret.row_ndata[key] = value[r_slice]
+            for key, value in self.col_ndata.items():
+                ret.col_ndata[key] = value[c_slice]
+            return ret
+
+        if has_r and not has_c:
+            graph, edge_index = self._graph._CAPI_BatchRowSlicing(r_slice, r_ptr)
+            ret._graph = graph
+            if "_ID" not in self.row_ndata:
+                ret.row_ndata["_ID"] = r_slice
+            for key, value in self.edata.items():
+                ret._edata[key] = data_index(value, edge_index)
+            for key, value in self.row_ndata.items():
+                ret.row_ndata[key] = value[r_slice]
+            for key, value in self.col_ndata.items():
+                ret.col_ndata[key] = value
+            return ret
+
+        if has_c and not has_r:
+            if "_ID" in self.col_ndata:
+                raise NotImplementedError
+            ret.col_ndata["_ID"] = c_slice
+            for key, value in self.col_ndata.items():
+                ret.col_ndata[key] = value[c_slice]
+            if self.encoding:
+                graph, edge_index = self._graph._CAPI_BatchColSlicing(c_slice, c_ptr, True)
+                if "_ID" in self.row_ndata:
+                    raise NotImplementedError
+                row_ids, _ = graph._CAPI_BatchGetRows()
+                ret.row_ndata["_ID"] = row_ids
+                ret._graph = graph
+                for key, value in self.edata.items():
+                    ret._edata[key] = data_index(value, edge_index)
+            else:
+                ret._pending = (self._graph, c_slice, self.edata)
+                ret._pending_ptr = c_ptr
+            for key, value in self.row_ndata.items():
+                ret.row_ndata.setdefault(key, value)
+            return ret
+
+        raise NotImplementedError
+
+    def individual_sampling(self, K, probs, replace):
+        ret = self._new()
+        if self._pending is not None and probs is None:
+            parent, seeds, pedata = self._pending
+            subgraph, edge_index = parent._CAPI_BatchFusedSlicingSampling(
+                seeds, self._pending_ptr, K, replace)
+            src_edata = pedata
+        else:
+            if probs is None:
+                subgraph, edge_index = self._graph._CAPI_BatchRowSampling(K, replace)
+            else:
+                subgraph, edge_index = self._graph._CAPI_BatchRowSamplingProbs(K, replace, probs)
+            src_edata = self.edata
+        ret._graph = subgraph
+        ret.row_ndata = self.row_ndata
+        ret.col_ndata = self.col_ndata
+        for key, value in src_edata.items():
+            ret._edata[key] = value[edge_index]
+        return ret
+
+    def collective_sampling(self, K, probs, probs_ptr, replace):
+        if probs is None:
+            raise NotImplementedError
+        selected_index, index_ptr = torch.ops.gs_ops._CAPI_BatchListSamplingWithProbs(
+            probs, K, replace, probs_ptr)
+        return self[selected_index::index_ptr, :], selected_index
+
+    def to_dgl_block(self, prefetch_edata={}):
+        (frontiers, frontiers_ptr, coo_row, coo_col, coo_eids,
+         coo_bptr) = self._graph._CAPI_BatchGraphRelabel(
+             self.col_ndata.get("_ID", self.null_tensor), self.row_ndata.get("_ID", self.null_tensor))
+        split = torch.ops.gs_ops._CAPI_BatchSplitByOffset
+        frontier_list = split(frontiers, frontiers_ptr)
+        coo_row_list = split(coo_row, coo_bptr)
+        coo_col_list = split(coo_col, coo_bptr)
+        col_counts = self._graph._CAPI_BatchGetColCounts()
+        assign_edata = {key: self.edata[key] for key in prefetch_edata}
+        return batch_gen_block(frontier_list, coo_row_list, coo_col_list, coo_eids, coo_bptr,
+                               assign_edata, col_counts)
+
+    def sum(self, key, axis) -> torch.Tensor:
+        rhs = self.edata[key]
+        if axis == 0:
+            return gspmm(self, "copy_rhs", "sum", None, rhs, 0, _COO)
+        elif axis == 1:
+            return gspmm(self, "copy_rhs", "sum", None, rhs, 2, _COO)
+        raise ValueError("axis should be 0 or 1")
+
+    def div(self, key, divisor, axis):
+        ret_m = BatchMatrix(self._graph, self.row_ndata, self.col_ndata, self.edata.copy(),
+                            self.encoding)
+        lhs = self.edata[key]
+        if axis == 0:
+            ret_data = gsddmm(ret_m, "div", lhs, divisor, "e", "v", _COO)
+        elif axis == 1:
+            ret_data = gsddmm(ret_m, "div", lhs, divisor, "e", "u", _COO)
+        else:
+            raise ValueError("axis should be 0 or 1")
+        ret_m._edata[key] = ret_data
+        return ret_m
+
+    def all_nodes(self):
+        return self._graph._CAPI_BatchGetValidNodes(self.col_ndata.get("_ID", self.null_tensor),
+                                                    self.row_ndata.get("_ID", self.null_tensor))
+
+    def all_rows(self):
+        return self._graph._CAPI_BatchGetRows()
+
+    def all_cols(self):
+        return self._graph._CAPI_BatchGetCols()
+
+    def random_walk(self, seeds, seeds_ptr, walk_length):
+        return torch.ops.gs_ops._CAPI_BatchSplitByOffset(
+            self._graph._CAPI_RandomWalk(seeds, walk_length), seeds_ptr)
+
+    def node2vec(self, seeds, seeds_ptr, walk_length, p, q):
+        return torch.ops.gs_ops._CAPI_BatchSplitByOffset(
+            self._graph._CAPI_Node2Vec(seeds, walk_length, p, q), seeds_ptr)
+
+    def graphsage(self, seeds, seeds_ptr, fanouts):
+        """All layers of the GraphSAGE super-batch sampler in one native call (no host
+        synchronisation between layers).  Returns the per-layer tensors of
+        ``Graph._CAPI_BatchGraphSAGE``."""
+        return self._graph._CAPI_BatchGraphSAGE(seeds, seeds_ptr, list(fanouts))

@@ -1,0 +1,205 @@
+/*
+ * gsb200 -- C ABI of the B200 (sm_100a) sampling kernels.
+ *
+ * This is the boundary a host layer binds to (ctypes, cgo, JNI, a torch
+ * extension ...): plain pointers and sizes, no framework types.  Every pointer
+ * named "device" must point into the memory of the CUDA device that is current
+ * on the calling thread; `cuda_stream` is a cudaStream_t passed as void*.
+ * Functions enqueue work on that stream and return without synchronising
+ * unless their comment says otherwise.  There is no CPU fallback: a call on a
+ * machine without a usable device returns GSB_ERR_CUDA.
+ *
+ * Each entry point names the gSampler interface it replaces (path:line in the
+ * gSampler source tree).  Ids crossing this ABI are int64 except the graph's
+ * `indices` array, which may be int32 or int64 (`indices_dtype`).
+ *
+ * Sizes that are only known on the device (number of sampled edges, number of
+ * unique nodes) are returned in device memory; entry points that consume such
+ * a size accept it as a device pointer so that layers chain without a host
+ * round trip.  Outputs are written into caller-allocated buffers whose
+ * capacity the caller states; exceeding a capacity raises GSB_ERRBIT_CAPACITY
+ * in the device error word instead of writing out of bounds.
+ */
+#ifndef GSB200_H_
+#define GSB200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define GSB_API __attribute__((visibility("default")))
+#else
+#define GSB_API
+#endif
+
+/* return codes */
+enum {
+  GSB_OK = 0,
+  GSB_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, bad enum) */
+  GSB_ERR_UNSUPPORTED = 2, /* valid request outside the implemented range (see message) */
+  GSB_ERR_WORKSPACE = 3,   /* workspace smaller than *_workspace_bytes() */
+  GSB_ERR_CUDA = 4         /* a CUDA runtime call failed; see gsb_last_cuda_error() */
+};
+
+/* indices_dtype */
+enum { GSB_I32 = 0, GSB_I64 = 1 };
+
+/* bits of the device error word (`d_err`, an int in device memory that the
+ * caller zeroes once and may poll after synchronising) */
+enum {
+  GSB_ERRBIT_LOOKBACK_TIMEOUT = 1,
+  GSB_ERRBIT_TABLE_FULL = 2,
+  GSB_ERRBIT_KEY_MISSING = 4,
+  GSB_ERRBIT_CAPACITY = 8,
+  GSB_ERRBIT_BAD_INPUT = 16
+};
+
+GSB_API int gsb_abi_version(void);
+GSB_API const char* gsb_status_string(int status);
+/* cudaGetErrorString of the last failing runtime call made by this library on
+ * the calling thread ("" if none). */
+GSB_API const char* gsb_last_cuda_error(void);
+
+/* ------------------------------------------------------------------ sampling
+ * Per-column fanout sampling, optionally fused with column slicing.
+ * Replaces Graph::FusedSlicingSampling / BatchFusedSlicingSampling
+ * (src/graph.cc:383-454, src/batch_graph.cc:190-212 ->
+ * src/cuda/fusion/slice_sampling.cu:99-177) when `seeds` is given, and
+ * Graph::Sampling on CSC (src/graph.cc:182-244 -> src/cuda/sampling.cu:103-172)
+ * when `seeds` is NULL (column i of the operand is column slot i).
+ *
+ *  indptr[ncols+1] int64, indices[nnz] (int32|int64), device.
+ *  seeds[S_max] int64 device or NULL.  d_S: optional device int64 holding the
+ *  live number of column slots (<= S_max); NULL means S_max.
+ *  K fanout (1..8192).  replace: 0 = min(deg,K) distinct edges per column,
+ *  1 = K draws (0 for an empty column).
+ *  (seed, stream) select the random stream; column slot i always consumes
+ *  draws (seed, stream, i, 0..K-1), independent of launch geometry.
+ *  Outputs (device): sub_indptr[S_max+1]; out_rows / out_cols / out_sel with
+ *  capacity E_cap elements (out_cols may be NULL): row id, local column slot,
+ *  edge position in `indices`.  d_num_edges (optional) receives the edge count.
+ *  Column degrees must be < 2^32.
+ */
+GSB_API size_t gsb_sample_cols_workspace_bytes(int64_t S_max, int64_t K);
+GSB_API int gsb_sample_cols(const int64_t* indptr, const void* indices, int indices_dtype,
+                            const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K,
+                            int replace, uint64_t seed, uint32_t stream, int64_t* sub_indptr,
+                            int64_t* out_rows, int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
+                            int64_t* d_num_edges, void* workspace, size_t workspace_bytes,
+                            int* d_err, void* cuda_stream);
+
+/* Weighted per-column sampling (A-Res keys, without replacement; CDF search
+ * with replacement).  Replaces Graph::SamplingProbs (src/graph.cc:246-308 ->
+ * src/cuda/sampling_probs.cu:190-281).  probs[nnz] float32 device, aligned
+ * with `indices`.  Same outputs as gsb_sample_cols.  K <= 1024. */
+GSB_API size_t gsb_sample_cols_probs_workspace_bytes(int64_t S_max, int64_t K);
+GSB_API int gsb_sample_cols_probs(const int64_t* indptr, const void* indices, int indices_dtype,
+                                  const float* probs, const int64_t* seeds, int64_t S_max,
+                                  const int64_t* d_S, int64_t K, int replace, uint64_t seed,
+                                  uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
+                                  int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
+                                  int64_t* d_num_edges, void* workspace, size_t workspace_bytes,
+                                  int* d_err, void* cuda_stream);
+
+/* ------------------------------------------------------------------ slicing
+ * Column slicing A[:, seeds].  Replaces Graph::Slicing axis=1 on CSC and
+ * Graph::BatchColSlicing (src/graph.cc:90-179, src/batch_graph.cc:13-104 ->
+ * src/cuda/slicing.cu:121-181, src/cuda/batch/slicing.cu:40-120).
+ * Two calls because the edge count sizes the outputs:
+ *   count: sub_indptr[S+1] = exclusive scan of the seeds' degrees.
+ *   fill : out_rows/out_cols/out_sel[E] with E = sub_indptr[S] (host value).
+ * col_bptr[B+1] + encoding_size > 0 add b*encoding_size to the row ids of
+ * minibatch b (the reference's `encoding` mode); pass NULL/0 otherwise. */
+GSB_API size_t gsb_slice_cols_workspace_bytes(int64_t S);
+GSB_API int gsb_slice_cols_count(const int64_t* indptr, const int64_t* seeds, int64_t S,
+                                 int64_t* sub_indptr, void* workspace, size_t workspace_bytes,
+                                 int* d_err, void* cuda_stream);
+GSB_API int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, int indices_dtype,
+                                const int64_t* seeds, int64_t S, const int64_t* sub_indptr,
+                                int64_t E, int64_t* out_rows, int64_t* out_cols, int64_t* out_sel,
+                                const int64_t* col_bptr, int64_t B, int64_t encoding_size,
+                                void* cuda_stream);
+
+/* ------------------------------------------------------------------ unique / relabel
+ * Per-minibatch first-occurrence unique + relabel.  Replaces
+ * Graph::BatchGraphRelabel / BatchGetValidNodes (src/batch_graph.cc:214-284 ->
+ * src/cuda/batch/batch_relabel.cu:376-499) and, with B = 1, Graph::GraphRelabel
+ * / GetValidNodes (src/graph.cc:577-608 -> src/cuda/unique_reindex.cu:80-199).
+ *
+ * Minibatch b owns seeds[seeds_ptr[b]..seeds_ptr[b+1]) and edges
+ * [edge_ptr[b]..edge_ptr[b+1]).  Its node list is the first-occurrence unique
+ * of [seeds_b..., coo_row_b...]; `unique` is the concatenation of the lists,
+ * unique_ptr[B+1] their offsets.  out_row[e] / out_col[e] are the positions of
+ * coo_row[e] and of seeds[coo_col[e]] inside the minibatch's list (coo_col
+ * holds LOCAL column slots, i.e. indices into `seeds`).  out_row/out_col may
+ * both be NULL (all_nodes only).  S_max/E_max bound seeds_ptr[B]/edge_ptr[B],
+ * which are read on the device.  `unique` has capacity U_cap.
+ * Limits: node ids < 2^32-1 (id_bound states the exclusive upper bound of the
+ * ids), S_max+E_max < 2^31.
+ */
+GSB_API size_t gsb_batch_relabel_workspace_bytes(int64_t S_max, int64_t E_max, int64_t B);
+GSB_API int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B,
+                              int64_t S_max, const int64_t* coo_row, const int64_t* coo_col,
+                              const int64_t* edge_ptr, int64_t E_max, int64_t id_bound,
+                              int64_t* unique, int64_t U_cap, int64_t* unique_ptr,
+                              int64_t* out_row, int64_t* out_col, void* workspace,
+                              size_t workspace_bytes, int* d_err, void* cuda_stream);
+
+/* out[i] = src[idx[i]] for i < n (int64).  Used for edge_ptr =
+ * sub_indptr[seeds_ptr] (src/batch_graph.cc:203). */
+GSB_API int gsb_gather_i64(const int64_t* src, const int64_t* idx, int64_t n, int64_t* out,
+                           void* cuda_stream);
+
+/* ------------------------------------------------------------------ format conversion
+ * CSC -> COO column expansion: out[e] = column owning edge e.  Replaces
+ * CSC2COOCUDA (src/cuda/format_transform.cu:23-46). */
+GSB_API int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nnz, int64_t* out,
+                              void* cuda_stream);
+/* Sorted COO -> CSC offsets: indptr[k] = #keys < k, k in [0,nkeys].  Replaces the
+ * col_sorted branch of COO2CSCCUDA (src/cuda/format_transform.cu:121-142). */
+GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nkeys,
+                                   int64_t* indptr, void* cuda_stream);
+
+/* ------------------------------------------------------------------ whole sampler
+ * L-layer GraphSAGE super-batch sampler: per layer fused slice+sample then
+ * per-minibatch unique/relabel, the next layer's seeds being this layer's
+ * node lists -- the operator sequence of examples/graphsage/graphsage_e2e.py:37-44
+ * after gs.jit.compile's fusion passes (python/gs/jit/optimize.py:124-179,
+ * 280-325).  No host synchronisation between layers.
+ *
+ * The caller provides, per layer l, the buffers of gsb_layer_buffers with the
+ * stated capacities; S_cap[0] >= S0, S_cap[l+1] >= S_cap[l] + E_cap[l].
+ * After the call (and a stream sync) each layer's counts are in d_counts[3*l
+ * .. 3*l+2] = {S_l, E_l, U_l}.
+ */
+typedef struct {
+  int64_t S_cap, E_cap;   /* capacities in elements: seeds / edges of this layer      */
+  int64_t* sub_indptr;    /* [S_cap+1]                                                */
+  int64_t* rows;          /* [E_cap] sampled row ids (global)                         */
+  int64_t* cols;          /* [E_cap] local column slot                                */
+  int64_t* sel;           /* [E_cap] edge position in the graph                       */
+  int64_t* edge_ptr;      /* [B+1]                                                    */
+  int64_t* unique;        /* [S_cap+E_cap] node lists; seeds of the next layer        */
+  int64_t* unique_ptr;    /* [B+1]                                                    */
+  int64_t* block_row;     /* [E_cap] relabelled rows                                  */
+  int64_t* block_col;     /* [E_cap] relabelled cols                                  */
+} gsb_layer_buffers;
+
+GSB_API size_t gsb_graphsage_workspace_bytes(int64_t B, int num_layers,
+                                             const gsb_layer_buffers* layers,
+                                             const int64_t* fanouts);
+GSB_API int gsb_graphsage_sample(const int64_t* indptr, const void* indices, int indices_dtype,
+                                 int64_t id_bound, const int64_t* seeds, const int64_t* seeds_ptr,
+                                 int64_t B, int64_t S0, int num_layers, const int64_t* fanouts,
+                                 uint64_t seed, const gsb_layer_buffers* layers,
+                                 int64_t* d_counts, void* workspace, size_t workspace_bytes,
+                                 int* d_err, void* cuda_stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* GSB200_H_ */
