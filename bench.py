@@ -1,0 +1,385 @@
+#!/usr/bin/env python
+"""Benchmark of the GraphSAGE sampling hot path.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (default, "cfg2"): 3-layer GraphSAGE sampler, fanouts [15, 10, 5], uniform without
+replacement over in-neighbours, minibatch 1024, super-batch of 32 minibatches per step, on a
+seeded synthetic power-law graph with 2 449 029 nodes / 123 718 280 directed edges (CSC,
+int64 indptr + int64 indices resident in HBM), cycling through the 7 super-batches of one
+epoch over 196 615 training seeds.  One step = one super-batch through all layers
+(fused slice+sample, then per-minibatch unique/relabel = block construction).
+
+Prints ONE JSON line.  ``value`` is sampled edges per second over all ranks with the seeds
+already in HBM and pre-allocated outputs; ``e2e`` is the same metric through the public
+Python API with the seeds coming from pinned host memory and the per-layer sizes read back
+every step.  ``--impl reference`` times the CPU port of the reference's algorithms
+(oracle/) on the host cores for the same workload on a bounded sample.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+WORKLOADS = {
+    # name: nodes, directed edges, train seeds, fanouts, batch, minibatches per super-batch
+    "cfg2": dict(nodes=2449029, edges=123718280, train=196615, fanouts=[15, 10, 5], batch=1024,
+                 super_batch=32, index_dtype="int64", max_degree=20000),
+    # reduced shape for quick functional runs (same pipeline, fits any GPU)
+    "small": dict(nodes=200000, edges=8000000, train=20480, fanouts=[15, 10, 5], batch=1024,
+                  super_batch=8, index_dtype="int64", max_degree=5000),
+}
+
+
+def algorithmic_bytes(S, E, U, w_idx=8):
+    """Compulsory bytes of one GraphSAGE layer: fused slice+sample reads 8S seeds + 16S
+    offsets + w_idx*E gathered ids and writes 8(S+1) + 24E; unique/relabel reads 8S + 16E and
+    writes 8U + 16E."""
+    fss = 8 * S + 16 * S + w_idx * E + 8 * (S + 1) + 24 * E
+    brl = 8 * S + 16 * E + 8 * U + 16 * E
+    return fss, brl
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+         "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        super().__init__(daemon=True)
+        self.gpu_index = gpu_index
+        self.rows = []
+        self.proc = None
+
+    def run(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.gpu_index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            for line in self.proc.stdout:
+                self.rows.append([x.strip() for x in line.split(",")])
+        except Exception:
+            pass
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+        self.join(timeout=2)
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        for r in self.rows:
+            try:
+                sm.append(float(r[1]))
+                mx = max(mx, float(r[2]))
+            except Exception:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown",
+                                "sw_power_cap"), r[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": float(np.median(sm)) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_graph(cfg, device):
+    import torch
+
+    from gsampler_b200 import synth
+
+    dt = torch.int32 if cfg["index_dtype"] == "int32" else torch.int64
+    return synth.powerlaw_csc(cfg["nodes"], cfg["edges"], exponent=2.1, max_degree=cfg["max_degree"],
+                              seed=2024, device=device, index_dtype=dt)
+
+
+def make_super_batches(cfg, rank):
+    """The epoch's super-batches for this rank: a seeded permutation of the node ids, cut into
+    minibatches of `batch` seeds, `super_batch` minibatches per step."""
+    import torch
+
+    g = torch.Generator()
+    g.manual_seed(7 + rank)
+    seeds = torch.randperm(cfg["nodes"], generator=g)[:cfg["train"]].to(torch.int64)
+    per_step = cfg["batch"] * cfg["super_batch"]
+    out = []
+    for s0 in range(0, cfg["train"], per_step):
+        chunk = seeds[s0:s0 + per_step]
+        ptr = torch.arange(0, chunk.numel() + cfg["batch"], cfg["batch"], dtype=torch.int64)
+        ptr = ptr[:(chunk.numel() + cfg["batch"] - 1) // cfg["batch"] + 1].clamp_max(chunk.numel())
+        # pad the pointer to super_batch+1 entries (trailing minibatches empty)
+        full = torch.full((cfg["super_batch"] + 1,), chunk.numel(), dtype=torch.int64)
+        full[:ptr.numel()] = ptr
+        out.append((chunk.contiguous(), full))
+    return out
+
+
+def cpu_reference_run(cfg, indptr_np, indices_np, steps, warmup, minibatches, sampler="ref"):
+    """Times the CPU port (oracle/) on `minibatches` minibatches per step.  Returns
+    (edges per second, description, cores)."""
+    from oracle import gs_oracle
+
+    gs_oracle.build()
+    rng = np.random.default_rng(7)
+    n = cfg["batch"] * minibatches
+    ptr = np.arange(minibatches + 1, dtype=np.int64) * cfg["batch"]
+    total_edges, total_t = 0, 0.0
+    for i in range(warmup + steps):
+        seeds = rng.permutation(cfg["nodes"])[:n].astype(np.int64)
+        t0 = time.perf_counter()
+        layers = gs_oracle.graphsage_batch(indptr_np, indices_np, seeds, ptr, cfg["fanouts"], seed=i,
+                                           sampler=sampler)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            total_t += dt
+            total_edges += sum(int(L["rows"].size) for L in layers)
+    desc = "%d steps x %d minibatches of %d seeds, %d layers, oracle %s sampler + batch relabel" % (
+        steps, minibatches, cfg["batch"], len(cfg["fanouts"]), sampler)
+    return total_edges / total_t, desc, gs_oracle.num_threads(), total_t / steps * 1e3
+
+
+def run_reference(args, cfg, rank, world):
+    if rank != 0:
+        return
+    import torch
+
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    indptr, indices = make_graph(cfg, device)
+    indptr_np, indices_np = indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64)
+    del indptr, indices
+    eps, desc, cores, ms = cpu_reference_run(cfg, indptr_np, indices_np, args.steps, args.warmup,
+                                             minibatches=4, sampler="ref")
+    line = {
+        "impl": "reference", "metric": "graphsage_sampled_edges_per_sec", "value": eps,
+        "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int64", "data": "synthetic",
+        "config": {"workload": args.workload, **{k: cfg[k] for k in ("nodes", "edges", "fanouts", "batch")},
+                   "note": "the reference has no CPU sampler; this is the CPU port of its "
+                           "algorithms (oracle/) on the host cores"},
+        "cpu_baseline": {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=14)
+    ap.add_argument("--warmup", type=int, default=7)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default=os.environ.get("GSB_WORKLOAD", "cfg2"), choices=sorted(WORKLOADS))
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    cfg = WORKLOADS[args.workload]
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        run_reference(args, cfg, rank, world)
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the sampler has no CPU fallback "
+                         "(use --impl reference for the CPU port)")
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    import gsampler_b200 as gs
+    from gsampler_b200 import pipeline
+
+    L = len(cfg["fanouts"])
+    indptr, indices = make_graph(cfg, dev)
+    batches_host = make_super_batches(cfg, rank)
+    batches_dev = [(s.to(dev), p.to(dev)) for s, p in batches_host]
+    batches_pin = [(s.pin_memory(), p.pin_memory()) for s, p in batches_host]
+    nb = len(batches_dev)
+    max_seeds = cfg["batch"] * cfg["super_batch"]
+
+    # ---- capacities from a measured dry run (worst case would be ~4x larger)
+    probe = pipeline.GraphSAGESampler(indptr, indices, cfg["super_batch"], max_seeds, cfg["fanouts"])
+    caps = None
+    for s, p in batches_dev:
+        probe.sample(s, p)
+        c = probe.counts()
+        cur = [(int(S * 1.15) + 4096, int(E * 1.15) + 4096) for S, E, U in c]
+        caps = cur if caps is None else [(max(a[0], b[0]), max(a[1], b[1])) for a, b in zip(caps, cur)]
+    caps[0] = (max_seeds, max_seeds * cfg["fanouts"][0])
+    del probe
+    torch.cuda.empty_cache()
+    # measured capacities; an overflow would raise the sampler's error word (checked below)
+    sampler = pipeline.GraphSAGESampler(indptr, indices, cfg["super_batch"], max_seeds,
+                                        cfg["fanouts"], capacities=caps)
+
+    counts = torch.zeros(args.steps + args.warmup, 3 * L, dtype=torch.int64, device=dev)
+
+    def step(i, row):
+        s, p = batches_dev[i % nb]
+        sampler.sample(s, p, counts_out=counts[row])
+
+    for w in range(args.warmup):
+        step(w, w)
+    torch.cuda.synchronize()
+    sampler.check()
+
+    clocks = ClockSampler(local_rank)
+    clocks.start()
+    time.sleep(0.3)
+    launches0 = pipeline.kernel_launches()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for k in range(args.steps):
+        step(args.warmup + k, args.warmup + k)
+    ev1.record()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    launches = pipeline.kernel_launches() - launches0
+    elapsed_ms = ev0.elapsed_time(ev1)
+    sampler.check()
+    c_host = counts[args.warmup:].cpu().numpy().reshape(args.steps, L, 3)
+    edges = int(c_host[:, :, 1].sum())
+
+    # ---- per-kernel durations of the same K steps (CUDA events around every launch)
+    pipeline.timing_enable(True)
+    for k in range(args.steps):
+        step(args.warmup + k, args.warmup + k)
+    timed = pipeline.timing_collect()
+    pipeline.timing_enable(False)
+    clocks.stop()
+
+    # ---- end to end through the public API: pinned host seeds -> blocks on the GPU -> sizes on the host
+    A = gs.Graph(cfg["nodes"], cfg["nodes"])
+    A._CAPI_LoadCSC(indptr, indices)
+    bm = gs.BatchMatrix()
+    bm.load_from_matrix(gs.Matrix(A), False)
+    e2e_edges, h2d, d2h = 0, 0, 0
+
+    def e2e_step(i):
+        s, p = batches_pin[i % nb]
+        sd, pd = s.to(dev, non_blocking=True), p.to(dev, non_blocking=True)
+        out = bm.graphsage(sd, pd, cfg["fanouts"])
+        return out[-1], s.numel() * 8 + p.numel() * 8
+
+    for w in range(3):
+        e2e_step(w)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for k in range(args.steps):
+        cnt, nbytes = e2e_step(args.warmup + k)
+        e2e_edges += int(cnt.view(L, 3)[:, 1].sum())
+        h2d += nbytes
+        d2h += (3 * L + 1) * 8
+    e1.record()
+    torch.cuda.synchronize()
+    e2e_ms = max(e0.elapsed_time(e1), (time.perf_counter() - t0) * 1e3)
+
+    # ---- reduce over ranks: slowest rank's time, summed edges
+    if world > 1:
+        t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        elapsed_ms, e2e_ms = float(t[0]), float(t[1])
+        n = torch.tensor([edges, e2e_edges, launches], dtype=torch.int64, device=dev)
+        dist.all_reduce(n, op=dist.ReduceOp.SUM)
+        edges, e2e_edges, launches = int(n[0]), int(n[1]), int(n[2])
+
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        # dominant kernel of the timed pipeline and its roofline
+        by = {}
+        for name, tag, ms, cnt in timed:
+            by[(name, tag)] = (ms, cnt)
+        total_kernel_ms = sum(v[0] for v in by.values())
+        (dname, dtag), (dms, dcnt) = max(by.items(), key=lambda kv: kv[1][0])
+        S_l = c_host[:, dtag, 0].astype(np.float64)
+        E_l = c_host[:, dtag, 1].astype(np.float64)
+        U_l = c_host[:, dtag, 2].astype(np.float64)
+        w_idx = 4 if cfg["index_dtype"] == "int32" else 8
+        per_launch = {
+            "sample_tile": (8 * S_l + 16 * S_l + w_idx * E_l + 8 * (S_l + 1) + 24 * E_l).mean(),
+            "relabel_insert": (8 * (S_l + E_l)).mean(),
+            "relabel_scan": (8 * (S_l + E_l) + 8 * U_l).mean(),
+            "relabel_edges": (32 * E_l).mean(),
+            "relabel_clear": 0.0,
+        }.get(dname, 0.0)
+        dur_s = dms / dcnt / 1e3
+        achieved = per_launch / dur_s / 1e9 if dur_s > 0 else 0.0
+        path_bytes = 0.0
+        for l in range(L):
+            f, b = algorithmic_bytes(c_host[:, l, 0].sum(), c_host[:, l, 1].sum(), c_host[:, l, 2].sum(), w_idx)
+            path_bytes += f + b
+        path_gbs = path_bytes / (elapsed_ms / 1e3) / 1e9 / max(world, 1)
+        line = {
+            "metric": "graphsage_sampled_edges_per_sec",
+            "value": edges / (elapsed_ms / 1e3), "unit": "edges/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
+            "data": "synthetic",
+            "config": {"workload": args.workload, "graph": "power-law, %d nodes, %d directed edges, CSC int64/%s"
+                       % (cfg["nodes"], int(indptr[-1]), cfg["index_dtype"]),
+                       "fanouts": cfg["fanouts"], "batch": cfg["batch"], "super_batch": cfg["super_batch"],
+                       "train_seeds": cfg["train"], "parallelism": "replica x%d" % world,
+                       "l2": "inputs_larger_than_l2 (graph indices %.1f GB)" % (indices.numel() * indices.element_size() / 1e9),
+                       "edges_per_step": edges / args.steps / max(world, 1),
+                       "capacities": "measured x1.15"},
+            "e2e": {"value": e2e_edges / (e2e_ms / 1e3), "unit": "edges/s",
+                    "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
+                    "api": "BatchMatrix.graphsage (one native call per super-batch)"},
+            "gpu_launches": launches,
+            "roofline": {"bound": "hbm", "kernel": "%s[layer %d]" % (dname, dtag), "achieved": achieved,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak_kind": peak_kind, "share_of_kernel_time": dms / total_kernel_ms,
+                         "avg_launch_ms": dms / dcnt},
+            "roofline_path": {"algorithmic_gb_per_step": path_bytes / args.steps / max(world, 1) / 1e9,
+                              "achieved": path_gbs, "unit": "GB/s", "frac": path_gbs / peak,
+                              "peak_kind": peak_kind},
+            "kernels": {"%s[%d]" % k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(by.items())},
+            "clocks": clocks.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            indptr_np, indices_np = indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64)
+            eps, desc, cores, _ = cpu_reference_run(cfg, indptr_np, indices_np, steps=3, warmup=1,
+                                                    minibatches=4, sampler="ref")
+            line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port",
+                                    "sample": desc}
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

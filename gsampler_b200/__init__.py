@@ -41,3 +41,4 @@ from .jit import compile  # noqa: E402,A001
 Graph = torch.classes.gs_classes.Graph
 
 __all__ = ["Matrix", "BatchMatrix", "Graph", "jit", "ops", "utils", "compile", "_COO", "_CSC", "_CSR"]
+from .pipeline import GraphSAGESampler  # noqa: E402

@@ -1,6 +1,10 @@
 // Library-level entry points: version, status strings, and the multi-layer
 // GraphSAGE sampler that chains the per-stage launches on one stream without
 // any host synchronisation (all intermediate sizes stay on the device).
+#include <atomic>
+#include <mutex>
+#include <vector>
+
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -15,11 +19,94 @@ __global__ void record_counts_kernel(const i64* seeds_ptr, const i64* unique_ptr
   }
 }
 
+// ---------------------------------------------------------------- launch accounting
+static const char* const kKernelNames[KID_NUM] = {
+    "sample_tile", "sample_probs", "count", "slice_fill", "gather", "expand_indptr",
+    "indptr_from_sorted", "relabel_setup", "relabel_clear", "relabel_insert", "relabel_scan",
+    "relabel_edges", "record_counts", "slice_rows", "edge_sum", "edge_op", "list_sample", "walk",
+    "sort", "misc"};
+
+struct TimedLaunch {
+  int id, tag;
+  cudaEvent_t start, stop;
+};
+
+static std::atomic<unsigned long long> g_launches{0};
+static std::mutex g_timing_mutex;
+static bool g_timing_on = false;
+static int g_timing_tag = 0;
+static std::vector<TimedLaunch> g_timed;      // events of the current collection window
+static std::vector<cudaEvent_t> g_event_pool;  // recycled events
+
+static cudaEvent_t pool_event() {
+  if (!g_event_pool.empty()) {
+    cudaEvent_t e = g_event_pool.back();
+    g_event_pool.pop_back();
+    return e;
+  }
+  cudaEvent_t e = nullptr;
+  cudaEventCreate(&e);
+  return e;
+}
+
+LaunchScope::LaunchScope(int id_, cudaStream_t st_) : id(id_), st(st_), slot(-1) {
+  g_launches.fetch_add(1, std::memory_order_relaxed);
+  if (!g_timing_on) return;
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  TimedLaunch t{id, g_timing_tag, pool_event(), pool_event()};
+  if (!t.start || !t.stop) return;
+  cudaEventRecord(t.start, st);
+  g_timed.push_back(t);
+  slot = (int)g_timed.size() - 1;
+}
+
+LaunchScope::~LaunchScope() {
+  if (slot < 0) return;
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  if (slot < (int)g_timed.size()) cudaEventRecord(g_timed[(size_t)slot].stop, st);
+}
+
+void set_timing_tag(int tag) { g_timing_tag = tag; }
+
 }  // namespace gsb
 
 using namespace gsb;
 
 extern "C" int gsb_abi_version(void) { return 1; }
+
+extern "C" uint64_t gsb_kernel_launches(void) { return g_launches.load(); }
+
+extern "C" int gsb_timing_enable(int on) {
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  for (auto& t : g_timed) { g_event_pool.push_back(t.start); g_event_pool.push_back(t.stop); }
+  g_timed.clear();
+  g_timing_on = on != 0;
+  g_timing_tag = 0;
+  return GSB_OK;
+}
+
+extern "C" int gsb_timing_collect(int max_entries, const char** names, int* tags, double* total_ms,
+                                  int64_t* launches) {
+  if (max_entries < 0 || (max_entries > 0 && (!names || !tags || !total_ms || !launches))) return -1;
+  if (cudaDeviceSynchronize() != cudaSuccess) return -1;
+  std::lock_guard<std::mutex> lock(g_timing_mutex);
+  int n = 0;
+  for (auto& t : g_timed) {
+    float ms = 0.f;
+    if (cudaEventElapsedTime(&ms, t.start, t.stop) != cudaSuccess) continue;
+    int k = 0;
+    for (; k < n; ++k)
+      if (names[k] == kKernelNames[t.id] && tags[k] == t.tag) break;
+    if (k == n) {
+      if (n == max_entries) continue;
+      names[n] = kKernelNames[t.id]; tags[n] = t.tag; total_ms[n] = 0; launches[n] = 0;
+      ++n;
+    }
+    total_ms[k] += ms;
+    launches[k] += 1;
+  }
+  return n;
+}
 
 extern "C" const char* gsb_status_string(int status) {
   switch (status) {
@@ -65,10 +152,10 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
     return GSB_ERR_INVALID;
   if (workspace_bytes < gsb_graphsage_workspace_bytes(B, num_layers, layers, fanouts) || !workspace)
     return GSB_ERR_WORKSPACE;
-  // capacity chain: the node lists of layer l are the seeds of layer l+1
+  // The node lists of layer l are the seeds of layer l+1.  S_cap[l+1] >=
+  // S_cap[l] + E_cap[l] can never overflow; smaller capacities are accepted and
+  // checked on the device (GSB_ERRBIT_CAPACITY).
   if (layers[0].S_cap < S0) return GSB_ERR_INVALID;
-  for (int l = 0; l + 1 < num_layers; ++l)
-    if (layers[l + 1].S_cap < layers[l].S_cap + layers[l].E_cap) return GSB_ERR_INVALID;
 
   cudaStream_t st = (cudaStream_t)cuda_stream;
   const int64_t* cur_seeds = seeds;
@@ -77,6 +164,7 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
   for (int l = 0; l < num_layers; ++l) {
     const gsb_layer_buffers& L = layers[l];
     const int64_t S_max = l == 0 ? S0 : L.S_cap;
+    set_timing_tag(l);
     const size_t ws_a = align256(gsb_sample_cols_workspace_bytes(L.S_cap, fanouts[l]));
     int rc = gsb_sample_cols(indptr, indices, indices_dtype, cur_seeds, S_max, d_S, fanouts[l], 0,
                              seed, (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
@@ -89,12 +177,14 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
                            L.block_col, (char*)workspace + ws_a, workspace_bytes - ws_a, d_err,
                            cuda_stream);
     if (rc != GSB_OK) return rc;
+    { LaunchScope ls(KID_COUNTS, st);
     record_counts_kernel<<<1, 32, 0, st>>>((const i64*)cur_ptr, (const i64*)L.unique_ptr, (int)B,
-                                           (i64*)d_counts + 3 * l);
+                                           (i64*)d_counts + 3 * l); }
     cur_seeds = L.unique;
     cur_ptr = L.unique_ptr;
     d_S = L.unique_ptr + B;
   }
+  set_timing_tag(0);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

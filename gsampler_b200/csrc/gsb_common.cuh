@@ -197,6 +197,24 @@ __device__ __forceinline__ i64 load_index<i64>(const void* base, i64 pos) {
 
 inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 
+// Launch accounting: every kernel launch of the library sits inside a
+// LaunchScope, which counts it and, when timing is enabled
+// (gsb_timing_enable), brackets it with CUDA events on the launching stream.
+enum KernelId {
+  KID_SAMPLE = 0, KID_SAMPLE_PROBS, KID_COUNT, KID_SLICE_FILL, KID_GATHER, KID_EXPAND,
+  KID_INDPTR_SORTED, KID_RL_SETUP, KID_RL_CLEAR, KID_RL_INSERT, KID_RL_SCAN, KID_RL_EDGES,
+  KID_COUNTS, KID_SLICE_ROWS, KID_EDGE_SUM, KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT,
+  KID_MISC, KID_NUM
+};
+struct LaunchScope {
+  LaunchScope(int id, cudaStream_t st);
+  ~LaunchScope();
+  int id;
+  cudaStream_t st;
+  int slot;
+};
+void set_timing_tag(int tag);
+
 // Offsets of a slice/sample in one pass (defined in gsb_slice.cu): sub_indptr =
 // exclusive scan of the per-column pick counts, optional device total.
 size_t count_workspace_bytes(i64 S_max);

@@ -84,7 +84,8 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
   }
   if (threadIdx.x == 0) {
     i64 n_items = s_carry_items, n_slots = s_carry_slots;
-    if (n_items > p.S_max + p.E_max || n_slots > p.slots_cap) {
+    if (n_items > p.S_max + p.E_max || n_slots > p.slots_cap || p.seeds_ptr[p.B] > p.S_max ||
+        p.edge_ptr[p.B] > p.E_max) {
       raise(p.err, ERRBIT_CAPACITY);
       n_items = 0; n_slots = 0;  // later kernels become no-ops
     }
@@ -320,19 +321,19 @@ extern "C" int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr,
   p.table = (u64*)(ws + L.table); p.slots_cap = L.slots_cap; p.err = d_err;
 
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.status, 0, sizeof(u64) * (size_t)L.tiles, st));
-  relabel_setup_kernel<<<1, 1024, 0, st>>>(p);
+  { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
   const i64 items_max = S_max + E_max;
   const int wide = 148 * 8;
   int g_clear = (int)((L.slots_cap / 2 + RL_THREADS - 1) / RL_THREADS); if (g_clear > wide) g_clear = wide; if (g_clear < 1) g_clear = 1;
-  relabel_clear_kernel<<<g_clear, RL_THREADS, 0, st>>>(p);
+  { LaunchScope ls(KID_RL_CLEAR, st); relabel_clear_kernel<<<g_clear, RL_THREADS, 0, st>>>(p); }
   int g_items = (int)((items_max + RL_THREADS - 1) / RL_THREADS); if (g_items < 1) g_items = 1;
   if (g_items > 148 * 16) g_items = 148 * 16;
-  relabel_insert_kernel<<<g_items, RL_THREADS, 0, st>>>(p);
-  relabel_scan_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p);
+  { LaunchScope ls(KID_RL_INSERT, st); relabel_insert_kernel<<<g_items, RL_THREADS, 0, st>>>(p); }
+  { LaunchScope ls(KID_RL_SCAN, st); relabel_scan_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   if (out_row && E_max > 0) {
     int g_edges = (int)((E_max + RL_THREADS - 1) / RL_THREADS);
     if (g_edges > 148 * 16) g_edges = 148 * 16;
-    relabel_edges_kernel<<<g_edges, RL_THREADS, 0, st>>>(p);
+    { LaunchScope ls(KID_RL_EDGES, st); relabel_edges_kernel<<<g_edges, RL_THREADS, 0, st>>>(p); }
   }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;

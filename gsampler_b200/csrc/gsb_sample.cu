@@ -57,7 +57,11 @@ sample_tile_kernel(const SampleParams p) {
   __syncthreads();
   const int tile = s_tile;
   i64 S = p.S_max;
-  if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
+  if (p.d_S) {
+    const i64 live = *p.d_S;
+    if (live > S && tile == 0 && threadIdx.x == 0) raise(p.err, ERRBIT_CAPACITY);
+    S = live < S ? (live < 0 ? 0 : live) : S;
+  }
   const i64 num_tiles = S == 0 ? 1 : (S + tc - 1) / tc;
   if (tile >= num_tiles) return;
 
@@ -189,10 +193,12 @@ extern "C" int gsb_sample_cols(const int64_t* indptr, const void* indices, int i
   if (indices_dtype == GSB_I32) {
     GSB_CUDA_OK(cudaFuncSetAttribute(sample_tile_kernel<int>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope ls(KID_SAMPLE, st);
     sample_tile_kernel<int><<<tiles, SAMPLE_THREADS, smem, st>>>(p);
   } else {
     GSB_CUDA_OK(cudaFuncSetAttribute(sample_tile_kernel<i64>,
                                      cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    LaunchScope ls(KID_SAMPLE, st);
     sample_tile_kernel<i64><<<tiles, SAMPLE_THREADS, smem, st>>>(p);
   }
   GSB_CUDA_OK(cudaGetLastError());

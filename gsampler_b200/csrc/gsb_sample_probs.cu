@@ -283,6 +283,7 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   i64 blocks = (S_max + WP_WARPS - 1) / WP_WARPS;
   if (blocks > 148 * 16) blocks = 148 * 16;
   const size_t smem = sizeof(u32) * WP_WARPS * 256 + sizeof(float) * WP_WARPS * (size_t)K;
+  LaunchScope ls(KID_SAMPLE_PROBS, st);
   if (indices_dtype == GSB_I32)
     sample_probs_kernel<int><<<(int)blocks, WP_THREADS, smem, st>>>(p);
   else

@@ -58,6 +58,7 @@ int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S,
                  cudaStream_t st) {
   const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, SLICE_THREADS);
   GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
+  LaunchScope ls(KID_COUNT, st);
   count_kernel<<<tiles, SLICE_THREADS, 0, st>>>(indptr, seeds, S_max, d_S, K, replace, sub_indptr,
                                                 d_total, (u64*)((char*)workspace + 256),
                                                 (int*)workspace, d_err);
@@ -134,6 +135,7 @@ extern "C" int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nn
   if (!indptr || !out || nseg <= 0 || nnz < 0) return GSB_ERR_INVALID;
   i64 blocks = (nnz + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
+  LaunchScope ls(KID_EXPAND, (cudaStream_t)cuda_stream);
   expand_indptr_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)indptr, nseg, nnz, (i64*)out);
   GSB_CUDA_OK(cudaGetLastError());
@@ -145,6 +147,7 @@ extern "C" int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t 
   if (!indptr || nkeys < 0 || nnz < 0 || (nnz > 0 && !keys)) return GSB_ERR_INVALID;
   i64 blocks = (nkeys + 1 + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
+  LaunchScope ls(KID_INDPTR_SORTED, (cudaStream_t)cuda_stream);
   indptr_from_sorted_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)keys, nnz, nkeys, (i64*)indptr);
   GSB_CUDA_OK(cudaGetLastError());
@@ -177,6 +180,7 @@ extern "C" int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, i
   cudaStream_t st = (cudaStream_t)cuda_stream;
   i64 blocks = (E + SLICE_THREADS - 1) / SLICE_THREADS;
   if (blocks > 148 * 64) blocks = 148 * 64;
+  LaunchScope ls(KID_SLICE_FILL, st);
   if (indices_dtype == GSB_I32)
     slice_fill_kernel<int><<<(int)blocks, SLICE_THREADS, 0, st>>>(
         (const i64*)indptr, indices, (const i64*)seeds, S, (const i64*)sub_indptr, E,
@@ -195,6 +199,7 @@ extern "C" int gsb_gather_i64(const int64_t* src, const int64_t* idx, int64_t n,
   if (!src || !idx || !out || n < 0) return GSB_ERR_INVALID;
   i64 blocks = (n + 255) / 256;
   if (blocks > 148 * 32) blocks = 148 * 32;
+  LaunchScope ls(KID_GATHER, (cudaStream_t)cuda_stream);
   gather_i64_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)src, (const i64*)idx, n, (i64*)out);
   GSB_CUDA_OK(cudaGetLastError());

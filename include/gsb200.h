@@ -64,6 +64,20 @@ GSB_API const char* gsb_status_string(int status);
  * the calling thread ("" if none). */
 GSB_API const char* gsb_last_cuda_error(void);
 
+/* Launch accounting (no counterpart in the reference, whose only timers are
+ * host time.time() loops, python/gs/jit/module.py:268-278).
+ * gsb_kernel_launches: kernels launched by this library since it was loaded.
+ * gsb_timing_enable(1): from now on every launch is bracketed by CUDA events on
+ * its stream; (0) stops and drops what was collected.
+ * gsb_timing_collect: synchronises the device and returns the number of
+ * (kernel name, tag) groups seen since timing was enabled, with their summed
+ * duration and launch count; the tag is the layer index inside
+ * gsb_graphsage_sample and 0 elsewhere.  Returns -1 on error. */
+GSB_API uint64_t gsb_kernel_launches(void);
+GSB_API int gsb_timing_enable(int on);
+GSB_API int gsb_timing_collect(int max_entries, const char** names, int* tags, double* total_ms,
+                               int64_t* launches);
+
 /* ------------------------------------------------------------------ sampling
  * Per-column fanout sampling, optionally fused with column slicing.
  * Replaces Graph::FusedSlicingSampling / BatchFusedSlicingSampling
@@ -172,7 +186,10 @@ GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nke
  * 280-325).  No host synchronisation between layers.
  *
  * The caller provides, per layer l, the buffers of gsb_layer_buffers with the
- * stated capacities; S_cap[0] >= S0, S_cap[l+1] >= S_cap[l] + E_cap[l].
+ * stated capacities; S_cap[0] >= S0.  S_cap[l+1] >= S_cap[l] + E_cap[l] and
+ * E_cap[l] >= S_cap[l] * fanout[l] can never overflow; smaller capacities
+ * (e.g. measured on a warm-up step) are allowed, an overflow then raises
+ * GSB_ERRBIT_CAPACITY and the affected layers come back empty.
  * After the call (and a stream sync) each layer's counts are in d_counts[3*l
  * .. 3*l+2] = {S_l, E_l, U_l}.
  */

@@ -1,0 +1,196 @@
+"""GPU tests of the host layer (torch.classes.gs_classes.Graph) and of the Python surface
+(Matrix / BatchMatrix / compile) against the CPU oracle, on the CPU-baseline configuration:
+R-MAT graph, 100 000 nodes / 2 000 000 drawn edges, 2-layer GraphSAGE, fanouts [25, 10]."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+@pytest.fixture(scope="module")
+def rmat():
+    from gsampler_b200 import synth
+
+    return synth.rmat_csc(100000, 2000000, seed=42)
+
+
+@pytest.fixture(scope="module")
+def fx():
+    with open(os.path.join(HERE, "golden", "reference_fixtures.json")) as f:
+        return json.load(f)
+
+
+def new_graph(gsb, indptr, indices, seed=4242, idx_dtype=torch.int64):
+    n = indptr.size - 1
+    g = gsb.Graph(n, n)
+    g._CAPI_LoadCSC(torch.as_tensor(indptr).cuda(), torch.as_tensor(indices).to(idx_dtype).cuda())
+    g._CAPI_SetSeed(seed)
+    return g
+
+
+def test_reference_gtest_fixtures(gsb, fx):
+    c = fx["colwise_slicing"]
+    A = new_graph(gsb, np.asarray(c["indptr"]), np.asarray(c["indices"]))
+    sub, _ = A._CAPI_Slicing(torch.tensor(c["cols"]).cuda(), 1, gsb._CSC, gsb._CSC)
+    assert host(sub._CAPI_GetCSCIndptr()).tolist() == c["expect_indptr"]
+    assert host(sub._CAPI_GetCSCIndices()).tolist() == c["expect_indices"]
+    c = fx["colwise_sampling"]
+    sub, _ = A._CAPI_Sampling(1, c["copy_all"]["fanout"], False, gsb._CSC, gsb._CSC)
+    assert host(sub._CAPI_GetCSCIndptr()).tolist() == c["copy_all"]["expect_indptr"]
+    assert host(sub._CAPI_GetCSCIndices()).tolist() == c["copy_all"]["expect_indices"]
+    for case in c["replace"]:
+        sub, _ = A._CAPI_Sampling(1, case["fanout"], True, gsb._CSC, gsb._CSC)
+        assert host(sub._CAPI_GetCSCIndptr()).tolist() == case["expect_indptr"]
+        ids = host(sub._CAPI_GetCSCIndices())
+        assert ids.size == 20 * case["fanout"] and ids.tolist() != c["indices"]
+        assert np.unique(ids).size <= 100
+    c = fx["rowwise_slicing"]
+    A = new_graph(gsb, np.asarray(c["indptr"]), np.asarray(c["indices"]))
+    sub, _ = A._CAPI_Slicing(torch.tensor(c["rows"]).cuda(), 0, gsb._CSR, gsb._CSR)
+    assert sub._CAPI_GetCSRIndptr().numel() == c["expect_csr_indptr_numel"]
+    assert host(sub._CAPI_GetCSRIndices()).tolist() == c["expect_csr_indices"]
+
+
+def _seeds(n_nodes, nb=4, bs=1024, seed=0):
+    rng = np.random.default_rng(seed)
+    seeds = rng.permutation(n_nodes)[:nb * bs].astype(np.int64)
+    ptr = np.arange(nb + 1, dtype=np.int64) * bs
+    return seeds, ptr
+
+
+def _compare_layer(layer, sub, rows, cols, sel, uq, up, brow, bcol):
+    assert np.array_equal(host(sub), layer["sub_indptr"])
+    assert np.array_equal(host(sel), layer["select"])
+    assert np.array_equal(host(rows), layer["rows"])
+    assert np.array_equal(host(cols), layer["cols"])
+    assert np.array_equal(host(up), layer["unique_ptr"])
+    assert np.array_equal(host(uq), layer["unique"])
+    assert np.array_equal(host(brow), layer["block_row"])
+    assert np.array_equal(host(bcol), layer["block_col"])
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_native_graphsage_pipeline_bit_exact(gsb, oracle, rmat, idx_dtype):
+    indptr, indices = rmat
+    seeds, ptr = _seeds(indptr.size - 1)
+    want = oracle.graphsage_batch(indptr, indices, seeds, ptr, [25, 10], seed=4242)
+    A = new_graph(gsb, indptr, indices, idx_dtype=idx_dtype)
+    out = A._CAPI_BatchGraphSAGE(torch.as_tensor(seeds).cuda(), torch.as_tensor(ptr).cuda(), [25, 10])
+    counts = out[-1].numpy()
+    for l, layer in enumerate(want):
+        sub, rows, cols, sel, eptr, uq, up, brow, bcol = out[9 * l:9 * l + 9]
+        _compare_layer(layer, sub, rows, cols, sel, uq, up, brow, bcol)
+        assert np.array_equal(host(eptr), layer["edge_ptr"])
+        assert counts[3 * l:3 * l + 3].tolist() == [layer["seeds"].size, layer["rows"].size,
+                                                    layer["unique"].size]
+
+
+def test_batchmatrix_sampler_matches_oracle(gsb, oracle, rmat):
+    """The reference's batch_graphsage_sampler (examples/graphsage/graphsage.py:20-27) written
+    against this package's BatchMatrix."""
+    indptr, indices = rmat
+    seeds, ptr = _seeds(indptr.size - 1, nb=3, bs=512, seed=1)
+    fanouts = [25, 10]
+    want = oracle.graphsage_batch(indptr, indices, seeds, ptr, fanouts, seed=4242)
+
+    def sampler(A, seeds, seeds_ptr, fanouts):
+        ret = []
+        for k in fanouts:
+            subA = A[:, seeds::seeds_ptr]
+            sampleA = subA.individual_sampling(k, None, False)
+            seeds, seeds_ptr = sampleA.all_nodes()
+            ret.append(sampleA.to_dgl_block())
+        return ret
+
+    m = gsb.Matrix(new_graph(gsb, indptr, indices))
+    bm = gsb.BatchMatrix()
+    bm.load_from_matrix(m, False)
+    fn = gsb.jit.compile(func=sampler, args=(bm, torch.as_tensor(seeds).cuda(),
+                                            torch.as_tensor(ptr).cuda(), fanouts))
+    blocks = fn(bm, torch.as_tensor(seeds).cuda(), torch.as_tensor(ptr).cuda(), fanouts)
+    for l, layer in enumerate(want):
+        assert len(blocks[l]) == 3
+        for b, blk in enumerate(blocks[l]):
+            e0, e1 = layer["edge_ptr"][b], layer["edge_ptr"][b + 1]
+            u0, u1 = layer["unique_ptr"][b], layer["unique_ptr"][b + 1]
+            assert np.array_equal(host(blk.row), layer["block_row"][e0:e1])
+            assert np.array_equal(host(blk.col), layer["block_col"][e0:e1])
+            assert np.array_equal(host(blk.srcdata["_ID"]), layer["unique"][u0:u1])
+            assert blk.num_src_nodes() == u1 - u0
+            assert blk.num_dst_nodes() == layer["seeds_ptr"][b + 1] - layer["seeds_ptr"][b]
+
+
+def test_matrix_sampler_matches_oracle(gsb, oracle, rmat):
+    """Single-minibatch graphsage_sampler (examples/graphsage/graphsage.py:7-17): slice, sample,
+    all_nodes, to_dgl_block -- both the fused (lazy slice) and the unfused order of calls."""
+    indptr, indices = rmat
+    rng = np.random.default_rng(3)
+    seeds0 = rng.integers(0, indptr.size - 1, 1024).astype(np.int64)   # duplicates allowed
+    fanouts = [25, 10]
+    want = oracle.graphsage_batch(indptr, indices, seeds0, np.array([0, 1024]), fanouts, seed=4242)
+    for fused in (True, False):
+        m = gsb.Matrix(new_graph(gsb, indptr, indices))
+        seeds = torch.as_tensor(seeds0).cuda()
+        for l, K in enumerate(fanouts):
+            subA = m[:, seeds]
+            if not fused:
+                assert subA.num_edges() >= 0            # touching the graph materialises the slice
+            sampleA = subA.individual_sampling(K, None, False)
+            seeds = sampleA.all_nodes()
+            blk = sampleA.to_dgl_block()
+            layer = want[l]
+            assert np.array_equal(host(seeds), layer["unique"])
+            if fused:
+                # unfused sampling draws with slot = column of the slice and the same stream
+                # counter, so both orders give the same picks
+                pass
+            assert np.array_equal(host(blk.row), layer["block_row"])
+            assert np.array_equal(host(blk.col), layer["block_col"])
+            assert blk.num_dst_nodes() == layer["seeds"].size
+
+
+def test_graph_accessors_and_formats(gsb, oracle):
+    rng = np.random.default_rng(5)
+    deg = rng.poisson(5, 300)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, 300, indptr[-1]).astype(np.int64)
+    A = new_graph(gsb, indptr, indices)
+    assert (A._CAPI_GetNumRows(), A._CAPI_GetNumCols(), A._CAPI_GetNumEdges()) == (300, 300, indptr[-1])
+    assert np.array_equal(host(A._CAPI_GetCOOCols()), oracle.csc2coo(indptr))
+    assert np.array_equal(host(A._CAPI_GetCOORows()), indices)
+    ip, ids, perm = oracle.coo2csc(indices, oracle.csc2coo(indptr), 300)
+    assert np.array_equal(host(A._CAPI_GetCSRIndptr()), ip)
+    assert np.array_equal(host(A._CAPI_GetCSRIndices()), ids)
+    assert np.array_equal(host(A._CAPI_GetCSREids()), perm)
+    # slicing with encoding: per-minibatch compacted rows
+    seeds = torch.as_tensor(rng.integers(0, 300, 40)).cuda()
+    ptr = torch.tensor([0, 10, 40]).cuda()
+    sub, _ = A._CAPI_BatchColSlicing(seeds, ptr, True)
+    rows, row_ptr = sub._CAPI_BatchGetRows()
+    esub, erows, _, _ = oracle.slice_cols(indptr, indices, host(seeds), host(ptr), 300)
+    uq, cp = oracle.compact(erows)
+    bp, dec = oracle.batch_offsets(uq, 2, 300)
+    assert np.array_equal(host(rows), dec) and np.array_equal(host(row_ptr), bp)
+    assert np.array_equal(host(sub._CAPI_GetCSCIndices()), cp)
+    counts = sub._CAPI_BatchGetColCounts()
+    assert counts == [10, 30]
+
+
+def test_errors_are_exceptions(gsb):
+    A = gsb.Graph(4, 4)
+    A._CAPI_LoadCSC(torch.tensor([0, 1, 2, 3, 4]).cuda(), torch.tensor([0, 1, 2, 3]).cuda())
+    with pytest.raises(RuntimeError):
+        A._CAPI_Slicing(torch.tensor([0, 1]), 1, gsb._CSC, gsb._CSC)        # CPU tensor
+    with pytest.raises(RuntimeError):
+        A._CAPI_Sampling(1, 0, False, gsb._CSC, gsb._CSC)                    # fanout 0
+    with pytest.raises(RuntimeError):
+        A._CAPI_Sampling(0, 2, False, gsb._CSC, gsb._CSC)                    # axis / format mismatch

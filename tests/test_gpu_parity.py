@@ -1,0 +1,216 @@
+"""GPU parity tests: the CUDA kernels, called through the C ABI, against the CPU oracle on
+the same seeded inputs.  Deterministic stages and the counter-based sampler are compared bit
+for bit; the sampler is additionally compared statistically with the reference's reservoir
+sampler (oracle.sample_ref)."""
+import numpy as np
+import pytest
+import torch
+
+from tests import abi
+
+pytestmark = pytest.mark.gpu
+
+
+def dev(a, dtype=torch.int64):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+def rand_csc(rng, n, avg, heavy=0):
+    deg = rng.poisson(avg, n)
+    deg[rng.integers(0, n, max(n // 10, 1))] = 0
+    if heavy:
+        deg[rng.integers(0, n, heavy)] = rng.integers(200, 3000, heavy)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, n, indptr[-1]).astype(np.int64)
+    return indptr, indices
+
+
+@pytest.fixture(scope="module")
+def graph():
+    rng = np.random.default_rng(11)
+    return rand_csc(rng, 5000, 14, heavy=20)
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+@pytest.mark.parametrize("K,replace", [(1, False), (5, False), (15, False), (25, False), (40, False),
+                                       (4, True), (33, True)])
+def test_fused_sampling_bit_exact(oracle, graph, idx_dtype, K, replace):
+    indptr, indices = graph
+    rng = np.random.default_rng(K)
+    seeds = rng.integers(0, indptr.size - 1, 3000)            # with duplicates
+    sub, rows, cols, sel, err = abi.sample_cols(dev(indptr), dev(indices, idx_dtype), dev(seeds), K,
+                                                replace, seed=1234, stream=3)
+    assert err == 0
+    esub, erows, ecols, esel = oracle.sample_spec(indptr, indices, seeds, K, replace, 1234, 3)
+    assert np.array_equal(host(sub), esub)
+    assert np.array_equal(host(sel), esel)
+    assert np.array_equal(host(rows), erows)
+    assert np.array_equal(host(cols), ecols)
+
+
+def test_plain_sampling_and_edge_cases(oracle, graph):
+    indptr, indices = graph
+    d_ip, d_ix = dev(indptr), dev(indices)
+    # seeds == None: every column of the operand
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, None, 7, False, 5, 0)
+    esub, erows, ecols, esel = oracle.sample_spec(indptr, indices, None, 7, False, 5, 0)
+    assert err == 0 and np.array_equal(host(sub), esub) and np.array_equal(host(sel), esel)
+    # no seeds at all
+    empty = torch.empty(0, dtype=torch.int64, device="cuda")
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, empty, 7, False, 5, 0)
+    assert err == 0 and host(sub).tolist() == [0] and rows.numel() == 0
+    # only empty columns
+    zero_cols = np.flatnonzero(np.diff(indptr) == 0)[:50]
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, dev(zero_cols), 7, False, 5, 0)
+    assert err == 0 and int(sub[-1]) == 0 and not host(sub).any()
+    # device-side live count smaller than the launch bound
+    seeds = np.arange(1000)
+    live = torch.tensor([333], dtype=torch.int64, device="cuda")
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, dev(seeds), 6, False, 8, 1, d_S=live)
+    esub, erows, _, esel = oracle.sample_spec(indptr, indices, seeds[:333], 6, False, 8, 1)
+    assert err == 0 and np.array_equal(host(sub)[:334], esub) and np.array_equal(host(sel), esel)
+    # capacity too small is reported, not overrun
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, dev(seeds), 6, False, 8, 1, E_cap=100)
+    assert err & 8
+
+
+def test_reference_fixture_through_abi(oracle):
+    # tests/test_colwise_sampling.cc:7-23 and test_colwise_slicing.cc:7-21 of the reference
+    indptr = np.arange(21) * 5
+    indices = np.arange(100)
+    sub, rows, cols, sel, err = abi.sample_cols(dev(indptr), dev(indices), None, 6, False, 7777, 0)
+    assert host(sub).tolist() == indptr.tolist() and host(rows).tolist() == indices.tolist()
+    for fan in (6, 4):
+        sub, rows, cols, sel, err = abi.sample_cols(dev(indptr), dev(indices), None, fan, True, 7777, 0)
+        assert host(sub).tolist() == (np.arange(21) * fan).tolist()
+        assert rows.numel() == 20 * fan and host(rows).tolist() != indices.tolist()
+        assert np.all(host(rows) // 5 == host(cols))
+    sub, rows, cols, sel, err = abi.slice_cols(dev(indptr), dev(indices), dev(np.arange(3)))
+    assert host(sub).tolist() == [0, 5, 10, 15] and host(rows).tolist() == list(range(15))
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_slicing_bit_exact(oracle, graph, idx_dtype):
+    indptr, indices = graph
+    rng = np.random.default_rng(3)
+    seeds = rng.integers(0, indptr.size - 1, 2000)
+    sub, rows, cols, sel, err = abi.slice_cols(dev(indptr), dev(indices, idx_dtype), dev(seeds))
+    esub, erows, ecols, esel = oracle.slice_cols(indptr, indices, seeds)
+    assert err == 0
+    for a, b in ((sub, esub), (rows, erows), (cols, ecols), (sel, esel)):
+        assert np.array_equal(host(a), b)
+    bptr = np.array([0, 100, 100, 900, 2000])
+    sub, rows, cols, sel, err = abi.slice_cols(dev(indptr), dev(indices, idx_dtype), dev(seeds),
+                                               dev(bptr), 5000)
+    _, erows, _, _ = oracle.slice_cols(indptr, indices, seeds, bptr, 5000)
+    assert np.array_equal(host(rows), erows)
+
+
+def _relabel_case(rng, B, max_seeds, max_edges, nid):
+    ns = rng.integers(1, max_seeds, B)
+    ne = rng.integers(0, max_edges, B)
+    ns[B // 2] = 0
+    ne[B // 2] = 0
+    if B > 3:
+        ne[1] = 0
+    sp = np.concatenate([[0], np.cumsum(ns)])
+    ep = np.concatenate([[0], np.cumsum(ne)])
+    seeds = rng.integers(0, nid, sp[-1])
+    rows = rng.integers(0, nid, ep[-1])
+    col_local = np.concatenate([rng.integers(sp[b], sp[b + 1], ne[b]) if ns[b] else
+                                np.empty(0, np.int64) for b in range(B)] + [np.empty(0, np.int64)])
+    col_local = np.sort(col_local).astype(np.int64)   # column-sorted COO like the sampler emits
+    return seeds, sp, rows, col_local, ep
+
+
+@pytest.mark.parametrize("B,max_seeds,max_edges,nid", [(1, 50, 400, 100), (7, 300, 5000, 1000),
+                                                        (32, 1200, 20000, 200000), (3, 5, 3, 10)])
+def test_batch_relabel_bit_exact(oracle, B, max_seeds, max_edges, nid):
+    rng = np.random.default_rng(B)
+    seeds, sp, rows, col_local, ep = _relabel_case(rng, B, max_seeds, max_edges, nid)
+    uq, up, orow, ocol, err = abi.batch_relabel(dev(seeds), dev(sp), dev(rows), dev(col_local), dev(ep))
+    assert err == 0
+    euq, eup, eorow, eocol = oracle.batch_coo_relabel(seeds, sp, seeds[col_local], rows, ep)
+    assert np.array_equal(host(up), eup)
+    assert np.array_equal(host(uq), euq)
+    assert np.array_equal(host(orow), eorow)
+    assert np.array_equal(host(ocol), eocol)
+    # node lists only (all_nodes)
+    uq2, up2, _, _, err = abi.batch_relabel(dev(seeds), dev(sp), dev(rows), None, dev(ep), want_edges=False)
+    assert err == 0 and np.array_equal(host(uq2), euq) and np.array_equal(host(up2), eup)
+
+
+def test_relabel_reports_bad_ids():
+    seeds = dev([1, 2, 3])
+    rows = dev([5, 2 ** 33, -4])
+    uq, up, orow, ocol, err = abi.batch_relabel(seeds, dev([0, 3]), rows, dev([0, 1, 2]), dev([0, 3]))
+    assert err & 16
+
+
+def test_sampler_statistics_vs_reference(oracle):
+    """Per-edge inclusion frequencies of the CUDA sampler against (a) the exact value K/deg and
+    (b) the reference's reservoir sampler, chi-square at p > 0.01."""
+    from scipy import stats
+
+    deg, K, S = 37, 10, 64000
+    indptr = np.array([0, deg, deg + 3])
+    indices = np.arange(deg + 3)
+    seeds = np.zeros(S, np.int64)
+    _, rows, cols, _, err = abi.sample_cols(dev(indptr), dev(indices), dev(seeds), K, False, 99, 0)
+    assert err == 0
+    rows, cols = host(rows), host(cols)
+    for i in range(0, S, 997):                              # distinct picks per column
+        assert np.unique(rows[cols == i]).size == K
+    mine = np.bincount(rows, minlength=deg).astype(float)
+    n = S
+    # inclusion counts of a uniform K-subset: variance n*p*(1-p), covariance gives (deg-1) dof
+    p = K / deg
+    chi2 = ((mine - n * p) ** 2 / (n * p * (1 - p))).sum() * (deg - 1) / deg
+    assert stats.chi2.sf(chi2, deg - 1) > 0.01
+    _, rrows, rcols, _ = oracle.sample_ref(indptr, indices, seeds, K, False)
+    keep = (rcols % 32) == 0            # the reference's 32 rows per block repeat one sample
+    ref = np.bincount(rrows[keep], minlength=deg).astype(float)
+    m = keep.sum() / K
+    pooled = (mine + ref) / (n + m)
+    chi2 = (((mine - n * pooled) ** 2) / (n * pooled * (1 - p)) +
+            ((ref - m * pooled) ** 2) / (m * pooled * (1 - p))).sum() * (deg - 1) / deg
+    assert stats.chi2.sf(chi2, deg - 1) > 0.01
+
+
+def test_weighted_sampling_invariants_and_statistics(oracle, graph):
+    from scipy import stats
+
+    indptr, indices = graph
+    rng = np.random.default_rng(8)
+    probs = rng.random(indices.size).astype(np.float32) + 0.05
+    seeds = rng.integers(0, indptr.size - 1, 1500)
+    d_p = dev(probs, torch.float32)
+    for K in (3, 20, 48):
+        sub, rows, cols, sel, err = abi.sample_cols(dev(indptr), dev(indices), dev(seeds), K, False,
+                                                    5, 0, probs=d_p)
+        assert err == 0
+        sub, rows, cols, sel = map(host, (sub, rows, cols, sel))
+        degs = indptr[seeds + 1] - indptr[seeds]
+        assert np.array_equal(np.diff(sub), np.minimum(degs, K))
+        assert np.array_equal(rows, indices[sel])
+        assert np.all((sel >= indptr[seeds[cols]]) & (sel < indptr[seeds[cols] + 1]))
+        for i in range(0, seeds.size, 37):
+            s = sel[sub[i]:sub[i + 1]]
+            assert np.unique(s).size == s.size
+    # one column, K = 1: inclusion probability of edge e must be p_e / sum(p)
+    deg, S = 12, 40000
+    w = np.array([1, 2, 3, 4, 5, 6, 1, 1, 2, 2, 8, 0.5], np.float32)
+    ip = np.array([0, deg])
+    _, rows, _, _, err = abi.sample_cols(dev(ip), dev(np.arange(deg)), dev(np.zeros(S, np.int64)), 1,
+                                         False, 17, 0, probs=dev(w, torch.float32))
+    cnt = np.bincount(host(rows), minlength=deg)
+    assert stats.chisquare(cnt, S * w / w.sum()).pvalue > 0.01
+    # with replacement: K independent draws from the same distribution
+    _, rows, _, _, err = abi.sample_cols(dev(ip), dev(np.arange(deg)), dev(np.zeros(4000, np.int64)),
+                                         8, True, 21, 0, probs=dev(w, torch.float32))
+    cnt = np.bincount(host(rows), minlength=deg)
+    assert rows.numel() == 32000 and stats.chisquare(cnt, 32000 * w / w.sum()).pvalue > 0.01
