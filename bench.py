@@ -35,6 +35,9 @@ WORKLOADS = {
     # name: nodes, directed edges, train seeds, fanouts, batch, minibatches per super-batch
     "cfg2": dict(nodes=2449029, edges=123718280, train=196615, fanouts=[15, 10, 5], batch=1024,
                  super_batch=32, index_dtype="int64", max_degree=20000),
+    # profiling shape: graph larger than L2, a few GB on the device, short kernels
+    "medium": dict(nodes=1000000, edges=50000000, train=65536, fanouts=[15, 10, 5], batch=1024,
+                   super_batch=16, index_dtype="int64", max_degree=20000),
     # reduced shape for quick functional runs (same pipeline, fits any GPU)
     "small": dict(nodes=200000, edges=8000000, train=20480, fanouts=[15, 10, 5], batch=1024,
                   super_batch=8, index_dtype="int64", max_degree=5000),
@@ -192,6 +195,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("GSB_WORKLOAD", "cfg2"), choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--streams", type=int, default=int(os.environ.get("GSB_STREAMS", "2")),
+                    help="independent super-batches in flight (each on its own CUDA stream)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -237,19 +242,43 @@ def main():
     del probe
     torch.cuda.empty_cache()
     # measured capacities; an overflow would raise the sampler's error word (checked below)
-    sampler = pipeline.GraphSAGESampler(indptr, indices, cfg["super_batch"], max_seeds,
-                                        cfg["fanouts"], capacities=caps)
+    # Super-batches are independent: `--streams` of them are in flight at once, each with its
+    # own pre-allocated sampler on its own CUDA stream, so the latency-bound relabel passes of
+    # one overlap the bandwidth-bound sampling pass of another.
+    nstreams = max(1, args.streams)
+    samplers = [pipeline.GraphSAGESampler(indptr, indices, cfg["super_batch"], max_seeds,
+                                          cfg["fanouts"], capacities=caps) for _ in range(nstreams)]
+    streams = [torch.cuda.Stream(device=dev) for _ in range(nstreams)]
+    sampler = samplers[0]
 
     counts = torch.zeros(args.steps + args.warmup, 3 * L, dtype=torch.int64, device=dev)
 
-    def step(i, row):
+    def step(i, row, overlapped=True):
         s, p = batches_dev[i % nb]
-        sampler.sample(s, p, counts_out=counts[row])
+        if not overlapped:
+            sampler.sample(s, p, counts_out=counts[row])
+            return
+        k = i % nstreams
+        with torch.cuda.stream(streams[k]):
+            samplers[k].sample(s, p, counts_out=counts[row])
 
+    def fork():
+        cur = torch.cuda.current_stream(dev)
+        for st in streams:
+            st.wait_stream(cur)
+
+    def join():
+        cur = torch.cuda.current_stream(dev)
+        for st in streams:
+            cur.wait_stream(st)
+
+    fork()
     for w in range(args.warmup):
         step(w, w)
+    join()
     torch.cuda.synchronize()
-    sampler.check()
+    for sm in samplers:
+        sm.check()
 
     clocks = ClockSampler(local_rank)
     clocks.start()
@@ -260,22 +289,26 @@ def main():
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     ev0.record()
+    fork()
     for k in range(args.steps):
         step(args.warmup + k, args.warmup + k)
+    join()
     ev1.record()
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     launches = pipeline.kernel_launches() - launches0
     elapsed_ms = ev0.elapsed_time(ev1)
-    sampler.check()
+    for sm in samplers:
+        sm.check()
     c_host = counts[args.warmup:].cpu().numpy().reshape(args.steps, L, 3)
     edges = int(c_host[:, :, 1].sum())
 
     # ---- per-kernel durations of the same K steps (CUDA events around every launch)
+    # (one stream, no overlap: a kernel's duration is then its own)
     pipeline.timing_enable(True)
     for k in range(args.steps):
-        step(args.warmup + k, args.warmup + k)
+        step(args.warmup + k, args.warmup + k, overlapped=False)
     timed = pipeline.timing_collect()
     pipeline.timing_enable(False)
     clocks.stop()
@@ -355,7 +388,10 @@ def main():
                        "train_seeds": cfg["train"], "parallelism": "replica x%d" % world,
                        "l2": "inputs_larger_than_l2 (graph indices %.1f GB)" % (indices.numel() * indices.element_size() / 1e9),
                        "edges_per_step": edges / args.steps / max(world, 1),
-                       "capacities": "measured x1.15"},
+                       "mean_SEU_per_layer": [[float(c_host[:, l, j].mean()) for j in range(3)]
+                                              for l in range(L)],
+                       "capacities": "measured x1.15",
+                       "streams": nstreams},
             "e2e": {"value": e2e_edges / (e2e_ms / 1e3), "unit": "edges/s",
                     "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
                     "api": "BatchMatrix.graphsage (one native call per super-batch)"},

@@ -168,7 +168,7 @@ __device__ __forceinline__ i64 find_slot(const u64* tab, u32 slots, u32 key, u64
   return -1;
 }
 
-__global__ void __launch_bounds__(RL_THREADS) relabel_scan_kernel(const RelabelParams p) {
+__global__ void __launch_bounds__(RL_THREADS, 6) relabel_scan_kernel(const RelabelParams p) {
   __shared__ i64 s_scan[34];
   __shared__ int s_tile;
   __shared__ i64 s_base;
@@ -248,7 +248,9 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_scan_kernel(const RelabelP
 
 __global__ void __launch_bounds__(RL_THREADS) relabel_edges_kernel(const RelabelParams p) {
   const i64 n = p.hdr->n_edges;
-  for (i64 e = (i64)blockIdx.x * RL_THREADS + threadIdx.x; e < n; e += (i64)gridDim.x * RL_THREADS) {
+  // last minibatch first: the scan pass ended there, its tables are in L2
+  for (i64 t = (i64)blockIdx.x * RL_THREADS + threadIdx.x; t < n; t += (i64)gridDim.x * RL_THREADS) {
+    const i64 e = n - 1 - t;
     const int b = find_segment(p.edge_ptr, p.B, e);
     const i64 base = p.table_ptr[b];
     const u32 slots = (u32)(p.table_ptr[b + 1] - base);

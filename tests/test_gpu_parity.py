@@ -208,9 +208,9 @@ def test_weighted_sampling_invariants_and_statistics(oracle, graph):
     _, rows, _, _, err = abi.sample_cols(dev(ip), dev(np.arange(deg)), dev(np.zeros(S, np.int64)), 1,
                                          False, 17, 0, probs=dev(w, torch.float32))
     cnt = np.bincount(host(rows), minlength=deg)
-    assert stats.chisquare(cnt, S * w / w.sum()).pvalue > 0.01
+    assert stats.chisquare(cnt, S * w.astype(np.float64) / w.astype(np.float64).sum()).pvalue > 0.01
     # with replacement: K independent draws from the same distribution
     _, rows, _, _, err = abi.sample_cols(dev(ip), dev(np.arange(deg)), dev(np.zeros(4000, np.int64)),
                                          8, True, 21, 0, probs=dev(w, torch.float32))
     cnt = np.bincount(host(rows), minlength=deg)
-    assert rows.numel() == 32000 and stats.chisquare(cnt, 32000 * w / w.sum()).pvalue > 0.01
+    assert rows.numel() == 32000 and stats.chisquare(cnt, 32000 * w.astype(np.float64) / w.astype(np.float64).sum()).pvalue > 0.01
