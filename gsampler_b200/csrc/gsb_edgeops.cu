@@ -1,0 +1,259 @@
+// Edge-map / reduce operators on sampled sub-matrices: generalised SpMM
+// (out[dst] = reduce over the edges of dst of op(u[src], e[edge])) and SDDMM
+// (out[edge] = op(lhs[sel], rhs[sel])), fp32, with the fused forms the LADIES /
+// FastGCN samplers use (sum of e^2, sum of e / u[src]).
+//
+// These are streaming, HBM-bound kernels: scalar features (the samplers' case)
+// are reduced with a warp per segment, lanes across the segment's edges and a
+// shuffle reduction, so one long column does not serialise on a single thread;
+// wider features put the lanes across the feature dimension.
+#include <math_constants.h>
+
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+enum { OP_ADD = 0, OP_SUB, OP_MUL, OP_DIV, OP_COPY_LHS, OP_COPY_RHS, OP_SQUARE_RHS, OP_RDIV };
+enum { RED_SUM = 0, RED_MAX, RED_MIN };
+
+__device__ __forceinline__ float apply_op(int op, float l, float r) {
+  switch (op) {
+    case OP_ADD: return l + r;
+    case OP_SUB: return l - r;
+    case OP_MUL: return l * r;
+    case OP_DIV: return l / r;
+    case OP_COPY_LHS: return l;
+    case OP_COPY_RHS: return r;
+    case OP_SQUARE_RHS: return r * r;
+    default: return r / l;  // OP_RDIV
+  }
+}
+__host__ __device__ inline bool op_uses_lhs(int op) { return op != OP_COPY_RHS && op != OP_SQUARE_RHS; }
+__host__ __device__ inline bool op_uses_rhs(int op) { return op != OP_COPY_LHS; }
+
+struct SpmmParams {
+  const i64* indptr;
+  const void* indices;
+  const i64* e_ids;  // nullable: storage position -> edge feature row
+  i64 nseg;
+  int op, reduce;
+  const float* u; i64 u_len;
+  const float* e; i64 e_len;
+  const i64* u_off; const i64* e_off;  // nullable broadcast offsets, [out_len]
+  float* out; i64 out_len;
+  i64* arg_u; i64* arg_e;  // nullable
+};
+
+constexpr int EO_THREADS = 256;
+
+// Scalar output per segment: warp per segment, lanes over edges.
+template <typename IndexT>
+__global__ void __launch_bounds__(EO_THREADS) spmm_scalar_kernel(const SpmmParams p) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * EO_THREADS + threadIdx.x) >> 5;
+  const i64 nwarps = ((i64)gridDim.x * EO_THREADS) >> 5;
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  for (i64 seg = warp0; seg < p.nseg; seg += nwarps) {
+    const i64 st = __ldg(p.indptr + seg), en = __ldg(p.indptr + seg + 1);
+    float acc = p.reduce == RED_SUM ? 0.f : (p.reduce == RED_MAX ? -CUDART_INF_F : CUDART_INF_F);
+    i64 au = -1, ae = -1;
+    for (i64 i = st + lane; i < en; i += 32) {
+      const i64 cid = ul || p.arg_u ? load_index<IndexT>(p.indices, i) : 0;
+      const i64 eid = p.e_ids ? __ldg(p.e_ids + i) : i;
+      const float l = ul ? __ldg(p.u + cid * p.u_len) : 0.f;
+      const float r = ur ? __ldg(p.e + eid * p.e_len) : 0.f;
+      const float v = apply_op(p.op, l, r);
+      if (p.reduce == RED_SUM) acc += v;
+      else if ((p.reduce == RED_MAX && v > acc) || (p.reduce == RED_MIN && v < acc)) { acc = v; au = cid; ae = eid; }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+      const float o = __shfl_xor_sync(0xffffffffu, acc, d);
+      const i64 ou = __shfl_xor_sync(0xffffffffu, au, d), oe = __shfl_xor_sync(0xffffffffu, ae, d);
+      if (p.reduce == RED_SUM) acc += o;
+      else if ((p.reduce == RED_MAX && (o > acc || (o == acc && oe >= 0 && (ae < 0 || oe < ae)))) ||
+               (p.reduce == RED_MIN && (o < acc || (o == acc && oe >= 0 && (ae < 0 || oe < ae))))) {
+        acc = o; au = ou; ae = oe;
+      }
+    }
+    if (lane == 0) {
+      if (p.reduce == RED_SUM) {
+        p.out[seg] += acc;  // the caller zero-fills `out` (accumulate semantics)
+      } else {
+        p.out[seg] = en > st ? acc : 0.f;  // empty segment -> 0
+        if (p.arg_u && ul) p.arg_u[seg] = en > st ? au : 0;
+        if (p.arg_e && ur) p.arg_e[seg] = en > st ? ae : 0;
+      }
+    }
+  }
+}
+
+// Feature vectors: warp per segment, lanes over the feature dimension.
+template <typename IndexT>
+__global__ void __launch_bounds__(EO_THREADS) spmm_vector_kernel(const SpmmParams p) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * EO_THREADS + threadIdx.x) >> 5;
+  const i64 nwarps = ((i64)gridDim.x * EO_THREADS) >> 5;
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  for (i64 seg = warp0; seg < p.nseg; seg += nwarps) {
+    const i64 st = __ldg(p.indptr + seg), en = __ldg(p.indptr + seg + 1);
+    for (i64 f = lane; f < p.out_len; f += 32) {
+      const i64 lo = p.u_off ? p.u_off[f] : (p.u_len == 1 ? 0 : f);
+      const i64 ro = p.e_off ? p.e_off[f] : (p.e_len == 1 ? 0 : f);
+      float acc = p.reduce == RED_SUM ? 0.f : (p.reduce == RED_MAX ? -CUDART_INF_F : CUDART_INF_F);
+      i64 au = 0, ae = 0;
+      for (i64 i = st; i < en; ++i) {
+        const i64 cid = load_index<IndexT>(p.indices, i);
+        const i64 eid = p.e_ids ? __ldg(p.e_ids + i) : i;
+        const float l = ul ? __ldg(p.u + cid * p.u_len + lo) : 0.f;
+        const float r = ur ? __ldg(p.e + eid * p.e_len + ro) : 0.f;
+        const float v = apply_op(p.op, l, r);
+        if (p.reduce == RED_SUM) acc += v;
+        else if ((p.reduce == RED_MAX && v > acc) || (p.reduce == RED_MIN && v < acc)) { acc = v; au = cid; ae = eid; }
+      }
+      const i64 o = seg * p.out_len + f;
+      if (p.reduce == RED_SUM) {
+        p.out[o] += acc;
+      } else {
+        p.out[o] = en > st ? acc : 0.f;
+        if (p.arg_u && ul) p.arg_u[o] = au;
+        if (p.arg_e && ur) p.arg_e[o] = ae;
+      }
+    }
+  }
+}
+
+struct CooParams {
+  const i64* row; const i64* col; const i64* e_ids; i64 nnz;
+  int op;
+  const float* lhs; i64 lhs_len; int lhs_target;
+  const float* rhs; i64 rhs_len; int rhs_target;
+  const i64* lhs_off; const i64* rhs_off;
+  float* out; i64 out_len;
+  int out_target;  // SpMM on COO: 0 = scatter to row, 2 = to col (unused by SDDMM)
+};
+
+__device__ __forceinline__ i64 select_target(int target, i64 src, i64 eid, i64 dst) {
+  return target == 0 ? src : (target == 1 ? eid : dst);
+}
+
+// out[eid, f] = op(lhs[sel_l], rhs[sel_r]); thread per (edge, feature)
+__global__ void __launch_bounds__(EO_THREADS) sddmm_coo_kernel(const CooParams p) {
+  const i64 total = p.nnz * p.out_len;
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  for (i64 t = (i64)blockIdx.x * EO_THREADS + threadIdx.x; t < total; t += (i64)gridDim.x * EO_THREADS) {
+    const i64 ed = t / p.out_len, f = t - ed * p.out_len;
+    const i64 src = __ldg(p.row + ed), dst = __ldg(p.col + ed);
+    const i64 eid = p.e_ids ? __ldg(p.e_ids + ed) : ed;
+    const i64 lo = p.lhs_off ? p.lhs_off[f] : (p.lhs_len == 1 ? 0 : f);
+    const i64 ro = p.rhs_off ? p.rhs_off[f] : (p.rhs_len == 1 ? 0 : f);
+    const float l = ul ? __ldg(p.lhs + select_target(p.lhs_target, src, eid, dst) * p.lhs_len + lo) : 0.f;
+    const float r = ur ? __ldg(p.rhs + select_target(p.rhs_target, src, eid, dst) * p.rhs_len + ro) : 0.f;
+    p.out[eid * p.out_len + f] = apply_op(p.op, l, r);
+  }
+}
+
+// sum-SpMM on an unsorted COO: atomicAdd per (edge, feature).  lhs = node
+// feature of the OTHER endpoint, rhs = edge feature.
+__global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_kernel(const CooParams p) {
+  const i64 total = p.nnz * p.out_len;
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  for (i64 t = (i64)blockIdx.x * EO_THREADS + threadIdx.x; t < total; t += (i64)gridDim.x * EO_THREADS) {
+    const i64 ed = t / p.out_len, f = t - ed * p.out_len;
+    const i64 r0 = __ldg(p.row + ed), c0 = __ldg(p.col + ed);
+    const i64 src = p.out_target == 2 ? r0 : c0;  // feature side
+    const i64 dst = p.out_target == 2 ? c0 : r0;  // reduced side
+    const i64 eid = p.e_ids ? __ldg(p.e_ids + ed) : ed;
+    const i64 lo = p.lhs_off ? p.lhs_off[f] : (p.lhs_len == 1 ? 0 : f);
+    const i64 ro = p.rhs_off ? p.rhs_off[f] : (p.rhs_len == 1 ? 0 : f);
+    const float l = ul ? __ldg(p.lhs + src * p.lhs_len + lo) : 0.f;
+    const float r = ur ? __ldg(p.rhs + eid * p.rhs_len + ro) : 0.f;
+    atomicAdd(p.out + dst * p.out_len + f, apply_op(p.op, l, r));
+  }
+}
+
+static int wide_grid(i64 work_items, int per_block) {
+  i64 g = (work_items + per_block - 1) / per_block;
+  if (g > 148 * 16) g = 148 * 16;
+  return g < 1 ? 1 : (int)g;
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" int gsb_spmm_segmented(const int64_t* indptr, const void* indices, int indices_dtype,
+                                  const int64_t* e_ids, int64_t nseg, int op, int reduce,
+                                  const float* u, int64_t u_len, const float* e, int64_t e_len,
+                                  const int64_t* u_off, const int64_t* e_off, float* out,
+                                  int64_t out_len, int64_t* arg_u, int64_t* arg_e,
+                                  void* cuda_stream) {
+  if (nseg == 0) return GSB_OK;
+  if (!indptr || !indices || !out || nseg < 0 || out_len < 1) return GSB_ERR_INVALID;
+  if (op < OP_ADD || op > OP_RDIV || reduce < RED_SUM || reduce > RED_MIN) return GSB_ERR_INVALID;
+  if ((op_uses_lhs(op) && (!u || u_len < 1)) || (op_uses_rhs(op) && (!e || e_len < 1)))
+    return GSB_ERR_INVALID;
+  if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
+  SpmmParams p{(const i64*)indptr, indices, (const i64*)e_ids, nseg, op, reduce, u, u_len, e, e_len,
+               (const i64*)u_off, (const i64*)e_off, out, out_len, (i64*)arg_u, (i64*)arg_e};
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  const int grid = wide_grid(nseg, EO_THREADS / 32);
+  LaunchScope ls(KID_EDGE_SUM, st);
+  const bool scalar = out_len == 1;
+  if (indices_dtype == GSB_I32) {
+    if (scalar) spmm_scalar_kernel<int><<<grid, EO_THREADS, 0, st>>>(p);
+    else spmm_vector_kernel<int><<<grid, EO_THREADS, 0, st>>>(p);
+  } else {
+    if (scalar) spmm_scalar_kernel<i64><<<grid, EO_THREADS, 0, st>>>(p);
+    else spmm_vector_kernel<i64><<<grid, EO_THREADS, 0, st>>>(p);
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+static int check_coo(const int64_t* row, const int64_t* col, int64_t nnz, int op, const float* lhs,
+                     int64_t lhs_len, const float* rhs, int64_t rhs_len, float* out,
+                     int64_t out_len) {
+  if (nnz < 0 || out_len < 1 || !row || !col || !out) return GSB_ERR_INVALID;
+  if (op < OP_ADD || op > OP_RDIV) return GSB_ERR_INVALID;
+  if ((op_uses_lhs(op) && (!lhs || lhs_len < 1)) || (op_uses_rhs(op) && (!rhs || rhs_len < 1)))
+    return GSB_ERR_INVALID;
+  return GSB_OK;
+}
+
+extern "C" int gsb_sddmm_coo(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                             int64_t nnz, int op, const float* lhs, int64_t lhs_len, int lhs_target,
+                             const float* rhs, int64_t rhs_len, int rhs_target,
+                             const int64_t* lhs_off, const int64_t* rhs_off, float* out,
+                             int64_t out_len, void* cuda_stream) {
+  if (nnz == 0) return GSB_OK;
+  int rc = check_coo(row, col, nnz, op, lhs, lhs_len, rhs, rhs_len, out, out_len);
+  if (rc != GSB_OK) return rc;
+  if (lhs_target < 0 || lhs_target > 2 || rhs_target < 0 || rhs_target > 2) return GSB_ERR_INVALID;
+  CooParams p{(const i64*)row, (const i64*)col, (const i64*)e_ids, nnz, op, lhs, lhs_len, lhs_target,
+              rhs, rhs_len, rhs_target, (const i64*)lhs_off, (const i64*)rhs_off, out, out_len, 0};
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  LaunchScope ls(KID_EDGE_OP, st);
+  sddmm_coo_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_spmm_coo_sum(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                                int64_t nnz, int op, int u_target, const float* u, int64_t u_len,
+                                const float* e, int64_t e_len, const int64_t* u_off,
+                                const int64_t* e_off, float* out, int64_t out_len,
+                                void* cuda_stream) {
+  if (nnz == 0) return GSB_OK;
+  int rc = check_coo(row, col, nnz, op, u, u_len, e, e_len, out, out_len);
+  if (rc != GSB_OK) return rc;
+  if (u_target != 0 && u_target != 2) return GSB_ERR_INVALID;
+  // u_target 0: features live on rows, the sum goes to columns; 2: the reverse
+  CooParams p{(const i64*)row, (const i64*)col, (const i64*)e_ids, nnz, op, u, u_len, 0, e, e_len, 1,
+              (const i64*)u_off, (const i64*)e_off, out, out_len, u_target == 0 ? 2 : 0};
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  LaunchScope ls(KID_EDGE_SUM, st);
+  spmm_coo_sum_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

@@ -1,0 +1,298 @@
+// Collective (layer-wise) selection: choose K of the R candidates of every
+// segment, uniformly or with probability weights, without replacement; plus
+// the with-replacement draws for a single segment.
+//
+// Weighted selection without replacement = the K largest A-Res keys
+// log2(u_i)/p_i (u_i = draw 0 of element i's counter-based stream); uniform
+// selection = the K largest raw draws.  Instead of sorting all R keys, the
+// K-th largest key of every segment is located by a 4-pass radix select over
+// 32-bit orderable keys (per-segment 256-bin histograms), and one ordered
+// compaction emits the winners in ascending index order; ties on the threshold
+// key go to the lowest indices.  Everything is sized by R, nothing by K.
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+constexpr int LS_THREADS = 256;
+
+struct SegState {
+  u32 prefix, mask, remaining, take_all;
+};
+
+struct ListParams {
+  const float* probs;  // nullable -> uniform
+  const i64* range;    // [B+1]
+  int B;
+  i64 R;               // range[B] upper bound (host value)
+  i64 K;
+  u64 seed; u32 stream;
+  u32* keys;           // [R]
+  u32* hist;           // [B*256]
+  SegState* state;     // [B]
+  u32* pre_gt;         // [R+1]
+  u32* pre_eq;         // [R+1]
+  i64* out_idx;        // [<= B*K]
+  i64* out_range;      // [B+1]
+  u64* status; int* ticket;
+  int* err;
+};
+
+__device__ __forceinline__ u32 list_key(const ListParams& p, i64 i) {
+  const Philox4 blk = stream_block(p.seed, p.stream, (u64)i, 0);
+  if (!p.probs) return blk.x;
+  const float pr = __ldg(p.probs + i);
+  if (!(pr > 0.f)) return 0u;
+  const float u = ((float)blk.x + 1.0f) * 2.3283064365386963e-10f;
+  const float k = __log2f(u) / pr;
+  u32 b = __float_as_uint(k);
+  b = (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+  return b == 0u ? 1u : b;
+}
+
+// one block: out_range = scan of min(K, len); reset the per-segment state
+__global__ void list_setup_kernel(const ListParams p) {
+  __shared__ i64 s_scan[34];
+  __shared__ i64 s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  for (int b0 = 0; b0 < p.B; b0 += blockDim.x) {
+    const int b = b0 + threadIdx.x;
+    i64 take = 0;
+    if (b < p.B) {
+      i64 len = p.range[b + 1] - p.range[b];
+      if (len < 0) { raise(p.err, ERRBIT_BAD_INPUT); len = 0; }
+      take = len < p.K ? len : p.K;
+      p.state[b] = SegState{0u, 0u, (u32)take, len <= p.K ? 1u : 0u};
+    }
+    i64 tot;
+    const i64 ex = block_exclusive_scan(take, s_scan, &tot);
+    if (b < p.B) p.out_range[b] = s_carry + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry += tot;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) {
+    p.out_range[p.B] = s_carry;
+    if (p.range[p.B] > p.R) raise(p.err, ERRBIT_CAPACITY);
+  }
+}
+
+__global__ void __launch_bounds__(LS_THREADS) list_keys_kernel(const ListParams p) {
+  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
+  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS)
+    p.keys[i] = list_key(p, i);
+}
+
+__global__ void __launch_bounds__(LS_THREADS) list_hist_kernel(const ListParams p, int shift) {
+  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
+  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS) {
+    const int b = find_segment(p.range, p.B, i);
+    const SegState s = p.state[b];
+    if (s.take_all) continue;
+    const u32 k = p.keys[i];
+    if ((k & s.mask) == s.prefix) atomicAdd(p.hist + b * 256 + ((k >> shift) & 255u), 1u);
+  }
+}
+
+// block per segment: locate the bucket that holds the `remaining`-th largest key
+__global__ void list_pick_kernel(const ListParams p, int shift) {
+  const int b = blockIdx.x;
+  __shared__ u32 s_h[256];
+  s_h[threadIdx.x] = p.hist[b * 256 + threadIdx.x];
+  p.hist[b * 256 + threadIdx.x] = 0;  // ready for the next pass
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    SegState s = p.state[b];
+    if (!s.take_all) {
+      u32 run = 0;
+      int d = 255;
+      for (; d > 0; --d) {
+        if (run + s_h[d] >= s.remaining) break;
+        run += s_h[d];
+      }
+      s.remaining -= run;
+      s.prefix |= (u32)d << shift;
+      s.mask |= 255u << shift;
+      p.state[b] = s;
+    }
+  }
+}
+
+// exclusive prefixes (over ALL items, segment starts are subtracted later) of
+// "key above the segment threshold" and "key equal to it"
+__global__ void __launch_bounds__(LS_THREADS) list_scan_kernel(const ListParams p) {
+  __shared__ i64 s_scan[34];
+  __shared__ int s_tile;
+  __shared__ i64 s_base;
+  if (threadIdx.x == 0) s_tile = atomicAdd(p.ticket, 1);
+  __syncthreads();
+  const int tile = s_tile;
+  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
+  const i64 tiles = n / LS_THREADS + 1;  // one spare slot so that pre_*[n] is written
+  if (tile >= tiles) return;
+  const i64 i = (i64)tile * LS_THREADS + threadIdx.x;
+  i64 packed = 0;  // gt count in the high 31 bits, eq count in the low 31
+  if (i < n) {
+    const int b = find_segment(p.range, p.B, i);
+    const SegState s = p.state[b];
+    const u32 k = p.keys[i];
+    if (s.take_all || k > s.prefix) packed = 1ll << 31;
+    else if (k == s.prefix) packed = 1;
+  }
+  i64 total;
+  const i64 loff = block_exclusive_scan(packed, s_scan, &total);
+  if (threadIdx.x < 32) {
+    i64 base = chained_exclusive_prefix(p.status, tile, total, p.err);
+    if (threadIdx.x == 0) s_base = base;
+  }
+  __syncthreads();
+  if (i <= n) {
+    const i64 v = s_base + loff;
+    p.pre_gt[i] = (u32)(v >> 31);
+    p.pre_eq[i] = (u32)(v & 0x7FFFFFFF);
+  }
+}
+
+__global__ void __launch_bounds__(LS_THREADS) list_emit_kernel(const ListParams p) {
+  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
+  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS) {
+    const int b = find_segment(p.range, p.B, i);
+    const SegState s = p.state[b];
+    const i64 r0 = p.range[b];
+    const u32 gt_before = p.pre_gt[i] - p.pre_gt[r0];
+    const u32 eq_before = p.pre_eq[i] - p.pre_eq[r0];
+    const u32 k = p.keys[i];
+    const bool gt = s.take_all || k > s.prefix;
+    const bool eq = !s.take_all && k == s.prefix;
+    if (gt || (eq && eq_before < s.remaining)) {
+      const u32 eq_taken = eq_before < s.remaining ? eq_before : s.remaining;
+      p.out_idx[p.out_range[b] + gt_before + (s.take_all ? 0u : eq_taken)] = i;
+    }
+  }
+}
+
+// K draws with replacement from one segment [0, n): uniform, or by inverse CDF
+__global__ void list_replace_uniform_kernel(i64 n, i64 K, u64 seed, u32 stream, i64* out) {
+  for (i64 k = (i64)blockIdx.x * blockDim.x + threadIdx.x; k < K; k += (i64)gridDim.x * blockDim.x) {
+    const Philox4 blk = stream_block(seed, stream, 0, (u32)(k >> 2));
+    out[k] = (i64)(((u64)pick_word(blk, (u32)k) * (u64)n) >> 32);
+  }
+}
+
+// inclusive prefix sums of probs (double accumulators) by one block
+__global__ void list_cdf_kernel(const float* __restrict__ probs, i64 n, double* __restrict__ cdf) {
+  __shared__ double s_part[1024];
+  const i64 per = (n + blockDim.x - 1) / blockDim.x;
+  const i64 lo = (i64)threadIdx.x * per, hi = lo + per < n ? lo + per : n;
+  double acc = 0;
+  for (i64 i = lo; i < hi; ++i) acc += fmaxf(probs[i], 0.f);
+  s_part[threadIdx.x] = acc;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    double run = 0;
+    for (int t = 0; t < (int)blockDim.x; ++t) { const double v = s_part[t]; s_part[t] = run; run += v; }
+  }
+  __syncthreads();
+  acc = s_part[threadIdx.x];
+  for (i64 i = lo; i < hi; ++i) { acc += fmaxf(probs[i], 0.f); cdf[i] = acc; }
+}
+
+__global__ void list_replace_cdf_kernel(const double* __restrict__ cdf, i64 n, i64 K, u64 seed,
+                                        u32 stream, i64* out) {
+  const double total = cdf[n - 1];
+  for (i64 k = (i64)blockIdx.x * blockDim.x + threadIdx.x; k < K; k += (i64)gridDim.x * blockDim.x) {
+    const Philox4 blk = stream_block(seed, stream, 0, (u32)(k >> 2));
+    const double target = ((double)pick_word(blk, (u32)k) + 1.0) * (1.0 / 4294967296.0) * total;
+    i64 lo = 0, hi = n - 1;  // first position with cdf >= target
+    while (lo < hi) {
+      const i64 mid = (lo + hi) >> 1;
+      if (cdf[mid] < target) lo = mid + 1; else hi = mid;
+    }
+    out[k] = lo;
+  }
+}
+
+struct ListLayout {
+  size_t ticket, status, keys, hist, state, pre_gt, pre_eq, total;
+  i64 tiles;
+};
+
+static ListLayout list_layout(i64 R, i64 B) {
+  ListLayout L;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  L.tiles = R / LS_THREADS + 2;
+  size_t o = 0;
+  L.ticket = o; o = up(o + 256);
+  L.status = o; o = up(o + sizeof(u64) * (size_t)L.tiles);
+  L.hist = o; o = up(o + sizeof(u32) * 256 * (size_t)(B > 0 ? B : 1));
+  L.keys = o; o = up(o + sizeof(u32) * (size_t)(R + 1));
+  L.state = o; o = up(o + sizeof(SegState) * (size_t)(B > 0 ? B : 1));
+  L.pre_gt = o; o = up(o + sizeof(u32) * (size_t)(R + 2));
+  L.pre_eq = o; o = up(o + sizeof(u32) * (size_t)(R + 2));
+  // the with-replacement path reuses the region as a double CDF
+  size_t cdf = up(sizeof(double) * (size_t)(R + 1));
+  L.total = o > cdf ? o : cdf;
+  return L;
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" size_t gsb_list_sample_workspace_bytes(int64_t R, int64_t B) {
+  if (R < 0 || B < 0) return 0;
+  return list_layout(R, B).total;
+}
+
+extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t B, int64_t R,
+                               int64_t K, uint64_t seed, uint32_t stream, int64_t* out_idx,
+                               int64_t* out_range, void* workspace, size_t workspace_bytes,
+                               int* d_err, void* cuda_stream) {
+  if (!range || !out_range || B < 1 || R < 0 || K < 0 || (R > 0 && K > 0 && !out_idx))
+    return GSB_ERR_INVALID;
+  if (R >= (1ll << 31) || B >= (1ll << 22)) return GSB_ERR_UNSUPPORTED;
+  const ListLayout L = list_layout(R, B);
+  if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  char* ws = (char*)workspace;
+  ListParams p;
+  p.probs = probs; p.range = (const i64*)range; p.B = (int)B; p.R = R; p.K = K; p.seed = seed;
+  p.stream = stream; p.keys = (u32*)(ws + L.keys); p.hist = (u32*)(ws + L.hist);
+  p.state = (SegState*)(ws + L.state); p.pre_gt = (u32*)(ws + L.pre_gt);
+  p.pre_eq = (u32*)(ws + L.pre_eq); p.out_idx = (i64*)out_idx; p.out_range = (i64*)out_range;
+  p.status = (u64*)(ws + L.status); p.ticket = (int*)(ws + L.ticket); p.err = d_err;
+  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.keys, st));  // ticket, status, histograms
+  i64 g = (R + LS_THREADS - 1) / LS_THREADS; if (g > 148 * 8) g = 148 * 8; if (g < 1) g = 1;
+  { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
+  if (R > 0 && K > 0) {
+    { LaunchScope ls(KID_LIST_SAMPLE, st); list_keys_kernel<<<(int)g, LS_THREADS, 0, st>>>(p); }
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      { LaunchScope ls(KID_LIST_SAMPLE, st); list_hist_kernel<<<(int)g, LS_THREADS, 0, st>>>(p, shift); }
+      { LaunchScope ls(KID_LIST_SAMPLE, st); list_pick_kernel<<<(int)B, 256, 0, st>>>(p, shift); }
+    }
+    { LaunchScope ls(KID_LIST_SAMPLE, st); list_scan_kernel<<<(int)L.tiles, LS_THREADS, 0, st>>>(p); }
+    { LaunchScope ls(KID_LIST_SAMPLE, st); list_emit_kernel<<<(int)g, LS_THREADS, 0, st>>>(p); }
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_list_sample_replace(const float* probs, int64_t n, int64_t K, uint64_t seed,
+                                       uint32_t stream, int64_t* out_idx, void* workspace,
+                                       size_t workspace_bytes, void* cuda_stream) {
+  if (K == 0) return GSB_OK;
+  if (n < 1 || K < 0 || !out_idx) return GSB_ERR_INVALID;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  i64 g = (K + 255) / 256; if (g > 148 * 8) g = 148 * 8;
+  if (!probs) {
+    LaunchScope ls(KID_LIST_SAMPLE, st);
+    list_replace_uniform_kernel<<<(int)g, 256, 0, st>>>(n, K, seed, stream, (i64*)out_idx);
+  } else {
+    if (!workspace || workspace_bytes < list_layout(n, 1).total) return GSB_ERR_WORKSPACE;
+    { LaunchScope ls(KID_LIST_SAMPLE, st); list_cdf_kernel<<<1, 1024, 0, st>>>(probs, n, (double*)workspace); }
+    { LaunchScope ls(KID_LIST_SAMPLE, st);
+      list_replace_cdf_kernel<<<(int)g, 256, 0, st>>>((const double*)workspace, n, K, seed, stream, (i64*)out_idx); }
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

@@ -71,19 +71,19 @@ class Graph : public torch::CustomClassHolder {
   torch::Tensor Node2Vec(torch::Tensor seeds, int64_t walk_length, double p, double q);
   void SortCSCIndices();
 
-  // compute operators
-  void SDDMM(const std::string& op, torch::Tensor lhs, torch::Tensor rhs, torch::Tensor out,
+  // compute operators (feature tensors the chosen op does not read may be None)
+  using OptTensor = c10::optional<torch::Tensor>;
+  void SDDMM(const std::string& op, OptTensor lhs, OptTensor rhs, torch::Tensor out,
              int64_t lhs_target, int64_t rhs_target, int64_t on_format);
-  void SpMM(const std::string& op, const std::string& reduce, torch::Tensor ufeat,
-            torch::Tensor efeat, torch::Tensor out, torch::Tensor argu, torch::Tensor arge,
-            int64_t u_target, int64_t on_format);
-  void FusedUOPV(const std::string& op, torch::Tensor lhs1, torch::Tensor rhs1, torch::Tensor out1,
-                 torch::Tensor lhs2, torch::Tensor rhs2, torch::Tensor out2, int64_t on_format);
-  void FusedESquareSum(const std::string& op, const std::string& reduce, torch::Tensor ufeat,
-                       torch::Tensor efeat, torch::Tensor out, torch::Tensor argu,
-                       torch::Tensor arge, int64_t u_target, int64_t on_format);
-  void FusedEDivUSum(const std::string& op, const std::string& reduce, torch::Tensor ufeat,
-                     torch::Tensor efeat, torch::Tensor out, torch::Tensor argu, torch::Tensor arge,
+  void SpMM(const std::string& op, const std::string& reduce, OptTensor ufeat, OptTensor efeat,
+            torch::Tensor out, OptTensor argu, OptTensor arge, int64_t u_target, int64_t on_format);
+  void FusedUOPV(const std::string& op, OptTensor lhs1, OptTensor rhs1, torch::Tensor out1,
+                 OptTensor lhs2, OptTensor rhs2, torch::Tensor out2, int64_t on_format);
+  void FusedESquareSum(const std::string& op, const std::string& reduce, OptTensor ufeat,
+                       OptTensor efeat, torch::Tensor out, OptTensor argu, OptTensor arge,
+                       int64_t u_target, int64_t on_format);
+  void FusedEDivUSum(const std::string& op, const std::string& reduce, OptTensor ufeat,
+                     OptTensor efeat, torch::Tensor out, OptTensor argu, OptTensor arge,
                      int64_t u_target, int64_t on_format);
 
   // super-batch operators (src/graph.h:126-216)
@@ -149,7 +149,10 @@ class Graph : public torch::CustomClassHolder {
   // row slicing of a CSC operand / column slicing of a CSR operand: keep the
   // entries whose id is in `ids`, relabelled to their position in `ids`
   std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> SliceAcross(
-      const Compressed& src, torch::Tensor ids);
+      const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound);
+  void ReduceImpl(int opcode, const std::string& reduce, OptTensor ufeat, OptTensor efeat,
+                  torch::Tensor out, OptTensor argu, OptTensor arge, int64_t u_target,
+                  int64_t on_format, const char* who);
   std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> SliceCoo(torch::Tensor ids, int64_t axis);
   void AttachSampled(bool is_csc, int64_t output_format, torch::Tensor sub_indptr,
                      torch::Tensor ids, torch::Tensor seg);

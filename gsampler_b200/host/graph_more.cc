@@ -6,6 +6,10 @@
 #include "gsb200.h"
 #include "ops.h"
 
+#include <c10/cuda/CUDAFunctions.h>
+
+#include <atomic>
+
 namespace gsb_host {
 
 static const int64_t* P(const torch::Tensor& t) { return t.data_ptr<int64_t>(); }
@@ -86,42 +90,462 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
 
 #define GSB_NOT_YET(name) TORCH_CHECK(false, name ": not implemented in this build")
 
-Graph::GraphAndIndex Graph::Compact(int64_t) { GSB_NOT_YET("Compact"); }
-torch::Tensor Graph::RandomWalk(torch::Tensor, int64_t) { GSB_NOT_YET("RandomWalk"); }
-torch::Tensor Graph::Node2Vec(torch::Tensor, int64_t, double, double) { GSB_NOT_YET("Node2Vec"); }
-void Graph::SortCSCIndices() { GSB_NOT_YET("SortCSCIndices"); }
-void Graph::SDDMM(const std::string&, torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t,
-                  int64_t) { GSB_NOT_YET("SDDMM"); }
-void Graph::SpMM(const std::string&, const std::string&, torch::Tensor, torch::Tensor,
-                 torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t) { GSB_NOT_YET("SpMM"); }
-void Graph::FusedUOPV(const std::string&, torch::Tensor, torch::Tensor, torch::Tensor,
-                      torch::Tensor, torch::Tensor, torch::Tensor, int64_t) { GSB_NOT_YET("FusedUOPV"); }
-void Graph::FusedESquareSum(const std::string&, const std::string&, torch::Tensor, torch::Tensor,
-                            torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t) {
-  GSB_NOT_YET("FusedESquareSum");
+static int64_t* PM(torch::Tensor& t) { return t.data_ptr<int64_t>(); }
+static torch::TensorOptions I64(const torch::Tensor& like) {
+  return torch::dtype(torch::kInt64).device(like.device());
 }
-void Graph::FusedEDivUSum(const std::string&, const std::string&, torch::Tensor, torch::Tensor,
-                          torch::Tensor, torch::Tensor, torch::Tensor, int64_t, int64_t) {
-  GSB_NOT_YET("FusedEDivUSum");
-}
-Graph::GraphAndIndex Graph::BatchColRowSlcing(torch::Tensor, torch::Tensor, torch::Tensor,
-                                              torch::Tensor) { GSB_NOT_YET("BatchColRowSlcing"); }
-Graph::GraphAndIndex Graph::BatchRowSlicing(torch::Tensor, torch::Tensor) { GSB_NOT_YET("BatchRowSlicing"); }
-std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceAcross(
-    const Compressed&, torch::Tensor) { GSB_NOT_YET("row slicing on CSC"); }
-std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceCoo(torch::Tensor, int64_t) {
-  GSB_NOT_YET("slicing on COO");
+static int IdxDtype(const torch::Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == torch::kInt32 || t.scalar_type() == torch::kInt64,
+              "indices must be int32 or int64");
+  return t.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
 }
 
-torch::Tensor ListSampling(int64_t, int64_t, bool) { GSB_NOT_YET("ListSampling"); }
-torch::Tensor ListSamplingProbs(torch::Tensor, int64_t, bool) { GSB_NOT_YET("ListSamplingWithProbs"); }
-std::tuple<torch::Tensor, torch::Tensor> BatchListSamplingProbs(torch::Tensor, int64_t, bool,
-                                                                torch::Tensor) {
-  GSB_NOT_YET("BatchListSamplingWithProbs");
+// ------------------------------------------------------------------ slicing across / on COO
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceAcross(
+    const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound) {
+  c10::cuda::CUDAGuard guard(src.indptr.device());
+  CheckIds(ids, "ids");
+  auto opt = I64(src.indptr);
+  auto sub_indptr = torch::empty({nseg + 1}, opt);
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(ids.device()));
+  auto ws = NewWorkspace(gsb_slice_across_workspace_bytes(nseg, id_bound), ids.device());
+  CheckStatus(gsb_slice_across_count(P(src.indptr), src.indices.data_ptr(), IdxDtype(src.indices),
+                                     nseg, P(ids), ids.numel(), id_bound, PM(sub_indptr),
+                                     ws.data_ptr(), (size_t)ws.numel(), err.data_ptr<int>(),
+                                     CurrentStream()),
+              "slice_across_count");
+  const int64_t E = sub_indptr.narrow(0, nseg, 1).item<int64_t>();
+  CheckDeviceError(err.item<int>(), "slice_across_count");
+  auto out_ids = torch::empty({E}, opt), seg = torch::empty({E}, opt), sel = torch::empty({E}, opt);
+  if (E > 0)
+    CheckStatus(gsb_slice_across_fill(P(src.indptr), src.indices.data_ptr(), IdxDtype(src.indices),
+                                    nseg, id_bound, P(sub_indptr), PM(out_ids), PM(seg), PM(sel),
+                                    ws.data_ptr(), CurrentStream()),
+              "slice_across_fill");
+  return {sub_indptr, out_ids, seg, sel};
 }
-std::tuple<torch::Tensor, torch::Tensor> BatchListSampling(int64_t, bool, torch::Tensor) {
-  GSB_NOT_YET("BatchListSampling");
+
+// src/graph_ops.cc:96-114: axis 0 filters on the rows, 1 on the columns
+std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceCoo(torch::Tensor ids,
+                                                                        int64_t axis) {
+  c10::cuda::CUDAGuard guard(coo_->row.device());
+  CheckIds(ids, "ids");
+  const auto& key = axis == 0 ? coo_->row : coo_->col;
+  const auto& other = axis == 0 ? coo_->col : coo_->row;
+  const int64_t nnz = key.numel(), bound = axis == 0 ? num_rows_ : num_cols_;
+  auto opt = I64(key);
+  auto ok = torch::empty({nnz}, opt), oo = torch::empty({nnz}, opt), sel = torch::empty({nnz}, opt);
+  auto scal = torch::zeros({2}, opt);
+  auto ws = NewWorkspace(gsb_coo_filter_workspace_bytes(nnz, bound), key.device());
+  CheckStatus(gsb_coo_filter(P(key), P(other), nnz, P(ids), ids.numel(), bound, PM(ok), PM(oo),
+                             PM(sel), PM(scal), ws.data_ptr(), (size_t)ws.numel(),
+                             (int*)(PM(scal) + 1), CurrentStream()),
+              "coo_filter");
+  auto host = scal.cpu();
+  const int64_t E = host.data_ptr<int64_t>()[0];
+  CheckDeviceError((int)host.data_ptr<int64_t>()[1], "coo_filter");
+  ok = ok.narrow(0, 0, E); oo = oo.narrow(0, 0, E); sel = sel.narrow(0, 0, E);
+  if (axis == 0) return {ok, oo, sel};
+  return {oo, ok, sel};
 }
-torch::Tensor IndexSearch(torch::Tensor, torch::Tensor) { GSB_NOT_YET("IndexSearch"); }
+
+// src/graph.cc:508-575 (sorted unique of one axis + remap, src/cuda/compact.cu:10-30).
+// Secondary path: the sorted unique is torch's library routine.
+Graph::GraphAndIndex Graph::Compact(int64_t axis) {
+  TORCH_CHECK(axis == 0 || axis == 1, "Compact: axis must be 0 or 1");
+  auto ret = Derive(num_rows_, num_cols_);
+  torch::Tensor frontiers;
+  auto compact = [&](const torch::Tensor& ids) {
+    auto uq = torch::_unique2(ids.to(torch::kInt64), true, true, false);
+    frontiers = std::get<0>(uq);
+    return std::get<1>(uq);
+  };
+  if (axis == 0) {
+    torch::Tensor mapped;
+    if (coo_) {
+      mapped = compact(coo_->row);
+      ret->coo_ = std::make_shared<Coordinate>(
+          Coordinate{mapped, coo_->col, coo_->e_ids, coo_->row_sorted, coo_->col_sorted});
+    }
+    if (csc_) {
+      if (!mapped.defined()) mapped = compact(csc_->indices);
+      ret->csc_ = std::make_shared<Compressed>(Compressed{csc_->indptr, mapped, csc_->e_ids});
+    }
+    TORCH_CHECK(frontiers.defined(), "Compact(0) needs a COO or CSC format");
+    ret->num_rows_ = frontiers.numel();
+  } else {
+    torch::Tensor mapped;
+    if (coo_) {
+      mapped = compact(coo_->col);
+      ret->coo_ = std::make_shared<Coordinate>(
+          Coordinate{coo_->row, mapped, coo_->e_ids, coo_->row_sorted, coo_->col_sorted});
+    }
+    if (csr_) {
+      if (!mapped.defined()) mapped = compact(csr_->indices);
+      ret->csr_ = std::make_shared<Compressed>(Compressed{csr_->indptr, mapped, csr_->e_ids});
+    }
+    TORCH_CHECK(frontiers.defined(), "Compact(1) needs a COO or CSR format");
+    ret->num_cols_ = frontiers.numel();
+  }
+  ret->num_edges_ = num_edges_;
+  return {ret, frontiers};
+}
+
+// ------------------------------------------------------------------ walks
+// src/graph.cc:310-317.  The buffer is step-major [(L+1), N]; like the
+// reference it is returned REINTERPRETED as [N, L+1] (a reshape, no transpose).
+torch::Tensor Graph::RandomWalk(torch::Tensor seeds, int64_t walk_length) {
+  TORCH_CHECK(csc_, "RandomWalk needs the CSC format");
+  c10::cuda::CUDAGuard guard(seeds.device());
+  CheckIds(seeds, "seeds");
+  const int64_t N = seeds.numel();
+  auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(seeds.device()));
+  CheckStatus(gsb_random_walk(P(csc_->indptr), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
+                              num_cols_, P(seeds), N, walk_length, seed_, NextStream(), PM(out),
+                              err.data_ptr<int>(), CurrentStream()),
+              "random_walk");
+  return out.reshape({N, -1});
+}
+
+torch::Tensor Graph::Node2Vec(torch::Tensor seeds, int64_t walk_length, double p, double q) {
+  TORCH_CHECK(csc_, "Node2Vec needs the CSC format (with sorted columns)");
+  c10::cuda::CUDAGuard guard(seeds.device());
+  CheckIds(seeds, "seeds");
+  const int64_t N = seeds.numel();
+  auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(seeds.device()));
+  CheckStatus(gsb_node2vec(P(csc_->indptr), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
+                           num_cols_, P(seeds), N, walk_length, p, q, seed_, NextStream(), PM(out),
+                           err.data_ptr<int>(), CurrentStream()),
+              "node2vec");
+  return out.reshape({N, -1});
+}
+
+// src/graph.cc:610-629.  Once-per-graph preprocessing: one library sort of the
+// (column, row) pairs (the reference calls CUB's segmented sort here).
+void Graph::SortCSCIndices() {
+  TORCH_CHECK(csc_, "SortCSCIndices needs the CSC format");
+  TORCH_CHECK(!csc_->e_ids.has_value(), "SortCSCIndices: the CSC carries edge ids");
+  const int64_t nnz = csc_->indices.numel();
+  if (nnz == 0) return;
+  auto seg = torch::empty({nnz}, I64(csc_->indptr));
+  CheckStatus(gsb_expand_indptr(P(csc_->indptr), num_cols_, nnz, PM(seg), CurrentStream()),
+              "expand_indptr");
+  const int64_t span = std::max<int64_t>(num_rows_, 1);
+  auto key = seg * span + csc_->indices.to(torch::kInt64);
+  auto sorted = std::get<0>(key.sort());
+  csc_->indices = (sorted - seg * span).to(csc_->indices.scalar_type());
+  coo_.reset();
+  csr_.reset();
+}
+
+// ------------------------------------------------------------------ SpMM / SDDMM
+namespace {
+enum { OP_ADD = 0, OP_SUB, OP_MUL, OP_DIV, OP_COPY_LHS, OP_COPY_RHS, OP_SQUARE_RHS, OP_RDIV };
+
+int OpCode(const std::string& op) {
+  if (op == "add") return OP_ADD;
+  if (op == "sub") return OP_SUB;
+  if (op == "mul") return OP_MUL;
+  if (op == "div") return OP_DIV;
+  if (op == "copy_lhs") return OP_COPY_LHS;
+  if (op == "copy_rhs") return OP_COPY_RHS;
+  TORCH_CHECK(false, "unsupported binary op '", op, "' (add, sub, mul, div, copy_lhs, copy_rhs)");
+}
+int ReduceCode(const std::string& r) {
+  if (r == "sum") return 0;
+  if (r == "max") return 1;
+  if (r == "min") return 2;
+  TORCH_CHECK(false, "unsupported reducer '", r, "' (sum, max, min)");
+}
+bool UsesLhs(int op) { return op != OP_COPY_RHS && op != OP_SQUARE_RHS; }
+bool UsesRhs(int op) { return op != OP_COPY_LHS; }
+
+struct Feature {
+  const float* ptr = nullptr;
+  int64_t len = 1;
+  std::vector<int64_t> shape;  // trailing dims
+};
+
+Feature AsFeature(const c10::optional<torch::Tensor>& t, bool used, const char* name) {
+  Feature f;
+  if (!used) return f;
+  TORCH_CHECK(t.has_value() && t.value().defined(), name, " is required by this op");
+  const auto& x = t.value();
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && x.is_contiguous(), name,
+              " must be a contiguous float32 CUDA tensor");
+  f.ptr = x.data_ptr<float>();
+  for (int64_t d = 1; d < x.dim(); ++d) { f.shape.push_back(x.size(d)); f.len *= x.size(d); }
+  return f;
+}
+
+// Broadcast of the trailing feature dims (the role of src/bcast.cc:24-76):
+// returns out_len and, when the shapes differ, per-output-element offsets.
+struct Bcast {
+  int64_t out_len = 1;
+  torch::Tensor lhs_off, rhs_off;  // undefined = identity / scalar broadcast
+};
+
+Bcast MakeBcast(const Feature& l, bool ul, const Feature& r, bool ur, const torch::Device& dev) {
+  Bcast b;
+  if (!ul || !ur) { b.out_len = ul ? l.len : r.len; return b; }
+  if (l.shape == r.shape || l.len == 1 || r.len == 1) { b.out_len = std::max(l.len, r.len); return b; }
+  const size_t nd = std::max(l.shape.size(), r.shape.size());
+  std::vector<int64_t> ls(nd, 1), rs(nd, 1), os(nd, 1);
+  for (size_t i = 0; i < l.shape.size(); ++i) ls[nd - l.shape.size() + i] = l.shape[i];
+  for (size_t i = 0; i < r.shape.size(); ++i) rs[nd - r.shape.size() + i] = r.shape[i];
+  for (size_t i = 0; i < nd; ++i) {
+    TORCH_CHECK(ls[i] == rs[i] || ls[i] == 1 || rs[i] == 1, "feature shapes do not broadcast");
+    os[i] = std::max(ls[i], rs[i]);
+    b.out_len *= os[i];
+  }
+  std::vector<int64_t> lo((size_t)b.out_len), ro((size_t)b.out_len);
+  for (int64_t o = 0; o < b.out_len; ++o) {
+    int64_t rem = o, lpos = 0, rpos = 0, lstride = 1, rstride = 1;
+    for (size_t i = nd; i-- > 0;) {
+      const int64_t c = rem % os[i];
+      rem /= os[i];
+      lpos += (ls[i] == 1 ? 0 : c) * lstride;
+      rpos += (rs[i] == 1 ? 0 : c) * rstride;
+      lstride *= ls[i];
+      rstride *= rs[i];
+    }
+    lo[(size_t)o] = lpos;
+    ro[(size_t)o] = rpos;
+  }
+  auto opt = torch::dtype(torch::kInt64);
+  b.lhs_off = torch::tensor(lo, opt).to(dev);
+  b.rhs_off = torch::tensor(ro, opt).to(dev);
+  return b;
+}
+
+const int64_t* OffPtr(const torch::Tensor& t) { return t.defined() ? t.data_ptr<int64_t>() : nullptr; }
+const int64_t* EidPtr(const c10::optional<torch::Tensor>& e) {
+  return e.has_value() && e.value().defined() ? e.value().data_ptr<int64_t>() : nullptr;
+}
+int64_t* ArgPtr(const c10::optional<torch::Tensor>& t) {
+  return t.has_value() && t.value().defined() ? t.value().data_ptr<int64_t>() : nullptr;
+}
+}  // namespace
+
+// src/graph.cc:320-338.  Always evaluated on the COO view: the CSC / CSR
+// flavours of the reference only differ in how they find an edge's endpoints.
+void Graph::SDDMM(const std::string& op, OptTensor lhs, OptTensor rhs, torch::Tensor out,
+                  int64_t lhs_target, int64_t rhs_target, int64_t on_format) {
+  if (num_edges_ <= 0) return;
+  TORCH_CHECK(on_format == kCOO || on_format == kCSC || on_format == kCSR, "SDDMM: bad format");
+  CreateSparseFormat(kCOO);
+  c10::cuda::CUDAGuard guard(out.device());
+  const int code = OpCode(op);
+  const Feature l = AsFeature(lhs, UsesLhs(code), "lhs"), r = AsFeature(rhs, UsesRhs(code), "rhs");
+  const Bcast bc = MakeBcast(l, UsesLhs(code), r, UsesRhs(code), out.device());
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kFloat32 && out.is_contiguous() &&
+                  out.numel() == num_edges_ * bc.out_len,
+              "SDDMM: out must be contiguous float32 [num_edges, ", bc.out_len, "]");
+  CheckStatus(gsb_sddmm_coo(P(coo_->row), P(coo_->col), EidPtr(coo_->e_ids), coo_->row.numel(), code,
+                            l.ptr, l.len, (int)lhs_target, r.ptr, r.len, (int)rhs_target,
+                            OffPtr(bc.lhs_off), OffPtr(bc.rhs_off), out.data_ptr<float>(), bc.out_len,
+                            CurrentStream()),
+              "sddmm");
+}
+
+void Graph::ReduceImpl(int code, const std::string& reduce, OptTensor ufeat, OptTensor efeat,
+                       torch::Tensor out, OptTensor argu, OptTensor arge, int64_t u_target,
+                       int64_t on_format, const char* who) {
+  if (num_edges_ <= 0) return;
+  TORCH_CHECK(u_target == 0 || u_target == 2, who, ": u_target must be 0 or 2");
+  c10::cuda::CUDAGuard guard(out.device());
+  const int red = ReduceCode(reduce);
+  const Feature u = AsFeature(ufeat, UsesLhs(code), "ufeat"), e = AsFeature(efeat, UsesRhs(code), "efeat");
+  const Bcast bc = MakeBcast(u, UsesLhs(code), e, UsesRhs(code), out.device());
+  const int64_t nout = u_target == 0 ? num_cols_ : num_rows_;
+  TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kFloat32 && out.is_contiguous() &&
+                  out.numel() == nout * bc.out_len,
+              who, ": out must be contiguous float32 [", nout, ", ", bc.out_len, "]");
+  // The compressed format that reduces along the wanted axis.  If it is not
+  // there and building it would need a sort, a sum is accumulated with atomics
+  // on the COO view instead (same result up to fp32 summation order).
+  const int64_t want = u_target == 0 ? kCSC : kCSR;
+  TORCH_CHECK(on_format == kCOO || on_format == want, who,
+              ": format and u_target mismatch (CSC with u_target 0, CSR with 2)");
+  TORCH_CHECK(coo_ || csc_ || csr_, who, ": graph holds no format");
+  const bool have = want == kCSC ? (bool)csc_ : (bool)csr_;
+  const bool sorted_coo = coo_ && (want == kCSC ? coo_->col_sorted : coo_->row_sorted);
+  const bool segmented = have || sorted_coo || red != 0;
+  if (!segmented) CreateSparseFormat(kCOO);
+  if (segmented) {
+    CreateSparseFormat(want);
+    const auto& c = want == kCSC ? *csc_ : *csr_;
+    CheckStatus(gsb_spmm_segmented(P(c.indptr), c.indices.data_ptr(), IdxDtype(c.indices),
+                                   EidPtr(c.e_ids), nout, code, red, u.ptr, u.len, e.ptr, e.len,
+                                   OffPtr(bc.lhs_off), OffPtr(bc.rhs_off), out.data_ptr<float>(),
+                                   bc.out_len, ArgPtr(argu), ArgPtr(arge), CurrentStream()),
+                who);
+  } else {
+    CheckStatus(gsb_spmm_coo_sum(P(coo_->row), P(coo_->col), EidPtr(coo_->e_ids), coo_->row.numel(),
+                                 code, (int)u_target, u.ptr, u.len, e.ptr, e.len, OffPtr(bc.lhs_off),
+                                 OffPtr(bc.rhs_off), out.data_ptr<float>(), bc.out_len,
+                                 CurrentStream()),
+                who);
+  }
+}
+
+// src/graph.cc:359-379
+void Graph::SpMM(const std::string& op, const std::string& reduce, OptTensor ufeat, OptTensor efeat,
+                 torch::Tensor out, OptTensor argu, OptTensor arge, int64_t u_target,
+                 int64_t on_format) {
+  ReduceImpl(OpCode(op), reduce, ufeat, efeat, out, argu, arge, u_target, on_format, "SpMM");
+}
+
+// src/graph.cc:457-479: out[n] = sum of e^2 over the edges of n
+void Graph::FusedESquareSum(const std::string&, const std::string& reduce, OptTensor ufeat,
+                            OptTensor efeat, torch::Tensor out, OptTensor argu, OptTensor arge,
+                            int64_t u_target, int64_t on_format) {
+  ReduceImpl(OP_SQUARE_RHS, reduce, ufeat, efeat, out, argu, arge, u_target, on_format,
+             "FusedESquareSum");
+}
+
+// src/graph.cc:482-503: out[n] = sum of e / u[other endpoint] over the edges of n
+void Graph::FusedEDivUSum(const std::string&, const std::string& reduce, OptTensor ufeat,
+                          OptTensor efeat, torch::Tensor out, OptTensor argu, OptTensor arge,
+                          int64_t u_target, int64_t on_format) {
+  ReduceImpl(OP_RDIV, reduce, ufeat, efeat, out, argu, arge, u_target, on_format, "FusedEDivUSum");
+}
+
+// src/graph.cc:341-356: two u-op-v edge maps over the same graph
+void Graph::FusedUOPV(const std::string& op, OptTensor lhs1, OptTensor rhs1, torch::Tensor out1,
+                      OptTensor lhs2, OptTensor rhs2, torch::Tensor out2, int64_t on_format) {
+  SDDMM(op, lhs1, rhs1, out1, 0, 2, on_format);
+  SDDMM(op, lhs2, rhs2, out2, 0, 2, on_format);
+}
+
+// ------------------------------------------------------------------ batch row slicing
+// src/batch_graph.cc:144-157
+Graph::GraphAndIndex Graph::BatchRowSlicing(torch::Tensor row_ids, torch::Tensor row_bptr) {
+  auto r = Slicing(row_ids, 0, kCSC, kCSC + kCOO);
+  auto g = std::get<0>(r);
+  g->col_bptr_ = col_bptr_;
+  g->row_bptr_ = row_bptr;
+  g->orig_col_ids_ = orig_col_ids_;
+  g->orig_row_ids_ = row_ids;
+  g->row_encoding_size_ = row_encoding_size_;
+  auto eb = torch::empty({col_bptr_.numel()}, I64(col_bptr_));
+  CheckStatus(gsb_gather_i64(P(g->csc_->indptr), P(col_bptr_), col_bptr_.numel(), PM(eb),
+                             CurrentStream()),
+              "gather");
+  g->edge_bptr_ = eb;
+  return r;
+}
+
+Graph::GraphAndIndex Graph::BatchColRowSlcing(torch::Tensor, torch::Tensor, torch::Tensor,
+                                              torch::Tensor) { GSB_NOT_YET("BatchColRowSlcing"); }
+
+// ------------------------------------------------------------------ gs_ops
+static std::tuple<torch::Tensor, torch::Tensor> ListSampleImpl(const c10::optional<torch::Tensor>& probs,
+                                                               torch::Tensor range, int64_t R,
+                                                               int64_t K, const torch::Device& dev) {
+  c10::cuda::CUDAGuard guard(dev);
+  const int64_t B = range.numel() - 1;
+  auto opt = torch::dtype(torch::kInt64).device(dev);
+  auto out_range = torch::empty({B + 1}, opt);
+  auto out_idx = torch::empty({std::min(B * K, R)}, opt);
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(dev));
+  auto ws = NewWorkspace(gsb_list_sample_workspace_bytes(R, B), dev);
+  const float* pp = nullptr;
+  if (probs.has_value()) {
+    const auto& pr = probs.value();
+    TORCH_CHECK(pr.is_cuda() && pr.scalar_type() == torch::kFloat32 && pr.is_contiguous(),
+                "probs must be a contiguous float32 CUDA tensor");
+    pp = pr.data_ptr<float>();
+  }
+  CheckStatus(gsb_list_sample(pp, P(range), B, R, K, ListSamplingSeed(), NextListStream(),
+                              PM(out_idx), PM(out_range), ws.data_ptr(), (size_t)ws.numel(),
+                              err.data_ptr<int>(), CurrentStream()),
+              "list_sample");
+  const int64_t total = out_range.narrow(0, B, 1).item<int64_t>();
+  CheckDeviceError(err.item<int>(), "list_sample");
+  return {out_idx.narrow(0, 0, total), out_range};
+}
+
+static torch::Tensor Range2(int64_t n, const torch::Device& dev) {
+  auto t = torch::empty({2}, torch::dtype(torch::kInt64).pinned_memory(true));
+  t.data_ptr<int64_t>()[0] = 0;
+  t.data_ptr<int64_t>()[1] = n;
+  return t.to(dev, /*non_blocking=*/true);
+}
+
+static torch::Tensor ListReplaceImpl(const c10::optional<torch::Tensor>& probs, int64_t n, int64_t K,
+                                     const torch::Device& dev) {
+  c10::cuda::CUDAGuard guard(dev);
+  TORCH_CHECK(n >= 1, "cannot draw from an empty list");
+  auto out = torch::empty({K}, torch::dtype(torch::kInt64).device(dev));
+  auto ws = NewWorkspace(gsb_list_sample_workspace_bytes(n, 1), dev);
+  CheckStatus(gsb_list_sample_replace(probs.has_value() ? probs.value().data_ptr<float>() : nullptr, n,
+                                      K, ListSamplingSeed(), NextListStream(), PM(out), ws.data_ptr(),
+                                      (size_t)ws.numel(), CurrentStream()),
+              "list_sample_replace");
+  return out;
+}
+
+static torch::Device CurrentCudaDevice() { return torch::Device(torch::kCUDA, c10::cuda::current_device()); }
+
+// src/tensor_ops.cc:6-8
+torch::Tensor ListSampling(int64_t num_items, int64_t num_picks, bool replace) {
+  const auto dev = CurrentCudaDevice();
+  if (replace) return ListReplaceImpl(c10::nullopt, num_items, num_picks, dev);
+  return std::get<0>(ListSampleImpl(c10::nullopt, Range2(num_items, dev), num_items, num_picks, dev));
+}
+
+// src/tensor_ops.cc:10-13
+torch::Tensor ListSamplingProbs(torch::Tensor probs, int64_t num_picks, bool replace) {
+  TORCH_CHECK(probs.is_cuda() && probs.scalar_type() == torch::kFloat32, "probs must be float32 CUDA");
+  probs = probs.contiguous();
+  if (replace) return ListReplaceImpl(probs, probs.numel(), num_picks, probs.device());
+  return std::get<0>(ListSampleImpl(probs, Range2(probs.numel(), probs.device()), probs.numel(),
+                                    num_picks, probs.device()));
+}
+
+// src/tensor_ops.cc:15-19
+std::tuple<torch::Tensor, torch::Tensor> BatchListSamplingProbs(torch::Tensor probs,
+                                                                int64_t num_picks, bool replace,
+                                                                torch::Tensor range) {
+  TORCH_CHECK(!replace, "BatchListSamplingWithProbs: replace=True is not implemented "
+                        "(nor is it in the reference, batch/list_sampling_probs.cu:38-39)");
+  TORCH_CHECK(probs.is_cuda() && probs.scalar_type() == torch::kFloat32, "probs must be float32 CUDA");
+  CheckIds(range, "range");
+  return ListSampleImpl(probs.contiguous(), range, probs.numel(), num_picks, probs.device());
+}
+
+// src/tensor_ops.cc:21-28: uniform choice inside every segment
+std::tuple<torch::Tensor, torch::Tensor> BatchListSampling(int64_t num_picks, bool replace,
+                                                           torch::Tensor range) {
+  TORCH_CHECK(!replace, "BatchListSampling: replace=True is not implemented");
+  CheckIds(range, "range");
+  const int64_t R = range.narrow(0, range.numel() - 1, 1).item<int64_t>();
+  return ListSampleImpl(c10::nullopt, range, R, num_picks, range.device());
+}
+
+// src/tensor_ops.cc:30-38: position of every key in `origin_data`, -1 if absent.
+// Utility operator outside the sampling path: a library sort + binary search.
+torch::Tensor IndexSearch(torch::Tensor origin_data, torch::Tensor keys) {
+  auto sorted = origin_data.sort();
+  const auto& vals = std::get<0>(sorted);
+  const auto& perm = std::get<1>(sorted);
+  if (vals.numel() == 0) return torch::full_like(keys, -1);
+  auto pos = torch::searchsorted(vals, keys).clamp_max(vals.numel() - 1);
+  auto hit = vals.index_select(0, pos.reshape({-1})).reshape(keys.sizes()) == keys;
+  return torch::where(hit, perm.index_select(0, pos.reshape({-1})).reshape(keys.sizes()),
+                      torch::full_like(keys, -1));
+}
+
+static std::atomic<uint64_t> g_list_seed{7777};
+static std::atomic<uint32_t> g_list_calls{0};
+uint64_t ListSamplingSeed() { return g_list_seed.load(); }
+uint32_t NextListStream() { return g_list_calls.fetch_add(1); }
+void SetListSamplingSeed(int64_t seed) {
+  g_list_seed.store((uint64_t)seed);
+  g_list_calls.store(0);
+}
 
 }  // namespace gsb_host

@@ -178,6 +178,104 @@ GSB_API int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nnz, 
 GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nkeys,
                                    int64_t* indptr, void* cuda_stream);
 
+/* ------------------------------------------------------------------ slicing across
+ * Keep the entries of a CSC (CSR) whose row (column) id is in `ids[R]`, each
+ * renamed to its position in `ids` (the smallest one for a repeated id), the
+ * entry order inside every segment preserved.  Replaces OnIndicesSlicingCUDA
+ * (src/cuda/slicing.cu:184-308), reached from Graph::Slicing axis=0 on CSC
+ * (src/graph.cc:116-119) and Graph::BatchRowSlicing (src/batch_graph.cc:144-157).
+ * count: out_indptr[nseg+1]; builds the membership map in the workspace.
+ * fill : out_ids / out_seg (nullable) / out_sel [E], E = out_indptr[nseg]
+ *        (host value); must be given the workspace of the matching count call.
+ * id_bound = exclusive upper bound of the ids stored in `indices`. */
+GSB_API size_t gsb_slice_across_workspace_bytes(int64_t nseg, int64_t id_bound);
+GSB_API int gsb_slice_across_count(const int64_t* indptr, const void* indices, int indices_dtype,
+                                   int64_t nseg, const int64_t* ids, int64_t R, int64_t id_bound,
+                                   int64_t* out_indptr, void* workspace, size_t workspace_bytes,
+                                   int* d_err, void* cuda_stream);
+GSB_API int gsb_slice_across_fill(const int64_t* indptr, const void* indices, int indices_dtype,
+                                  int64_t nseg, int64_t id_bound, const int64_t* out_indptr,
+                                  int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
+                                  const void* workspace, void* cuda_stream);
+/* The same filter on a COO: keep edge e iff key[e] is in `ids`; out_key = the
+ * position in `ids`, out_other = other[e], out_sel = e, in edge order; the
+ * count goes to *d_count (device).  Outputs need capacity nnz.  Replaces
+ * COORowSlicingCUDA (src/cuda/slicing.cu:310-377). */
+GSB_API size_t gsb_coo_filter_workspace_bytes(int64_t nnz, int64_t id_bound);
+GSB_API int gsb_coo_filter(const int64_t* key, const int64_t* other, int64_t nnz,
+                           const int64_t* ids, int64_t R, int64_t id_bound, int64_t* out_key,
+                           int64_t* out_other, int64_t* out_sel, int64_t* d_count, void* workspace,
+                           size_t workspace_bytes, int* d_err, void* cuda_stream);
+
+/* ------------------------------------------------------------------ SpMM / SDDMM (fp32)
+ * op: 0 add, 1 sub, 2 mul, 3 div, 4 copy_lhs, 5 copy_rhs, 6 square_rhs, 7 rhs/lhs.
+ * reduce: 0 sum, 1 max, 2 min.  Feature rows are contiguous ([n, len]); *_off
+ * are optional broadcast offset tables of out_len entries (NULL = identity, a
+ * length-1 operand broadcasts).
+ * gsb_spmm_segmented: out[seg, :] (+)= reduce over the entries i of segment
+ *   seg of op(u[indices[i], :], e[eid(i), :]), eid = e_ids[i] or i.  sum adds
+ *   into `out` (caller zero-fills); max/min overwrite, empty segments give 0.
+ *   Replaces SpMMCSC and the fused CSC reductions (src/cuda/spmm.cu:107-148,
+ *   253-348; src/cuda/fusion/fused_csc_e_square_sum.cu:21-131;
+ *   src/cuda/fusion/fused_csc_e_div_u_sum.cu:15-124).
+ * gsb_spmm_coo_sum: sum reduction on an unsorted COO with atomics; u_target 0:
+ *   features on rows, sums on columns; 2: the reverse.  Replaces SpMMCOO
+ *   (src/cuda/spmm.cu:23-56,170-210) and the fused COO sums.
+ * gsb_sddmm_coo: out[eid, :] = op(lhs[sel], rhs[sel]), target 0 = row id,
+ *   1 = edge id, 2 = column id.  Replaces SDDMMCOO / SDDMMCSC
+ *   (src/cuda/sddmm.cu:23-61,120-297). */
+GSB_API int gsb_spmm_segmented(const int64_t* indptr, const void* indices, int indices_dtype,
+                               const int64_t* e_ids, int64_t nseg, int op, int reduce,
+                               const float* u, int64_t u_len, const float* e, int64_t e_len,
+                               const int64_t* u_off, const int64_t* e_off, float* out,
+                               int64_t out_len, int64_t* arg_u, int64_t* arg_e, void* cuda_stream);
+GSB_API int gsb_spmm_coo_sum(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                             int64_t nnz, int op, int u_target, const float* u, int64_t u_len,
+                             const float* e, int64_t e_len, const int64_t* u_off,
+                             const int64_t* e_off, float* out, int64_t out_len, void* cuda_stream);
+GSB_API int gsb_sddmm_coo(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                          int64_t nnz, int op, const float* lhs, int64_t lhs_len, int lhs_target,
+                          const float* rhs, int64_t rhs_len, int rhs_target, const int64_t* lhs_off,
+                          const int64_t* rhs_off, float* out, int64_t out_len, void* cuda_stream);
+
+/* ------------------------------------------------------------------ collective sampling
+ * gsb_list_sample: for every segment [range[b], range[b+1]) choose min(K, len)
+ * candidates without replacement -- uniformly (probs NULL) or with weights
+ * probs[R] (A-Res keys; weight <= 0 is chosen last) -- and write their
+ * positions in ascending order to out_idx; out_range[B+1] = offsets of the
+ * picks.  R bounds range[B].  Replaces ListSampling / ListSamplingProbs /
+ * BatchListSamplingProbs without replacement (src/cuda/list_sampling.cu:20-73,
+ * src/cuda/list_sampling_probs.cu:11-89, src/cuda/batch/list_sampling_probs.cu:29-107),
+ * which return the same set in descending-key order.
+ * gsb_list_sample_replace: K independent draws from [0, n), uniform or by
+ * inverse CDF (the reference's replace=true branches). */
+GSB_API size_t gsb_list_sample_workspace_bytes(int64_t R, int64_t B);
+GSB_API int gsb_list_sample(const float* probs, const int64_t* range, int64_t B, int64_t R,
+                            int64_t K, uint64_t seed, uint32_t stream, int64_t* out_idx,
+                            int64_t* out_range, void* workspace, size_t workspace_bytes,
+                            int* d_err, void* cuda_stream);
+GSB_API int gsb_list_sample_replace(const float* probs, int64_t n, int64_t K, uint64_t seed,
+                                    uint32_t stream, int64_t* out_idx, void* workspace,
+                                    size_t workspace_bytes, void* cuda_stream);
+
+/* ------------------------------------------------------------------ random walks
+ * N walkers, walk_length steps over the in-neighbour lists; out is step-major,
+ * out[s * N + w], s in [0, walk_length]; -1 from the first dead end on.  Walker
+ * w consumes the draws (seed, stream, w, 0..) in order.  Replaces
+ * FusedRandomWalkCUDA (src/cuda/fusion/random_walk.cu:10-70) and
+ * FusedNode2VecCUDA (src/cuda/fusion/node2vec.cu:67-162; needs sorted
+ * columns).  Unlike the reference, a draw equal to 1.0 is clamped to the last
+ * neighbour and a "previous node" outside [0, num_nodes) counts as unconnected
+ * instead of reading out of bounds. */
+GSB_API int gsb_random_walk(const int64_t* indptr, const void* indices, int indices_dtype,
+                            int64_t num_nodes, const int64_t* seeds, int64_t N,
+                            int64_t walk_length, uint64_t seed, uint32_t stream, int64_t* out,
+                            int* d_err, void* cuda_stream);
+GSB_API int gsb_node2vec(const int64_t* indptr, const void* indices, int indices_dtype,
+                         int64_t num_nodes, const int64_t* seeds, int64_t N, int64_t walk_length,
+                         double p, double q, uint64_t seed, uint32_t stream, int64_t* out,
+                         int* d_err, void* cuda_stream);
+
 /* ------------------------------------------------------------------ whole sampler
  * L-layer GraphSAGE super-batch sampler: per layer fused slice+sample then
  * per-minibatch unique/relabel, the next layer's seeds being this layer's

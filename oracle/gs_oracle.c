@@ -606,39 +606,54 @@ static int cmp_kv_desc(const void* a, const void* b) {
   if (x->key < y->key) return 1;
   return (x->idx > y->idx) - (x->idx < y->idx);
 }
-/* returns number of picks written (min(K, n) without replacement) */
+static int cmp_i64_asc(const void* a, const void* b) {
+  i64 x = *(const i64*)a, y = *(const i64*)b;
+  return (x > y) - (x < y);
+}
+/* Weighted, without replacement, over the candidates [begin,end): the K largest
+ * keys (ties to the lower index) -- the set the reference obtains by sorting
+ * all keys descending and keeping the first K (list_sampling_probs.cu:47-77).
+ * The picks are returned in ASCENDING INDEX order (the reference returns them
+ * in descending key order, i.e. a random order; nothing downstream depends on
+ * it).  probs == NULL selects uniformly: key = the raw 32-bit draw.
+ * returns the number of picks written (min(K, n)). */
 GO_API i64 go_list_sample_probs_spec(const float* probs, i64 begin, i64 end, i64 K, u64 seed,
                                      u32 stream, i64* out_idx) {
   i64 n = end - begin;
   if (n <= K) { for (i64 i = 0; i < n; ++i) out_idx[i] = begin + i; return n; }
   kv_t* kv = (kv_t*)malloc(sizeof(kv_t) * (size_t)n);
   for (i64 i = 0; i < n; ++i) {
-    double u = ((double)spec_draw(seed, stream, (u64)(begin + i), 0) + 1.0) * (1.0 / 4294967296.0);
-    double p = probs[begin + i];
-    kv[i].key = p > 0 ? log2(u) / p : -INFINITY;
+    u32 d = spec_draw(seed, stream, (u64)(begin + i), 0);
+    if (probs) {
+      double u = ((double)d + 1.0) * (1.0 / 4294967296.0);
+      double p = probs[begin + i];
+      kv[i].key = p > 0 ? log2(u) / p : -INFINITY;
+    } else {
+      kv[i].key = (double)d;
+    }
     kv[i].idx = begin + i;
   }
   qsort(kv, (size_t)n, sizeof(kv_t), cmp_kv_desc);
   for (i64 k = 0; k < K; ++k) out_idx[k] = kv[k].idx;
   free(kv);
+  qsort(out_idx, (size_t)K, sizeof(i64), cmp_i64_asc);
   return K;
 }
 
-/* uniform without replacement over [0,n): same Floyd selection as the column
- * sampler, slot 0 of the stream. */
-GO_API i64 go_list_sample_spec(i64 n, i64 K, int replace, u64 seed, u32 stream, i64* out_idx) {
-  if (replace) {
-    for (i64 k = 0; k < K; ++k)
-      out_idx[k] = (i64)(((u64)spec_draw(seed, stream, 0, (u32)k) * (u64)n) >> 32);
-    return K;
-  }
-  if (n <= K) { for (i64 i = 0; i < n; ++i) out_idx[i] = i; return n; }
+/* with replacement over [0,n): K independent draws; uniform when probs == NULL
+ * (list_sampling.cu:32-46), else by inverse CDF (list_sampling_probs.cu:25-46);
+ * draw k is word k of slot 0's stream. */
+GO_API i64 go_list_sample_replace_spec(const float* probs, i64 n, i64 K, u64 seed, u32 stream,
+                                       i64* out_idx) {
+  double total = 0;
+  if (probs) for (i64 i = 0; i < n; ++i) total += probs[i] > 0 ? probs[i] : 0;
   for (i64 k = 0; k < K; ++k) {
-    i64 j = n - K + k;
-    i64 t = (i64)(((u64)spec_draw(seed, stream, 0, (u32)k) * (u64)(j + 1)) >> 32);
-    int dup = 0;
-    for (i64 m = 0; m < k; ++m) if (out_idx[m] == t) { dup = 1; break; }
-    out_idx[k] = dup ? j : t;
+    u32 d = spec_draw(seed, stream, 0, (u32)k);
+    if (!probs) { out_idx[k] = (i64)(((u64)d * (u64)n) >> 32); continue; }
+    double target = ((double)d + 1.0) * (1.0 / 4294967296.0) * total, run = 0;
+    i64 pick = n - 1;
+    for (i64 i = 0; i < n; ++i) { run += probs[i] > 0 ? probs[i] : 0; if (run >= target) { pick = i; break; } }
+    out_idx[k] = pick;
   }
   return K;
 }

@@ -41,7 +41,7 @@ def lib():
         _lib.go_compact.restype = C.c_int64
         _lib.go_slice_rows.restype = C.c_int64
         _lib.go_list_sample_probs_spec.restype = C.c_int64
-        _lib.go_list_sample_spec.restype = C.c_int64
+        _lib.go_list_sample_replace_spec.restype = C.c_int64
         _lib.go_spec_draw.restype = C.c_uint32
         _lib.go_num_threads.restype = C.c_int
     return _lib
@@ -239,32 +239,42 @@ def edge_op_node(idx, e, node, op):
 
 
 # --------------------------------------------------------------------------- list sampling
-def list_sample_probs_spec(probs, K, seed=0, stream=0, range_ptr=None):
-    probs = _f32(probs)
+def list_sample_probs_spec(probs, K, seed=0, stream=0, range_ptr=None, n=None):
+    """K of the candidates of every segment without replacement, ascending index order.
+    ``probs`` None -> uniform over ``n`` candidates."""
+    if probs is not None:
+        probs = _f32(probs)
+        n = probs.size
     if range_ptr is None:
-        out = np.empty(min(K, probs.size), np.int64)
-        n = lib().go_list_sample_probs_spec(_p(probs), C.c_int64(0), C.c_int64(probs.size),
-                                            C.c_int64(K), C.c_uint64(seed), C.c_uint32(stream),
-                                            _p(out))
-        return out[:n]
+        out = np.empty(min(K, n), np.int64)
+        m = lib().go_list_sample_probs_spec(_p(probs), C.c_int64(0), C.c_int64(n), C.c_int64(K),
+                                            C.c_uint64(seed), C.c_uint32(stream), _p(out))
+        return out[:m]
     rp = _i64(range_ptr)
     outs, optr = [], [0]
     for b in range(rp.size - 1):
         n_b = int(rp[b + 1] - rp[b])
         out = np.empty(min(K, n_b), np.int64)
-        n = lib().go_list_sample_probs_spec(_p(probs), C.c_int64(int(rp[b])),
+        m = lib().go_list_sample_probs_spec(_p(probs), C.c_int64(int(rp[b])),
                                             C.c_int64(int(rp[b + 1])), C.c_int64(K),
                                             C.c_uint64(seed), C.c_uint32(stream), _p(out))
-        outs.append(out[:n])
-        optr.append(optr[-1] + n)
+        outs.append(out[:m])
+        optr.append(optr[-1] + m)
     return (np.concatenate(outs) if outs else np.empty(0, np.int64)), np.asarray(optr, np.int64)
 
 
 def list_sample_spec(n, K, replace=False, seed=0, stream=0):
-    out = np.empty(K if replace else min(n, K), np.int64)
-    m = lib().go_list_sample_spec(C.c_int64(n), C.c_int64(K), C.c_int(int(replace)),
-                                  C.c_uint64(seed), C.c_uint32(stream), _p(out))
-    return out[:m]
+    if replace:
+        return list_sample_replace_spec(None, n, K, seed, stream)
+    return list_sample_probs_spec(None, K, seed, stream, n=n)
+
+
+def list_sample_replace_spec(probs, n, K, seed=0, stream=0):
+    pr = None if probs is None else _f32(probs)
+    out = np.empty(K, np.int64)
+    lib().go_list_sample_replace_spec(_p(pr), C.c_int64(n), C.c_int64(K), C.c_uint64(seed),
+                                      C.c_uint32(stream), _p(out))
+    return out
 
 
 # --------------------------------------------------------------------------- walks

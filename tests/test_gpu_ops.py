@@ -1,0 +1,285 @@
+"""GPU tests of the operators around the GraphSAGE path: slicing across the compressed
+dimension, COO slicing, SpMM / SDDMM and their fused forms, collective (list) sampling, random
+walks / node2vec, column sort, compact -- each against the CPU oracle -- and the LADIES and
+node2vec samplers of the reference's examples written against this package's Matrix API."""
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+def cuda(a, dtype=torch.int64):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype).cuda()
+
+
+def rand_csc(rng, n, avg, heavy=0):
+    deg = rng.poisson(avg, n)
+    deg[rng.integers(0, n, max(n // 10, 1))] = 0
+    if heavy:
+        deg[rng.integers(0, n, heavy)] = rng.integers(200, 1500, heavy)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, n, indptr[-1]).astype(np.int64)
+    return indptr, indices
+
+
+def new_graph(gsb, indptr, indices, seed=99, idx_dtype=torch.int64):
+    n = indptr.size - 1
+    g = gsb.Graph(n, n)
+    g._CAPI_LoadCSC(cuda(indptr), cuda(indices, idx_dtype))
+    g._CAPI_SetSeed(seed)
+    return g
+
+
+@pytest.fixture(scope="module")
+def graph():
+    return rand_csc(np.random.default_rng(21), 3000, 12, heavy=10)
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_row_slicing_on_csc(gsb, oracle, graph, idx_dtype):
+    indptr, indices = graph
+    rng = np.random.default_rng(1)
+    rows = rng.permutation(3000)[:700].astype(np.int64)
+    A = new_graph(gsb, indptr, indices, idx_dtype=idx_dtype)
+    sub, sel = A._CAPI_Slicing(cuda(rows), 0, gsb._CSC, gsb._CSC + gsb._COO)
+    eip, eids, esel = oracle.slice_rows(indptr, indices, rows)
+    assert np.array_equal(host(sub._CAPI_GetCSCIndptr()), eip)
+    assert np.array_equal(host(sub._CAPI_GetCSCIndices()), eids)
+    assert np.array_equal(host(sel), esel)
+    assert np.array_equal(host(sub._CAPI_GetCOORows()), eids)
+    assert np.array_equal(host(sub._CAPI_GetCOOCols()), oracle.csc2coo(eip))
+    assert (sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols(), sub._CAPI_GetNumEdges()) == (700, 3000, eids.size)
+    # empty selection
+    sub, sel = A._CAPI_Slicing(cuda(np.empty(0, np.int64)), 0, gsb._CSC, gsb._CSC)
+    assert sel.numel() == 0 and not host(sub._CAPI_GetCSCIndptr()).any()
+
+
+def test_slicing_on_coo(gsb, oracle, graph):
+    indptr, indices = graph
+    col = oracle.csc2coo(indptr)
+    A = gsb.Graph(3000, 3000)
+    A._CAPI_LoadCOO(cuda(indices), cuda(col), False, True)
+    rng = np.random.default_rng(2)
+    rows = rng.permutation(3000)[:500].astype(np.int64)
+    sub, sel = A._CAPI_Slicing(cuda(rows), 0, gsb._COO, gsb._COO)
+    pos = np.full(3000, -1)
+    pos[rows] = np.arange(500)
+    keep = np.flatnonzero(pos[indices] >= 0)
+    assert np.array_equal(host(sel), keep)
+    assert np.array_equal(host(sub._CAPI_GetCOORows()), pos[indices[keep]])
+    assert np.array_equal(host(sub._CAPI_GetCOOCols()), col[keep])
+    cols = rng.permutation(3000)[:400].astype(np.int64)
+    sub, sel = A._CAPI_Slicing(cuda(cols), 1, gsb._COO, gsb._COO)
+    pos = np.full(3000, -1)
+    pos[cols] = np.arange(400)
+    keep = np.flatnonzero(pos[col] >= 0)
+    assert np.array_equal(host(sel), keep)
+    assert np.array_equal(host(sub._CAPI_GetCOOCols()), pos[col[keep]])
+
+
+def test_spmm_sddmm_against_oracle(gsb, oracle, graph):
+    indptr, indices = graph
+    n, E = indptr.size - 1, indices.size
+    col = oracle.csc2coo(indptr)
+    rng = np.random.default_rng(3)
+    w = (rng.random(E) + 0.01).astype(np.float32)
+    A = new_graph(gsb, indptr, indices)
+    m = gsb.Matrix(A)
+    m.edata["w"] = cuda(w, torch.float32)
+    tol = dict(rtol=1e-5, atol=1e-6)
+    # column sums (CSC, one warp per column) and row sums (COO atomics / CSR)
+    assert np.allclose(host(m.sum("w", axis=0)), oracle.edge_sum(indices, col, w, 2, n), **tol)
+    assert np.allclose(host(m.sum("w", axis=1)), oracle.edge_sum(indices, col, w, 0, n), **tol)
+    A._CAPI_GetCSRIndptr()                     # now a CSR exists: the segmented kernel runs
+    assert np.allclose(host(m.sum("w", axis=1)), oracle.edge_sum(indices, col, w, 0, n), **tol)
+    # fused sum of squares
+    assert np.allclose(host(gsb.ops.e_square_sum(m, m.edata["w"], 0, gsb._CSC)),
+                       oracle.edge_sum(indices, col, w, 2, n, square=True), **tol)
+    # e / node (SDDMM with the Python-side div -> mul rewrite)
+    node = (rng.random(n) + 0.5).astype(np.float32)
+    got = m.div("w", cuda(node, torch.float32), axis=1).edata["w"]
+    assert np.allclose(host(got), oracle.edge_op_node(indices, w, node, "div"), **tol)
+    got = m.div("w", cuda(node, torch.float32), axis=0).edata["w"]
+    assert np.allclose(host(got), oracle.edge_op_node(col, w, node, "div"), **tol)
+    # e / u summed per column, fused
+    got = gsb.ops.e_div_u_sum(m, m.edata["w"], cuda(node, torch.float32), 0, gsb._CSC)
+    want = oracle.edge_sum(indices, col, oracle.edge_op_node(indices, w, node, "div"), 2, n)
+    assert np.allclose(host(got), want, rtol=2e-5, atol=1e-6)
+    # vector features with broadcasting and a max reducer
+    u = rng.random((n, 4)).astype(np.float32)
+    e = rng.random((E, 1)).astype(np.float32)
+    out = gsb.ops.gspmm(m, "mul", "max", cuda(u, torch.float32), cuda(e, torch.float32), 0, gsb._CSC)
+    ref = np.zeros((n, 4), np.float32)
+    for c in range(n):
+        s, t = indptr[c], indptr[c + 1]
+        if t > s:
+            ref[c] = (u[indices[s:t]] * e[s:t]).max(axis=0)
+    assert np.allclose(host(out), ref, **tol)
+    out = gsb.ops.gsddmm(m, "add", cuda(u, torch.float32), cuda(u[:, :1].copy(), torch.float32), "u", "v")
+    assert np.allclose(host(out), u[indices] + u[col, :1], **tol)
+
+
+def test_list_sampling(gsb, oracle):
+    from scipy import stats
+
+    ops = torch.ops.gs_ops
+    ops._CAPI_SetListSamplingSeed(31)
+    # uniform without replacement: bit-exact with the oracle (integer keys)
+    got = host(ops._CAPI_ListSampling(5000, 400, False))
+    assert np.array_equal(got, oracle.list_sample_spec(5000, 400, False, seed=31, stream=0))
+    got = host(ops._CAPI_ListSampling(100, 400, False))
+    assert got.tolist() == list(range(100))
+    got = host(ops._CAPI_ListSampling(5000, 64, True))
+    assert np.array_equal(got, oracle.list_sample_spec(5000, 64, True, seed=31, stream=2))
+    # weighted: zero-weight items never win while positive ones remain; high overlap with the
+    # double-precision oracle (fp32 keys may reorder near-ties at the threshold)
+    rng = np.random.default_rng(4)
+    probs = rng.random(20000).astype(np.float32)
+    probs[:3000] = 0
+    ops._CAPI_SetListSamplingSeed(5)
+    got = host(ops._CAPI_ListSamplingWithProbs(cuda(probs, torch.float32), 2000, False))
+    want = oracle.list_sample_probs_spec(probs, 2000, seed=5, stream=0)
+    assert got.size == 2000 and np.unique(got).size == 2000 and np.all(np.diff(got) > 0)
+    assert np.all(probs[got] > 0)
+    assert np.intersect1d(got, want).size >= 1990
+    # segments, including one shorter than K and an empty one
+    rp = np.array([0, 50, 50, 9000, 20000])
+    idx, optr = ops._CAPI_BatchListSamplingWithProbs(cuda(probs, torch.float32), 300, False, cuda(rp))
+    idx, optr = host(idx), host(optr)
+    assert optr.tolist() == [0, 50, 50, 350, 650]
+    assert idx[:50].tolist() == list(range(50))
+    for b in (2, 3):
+        seg = idx[optr[b]:optr[b + 1]]
+        assert np.all((seg >= rp[b]) & (seg < rp[b + 1])) and np.unique(seg).size == 300
+    idx, optr = ops._CAPI_BatchListSampling(10, False, cuda(np.array([0, 4, 104])))
+    assert host(optr).tolist() == [0, 4, 14]
+    # distribution: K = 1 of 8 weighted items, many independent calls
+    w = np.array([1, 2, 3, 4, 0.5, 0.5, 6, 3], np.float32)
+    big = np.tile(w, 4000)
+    rp = np.arange(4001) * 8
+    idx, _ = ops._CAPI_BatchListSamplingWithProbs(cuda(big, torch.float32), 1, False, cuda(rp))
+    cnt = np.bincount(host(idx) % 8, minlength=8)
+    w64 = w.astype(np.float64)
+    assert stats.chisquare(cnt, 4000 * w64 / w64.sum()).pvalue > 0.01
+    # with replacement, weighted
+    got = host(ops._CAPI_ListSamplingWithProbs(cuda(w, torch.float32), 16000, True))
+    assert stats.chisquare(np.bincount(got, minlength=8), 16000 * w64 / w64.sum()).pvalue > 0.01
+
+
+def test_walks_bit_exact(gsb, oracle, graph):
+    indptr, indices = graph
+    srt = oracle.sort_indices(indptr, indices)
+    rng = np.random.default_rng(6)
+    seeds = rng.integers(0, 3000, 5000).astype(np.int64)
+    for idx_dtype in (torch.int64, torch.int32):
+        A = new_graph(gsb, indptr, indices, seed=77, idx_dtype=idx_dtype)
+        A._CAPI_SortCSCIndices()
+        assert np.array_equal(host(A._CAPI_GetCSCIndices()), srt)
+        tr = A._CAPI_RandomWalk(cuda(seeds), 12)
+        assert tuple(tr.shape) == (5000, 13)
+        assert np.array_equal(host(tr).reshape(-1), oracle.random_walk_spec(indptr, srt, seeds, 12, 77, 0))
+        tr = A._CAPI_Node2Vec(cuda(seeds), 12, 2.0, 0.5)
+        assert np.array_equal(host(tr).reshape(-1), oracle.node2vec_spec(indptr, srt, seeds, 12, 2.0, 0.5, 77, 1))
+        tr = A._CAPI_Node2Vec(cuda(seeds), 5, 0.25, 4.0)
+        assert np.array_equal(host(tr).reshape(-1), oracle.node2vec_spec(indptr, srt, seeds, 5, 0.25, 4.0, 77, 2))
+
+
+def test_reference_walk_fixture(gsb):
+    with open(os.path.join(HERE, "golden", "reference_fixtures.json")) as f:
+        c = json.load(f)["walks"]
+    indptr, indices = np.asarray(c["indptr"]), np.asarray(c["indices"])
+    A = new_graph(gsb, indptr, indices)
+    L, seeds = c["walk_length"], c["seeds"]
+    for walk in (A._CAPI_RandomWalk(cuda(seeds), L), A._CAPI_Node2Vec(cuda(seeds), L, c["p"], c["q"])):
+        t = host(walk.reshape(-1, len(seeds)))          # step-major, as the reference's test reads it
+        assert t[0].tolist() == seeds
+        for w in range(len(seeds)):
+            for s in range(L):
+                a, b = t[s, w], t[s + 1, w]
+                assert b == -1 or b in indices[indptr[a]:indptr[a + 1]]
+        assert t[:, 3].tolist() == [1, 0, -1, -1]
+
+
+def test_compact_and_index_search(gsb, oracle, graph):
+    indptr, indices = graph
+    A = new_graph(gsb, indptr, indices)
+    sub, _ = A._CAPI_Slicing(cuda(np.arange(100)), 1, gsb._CSC, gsb._CSC + gsb._COO)
+    g2, frontier = sub._CAPI_Compact(0)
+    uq, cp = oracle.compact(host(sub._CAPI_GetCSCIndices()))
+    assert np.array_equal(host(frontier), uq) and np.array_equal(host(g2._CAPI_GetCSCIndices()), cp)
+    assert g2._CAPI_GetNumRows() == uq.size
+    data = cuda(np.array([7, 3, 9, 11]))
+    keys = cuda(np.array([9, 4, 7, 11, 3]))
+    assert host(torch.ops.gs_ops._CAPI_IndexSearch(data, keys)).tolist() == [2, -1, 0, 3, 1]
+
+
+def test_ladies_sampler_layer(gsb, oracle):
+    """One LADIES layer (examples/ladies/ladies.py:7-21 of the reference) on the Matrix API; every
+    deterministic stage is recomputed with the oracle from the rows the GPU selected."""
+    rng = np.random.default_rng(9)
+    indptr, indices = rand_csc(rng, 4000, 60)
+    n, E = indptr.size - 1, indices.size
+    w = (rng.random(E) + 0.05).astype(np.float32)
+    m = gsb.Matrix(new_graph(gsb, indptr, indices))
+    m.edata["w"] = cuda(w, torch.float32)
+    torch.ops.gs_ops._CAPI_SetListSamplingSeed(3)
+    seeds = rng.permutation(n)[:128].astype(np.int64)
+    K = 500
+
+    subA = m[:, cuda(seeds)]
+    subA.edata["p"] = subA.edata["w"] ** 2
+    prob = subA.sum("p", axis=1)
+    sampleA, select_index = subA.collective_sampling(K, prob, False)
+    sampleA = sampleA.div("w", prob[select_index], axis=1)
+    out = sampleA.sum("w", axis=0)
+    sampleA = sampleA.div("w", out, axis=0)
+    nodes = sampleA.all_nodes()
+    block = sampleA.to_dgl_block(prefetch_edata={"w"})
+
+    sip, srows, scols, ssel = oracle.slice_cols(indptr, indices, seeds)
+    p_ref = oracle.edge_sum(srows, scols, w[ssel], 0, n, square=True)
+    assert np.allclose(host(prob), p_ref, rtol=1e-5, atol=1e-7)
+    sel = host(select_index)
+    assert sel.size == K and np.unique(sel).size == K and np.all(p_ref[sel] > 0)
+    # row slice of the column slice, taken on the CSR view like Matrix.__getitem__ does
+    csr_ip, csr_cols, perm = oracle.coo2csc(srows, scols, n)
+    rip, rcols, rloc, rsel = oracle.slice_cols(csr_ip, csr_cols, sel)
+    edge_w = w[ssel][perm][rsel]
+    w1 = oracle.edge_op_node(rloc, edge_w, p_ref[sel], "div")
+    colsum = oracle.edge_sum(rloc, rcols, w1, 2, seeds.size)
+    w2 = oracle.edge_op_node(rcols, w1, colsum, "div")
+    assert np.allclose(host(out), colsum, rtol=2e-5, atol=1e-7)
+    assert np.array_equal(host(sampleA._graph._CAPI_GetCOORows()), rloc)
+    assert np.array_equal(host(sampleA._graph._CAPI_GetCOOCols()), rcols)
+    assert np.allclose(host(sampleA.edata["w"]), w2, rtol=3e-5, atol=1e-7)
+    # frontier and block: unique(cat(seeds, selected rows that carry an edge)), relabelled COO
+    frontier, nrow, ncol = oracle.relabel(seeds, sel[rloc], rcols)
+    assert np.array_equal(host(block.srcdata["_ID"]), frontier)
+    assert np.array_equal(host(block.row), nrow) and np.array_equal(host(block.col), ncol)
+    assert np.allclose(host(block.edata["w"]), w2, rtol=3e-5, atol=1e-7)
+    assert np.array_equal(np.sort(host(nodes)), np.sort(frontier))
+
+
+def test_node2vec_sampler_api(gsb, oracle, graph):
+    """examples/node2vec/node2vec.py:10-29 of the reference on this package's Matrix."""
+    indptr, indices = graph
+    m = gsb.Matrix(new_graph(gsb, indptr, indices, seed=5))
+    m._graph._CAPI_SortCSCIndices()
+    seeds = np.random.default_rng(0).integers(0, 3000, 128).astype(np.int64)
+
+    def node2vec_sampler(A, seeds, walk_length, p, q):
+        return A.node2vec(seeds, walk_length, p, q)
+
+    fn = gsb.jit.compile(func=node2vec_sampler, args=(m, cuda(seeds), 80, 2.0, 0.5))
+    paths = fn(m, cuda(seeds), 80, 2.0, 0.5)
+    srt = oracle.sort_indices(indptr, indices)
+    assert np.array_equal(host(paths).reshape(-1), oracle.node2vec_spec(indptr, srt, seeds, 80, 2.0, 0.5, 5, 0))
