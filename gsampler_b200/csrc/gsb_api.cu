@@ -115,6 +115,7 @@ extern "C" const char* gsb_status_string(int status) {
     case GSB_ERR_UNSUPPORTED: return "request outside the supported range";
     case GSB_ERR_WORKSPACE: return "workspace missing or too small";
     case GSB_ERR_CUDA: return "CUDA runtime error";
+    case GSB_ERR_SCRATCH_LIMIT: return "size exceeds the fixed scratch of this entry point";
     default: return "unknown status";
   }
 }

@@ -204,3 +204,54 @@ extern "C" int gsb_sample_cols(const int64_t* indptr, const void* indices, int i
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }
+
+// ---------------------------------------------------------------- fixed-scratch variant
+// Some callers may not allocate device memory at all: a plugin that runs inside
+// a host application's memory budget and is handed only its input and output
+// buffers, or a service thread that must stay off the allocator because
+// cudaMalloc/cudaFree synchronise the whole device and would stall the other
+// streams of the process.  For them the tile ticket and the chained-prefix
+// status words of the sampling kernel live in the array below instead of a
+// caller-provided workspace.  Every GPU that loads the library holds these
+// bytes until the process exits.
+constexpr long long NOALLOC_MAX_TILES = 65536;  // 16.7 M column slots at fanout <= 32
+constexpr size_t NOALLOC_SCRATCH_BYTES = 256 + (size_t)(NOALLOC_MAX_TILES + 1) * sizeof(unsigned long long);
+static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH_BYTES];
+
+namespace {
+constexpr int NOALLOC_MAX_DEVICES = 64;
+void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
+}  // namespace
+
+extern "C" int64_t gsb_sample_cols_noalloc_max_columns(int64_t K) {
+  if (K < 1 || K > gsb::SAMPLE_MAX_TILE_EDGES) return 0;
+  return NOALLOC_MAX_TILES * (int64_t)gsb::sample_tile_cols(K);
+}
+
+extern "C" int gsb_sample_cols_noalloc(const int64_t* indptr, const void* indices,
+                                       int indices_dtype, const int64_t* seeds, int64_t S_max,
+                                       const int64_t* d_S, int64_t K, int replace, uint64_t seed,
+                                       uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
+                                       int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
+                                       int64_t* d_num_edges, int* d_err, void* cuda_stream) {
+  if (K < 1 || S_max < 0) return GSB_ERR_INVALID;
+  if (K > gsb::SAMPLE_MAX_TILE_EDGES) return GSB_ERR_UNSUPPORTED;
+  // sizes beyond the fixed scratch are refused, never truncated
+  if (S_max > gsb_sample_cols_noalloc_max_columns(K)) return GSB_ERR_SCRATCH_LIMIT;
+  int dev = -1;
+  GSB_CUDA_OK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return GSB_ERR_UNSUPPORTED;
+  if (!g_noalloc_ptr[dev]) {
+    // first call on this device: resolve the array's DEVICE address.  In host
+    // code the symbol's name is only a handle; passing it to a kernel would
+    // hand the kernel a host address.
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return GSB_ERR_CUDA;
+    g_noalloc_ptr[dev] = p;
+  }
+  // the scratch keeps the previous call's ticket and status words;
+  // gsb_sample_cols zeroes the part it uses on the stream before the launch
+  return gsb_sample_cols(indptr, indices, indices_dtype, seeds, S_max, d_S, K, replace, seed, stream,
+                         sub_indptr, out_rows, out_cols, out_sel, E_cap, d_num_edges,
+                         g_noalloc_ptr[dev], NOALLOC_SCRATCH_BYTES, d_err, cuda_stream);
+}

@@ -42,7 +42,8 @@ enum {
   GSB_ERR_INVALID = 1,     /* bad argument (null pointer, negative size, bad enum) */
   GSB_ERR_UNSUPPORTED = 2, /* valid request outside the implemented range (see message) */
   GSB_ERR_WORKSPACE = 3,   /* workspace smaller than *_workspace_bytes() */
-  GSB_ERR_CUDA = 4         /* a CUDA runtime call failed; see gsb_last_cuda_error() */
+  GSB_ERR_CUDA = 4,        /* a CUDA runtime call failed; see gsb_last_cuda_error() */
+  GSB_ERR_SCRATCH_LIMIT = 5 /* request larger than the fixed scratch of a *_noalloc entry point */
 };
 
 /* indices_dtype */
@@ -105,6 +106,32 @@ GSB_API int gsb_sample_cols(const int64_t* indptr, const void* indices, int indi
                             int64_t* out_rows, int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
                             int64_t* d_num_edges, void* workspace, size_t workspace_bytes,
                             int* d_err, void* cuda_stream);
+
+/* gsb_sample_cols without a workspace and without any allocation.  It has no
+ * counterpart in the reference (whose operators allocate through torch on every
+ * call).  It exists for callers that are not allowed to allocate device memory:
+ * code embedded in an application that owns the memory budget and passes in
+ * only input and output buffers, or latency-sensitive threads that must not
+ * touch the allocator because cudaMalloc / cudaFree synchronise the device.
+ * The kernel's scratch (tile ticket + prefix status words) is a fixed array
+ * inside the library, 512 KB + 264 B per GPU that loads it, so the call accepts
+ * at most gsb_sample_cols_noalloc_max_columns(K) column slots (65 536 tiles:
+ * 16 777 216 slots for K <= 32) and returns GSB_ERR_SCRATCH_LIMIT beyond that.
+ * The first call on each device looks up the array's device address (the
+ * device must be current); make that first call before starting any stream
+ * capture.  All calls on a device share the one array: it still holds the
+ * previous call's words when a call starts (the used part is zeroed on the
+ * stream before the launch), and two calls that overlap on the GPU -- different
+ * streams, or a second host thread -- race on it.  Same arguments and results
+ * as gsb_sample_cols otherwise; no cudaMalloc/cudaFree or allocating library
+ * routine is called while launch timing (gsb_timing_enable) is off. */
+GSB_API int64_t gsb_sample_cols_noalloc_max_columns(int64_t K);
+GSB_API int gsb_sample_cols_noalloc(const int64_t* indptr, const void* indices, int indices_dtype,
+                                    const int64_t* seeds, int64_t S_max, const int64_t* d_S,
+                                    int64_t K, int replace, uint64_t seed, uint32_t stream,
+                                    int64_t* sub_indptr, int64_t* out_rows, int64_t* out_cols,
+                                    int64_t* out_sel, int64_t E_cap, int64_t* d_num_edges,
+                                    int* d_err, void* cuda_stream);
 
 /* Weighted per-column sampling (A-Res keys, without replacement; CDF search
  * with replacement).  Replaces Graph::SamplingProbs (src/graph.cc:246-308 ->
