@@ -365,8 +365,9 @@ def main():
         per_launch = {
             "sample_tile": (8 * S_l + 16 * S_l + w_idx * E_l + 8 * (S_l + 1) + 24 * E_l).mean(),
             "relabel_insert": (8 * (S_l + E_l)).mean(),
-            "relabel_scan": (8 * (S_l + E_l) + 8 * U_l).mean(),
-            "relabel_edges": (32 * E_l).mean(),
+            "relabel_lookup": (8 * (S_l + E_l)).mean(),
+            "relabel_rank": (8 * (S_l + E_l) + 8 * U_l).mean(),
+            "relabel_emit": (24 * E_l).mean(),
             "relabel_clear": 0.0,
         }.get(dname, 0.0)
         dur_s = dms / dcnt / 1e3

@@ -204,7 +204,7 @@ enum KernelId {
   KID_SAMPLE = 0, KID_SAMPLE_PROBS, KID_COUNT, KID_SLICE_FILL, KID_GATHER, KID_EXPAND,
   KID_INDPTR_SORTED, KID_RL_SETUP, KID_RL_CLEAR, KID_RL_INSERT, KID_RL_SCAN, KID_RL_EDGES,
   KID_COUNTS, KID_SLICE_ROWS, KID_EDGE_SUM, KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT,
-  KID_MISC, KID_NUM
+  KID_RL_LOOKUP, KID_RL_TILES, KID_MISC, KID_NUM
 };
 struct LaunchScope {
   LaunchScope(int id, cudaStream_t st);
