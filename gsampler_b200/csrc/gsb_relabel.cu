@@ -18,6 +18,10 @@
 //   emit   : every edge reads rank[first item of its row id] and of its
 //            column's seed -> relabelled COO                     (streaming +
 //            one gather for ids that were seen before)
+// When the caller states a bound on the ids and B * bound 32-bit words are not
+// more memory than the hash tables would be, the tables are direct-address
+// arrays instead (word = smallest item index of that id): no probing, no key
+// compare, and the insert is a fire-and-forget atomic min.
 // The tables are written only by `insert`; nothing is finalised in place.  The
 // measured limiter of the stage is the number of random L2/DRAM transactions,
 // which this arrangement keeps at about two per item (one RMW, one read).
@@ -61,10 +65,11 @@ struct RelabelParams {
   u32* rank;         // [items] position in `unique`, valid for first occurrences
   i64 slots_cap;
   i64 tiles_cap;
+  i64 direct_bound;  // > 0: direct-address tables of this many 32-bit words per minibatch
   int* err;
 };
 
-__host__ __device__ inline i64 table_slots_for(i64 items) { return items + (items >> 2) + 32; }
+__host__ __device__ inline i64 table_slots_for(i64 items) { return items * 2 + 32; }
 
 // One block: item_ptr / table_ptr = running sums over the minibatches.
 __global__ void relabel_setup_kernel(const RelabelParams p) {
@@ -96,6 +101,7 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
   }
   if (threadIdx.x == 0) {
     i64 n_items = s_carry_items, n_slots = s_carry_slots;
+    if (p.direct_bound > 0) n_slots = (p.direct_bound * p.B + 1) / 2;  // 64-bit words to clear
     i64 n_seeds = p.seeds_ptr[p.B], n_edges = p.edge_ptr[p.B];
     if (n_items > p.S_max + p.E_max || n_slots > p.slots_cap || n_seeds > p.S_max ||
         n_edges > p.E_max || n_seeds < 0 || n_edges < 0) {
@@ -160,6 +166,14 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_insert_kernel(const Relabe
     const int b_hint = find_segment(p.item_ptr, p.B, g - (threadIdx.x & 31));  // warp-uniform
     const Item it = fetch_item(p, g, b_hint);
     if (!it.ok) { raise(p.err, ERRBIT_BAD_INPUT); continue; }
+    if (p.direct_bound > 0) {
+      if ((i64)it.key >= p.direct_bound) { raise(p.err, ERRBIT_BAD_INPUT); continue; }
+      u32* w = reinterpret_cast<u32*>(p.table) + (i64)it.b * p.direct_bound + it.key;
+      u32 cur;  // read first: later duplicates of a popular id leave without an atomic
+      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(w) : "memory");
+      if (cur > it.idx) atomicMin(w, it.idx);
+      continue;
+    }
     const i64 base = p.table_ptr[it.b];
     const u32 slots = (u32)(p.table_ptr[it.b + 1] - base);
     u64* tab = p.table + base;
@@ -208,7 +222,11 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_lookup_kernel(const Relabe
       const int b_hint = find_segment(p.item_ptr, p.B, g - lane);
       const Item it = fetch_item(p, g, b_hint);
       u32 m = IDX_UNSET;
-      if (it.ok) {
+      if (it.ok && p.direct_bound > 0) {
+        if ((i64)it.key < p.direct_bound)
+          m = __ldg(reinterpret_cast<const u32*>(p.table) + (i64)it.b * p.direct_bound + it.key);
+        first = m == it.idx;
+      } else if (it.ok) {
         const i64 base = p.table_ptr[it.b];
         m = lookup_min_index(p.table + base, (u32)(p.table_ptr[it.b + 1] - base), it.key);
         if (m == IDX_UNSET) raise(p.err, ERRBIT_KEY_MISSING);
@@ -335,11 +353,18 @@ struct RelabelLayout {
   i64 slots_cap, tiles;
 };
 
+// Direct-address tables are used when they need no more memory than hashing.
+static bool use_direct(i64 S_max, i64 E_max, i64 B, i64 id_bound) {
+  if (id_bound <= 0 || id_bound >= 0xFFFFFFFFll) return false;
+  const i64 hash_words = (S_max + E_max) * 2 + 32 * (B + 1);          // 64-bit words
+  return (id_bound * B + 1) / 2 <= hash_words;
+}
+
 static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   RelabelLayout L;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
   L.tiles = (S_max + E_max + RL_TILE - 1) / RL_TILE + 1;
-  L.slots_cap = (S_max + E_max) + ((S_max + E_max) >> 2) + 32 * (B + 1);
+  L.slots_cap = (S_max + E_max) * 2 + 32 * (B + 1);
   size_t o = 0;
   L.hdr = o; o = up(o + sizeof(RelabelHeader));
   L.item_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
@@ -387,6 +412,7 @@ extern "C" int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr,
   p.table_ptr = (i64*)(ws + L.table_ptr); p.tile_count = (u32*)(ws + L.tile_count);
   p.min_idx = (u32*)(ws + L.min_idx); p.rank = (u32*)(ws + L.rank);
   p.table = (u64*)(ws + L.table); p.slots_cap = L.slots_cap; p.tiles_cap = L.tiles; p.err = d_err;
+  p.direct_bound = use_direct(S_max, E_max, B, id_bound) ? id_bound : 0;
 
   { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
   const i64 items_max = S_max + E_max;

@@ -60,7 +60,8 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
   const size_t ws_bytes = gsb_graphsage_workspace_bytes(B, L, bufs.data(), fanouts.data());
   auto ws = NewWorkspace(ws_bytes, seeds.device());
   const int dtype = csc_->indices.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
-  CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype, 0, P(seeds),
+  CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype,
+                                   std::max(num_rows_, num_cols_), P(seeds),
                                    P(seeds_ptr), B, S0, L, fanouts.data(), GetSeedU64(),
                                    bufs.data(), counts.data_ptr<int64_t>(), ws.data_ptr(),
                                    (size_t)ws.numel(),

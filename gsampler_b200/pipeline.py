@@ -76,6 +76,7 @@ class GraphSAGESampler(object):
     num_batches       minibatches per super-batch (B)
     max_seeds         upper bound of the number of seeds in one super-batch
     fanouts           per-layer fanout
+    num_nodes         exclusive upper bound of the node ids (default: number of columns)
     capacities        optional [(S_cap, E_cap)] per layer; default = worst case
                       (S_cap[l+1] = S_cap[l] + E_cap[l], E_cap[l] = S_cap[l] * fanout[l]).
                       Smaller capacities save memory; overflow is reported through the error
@@ -84,7 +85,7 @@ class GraphSAGESampler(object):
 
     def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, num_batches: int,
                  max_seeds: int, fanouts: Sequence[int], seed: int = 7777,
-                 capacities: Optional[Sequence] = None):
+                 capacities: Optional[Sequence] = None, num_nodes: Optional[int] = None):
         if not (indptr.is_cuda and indices.is_cuda):
             raise ValueError("the graph must live on a CUDA device (there is no CPU path)")
         if indptr.dtype != torch.int64 or indices.dtype not in (torch.int32, torch.int64):
@@ -95,6 +96,9 @@ class GraphSAGESampler(object):
         self.fanouts = [int(k) for k in fanouts]
         self.seed = int(seed)
         self.max_seeds = int(max_seeds)
+        # exclusive bound of all node ids (seeds and row ids); lets the relabel stage pick
+        # direct-address tables when that is the smaller representation
+        self.num_nodes = int(indptr.numel() - 1 if num_nodes is None else num_nodes)
         opt = dict(dtype=torch.int64, device=self.device)
         self._bufs = (_LayerBuffers * self.L)()
         self.layers: List[dict] = []
@@ -132,7 +136,7 @@ class GraphSAGESampler(object):
         counts = self._counts if counts_out is None else counts_out
         rc = cabi().gsb_graphsage_sample(
             C.c_void_p(self.indptr.data_ptr()), C.c_void_p(self.indices.data_ptr()), self._dtype,
-            C.c_int64(0), C.c_void_p(seeds.data_ptr()), C.c_void_p(seeds_ptr.data_ptr()),
+            C.c_int64(self.num_nodes), C.c_void_p(seeds.data_ptr()), C.c_void_p(seeds_ptr.data_ptr()),
             C.c_int64(self.B), C.c_int64(seeds.numel()), self.L, self._fan, C.c_uint64(self.seed),
             self._bufs, C.c_void_p(counts.data_ptr()), C.c_void_p(self._ws.data_ptr()),
             C.c_size_t(self._ws.numel()), C.c_void_p(self._err.data_ptr()),
