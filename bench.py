@@ -98,6 +98,17 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# DRAM bytes (read + write) per sampled edge / per relabel item of one launch, from the
+# `ncu --set full` capture of the "medium" case summarised under profiles/; the access pattern
+# per unit is the same on the bench workload, so the per-launch traffic is scaled by the units.
+NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 94.3}
+
+
+def ncu_traffic(kernel, mean_edges):
+    per = NCU_DRAM_BYTES_PER_EDGE.get(kernel)
+    return None if per is None else per * mean_edges
+
+
 def load_peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -217,6 +228,8 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
+            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
     import gsampler_b200 as gs
@@ -376,7 +389,7 @@ def main():
         for l in range(L):
             f, b = algorithmic_bytes(c_host[:, l, 0].sum(), c_host[:, l, 1].sum(), c_host[:, l, 2].sum(), w_idx)
             path_bytes += f + b
-        path_gbs = path_bytes / (elapsed_ms / 1e3) / 1e9 / max(world, 1)
+        path_gbs = path_bytes / (elapsed_ms / 1e3) / 1e9  # per GPU (rank 0's own counts)
         line = {
             "metric": "graphsage_sampled_edges_per_sec",
             "value": edges / (elapsed_ms / 1e3), "unit": "edges/s", "n_gpus": world,
@@ -398,10 +411,11 @@ def main():
                     "api": "BatchMatrix.graphsage (one native call per super-batch)"},
             "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": "%s[layer %d]" % (dname, dtag), "achieved": achieved,
-                         "peak": peak, "unit": "GB/s", "frac": achieved / peak, "traffic": None,
+                         "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "traffic": ncu_traffic(dname, float(E_l.mean())),
                          "peak_kind": peak_kind, "share_of_kernel_time": dms / total_kernel_ms,
                          "avg_launch_ms": dms / dcnt},
-            "roofline_path": {"algorithmic_gb_per_step": path_bytes / args.steps / max(world, 1) / 1e9,
+            "roofline_path": {"algorithmic_gb_per_step": path_bytes / args.steps / 1e9,
                               "achieved": path_gbs, "unit": "GB/s", "frac": path_gbs / peak,
                               "peak_kind": peak_kind},
             "kernels": {"%s[%d]" % k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(by.items())},
