@@ -1,0 +1,177 @@
+"""Secondary benchmarks of the operators next to the GraphSAGE path (``bench.py`` at the
+repository root holds the headline one):
+
+    python -m gsampler_b200.benchmarks ladies     # 2-layer LADIES, 4000 nodes/layer, 512 seeds,
+                                                  # 232 965 nodes / 114.6 M weighted edges
+    python -m gsampler_b200.benchmarks node2vec   # 1 M walkers x 80 steps, p=2, q=0.5,
+                                                  # 2 449 029 nodes / 123.7 M edges
+    python -m gsampler_b200.benchmarks cfg5s      # GraphSAGE [15,10,5] on an int32-index R-MAT-like
+                                                  # power-law graph, 11.1 M nodes / 320 M edges
+
+Each prints one JSON line with the metric, the per-kernel CUDA-event times collected by the
+library's launch accounting, and the algorithmic GB/s of the dominant kernel.  Graphs are
+seeded synthetic stand-ins with the shapes named above.
+"""
+from __future__ import annotations
+
+import json
+import sys
+import time
+
+import torch
+
+import gsampler_b200 as gs
+from gsampler_b200 import pipeline, synth
+
+PEAK_GBS = 6535.4  # measured copy bandwidth of this pool's B200 (MEASURED_PEAKS.json)
+
+
+def _events():
+    return torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+
+
+def _kernel_table(timed):
+    by = {}
+    for name, tag, ms, cnt in timed:
+        a = by.setdefault(name, [0.0, 0])
+        a[0] += ms
+        a[1] += cnt
+    return {k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(by.items())}
+
+
+def ladies(steps=10, warmup=3):
+    dev = torch.device("cuda")
+    n, e, nseeds, K = 232965, 114615892, 512, 4000
+    indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=30000, seed=11, device=dev)
+    g = torch.Generator(device=dev)
+    g.manual_seed(5)
+    w = torch.rand(indices.numel(), generator=g, device=dev).clamp_min_(1e-3)
+    A = gs.Graph(n, n)
+    A._CAPI_LoadCSC(indptr, indices)
+    m = gs.Matrix(A)
+    m.edata["w"] = w
+    # column-normalise once (the reference's P = D^-1/2 A D^-1/2 preprocessing is out of the loop)
+    colsum = m.sum("w", axis=0)
+    m = m.div("w", colsum.clamp_min(1e-12), axis=0)
+
+    def layer_fn(A, seeds, fanouts):
+        edges = 0
+        for k in fanouts:
+            subA = A[:, seeds]
+            subA.edata["p"] = subA.edata["w"] ** 2
+            prob = subA.sum("p", axis=1)
+            sampleA, sel = subA.collective_sampling(k, prob, False)
+            sampleA = sampleA.div("w", prob[sel], axis=1)
+            out = sampleA.sum("w", axis=0)
+            sampleA = sampleA.div("w", out, axis=0)
+            seeds = sampleA.all_nodes()
+            blk = sampleA.to_dgl_block(prefetch_edata={"w"})
+            edges += blk.num_edges()
+        return edges
+
+    gen = torch.Generator()
+    gen.manual_seed(1)
+    batches = [torch.randperm(n, generator=gen)[:nseeds].to(dev) for _ in range(steps + warmup)]
+    for i in range(warmup):
+        layer_fn(m, batches[i], [K, K])
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    edges = 0
+    for i in range(steps):
+        edges += layer_fn(m, batches[warmup + i], [K, K])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    pipeline.timing_enable(True)
+    for i in range(steps):
+        layer_fn(m, batches[warmup + i], [K, K])
+    timed = pipeline.timing_collect()
+    pipeline.timing_enable(False)
+    print(json.dumps({"metric": "ladies_block_edges_per_sec", "value": edges / (ms / 1e3), "unit": "edges/s",
+                      "ms_per_step": ms / steps, "steps": steps, "edges_per_step": edges / steps,
+                      "config": {"workload": "LADIES 2 layers x %d nodes, %d seeds, %d nodes / %d edges fp32 w"
+                                 % (K, nseeds, n, int(indptr[-1]))},
+                      "kernels": _kernel_table(timed)}))
+
+
+def node2vec(steps=3, warmup=1, walkers=1000000, length=80):
+    dev = torch.device("cuda")
+    n, e = 2449029, 123718280
+    indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=20000, seed=2024, device=dev)
+    A = gs.Graph(n, n)
+    A._CAPI_LoadCSC(indptr, indices)
+    A._CAPI_SortCSCIndices()     # generator output is already sorted; kept for the API contract
+    gen = torch.Generator()
+    gen.manual_seed(7)
+    seeds = torch.randint(0, n, (walkers,), generator=gen).to(dev)
+    out = {}
+    for name, fn in (("node2vec", lambda: A._CAPI_Node2Vec(seeds, length, 2.0, 0.5)),
+                     ("random_walk", lambda: A._CAPI_RandomWalk(seeds, length))):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            tr = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        live = int((tr.reshape(length + 1, walkers)[1:] >= 0).sum())
+        # compulsory bytes per taken step: indptr pair + one id + the trace entry
+        alg = live * (16 + 8 + 8)
+        out[name] = {"ms_per_call": ms, "steps_per_sec": live / (ms / 1e3),
+                     "algorithmic_gbs": alg / (ms / 1e3) / 1e9, "frac_of_copy_peak": alg / (ms / 1e3) / 1e9 / PEAK_GBS,
+                     "live_steps": live}
+    print(json.dumps({"metric": "walk_steps_per_sec", "value": out["node2vec"]["steps_per_sec"],
+                      "unit": "steps/s",
+                      "config": {"workload": "%d walkers x %d steps, p=2 q=0.5, %d nodes / %d edges"
+                                 % (walkers, length, n, int(indptr[-1]))}, **out}))
+
+
+def cfg5s(steps=6, warmup=3):
+    dev = torch.device("cuda")
+    n, e, batch, sb = 11105996, 320000000, 1024, 64
+    indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=100000, seed=9, device=dev,
+                                         index_dtype=torch.int32)
+    fan = [15, 10, 5]
+    gen = torch.Generator()
+    gen.manual_seed(3)
+    seeds_all = torch.randperm(n, generator=gen)[:batch * sb * (steps + warmup)].to(dev)
+    ptr = (torch.arange(sb + 1, dtype=torch.int64) * batch).to(dev)
+    probe = pipeline.GraphSAGESampler(indptr, indices, sb, batch * sb, fan)
+    probe.sample(seeds_all[:batch * sb], ptr)
+    caps = [(int(S * 1.2) + 4096, int(E * 1.2) + 4096) for S, E, U in probe.counts()]
+    caps[0] = (batch * sb, batch * sb * fan[0])
+    del probe
+    torch.cuda.empty_cache()
+    smp = pipeline.GraphSAGESampler(indptr, indices, sb, batch * sb, fan, capacities=caps)
+    counts = torch.zeros(steps + warmup, 9, dtype=torch.int64, device=dev)
+    for i in range(warmup):
+        smp.sample(seeds_all[i * batch * sb:(i + 1) * batch * sb], ptr, counts_out=counts[i])
+    torch.cuda.synchronize()
+    smp.check()
+    e0, e1 = _events()
+    e0.record()
+    for i in range(warmup, warmup + steps):
+        smp.sample(seeds_all[i * batch * sb:(i + 1) * batch * sb], ptr, counts_out=counts[i])
+    e1.record()
+    torch.cuda.synchronize()
+    smp.check()
+    ms = e0.elapsed_time(e1)
+    c = counts[warmup:].cpu().view(steps, 3, 3)
+    edges = int(c[:, :, 1].sum())
+    print(json.dumps({"metric": "graphsage_sampled_edges_per_sec", "value": edges / (ms / 1e3), "unit": "edges/s",
+                      "ms_per_step": ms / steps, "steps": steps,
+                      "config": {"workload": "GraphSAGE [15,10,5], %d x %d seeds, %d nodes / %d edges, int32 indices"
+                                 % (sb, batch, n, int(indptr[-1])),
+                                 "graph_gb": (indices.numel() * 4 + indptr.numel() * 8) / 1e9,
+                                 "mean_SEU_per_layer": c.double().mean(0).tolist()}}))
+
+
+if __name__ == "__main__":
+    which = sys.argv[1] if len(sys.argv) > 1 else "node2vec"
+    t0 = time.time()
+    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s}[which]()
+    print("# %s finished in %.1f s" % (which, time.time() - t0), file=sys.stderr)

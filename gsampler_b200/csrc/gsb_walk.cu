@@ -91,8 +91,12 @@ node2vec_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices
             if (x >= deg) x = deg - 1;
             const i64 cand = load_index<IndexT>(indices, st + x);
             if ((double)y < accept_below) { pick = cand; break; }
+            // h = p for a return, q for a neighbour of the previous node, 1
+            // otherwise.  The membership search only matters when q and 1 lie
+            // on different sides of y; for (p, q) = (2, 0.5) it never runs.
             double h;
             if (cand == last) h = p;
+            else if (((double)y < q) == ((double)y < 1.0)) h = 1.0;
             else if (column_contains<IndexT>(indptr, indices, num_nodes, last, cand)) h = q;
             else h = 1.0;
             if ((double)y < h) { pick = cand; break; }
