@@ -40,5 +40,19 @@ from .jit import compile  # noqa: E402,A001
 
 Graph = torch.classes.gs_classes.Graph
 
-__all__ = ["Matrix", "BatchMatrix", "Graph", "jit", "ops", "utils", "compile", "_COO", "_CSC", "_CSR"]
+
+def gather_rows(data: torch.Tensor, index: torch.Tensor) -> torch.Tensor:
+    """``data[index]`` along the first dimension by the library's row-gather kernel: ``data`` on
+    the index's GPU or in pinned host memory (read in place), no synchronisation.  This is the
+    feature fetch that follows sampling (examples/graphsage/graphsage_e2e.py:111-118 in
+    gSampler, where DGL's ``gather_pinned_tensor_rows`` does it).  A bad index is reported by
+    ``check_async_errors()``."""
+    return torch.ops.gs_ops._CAPI_GatherRows(data, index)
+
+
+def check_async_errors() -> None:
+    """Raise if a sync-free operator (``gather_rows``) met invalid input since the last check."""
+    torch.ops.gs_ops._CAPI_CheckAsyncErrors()
+
+__all__ = ["Matrix", "BatchMatrix", "Graph", "gather_rows", "check_async_errors", "jit", "ops", "utils", "compile", "_COO", "_CSC", "_CSR"]
 from .pipeline import GraphSAGESampler  # noqa: E402

@@ -5,6 +5,7 @@ repository root holds the headline one):
                                                   # 232 965 nodes / 114.6 M weighted edges
     python -m gsampler_b200.benchmarks node2vec   # 1 M walkers x 80 steps, p=2, q=0.5,
                                                   # 2 449 029 nodes / 123.7 M edges
+    python -m gsampler_b200.benchmarks gather     # feature fetch: 4 M rows of 100 fp32 out of 2 449 029
     python -m gsampler_b200.benchmarks cfg5s      # GraphSAGE [15,10,5] on an int32-index R-MAT-like
                                                   # power-law graph, 11.1 M nodes / 320 M edges
 
@@ -130,6 +131,36 @@ def node2vec(steps=3, warmup=1, walkers=1000000, length=80):
                                  % (walkers, length, n, int(indptr[-1]))}, **out}))
 
 
+def gather(steps=10, warmup=3, rows=4000000, width=100):
+    """Feature fetch for a sampled frontier: random rows of a [2 449 029, 100] fp32 table."""
+    dev = torch.device("cuda")
+    n = 2449029
+    g = torch.Generator(device=dev)
+    g.manual_seed(1)
+    feat = torch.rand(n, width, generator=g, device=dev)
+    idx = torch.randint(0, n, (rows,), generator=g, device=dev)
+    out = {}
+    for name, src in (("device", feat), ("pinned_host", feat[:200000].cpu().pin_memory())):
+        ix = idx if name == "device" else idx[:400000] % 200000
+        for _ in range(warmup):
+            gs.gather_rows(src, ix)
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            o = gs.gather_rows(src, ix)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        alg = ix.numel() * (8 + 2 * width * 4)       # index + row read + row write
+        out[name] = {"ms_per_call": ms, "rows": ix.numel(), "algorithmic_gbs": alg / (ms / 1e3) / 1e9,
+                     "frac_of_copy_peak": alg / (ms / 1e3) / 1e9 / PEAK_GBS}
+        assert torch.equal(o[:1000], src[ix[:1000].cpu()].to(dev) if name != "device" else src[ix[:1000]])
+    gs.check_async_errors()
+    print(json.dumps({"metric": "gather_rows_gbs", "value": out["device"]["algorithmic_gbs"], "unit": "GB/s",
+                      "config": {"workload": "%d rows x %d fp32 out of %d" % (rows, width, n)}, **out}))
+
+
 def cfg5s(steps=6, warmup=3):
     dev = torch.device("cuda")
     n, e, batch, sb = 11105996, 320000000, 1024, 64
@@ -173,5 +204,5 @@ def cfg5s(steps=6, warmup=3):
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "node2vec"
     t0 = time.time()
-    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s}[which]()
+    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s, "gather": gather}[which]()
     print("# %s finished in %.1f s" % (which, time.time() - t0), file=sys.stderr)

@@ -171,6 +171,164 @@ static int build_map(char* ws, const AcrossLayout& L, const i64* ids, i64 R, i64
   return GSB_OK;
 }
 
+
+// ---------------------------------------------------------------- columns AND rows, per minibatch
+// Induced sub-matrices: minibatch b keeps, of its columns cols[col_ptr[b]..),
+// the entries whose row id is in its own row list rows[row_ptr[b]..).  B direct
+// maps would be B * id_bound words, so membership is one open-addressing table
+// per minibatch (slot = id:32 | position:32, smallest position wins), sized
+// 2 * |rows_b| + 32 and placed at 2 * row_ptr[b] + 32 * b -- both follow from
+// row_ptr alone, no set-up pass.
+constexpr u64 RT_EMPTY = ~0ull;
+
+__device__ __forceinline__ u64* rowtab_of(u64* table, const i64* __restrict__ row_ptr, int b,
+                                          u32* slots) {
+  const i64 r0 = row_ptr[b];
+  *slots = (u32)(2 * (row_ptr[b + 1] - r0) + 32);
+  return table + 2 * r0 + 32 * (i64)b;
+}
+
+__global__ void rowtab_insert_kernel(const i64* __restrict__ rows, const i64* __restrict__ row_ptr,
+                                     int B, u64* table, int* err) {
+  const i64 R = row_ptr[B];
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < R; i += (i64)gridDim.x * blockDim.x) {
+    const int b = find_segment(row_ptr, B, i);
+    const i64 id = rows[i];
+    if (id < 0 || id >= 0xFFFFFFFFll) { raise(err, ERRBIT_BAD_INPUT); continue; }
+    u32 slots;
+    u64* tab = rowtab_of(table, row_ptr, b, &slots);
+    const u64 packed = ((u64)(u32)id << 32) | (u32)i;
+    u32 pos = __umulhi(hash32((u32)id), slots);
+    u32 probes = 0;
+    for (; probes < slots; ++probes) {
+      u64 cur = ld_relaxed(tab + pos);
+      if (cur == RT_EMPTY) {
+        cur = atomicCAS(tab + pos, RT_EMPTY, packed);
+        if (cur == RT_EMPTY) break;
+      }
+      if ((u32)(cur >> 32) == (u32)id) {
+        if ((u32)cur > (u32)i) atomicMin(tab + pos, packed);
+        break;
+      }
+      pos = pos + 1 == slots ? 0 : pos + 1;
+    }
+    if (probes == slots) raise(err, ERRBIT_TABLE_FULL);
+  }
+}
+
+__device__ __forceinline__ u32 rowtab_find(const u64* __restrict__ tab, u32 slots, i64 id) {
+  if (id < 0 || id >= 0xFFFFFFFFll) return MAP_ABSENT;
+  u32 pos = __umulhi(hash32((u32)id), slots);
+  for (u32 probes = 0; probes < slots; ++probes) {
+    const u64 cur = __ldg(tab + pos);
+    if (cur == RT_EMPTY) return MAP_ABSENT;
+    if ((u32)(cur >> 32) == (u32)id) return (u32)cur;
+    pos = pos + 1 == slots ? 0 : pos + 1;
+  }
+  return MAP_ABSENT;
+}
+
+// CTA = RS_THREADS consecutive column slots; a warp walks one column at a time.
+template <typename IndexT>
+__global__ void __launch_bounds__(RS_THREADS)
+colrow_count_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 num_cols,
+                    const i64* __restrict__ cols, const i64* __restrict__ col_ptr,
+                    const i64* __restrict__ row_ptr, int B, u64* table, i64* __restrict__ out_indptr,
+                    u64* status, int* ticket, int* err) {
+  __shared__ i64 s_scan[34];
+  __shared__ int s_cnt[RS_THREADS];
+  __shared__ int s_tile;
+  __shared__ i64 s_base;
+  if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
+  __syncthreads();
+  const int tile = s_tile;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const i64 nseg = col_ptr[B];
+  const i64 seg0 = (i64)tile * RS_THREADS;
+  for (int k = wid; k < RS_THREADS; k += RS_WARPS) {
+    const i64 seg = seg0 + k;
+    int cnt = 0;
+    if (seg < nseg) {
+      const i64 c = cols[seg];
+      if (c < 0 || c >= num_cols) {
+        if (lane == 0) raise(err, ERRBIT_BAD_INPUT);
+      } else {
+        u32 slots;
+        const u64* tab = rowtab_of(table, row_ptr, find_segment(col_ptr, B, seg), &slots);
+        const i64 st = __ldg(indptr + c), en = __ldg(indptr + c + 1);
+        for (i64 e = st + lane; e < en; e += 32)
+          if (rowtab_find(tab, slots, load_index<IndexT>(indices, e)) != MAP_ABSENT) ++cnt;
+#pragma unroll
+        for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
+      }
+    }
+    if (lane == 0) s_cnt[k] = cnt;
+  }
+  __syncthreads();
+  i64 total;
+  const i64 loff = block_exclusive_scan((i64)s_cnt[threadIdx.x], s_scan, &total);
+  if (threadIdx.x < 32) {
+    i64 base = chained_exclusive_prefix(status, tile, total, err);
+    if (threadIdx.x == 0) s_base = base;
+  }
+  __syncthreads();
+  const i64 seg = seg0 + threadIdx.x;
+  if (seg < nseg) out_indptr[seg] = s_base + loff;
+  if (seg == nseg - 1 || (nseg == 0 && seg == 0)) out_indptr[nseg] = s_base + total;
+}
+
+template <typename IndexT>
+__global__ void __launch_bounds__(RS_THREADS)
+colrow_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 num_cols,
+                   const i64* __restrict__ cols, const i64* __restrict__ col_ptr,
+                   const i64* __restrict__ row_ptr, int B, const u64* __restrict__ table,
+                   const i64* __restrict__ out_indptr, i64* __restrict__ out_ids,
+                   i64* __restrict__ out_seg, i64* __restrict__ out_sel) {
+  const int lane = threadIdx.x & 31;
+  const i64 nseg = col_ptr[B];
+  const i64 warp0 = ((i64)blockIdx.x * RS_THREADS + threadIdx.x) >> 5;
+  const i64 nwarps = ((i64)gridDim.x * RS_THREADS) >> 5;
+  for (i64 seg = warp0; seg < nseg; seg += nwarps) {
+    const i64 c = cols[seg];
+    if (c < 0 || c >= num_cols) continue;
+    u32 slots;
+    const u64* tab = rowtab_of(const_cast<u64*>(table), row_ptr, find_segment(col_ptr, B, seg), &slots);
+    const i64 st = __ldg(indptr + c), en = __ldg(indptr + c + 1);
+    i64 o = out_indptr[seg];
+    for (i64 e0 = st; e0 < en; e0 += 32) {
+      const i64 e = e0 + lane;
+      u32 pos = MAP_ABSENT;
+      if (e < en) pos = rowtab_find(tab, slots, load_index<IndexT>(indices, e));
+      const unsigned keep = __ballot_sync(0xffffffffu, pos != MAP_ABSENT);
+      if (pos != MAP_ABSENT) {
+        const i64 w = o + __popc(keep & ((1u << lane) - 1u));
+        out_ids[w] = (i64)pos;
+        out_sel[w] = e;
+        if (out_seg) out_seg[w] = seg;
+      }
+      o += __popc(keep);
+    }
+  }
+}
+
+struct ColRowLayout {
+  size_t ticket, status, table, total;
+  i64 tiles, slots;
+};
+
+static ColRowLayout colrow_layout(i64 S, i64 R, i64 B) {
+  ColRowLayout L;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  L.tiles = (S + RS_THREADS - 1) / RS_THREADS + 1;
+  L.slots = 2 * R + 32 * (B + 1);
+  size_t o = 0;
+  L.ticket = o; o = up(o + 256);
+  L.status = o; o = up(o + sizeof(u64) * (size_t)L.tiles);
+  L.table = o; o = up(o + sizeof(u64) * (size_t)L.slots);
+  L.total = o;
+  return L;
+}
+
 }  // namespace gsb
 
 using namespace gsb;
@@ -258,6 +416,80 @@ extern "C" int gsb_coo_filter(const int64_t* key, const int64_t* other, int64_t 
       (const i64*)key, (const i64*)other, nnz, (const u32*)(ws + L.map), id_bound, (i64*)out_key,
       (i64*)out_other, (i64*)out_sel, (i64*)d_count, (u64*)(ws + L.status), (int*)(ws + L.ticket),
       d_err);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" size_t gsb_slice_cols_rows_workspace_bytes(int64_t S, int64_t R, int64_t B) {
+  if (S < 0 || R < 0 || B < 0) return 0;
+  return colrow_layout(S, R, B).total;
+}
+
+extern "C" int gsb_slice_cols_rows_count(const int64_t* indptr, const void* indices,
+                                         int indices_dtype, int64_t num_cols, const int64_t* cols,
+                                         const int64_t* col_ptr, int64_t S, const int64_t* rows,
+                                         const int64_t* row_ptr, int64_t R, int64_t B,
+                                         int64_t* out_indptr, void* workspace,
+                                         size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (!indptr || !out_indptr || !col_ptr || !row_ptr || S < 0 || R < 0 || B < 1 || num_cols < 0 ||
+      (S > 0 && (!cols || !indices)) || (R > 0 && !rows))
+    return GSB_ERR_INVALID;
+  if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
+  if (R >= 0x7FFFFFFFll || B >= (1ll << 24)) return GSB_ERR_UNSUPPORTED;
+  const ColRowLayout L = colrow_layout(S, R, B);
+  if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  char* ws = (char*)workspace;
+  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.table, st));                               // ticket + status
+  GSB_CUDA_OK(cudaMemsetAsync(ws + L.table, 0xFF, sizeof(u64) * (size_t)L.slots, st));  // empty slots
+  if (R > 0) {
+    i64 g = (R + 255) / 256; if (g > 148 * 16) g = 148 * 16;
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    rowtab_insert_kernel<<<(int)g, 256, 0, st>>>((const i64*)rows, (const i64*)row_ptr, (int)B,
+                                                 (u64*)(ws + L.table), d_err);
+  }
+  const int tiles = S == 0 ? 1 : ceil_div_i(S, RS_THREADS);
+  LaunchScope ls(KID_SLICE_ROWS, st);
+  if (indices_dtype == GSB_I32)
+    colrow_count_kernel<int><<<tiles, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
+        (const i64*)row_ptr, (int)B, (u64*)(ws + L.table), (i64*)out_indptr, (u64*)(ws + L.status),
+        (int*)(ws + L.ticket), d_err);
+  else
+    colrow_count_kernel<i64><<<tiles, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
+        (const i64*)row_ptr, (int)B, (u64*)(ws + L.table), (i64*)out_indptr, (u64*)(ws + L.status),
+        (int*)(ws + L.ticket), d_err);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_slice_cols_rows_fill(const int64_t* indptr, const void* indices,
+                                        int indices_dtype, int64_t num_cols, const int64_t* cols,
+                                        const int64_t* col_ptr, int64_t S, const int64_t* row_ptr,
+                                        int64_t R, int64_t B, const int64_t* out_indptr,
+                                        int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
+                                        const void* workspace, void* cuda_stream) {
+  if (S == 0) return GSB_OK;
+  if (!indptr || !indices || !cols || !col_ptr || !row_ptr || !out_indptr || !out_ids || !out_sel ||
+      !workspace || S < 0 || B < 1)
+    return GSB_ERR_INVALID;
+  if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
+  const ColRowLayout L = colrow_layout(S, R, B);
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  i64 g = (S + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
+  const u64* table = (const u64*)((const char*)workspace + L.table);
+  LaunchScope ls(KID_SLICE_ROWS, st);
+  if (indices_dtype == GSB_I32)
+    colrow_fill_kernel<int><<<(int)g, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
+        (const i64*)row_ptr, (int)B, table, (const i64*)out_indptr, (i64*)out_ids, (i64*)out_seg,
+        (i64*)out_sel);
+  else
+    colrow_fill_kernel<i64><<<(int)g, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
+        (const i64*)row_ptr, (int)B, table, (const i64*)out_indptr, (i64*)out_ids, (i64*)out_seg,
+        (i64*)out_sel);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

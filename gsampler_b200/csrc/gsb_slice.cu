@@ -97,6 +97,24 @@ __global__ void gather_i64_kernel(const i64* __restrict__ src, const i64* __rest
     out[i] = src[idx[i]];
 }
 
+// Row gather for node / edge data: out row i = src row idx[i].  A row is cut
+// into chunks of VecT; consecutive threads copy consecutive chunks of the same
+// row, so both the reads and the writes of a row are contiguous.  `src` may be
+// device memory or page-locked host memory (read in place over the bus).
+template <typename VecT>
+__global__ void __launch_bounds__(256)
+gather_rows_kernel(const VecT* __restrict__ src, i64 chunks_per_row, i64 src_rows,
+                   const i64* __restrict__ idx, i64 n, VecT* __restrict__ out, int* err) {
+  const i64 total = n * chunks_per_row;
+  for (i64 g = (i64)blockIdx.x * blockDim.x + threadIdx.x; g < total;
+       g += (i64)gridDim.x * blockDim.x) {
+    const i64 i = g / chunks_per_row, c = g - i * chunks_per_row;
+    const i64 r = __ldg(idx + i);
+    if (r < 0 || r >= src_rows) { raise(err, ERRBIT_BAD_INPUT); continue; }
+    out[g] = __ldg(src + r * chunks_per_row + c);
+  }
+}
+
 // out[e] = segment (column) that owns position e of a CSC/CSR offset array
 __global__ void expand_indptr_kernel(const i64* __restrict__ indptr, i64 nseg, i64 nnz,
                                      i64* __restrict__ out) {
@@ -202,6 +220,33 @@ extern "C" int gsb_gather_i64(const int64_t* src, const int64_t* idx, int64_t n,
   LaunchScope ls(KID_GATHER, (cudaStream_t)cuda_stream);
   gather_i64_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)src, (const i64*)idx, n, (i64*)out);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+template <typename VecT>
+static void launch_gather_rows(const void* src, i64 row_bytes, i64 src_rows, const i64* idx, i64 n,
+                               void* out, int* d_err, cudaStream_t st) {
+  const i64 cpr = row_bytes / (i64)sizeof(VecT);
+  i64 blocks = (n * cpr + 255) / 256;
+  if (blocks > 148 * 32) blocks = 148 * 32;
+  gather_rows_kernel<VecT><<<(int)blocks, 256, 0, st>>>((const VecT*)src, cpr, src_rows, idx, n,
+                                                        (VecT*)out, d_err);
+}
+
+extern "C" int gsb_gather_rows(const void* src, int64_t row_bytes, int64_t src_rows,
+                               const int64_t* idx, int64_t n, void* out, int* d_err,
+                               void* cuda_stream) {
+  if (n == 0 || row_bytes == 0) return GSB_OK;
+  if (!src || !idx || !out || n < 0 || row_bytes < 0 || src_rows < 0) return GSB_ERR_INVALID;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  const uintptr_t align = (uintptr_t)src | (uintptr_t)out | (uintptr_t)row_bytes;
+  LaunchScope ls(KID_GATHER, st);
+  if ((align & 15) == 0) launch_gather_rows<uint4>(src, row_bytes, src_rows, (const i64*)idx, n, out, d_err, st);
+  else if ((align & 7) == 0) launch_gather_rows<uint2>(src, row_bytes, src_rows, (const i64*)idx, n, out, d_err, st);
+  else if ((align & 3) == 0) launch_gather_rows<u32>(src, row_bytes, src_rows, (const i64*)idx, n, out, d_err, st);
+  else if ((align & 1) == 0) launch_gather_rows<unsigned short>(src, row_bytes, src_rows, (const i64*)idx, n, out, d_err, st);
+  else launch_gather_rows<unsigned char>(src, row_bytes, src_rows, (const i64*)idx, n, out, d_err, st);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

@@ -1,4 +1,5 @@
 #include "graph.h"
+#include "ops.h"
 
 #include <c10/cuda/CUDAGuard.h>
 #include <c10/cuda/CUDAStream.h>
@@ -38,15 +39,33 @@ void CheckIds(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
 
+// The device a graph tensor is processed on: its own GPU, or -- for a graph kept
+// in page-locked host memory, which the kernels read in place (src/graph_ops.cc:67,
+// 159,192 and src/cuda/slicing.cu:128-130 in gSampler) -- the current GPU.
+torch::Device ComputeDevice(const torch::Tensor& t) {
+  if (t.is_cuda()) return t.device();
+  TORCH_CHECK(t.is_pinned(), "graph tensors must live on a GPU or in pinned host memory");
+  return torch::Device(torch::kCUDA, c10::cuda::current_device());
+}
+
+static void CheckGraphIndptr(const torch::Tensor& t, const char* name) {
+  TORCH_CHECK(t.defined(), name, " is undefined");
+  TORCH_CHECK(t.is_cuda() || t.is_pinned(), name,
+              " must be a CUDA tensor or a pinned host tensor (this library has no CPU path)");
+  TORCH_CHECK(t.scalar_type() == torch::kInt64, name, " must be int64");
+  TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
+}
+
 static int IndicesDtype(const torch::Tensor& indices) {
-  TORCH_CHECK(indices.is_cuda() && indices.is_contiguous(), "indices must be contiguous CUDA");
+  TORCH_CHECK((indices.is_cuda() || indices.is_pinned()) && indices.is_contiguous(),
+              "indices must be contiguous, on a GPU or in pinned host memory");
   if (indices.scalar_type() == torch::kInt64) return GSB_I64;
   if (indices.scalar_type() == torch::kInt32) return GSB_I32;
   TORCH_CHECK(false, "indices must be int32 or int64");
 }
 
 static torch::TensorOptions I64(const torch::Tensor& like) {
-  return torch::dtype(torch::kInt64).device(like.device());
+  return torch::dtype(torch::kInt64).device(ComputeDevice(like));
 }
 
 static const int64_t* P(const torch::Tensor& t) { return t.data_ptr<int64_t>(); }
@@ -65,13 +84,13 @@ static torch::Tensor AsI64(const torch::Tensor& t) {
 
 // ------------------------------------------------------------------ loaders
 void Graph::LoadCSC(torch::Tensor indptr, torch::Tensor indices) {
-  CheckIds(indptr, "indptr");
+  CheckGraphIndptr(indptr, "indptr");
   IndicesDtype(indices);
   csc_ = std::make_shared<Compressed>(Compressed{indptr, indices, c10::nullopt});
   num_edges_ = indices.numel();
 }
 void Graph::LoadCSR(torch::Tensor indptr, torch::Tensor indices) {
-  CheckIds(indptr, "indptr");
+  CheckGraphIndptr(indptr, "indptr");
   IndicesDtype(indices);
   csr_ = std::make_shared<Compressed>(Compressed{indptr, indices, c10::nullopt});
   num_edges_ = indices.numel();
@@ -155,15 +174,16 @@ torch::Tensor Graph::GetCSREids() {
 torch::Tensor Graph::MapThroughEids(const c10::optional<torch::Tensor>& e_ids,
                                     torch::Tensor select) {
   // src/graph.cc:169-176
-  if (e_ids.has_value()) return e_ids.value().index_select(0, select);
-  return select;
+  if (!e_ids.has_value()) return select;
+  if (e_ids.value().is_pinned()) return GatherRows(e_ids.value(), select);  // read in place
+  return e_ids.value().index_select(0, select);
 }
 
 // ------------------------------------------------------------------ kernels glue
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SampleCompressed(
     const Compressed& src, const c10::optional<torch::Tensor>& seeds, int64_t fanout, bool replace,
     const c10::optional<torch::Tensor>& probs, int64_t num_segments) {
-  c10::cuda::CUDAGuard guard(src.indptr.device());
+  c10::cuda::CUDAGuard guard(ComputeDevice(src.indptr));
   TORCH_CHECK(fanout >= 1, "fanout must be positive");
   if (seeds.has_value()) CheckIds(seeds.value(), "seeds");
   const int64_t S = seeds.has_value() ? seeds.value().numel() : num_segments;
@@ -180,7 +200,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sa
     TORCH_CHECK(pr.is_cuda() && pr.scalar_type() == torch::kFloat32 && pr.is_contiguous() &&
                     pr.numel() == src.indices.numel(),
                 "edge_probs must be a contiguous float32 CUDA tensor with one entry per edge");
-    auto ws = NewWorkspace(gsb_sample_cols_probs_workspace_bytes(S, fanout), src.indptr.device());
+    auto ws = NewWorkspace(gsb_sample_cols_probs_workspace_bytes(S, fanout), ComputeDevice(src.indptr));
     CheckStatus(gsb_sample_cols_probs(
                     P(src.indptr), src.indices.data_ptr(), IndicesDtype(src.indices),
                     pr.data_ptr<float>(), seeds.has_value() ? P(seeds.value()) : nullptr, S, nullptr,
@@ -189,7 +209,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sa
                     (int*)(PM(scal) + 1), CurrentStream()),
                 "sample_cols_probs");
   } else {
-    auto ws = NewWorkspace(gsb_sample_cols_workspace_bytes(S, fanout), src.indptr.device());
+    auto ws = NewWorkspace(gsb_sample_cols_workspace_bytes(S, fanout), ComputeDevice(src.indptr));
     CheckStatus(gsb_sample_cols(P(src.indptr), src.indices.data_ptr(), IndicesDtype(src.indices),
                                 seeds.has_value() ? P(seeds.value()) : nullptr, S, nullptr, fanout,
                                 replace, seed_, stream, PM(sub_indptr), PM(rows), PM(cols), PM(sel),
@@ -206,7 +226,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sa
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceCompressed(
     const Compressed& src, torch::Tensor seeds, const c10::optional<torch::Tensor>& bptr,
     int64_t encoding_size) {
-  c10::cuda::CUDAGuard guard(src.indptr.device());
+  c10::cuda::CUDAGuard guard(ComputeDevice(src.indptr));
   CheckIds(seeds, "seeds");
   const int64_t S = seeds.numel();
   auto opt = I64(src.indptr);

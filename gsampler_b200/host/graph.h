@@ -182,5 +182,6 @@ void CheckDeviceError(int err, const char* what);
 torch::Tensor NewWorkspace(size_t bytes, const torch::Device& dev);
 void* CurrentStream();
 void CheckIds(const torch::Tensor& t, const char* name);
+torch::Device ComputeDevice(const torch::Tensor& t);
 
 }  // namespace gsb_host

@@ -9,6 +9,8 @@
 #include <c10/cuda/CUDAFunctions.h>
 
 #include <atomic>
+#include <map>
+#include <mutex>
 
 namespace gsb_host {
 
@@ -93,7 +95,7 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
 
 static int64_t* PM(torch::Tensor& t) { return t.data_ptr<int64_t>(); }
 static torch::TensorOptions I64(const torch::Tensor& like) {
-  return torch::dtype(torch::kInt64).device(like.device());
+  return torch::dtype(torch::kInt64).device(ComputeDevice(like));
 }
 static int IdxDtype(const torch::Tensor& t) {
   TORCH_CHECK(t.scalar_type() == torch::kInt32 || t.scalar_type() == torch::kInt64,
@@ -104,7 +106,7 @@ static int IdxDtype(const torch::Tensor& t) {
 // ------------------------------------------------------------------ slicing across / on COO
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceAcross(
     const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound) {
-  c10::cuda::CUDAGuard guard(src.indptr.device());
+  c10::cuda::CUDAGuard guard(ComputeDevice(src.indptr));
   CheckIds(ids, "ids");
   auto opt = I64(src.indptr);
   auto sub_indptr = torch::empty({nseg + 1}, opt);
@@ -439,8 +441,48 @@ Graph::GraphAndIndex Graph::BatchRowSlicing(torch::Tensor row_ids, torch::Tensor
   return r;
 }
 
-Graph::GraphAndIndex Graph::BatchColRowSlcing(torch::Tensor, torch::Tensor, torch::Tensor,
-                                              torch::Tensor) { GSB_NOT_YET("BatchColRowSlcing"); }
+// src/batch_graph.cc:107-141.  The returned index holds positions in THIS graph's
+// edge order (mapped through e_ids when present), which is what the callers
+// index the parent's edge data with (python/gs/matrix_api/batch_matrix.py:72-80).
+Graph::GraphAndIndex Graph::BatchColRowSlcing(torch::Tensor col, torch::Tensor col_bptr,
+                                              torch::Tensor row, torch::Tensor row_bptr) {
+  CreateSparseFormat(kCSC);
+  CheckIds(col, "col"); CheckIds(col_bptr, "col_bptr"); CheckIds(row, "row"); CheckIds(row_bptr, "row_bptr");
+  TORCH_CHECK(col_bptr.numel() == row_bptr.numel() && col_bptr.numel() >= 2,
+              "BatchColRowSlcing: col_bptr and row_bptr must have the same length >= 2");
+  c10::cuda::CUDAGuard guard(ComputeDevice(csc_->indptr));
+  const int64_t S = col.numel(), R = row.numel(), B = col_bptr.numel() - 1;
+  auto opt = I64(csc_->indptr);
+  auto sub_indptr = torch::empty({S + 1}, opt);
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(col.device()));
+  auto ws = NewWorkspace(gsb_slice_cols_rows_workspace_bytes(S, R, B), col.device());
+  CheckStatus(gsb_slice_cols_rows_count(P(csc_->indptr), csc_->indices.data_ptr(),
+                                        IdxDtype(csc_->indices), num_cols_, P(col), P(col_bptr), S,
+                                        P(row), P(row_bptr), R, B, PM(sub_indptr), ws.data_ptr(),
+                                        (size_t)ws.numel(), err.data_ptr<int>(), CurrentStream()),
+              "slice_cols_rows_count");
+  const int64_t E = sub_indptr.narrow(0, S, 1).item<int64_t>();
+  CheckDeviceError(err.item<int>(), "slice_cols_rows_count");
+  auto ids = torch::empty({E}, opt), seg = torch::empty({E}, opt), sel = torch::empty({E}, opt);
+  if (E > 0)
+    CheckStatus(gsb_slice_cols_rows_fill(P(csc_->indptr), csc_->indices.data_ptr(),
+                                         IdxDtype(csc_->indices), num_cols_, P(col), P(col_bptr), S,
+                                         P(row_bptr), R, B, P(sub_indptr), PM(ids), PM(seg), PM(sel),
+                                         ws.data_ptr(), CurrentStream()),
+                "slice_cols_rows_fill");
+  auto g = Derive(R, S);
+  g->csc_ = std::make_shared<Compressed>(Compressed{sub_indptr, ids, c10::nullopt});
+  g->coo_ = std::make_shared<Coordinate>(Coordinate{ids, seg, c10::nullopt, false, true});
+  g->num_edges_ = E;
+  g->col_bptr_ = col_bptr;
+  g->row_bptr_ = row_bptr;
+  g->orig_col_ids_ = col;
+  g->orig_row_ids_ = row;
+  auto eb = torch::empty({B + 1}, I64(col_bptr));
+  CheckStatus(gsb_gather_i64(P(sub_indptr), P(col_bptr), B + 1, PM(eb), CurrentStream()), "gather");
+  g->edge_bptr_ = eb;
+  return {g, MapThroughEids(csc_->e_ids, sel)};
+}
 
 // ------------------------------------------------------------------ gs_ops
 static std::tuple<torch::Tensor, torch::Tensor> ListSampleImpl(const c10::optional<torch::Tensor>& probs,
@@ -538,6 +580,52 @@ torch::Tensor IndexSearch(torch::Tensor origin_data, torch::Tensor keys) {
   auto hit = vals.index_select(0, pos.reshape({-1})).reshape(keys.sizes()) == keys;
   return torch::where(hit, perm.index_select(0, pos.reshape({-1})).reshape(keys.sizes()),
                       torch::full_like(keys, -1));
+}
+
+// ------------------------------------------------------------------ row gather
+// One error word per device that the sync-free operators raise bits in; it is
+// read (and cleared) by CheckAsyncErrors, the way CUDA reports kernel faults
+// at the next synchronising call rather than at the launch.
+static torch::Tensor& AsyncErrorWord(const torch::Device& dev) {
+  static std::mutex mu;
+  static std::map<int, torch::Tensor> words;
+  std::lock_guard<std::mutex> lock(mu);
+  auto it = words.find(dev.index());
+  if (it == words.end())
+    it = words.emplace(dev.index(), torch::zeros({1}, torch::dtype(torch::kInt32).device(dev))).first;
+  return it->second;
+}
+
+void CheckAsyncErrors() {
+  const auto dev = CurrentCudaDevice();
+  auto& w = AsyncErrorWord(dev);
+  const int bits = w.item<int>();
+  if (bits) w.zero_();
+  CheckDeviceError(bits, "an earlier sync-free operator (row gather)");
+}
+
+// out[i, ...] = data[index[i], ...].  `data` lives on the GPU or in page-locked
+// host memory (read in place, python/gs/matrix_api/matrix.py:19-23 and
+// src/cuda/index_select_uvm.cu:22-41 in gSampler); no synchronisation.
+torch::Tensor GatherRows(torch::Tensor data, torch::Tensor index) {
+  CheckIds(index, "index");
+  TORCH_CHECK(data.defined() && data.dim() >= 1 && data.is_contiguous(),
+              "GatherRows: data must be a contiguous tensor with at least one dimension");
+  TORCH_CHECK(data.is_cuda() ? data.device() == index.device() : data.is_pinned(),
+              "GatherRows: data must be on the index's GPU or in pinned host memory");
+  TORCH_CHECK(index.dim() == 1, "GatherRows: index must be one-dimensional");
+  c10::cuda::CUDAGuard guard(index.device());
+  auto sizes = data.sizes().vec();
+  const int64_t src_rows = sizes[0];
+  sizes[0] = index.numel();
+  auto out = torch::empty(sizes, data.options().device(index.device()).pinned_memory(false));
+  const int64_t row_bytes = src_rows == 0 ? 0 : data.nbytes() / src_rows;
+  TORCH_CHECK(src_rows > 0 || index.numel() == 0, "GatherRows: data has no rows");
+  CheckStatus(gsb_gather_rows(data.data_ptr(), row_bytes, src_rows, index.data_ptr<int64_t>(),
+                              index.numel(), out.data_ptr(), AsyncErrorWord(index.device()).data_ptr<int>(),
+                              CurrentStream()),
+              "gather_rows");
+  return out;
 }
 
 static std::atomic<uint64_t> g_list_seed{7777};

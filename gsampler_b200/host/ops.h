@@ -18,6 +18,10 @@ std::tuple<torch::Tensor, torch::Tensor> BatchListSampling(int64_t num_picks, bo
 std::vector<torch::Tensor> SplitByOffset(torch::Tensor data, torch::Tensor offset);
 std::vector<torch::Tensor> SplitIndptrByOffset(torch::Tensor indptr, torch::Tensor offsets);
 torch::Tensor IndexSearch(torch::Tensor origin_data, torch::Tensor keys);
+// row gather from GPU or pinned host memory (src/cuda/index_select_uvm.cu:22-49); sync-free:
+// a bad index raises a bit that CheckAsyncErrors reports
+torch::Tensor GatherRows(torch::Tensor data, torch::Tensor index);
+void CheckAsyncErrors();
 // random stream of the list-sampling operators (the reference hard-codes 7777,
 // src/cuda/list_sampling.cu:36); a per-process call counter advances the stream
 uint64_t ListSamplingSeed();

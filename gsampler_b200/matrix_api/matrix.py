@@ -23,6 +23,10 @@ from ..utils import Block, create_block_from_coo
 
 
 def data_index(data, index):
+    """``data[index]``; data kept in pinned host memory is gathered in place by a kernel
+    (gSampler: python/gs/matrix_api/matrix.py:19-23)."""
+    if not data.is_cuda and data.is_pinned():
+        return torch.ops.gs_ops._CAPI_GatherRows(data, index)
     return data[index]
 
 

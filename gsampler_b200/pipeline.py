@@ -72,7 +72,7 @@ class GraphSAGESampler(object):
     """Pre-allocated L-layer sampler over a CSC graph resident on one GPU.
 
     indptr            int64 [N+1] CUDA tensor
-    indices           int32 or int64 [nnz] CUDA tensor
+    indices           int32 or int64 [nnz] CUDA tensor (or both tensors in pinned host memory)
     num_batches       minibatches per super-batch (B)
     max_seeds         upper bound of the number of seeds in one super-batch
     fanouts           per-layer fanout
@@ -86,12 +86,14 @@ class GraphSAGESampler(object):
     def __init__(self, indptr: torch.Tensor, indices: torch.Tensor, num_batches: int,
                  max_seeds: int, fanouts: Sequence[int], seed: int = 7777,
                  capacities: Optional[Sequence] = None, num_nodes: Optional[int] = None):
-        if not (indptr.is_cuda and indices.is_cuda):
-            raise ValueError("the graph must live on a CUDA device (there is no CPU path)")
+        on_gpu = indptr.is_cuda and indices.is_cuda
+        if not on_gpu and not (indptr.is_pinned() and indices.is_pinned()):
+            raise ValueError("the graph must live on a CUDA device or in pinned host memory, which "
+                             "the kernels read in place (there is no CPU path)")
         if indptr.dtype != torch.int64 or indices.dtype not in (torch.int32, torch.int64):
             raise ValueError("indptr must be int64, indices int32 or int64")
         self.indptr, self.indices = indptr.contiguous(), indices.contiguous()
-        self.device = indptr.device
+        self.device = indptr.device if on_gpu else torch.device("cuda", torch.cuda.current_device())
         self.B, self.L = int(num_batches), len(fanouts)
         self.fanouts = [int(k) for k in fanouts]
         self.seed = int(seed)

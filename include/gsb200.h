@@ -195,6 +195,17 @@ GSB_API int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr, in
 GSB_API int gsb_gather_i64(const int64_t* src, const int64_t* idx, int64_t n, int64_t* out,
                            void* cuda_stream);
 
+/* Row gather for node / edge data: row i of `out` = row idx[i] of `src`, rows
+ * of row_bytes bytes, contiguous.  `src` is device memory or page-locked host
+ * memory (read in place); `out` is device memory.  An index outside
+ * [0, src_rows) sets GSB_ERRBIT_BAD_INPUT and leaves its output row untouched.
+ * Replaces IndexSelectCPUFromGPU (src/cuda/index_select_uvm.cu:8-49) and the
+ * feature / edge-data gathers the callers issue right after sampling
+ * (python/gs/matrix_api/matrix.py:19-23; examples/graphsage/graphsage_e2e.py:111-118). */
+GSB_API int gsb_gather_rows(const void* src, int64_t row_bytes, int64_t src_rows,
+                            const int64_t* idx, int64_t n, void* out, int* d_err,
+                            void* cuda_stream);
+
 /* ------------------------------------------------------------------ format conversion
  * CSC -> COO column expansion: out[e] = column owning edge e.  Replaces
  * CSC2COOCUDA (src/cuda/format_transform.cu:23-46). */
@@ -224,6 +235,27 @@ GSB_API int gsb_slice_across_fill(const int64_t* indptr, const void* indices, in
                                   int64_t nseg, int64_t id_bound, const int64_t* out_indptr,
                                   int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
                                   const void* workspace, void* cuda_stream);
+/* Column AND row selection per minibatch (induced sub-matrices): minibatch b
+ * keeps, of the columns cols[col_ptr[b]..col_ptr[b+1]), the entries whose row
+ * id occurs in rows[row_ptr[b]..row_ptr[b+1]).  out_ids = position of the row
+ * id in `rows` (counted from the start of the whole array; the smallest for a
+ * repeated id), out_seg = column slot, out_sel = position of the entry in the
+ * operand.  Same count / fill protocol as above (S = col_ptr[B], R =
+ * row_ptr[B]).  Replaces BatchCSCColRowSlicingCUDA and CSCColRowSlicingCUDA
+ * (src/cuda/fusion/column_row_slicing.cu:154-362), reached from
+ * Graph::BatchColRowSlcing (src/batch_graph.cc:107-141). */
+GSB_API size_t gsb_slice_cols_rows_workspace_bytes(int64_t S, int64_t R, int64_t B);
+GSB_API int gsb_slice_cols_rows_count(const int64_t* indptr, const void* indices,
+                                      int indices_dtype, int64_t num_cols, const int64_t* cols,
+                                      const int64_t* col_ptr, int64_t S, const int64_t* rows,
+                                      const int64_t* row_ptr, int64_t R, int64_t B,
+                                      int64_t* out_indptr, void* workspace, size_t workspace_bytes,
+                                      int* d_err, void* cuda_stream);
+GSB_API int gsb_slice_cols_rows_fill(const int64_t* indptr, const void* indices, int indices_dtype,
+                                     int64_t num_cols, const int64_t* cols, const int64_t* col_ptr,
+                                     int64_t S, const int64_t* row_ptr, int64_t R, int64_t B,
+                                     const int64_t* out_indptr, int64_t* out_ids, int64_t* out_seg,
+                                     int64_t* out_sel, const void* workspace, void* cuda_stream);
 /* The same filter on a COO: keep edge e iff key[e] is in `ids`; out_key = the
  * position in `ids`, out_other = other[e], out_sel = e, in edge order; the
  * count goes to *d_count (device).  Outputs need capacity nnz.  Replaces

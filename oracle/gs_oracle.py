@@ -219,6 +219,35 @@ def slice_rows(indptr, indices, row_ids):
     return oip, oi, os_
 
 
+def batch_slice_cols_rows(indptr, indices, cols, col_ptr, rows, row_ptr):
+    """Per-minibatch column + row selection, BatchCSCColRowSlicingCUDA
+    (src/cuda/fusion/column_row_slicing.cu:154-362; hash insert :283-292, query kernel
+    :219-264): minibatch b keeps, of its columns, the entries whose row id is in its own row
+    list; a kept entry is renamed to the position of its row id in the whole ``rows`` array
+    (:289, the value stored is ``ele``).  Returns (out_indptr, out_indices, position of the
+    entry in the operand).  Row ids are distinct within a minibatch in every caller; for a
+    repeated id this restatement takes the smallest position."""
+    indptr, indices = _i64(indptr), _i64(indices)
+    cols, col_ptr, rows, row_ptr = _i64(cols), _i64(col_ptr), _i64(rows), _i64(row_ptr)
+    oip = np.zeros(cols.size + 1, np.int64)
+    oi, osel = [], []
+    for b in range(col_ptr.size - 1):
+        pos = {}
+        for i in range(int(row_ptr[b]), int(row_ptr[b + 1])):
+            pos.setdefault(int(rows[i]), i)
+        for s in range(int(col_ptr[b]), int(col_ptr[b + 1])):
+            c = int(cols[s])
+            n = 0
+            for e in range(int(indptr[c]), int(indptr[c + 1])):
+                p = pos.get(int(indices[e]))
+                if p is not None:
+                    oi.append(p)
+                    osel.append(e)
+                    n += 1
+            oip[s + 1] = n
+    return np.cumsum(oip), np.asarray(oi, np.int64), np.asarray(osel, np.int64)
+
+
 # --------------------------------------------------------------------------- SpMM / SDDMM
 def edge_sum(row, col, e, target, nout, square=False):
     row, col, e = _i64(row), _i64(col), _f32(e)

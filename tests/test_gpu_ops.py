@@ -63,6 +63,48 @@ def test_row_slicing_on_csc(gsb, oracle, graph, idx_dtype):
     assert sel.numel() == 0 and not host(sub._CAPI_GetCSCIndptr()).any()
 
 
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_batch_col_row_slicing(gsb, oracle, graph, idx_dtype):
+    """Induced sub-matrices per minibatch (ShaDow-style): _CAPI_BatchColRowSlcing."""
+    indptr, indices = graph
+    rng = np.random.default_rng(4)
+    B = 5
+    ncol = np.array([200, 0, 333, 1, 150])
+    nrow = np.array([900, 50, 0, 2999, 400])
+    cols = np.concatenate([rng.integers(0, 3000, n) for n in ncol]).astype(np.int64)
+    rows = np.concatenate([rng.permutation(3000)[:n] for n in nrow]).astype(np.int64)
+    col_ptr = np.concatenate([[0], np.cumsum(ncol)]).astype(np.int64)
+    row_ptr = np.concatenate([[0], np.cumsum(nrow)]).astype(np.int64)
+    A = new_graph(gsb, indptr, indices, idx_dtype=idx_dtype)
+    sub, sel = A._CAPI_BatchColRowSlcing(cuda(cols), cuda(col_ptr), cuda(rows), cuda(row_ptr))
+    eip, eids, esel = oracle.batch_slice_cols_rows(indptr, indices, cols, col_ptr, rows, row_ptr)
+    assert esel.size > 100
+    assert np.array_equal(host(sub._CAPI_GetCSCIndptr()), eip)
+    assert np.array_equal(host(sub._CAPI_GetCSCIndices()), eids)
+    assert np.array_equal(host(sel), esel)
+    assert np.array_equal(host(sub._CAPI_GetCOORows()), eids)
+    assert np.array_equal(host(sub._CAPI_GetCOOCols()), oracle.csc2coo(eip))
+    assert np.array_equal(host(sub._CAPI_GetEdgeBptr()), eip[col_ptr])
+    assert (sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols(), sub._CAPI_GetNumEdges()) == (
+        rows.size, cols.size, eids.size)
+    # every kept entry: its row id is rows[new id] and belongs to the entry's own minibatch
+    assert np.array_equal(rows[eids], indices[esel])
+    b_of_edge = np.searchsorted(col_ptr, oracle.csc2coo(eip), side="right") - 1
+    assert np.all((eids >= row_ptr[b_of_edge]) & (eids < row_ptr[b_of_edge + 1]))
+    # through the BatchMatrix surface, with edge data carried along
+    m = gsb.Matrix(A)
+    w = torch.arange(indices.size, dtype=torch.float32).cuda()
+    m.edata["w"] = w
+    bm = gsb.BatchMatrix()
+    bm.load_from_matrix(m, False)
+    subm = bm[cuda(rows)::cuda(row_ptr), cuda(cols)::cuda(col_ptr)]
+    assert np.array_equal(host(subm.edata["w"]), esel.astype(np.float32))
+    # no rows at all
+    sub, sel = A._CAPI_BatchColRowSlcing(cuda(cols), cuda(col_ptr), cuda(np.empty(0, np.int64)),
+                                         cuda(np.zeros(B + 1, np.int64)))
+    assert sel.numel() == 0 and not host(sub._CAPI_GetCSCIndptr()).any()
+
+
 def test_slicing_on_coo(gsb, oracle, graph):
     indptr, indices = graph
     col = oracle.csc2coo(indptr)
@@ -283,3 +325,78 @@ def test_node2vec_sampler_api(gsb, oracle, graph):
     paths = fn(m, cuda(seeds), 80, 2.0, 0.5)
     srt = oracle.sort_indices(indptr, indices)
     assert np.array_equal(host(paths).reshape(-1), oracle.node2vec_spec(indptr, srt, seeds, 80, 2.0, 0.5, 5, 0))
+
+
+@pytest.mark.parametrize("dtype,width", [(torch.float32, 100), (torch.float32, 128), (torch.float16, 7),
+                                         (torch.int64, 1), (torch.uint8, 3), (torch.float32, 0)])
+def test_gather_rows_device_and_pinned(gsb, dtype, width):
+    """Feature fetch: rows gathered from GPU memory and, in place, from pinned host memory."""
+    g = torch.Generator()
+    g.manual_seed(3)
+    n = 5000
+    shape = (n,) if width == 0 else (n, width)
+    data = (torch.rand(shape, generator=g) * 200).to(dtype)
+    idx = torch.randint(0, n, (12345,), generator=g)
+    want = data[idx]
+    got = gsb.gather_rows(data.cuda(), idx.cuda())
+    assert got.dtype == dtype and got.shape == want.shape and torch.equal(got.cpu(), want)
+    got = gsb.gather_rows(data.pin_memory(), idx.cuda())
+    assert got.is_cuda and torch.equal(got.cpu(), want)
+    assert gsb.gather_rows(data.cuda(), idx[:0].cuda()).shape[0] == 0
+    gsb.check_async_errors()
+    with pytest.raises(RuntimeError):
+        gsb.gather_rows(data, idx.cuda())          # pageable host memory is rejected
+
+
+def test_gather_rows_reports_bad_index(gsb):
+    data = torch.arange(40, dtype=torch.float32).view(10, 4).cuda()
+    out = gsb.gather_rows(data, cuda(np.array([1, 10, 3, -1])))
+    assert torch.equal(out[0].cpu(), data[1].cpu()) and torch.equal(out[2].cpu(), data[3].cpu())
+    with pytest.raises(RuntimeError):
+        gsb.check_async_errors()
+    gsb.check_async_errors()                        # the word is cleared by the report
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_graph_in_pinned_host_memory(gsb, oracle, graph, idx_dtype):
+    """A CSC kept in pinned host memory is sliced / sampled in place, with the same results as
+    the GPU-resident graph (same seed, same streams)."""
+    indptr, indices = graph
+    n = indptr.size - 1
+    rng = np.random.default_rng(12)
+    seeds = cuda(rng.integers(0, n, 800))
+    ptr = cuda(np.array([0, 300, 300, 800]))
+
+    def make(pinned):
+        ip, ix = torch.from_numpy(indptr), torch.from_numpy(indices).to(idx_dtype)
+        g = gsb.Graph(n, n)
+        if pinned:
+            g._CAPI_LoadCSC(ip.pin_memory(), ix.pin_memory())
+        else:
+            g._CAPI_LoadCSC(ip.cuda(), ix.cuda())
+        g._CAPI_SetSeed(5)
+        return g
+
+    dev, pin = make(False), make(True)
+    for fn in (lambda g: g._CAPI_Slicing(seeds, 1, gsb._CSC, gsb._CSC + gsb._COO),
+               lambda g: g._CAPI_SlicingSampling(1, seeds, 7, False, gsb._CSC, gsb._CSC + gsb._COO),
+               lambda g: g._CAPI_BatchFusedSlicingSampling(seeds, ptr, 4, True)):
+        (ga, sa), (gb, sb) = fn(dev), fn(pin)
+        assert sb.is_cuda and torch.equal(sa, sb)
+        assert torch.equal(ga._CAPI_GetCSCIndptr(), gb._CAPI_GetCSCIndptr())
+        assert torch.equal(ga._CAPI_GetCSCIndices(), gb._CAPI_GetCSCIndices())
+        assert torch.equal(ga._CAPI_GetCOOCols(), gb._CAPI_GetCOOCols())
+    la = dev._CAPI_BatchGraphSAGE(seeds, ptr, [5, 3])
+    lb = pin._CAPI_BatchGraphSAGE(seeds, ptr, [5, 3])
+    assert len(la) == len(lb) and all(torch.equal(a.cpu(), b.cpu()) for a, b in zip(la, lb))
+    # pre-allocated pipeline on the pinned graph
+    smp = gsb.GraphSAGESampler(torch.from_numpy(indptr).pin_memory(),
+                               torch.from_numpy(indices).to(idx_dtype).pin_memory(), 3, 800, [5, 3], seed=5)
+    smp.sample(seeds, ptr)
+    counts = smp.counts()
+    ref = oracle.graphsage_batch(indptr, indices, host(seeds), host(ptr), [5, 3], seed=5)
+    for l in range(2):
+        S, E, U = counts[l]
+        assert (S, E, U) == (ref[l]["seeds"].size, ref[l]["rows"].size, ref[l]["unique"].size)
+        assert np.array_equal(host(smp.layers[l]["unique"][:U]), ref[l]["unique"])
+        assert np.array_equal(host(smp.layers[l]["block_row"][:E]), ref[l]["block_row"])

@@ -243,3 +243,26 @@ def test_graphsage_pipeline_shapes(oracle):
             e0, e1 = L["edge_ptr"][b], L["edge_ptr"][b + 1]
             assert np.array_equal(uq[L["block_row"][e0:e1]], L["rows"][e0:e1])
             assert np.array_equal(uq[L["block_col"][e0:e1]], L["seeds"][L["cols"][e0:e1]])
+
+
+def test_batch_slice_cols_rows_matches_composition(oracle):
+    """The fused column+row selection equals column slicing followed by a row filter with the
+    minibatch's own row list (the definition it is used for in batch_matrix.py:57-80)."""
+    rng = np.random.default_rng(8)
+    n = 400
+    deg = rng.poisson(6, n)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = rng.integers(0, n, indptr[-1]).astype(np.int64)
+    col_ptr = np.array([0, 30, 30, 75], np.int64)
+    row_ptr = np.array([0, 120, 200, 380], np.int64)
+    cols = rng.integers(0, n, 75).astype(np.int64)
+    rows = np.concatenate([rng.permutation(n)[:120], rng.permutation(n)[:80], rng.permutation(n)[:180]]).astype(np.int64)
+    oip, oi, osel = oracle.batch_slice_cols_rows(indptr, indices, cols, col_ptr, rows, row_ptr)
+    assert oip[-1] == oi.size == osel.size
+    for b in range(3):
+        sip, sidx, _, ssel = oracle.slice_cols(indptr, indices, cols[col_ptr[b]:col_ptr[b + 1]])
+        keep = np.isin(sidx, rows[row_ptr[b]:row_ptr[b + 1]])
+        lo, hi = oip[col_ptr[b]], oip[col_ptr[b + 1]]
+        assert np.array_equal(osel[lo:hi], ssel[keep])
+        assert np.array_equal(rows[oi[lo:hi]], sidx[keep])
+        assert np.all((oi[lo:hi] >= row_ptr[b]) & (oi[lo:hi] < row_ptr[b + 1]))
