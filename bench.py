@@ -377,11 +377,11 @@ def main():
         w_idx = 4 if cfg["index_dtype"] == "int32" else 8
         per_launch = {
             "sample_tile": (8 * S_l + 16 * S_l + w_idx * E_l + 8 * (S_l + 1) + 24 * E_l).mean(),
-            "relabel_insert": (8 * (S_l + E_l)).mean(),
-            "relabel_lookup": (8 * (S_l + E_l)).mean(),
+            "relabel_pcount": (8 * (S_l + E_l)).mean(),
+            "relabel_scatter": (8 * (S_l + E_l)).mean(),
+            "relabel_dedupe": (8 * (S_l + E_l)).mean(),
             "relabel_rank": (8 * (S_l + E_l) + 8 * U_l).mean(),
             "relabel_emit": (24 * E_l).mean(),
-            "relabel_clear": 0.0,
         }.get(dname, 0.0)
         dur_s = dms / dcnt / 1e3
         achieved = per_launch / dur_s / 1e9 if dur_s > 0 else 0.0

@@ -22,9 +22,9 @@ __global__ void record_counts_kernel(const i64* seeds_ptr, const i64* unique_ptr
 // ---------------------------------------------------------------- launch accounting
 static const char* const kKernelNames[KID_NUM] = {
     "sample_tile", "sample_probs", "count", "slice_fill", "gather", "expand_indptr",
-    "indptr_from_sorted", "relabel_setup", "relabel_clear", "relabel_insert", "relabel_rank",
-    "relabel_emit", "record_counts", "slice_rows", "edge_sum", "edge_op", "list_sample", "walk",
-    "sort", "relabel_lookup", "relabel_tiles", "misc"};
+    "indptr_from_sorted", "relabel_setup", "relabel_pcount", "relabel_pscan", "relabel_scatter",
+    "relabel_dedupe", "relabel_count", "relabel_tiles", "relabel_rank", "relabel_emit",
+    "record_counts", "slice_rows", "edge_sum", "edge_op", "list_sample", "walk", "sort", "misc"};
 
 struct TimedLaunch {
   int id, tag;

@@ -202,9 +202,9 @@ inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 // (gsb_timing_enable), brackets it with CUDA events on the launching stream.
 enum KernelId {
   KID_SAMPLE = 0, KID_SAMPLE_PROBS, KID_COUNT, KID_SLICE_FILL, KID_GATHER, KID_EXPAND,
-  KID_INDPTR_SORTED, KID_RL_SETUP, KID_RL_CLEAR, KID_RL_INSERT, KID_RL_SCAN, KID_RL_EDGES,
-  KID_COUNTS, KID_SLICE_ROWS, KID_EDGE_SUM, KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT,
-  KID_RL_LOOKUP, KID_RL_TILES, KID_MISC, KID_NUM
+  KID_INDPTR_SORTED, KID_RL_SETUP, KID_RL_PCOUNT, KID_RL_PSCAN, KID_RL_SCATTER, KID_RL_DEDUPE,
+  KID_RL_COUNT, KID_RL_TILES, KID_RL_SCAN, KID_RL_EDGES, KID_COUNTS, KID_SLICE_ROWS, KID_EDGE_SUM,
+  KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT, KID_MISC, KID_NUM
 };
 struct LaunchScope {
   LaunchScope(int id, cudaStream_t st);

@@ -1,30 +1,35 @@
 // Per-minibatch first-occurrence unique + relabel (block construction).
 //
-// Every minibatch gets its own open-addressing table; the tables sit back to
-// back in the workspace and are sized from the minibatch's item count (items =
-// its seeds followed by its sampled row ids).  A slot is ONE 64-bit word:
-// key in the high half, the smallest item index carrying that key in the low
-// half (atomicMin on the whole word; the key half is equal for all contenders,
-// so the minimum is the minimum index).  The item whose own index equals that
-// minimum is the first occurrence of its id.
+// Items of a minibatch = its seeds followed by its sampled row ids; the item
+// with the smallest index among those carrying an id is the id's first
+// occurrence, and `unique` lists the first occurrences in item order.
 //
-// Passes (each a plain data-parallel kernel; no CTA ever waits for another):
-//   insert : claim / lower the slot of every item                (random RMW)
-//   lookup : min_idx[item] = payload of the item's slot, and the number of
-//            first occurrences of every 1024-item tile           (random read)
-//   tiles  : exclusive scan of the per-tile counts               (one block)
-//   rank   : first occurrences get their position in `unique` (tile base +
-//            warp ballots), written to unique[] and rank[item]   (streaming)
-//   emit   : every edge reads rank[first item of its row id] and of its
-//            column's seed -> relabelled COO                     (streaming +
-//            one gather for ids that were seen before)
-// When the caller states a bound on the ids and B * bound 32-bit words are not
-// more memory than the hash tables would be, the tables are direct-address
-// arrays instead (word = smallest item index of that id): no probing, no key
-// compare, and the insert is a fire-and-forget atomic min.
-// The tables are written only by `insert`; nothing is finalised in place.  The
-// measured limiter of the stage is the number of random L2/DRAM transactions,
-// which this arrangement keeps at about two per item (one RMW, one read).
+// Finding the smallest index per id is a hashing problem whose cost on this
+// GPU is the number of random L2 transactions and atomics (whole-minibatch
+// tables in global memory -- open addressing or direct addressing -- measured
+// 0.6 ms for 23 M items and, worse, slowed down the kernels of the other
+// streams).  So the items are first PARTITIONED by hash into buckets of at
+// most a few thousand items, and every bucket is deduplicated by one CTA in a
+// SHARED-memory table:
+//   setup   : item / bucket geometry of every minibatch           (one block)
+//   pcount  : per-bucket item counts (shared histograms per 8192-item tile,
+//             one global atomic per tile and non-empty bucket)    (streaming)
+//   pscan   : bucket offsets                                      (one block)
+//   scatter : (id, index) pairs grouped by bucket; every tile reserves a run
+//             per bucket, its 8-byte stores meet in L2            (streaming)
+//   dedupe  : CTA per bucket: shared table id -> smallest index, then
+//             min_idx[item] for every item of the bucket; a bucket whose ids
+//             do not fit the shared table falls back to a table in global
+//             memory that the CTA owns                            (streaming
+//             read + one scattered 4-byte store per item)
+//   count   : number of first occurrences per 1024-item tile      (streaming)
+//   tiles   : exclusive scan of those counts                      (one block)
+//   rank    : first occurrences get their position in `unique`    (streaming)
+//   emit    : every edge reads rank[first item of its row id] and of its
+//             column's seed -> relabelled COO                     (streaming +
+//             one gather for ids seen before)
+// No CTA ever waits for another (a chained tile prefix inside the rank pass
+// measured 0.38 ms against 0.20 + 0.07 ms for count + tiles + rank).
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -34,13 +39,22 @@ constexpr int RL_ITEMS = 4;
 constexpr int RL_TILE = RL_THREADS * RL_ITEMS;
 constexpr u64 SLOT_EMPTY = ~0ull;
 constexpr u32 IDX_UNSET = 0xFFFFFFFFu;
+constexpr int PT_TILE = 8192;          // items per CTA tile of pcount / scatter
+constexpr int PT_THREADS = 512;
+constexpr int PT_BATCH = 8;            // loads in flight per thread
+constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch (power of two)
+constexpr int PT_BUCKET_ITEMS = 3072;  // a minibatch gets pow2ceil(items / this) buckets
+constexpr int DD_THREADS = 512;
+constexpr int DD_BATCH = 8;            // items a dedupe thread keeps in registers
+constexpr int DD_TAB = 8192;           // shared-table slots of the dedupe CTA
+constexpr u32 KEY_EMPTY = 0xFFFFFFFFu;
 
 struct RelabelHeader {
   i64 n_items;
-  i64 n_slots;
   i64 n_edges;
   i64 n_seeds;
   i64 n_tiles;
+  i64 n_buckets;
 };
 
 struct RelabelParams {
@@ -51,157 +65,106 @@ struct RelabelParams {
   const i64* edge_ptr;
   int B;
   i64 S_max, E_max;
+  u64 id_limit;       // ids must be below this (at most 2^32 - 1)
   i64* unique;
   i64 U_cap;
   i64* unique_ptr;
   i64* out_row;
   i64* out_col;
   RelabelHeader* hdr;
-  i64* item_ptr;     // [B+1] start of minibatch b in the interleaved item order
-  i64* table_ptr;    // [B+1] start of minibatch b's table
-  u32* tile_count;   // [tiles+1] first occurrences per tile, then their exclusive scan
-  u64* table;
-  u32* min_idx;      // [items] smallest item index carrying the item's id
-  u32* rank;         // [items] position in `unique`, valid for first occurrences
-  i64 slots_cap;
-  i64 tiles_cap;
-  i64 direct_bound;  // > 0: direct-address tables of this many 32-bit words per minibatch
+  i64* item_ptr;      // [B+1] start of minibatch b in the interleaved item order
+  u32* tile_count;    // [tiles+1] first occurrences per tile, then their exclusive scan
+  u32* min_idx;       // [items] smallest item index carrying the item's id
+  u32* rank;          // [items] position in `unique`, valid for first occurrences
+  i64* bucket_ptr;    // [B+1] first bucket of minibatch b
+  int* bucket_shift;  // [B] bucket of an id = hash >> shift (32: the single bucket 0)
+  u32* bucket_start;  // [buckets+1] counts, then their exclusive scan (positions in `part`)
+  u32* bucket_cursor; // [buckets] fill level during the scatter pass
+  u64* part;          // [items] id:32 | index:32, grouped by bucket
+  u64* overflow;      // global tables of buckets that overflow the shared one
+  i64 buckets_cap;
   int* err;
 };
 
-__host__ __device__ inline i64 table_slots_for(i64 items) { return items * 2 + 32; }
-
-// One block: item_ptr / table_ptr = running sums over the minibatches.
+// One block: item_ptr / bucket_ptr = running sums over the minibatches.
 __global__ void relabel_setup_kernel(const RelabelParams p) {
   __shared__ i64 s_scan[34];
-  __shared__ i64 s_carry_items, s_carry_slots;
-  if (threadIdx.x == 0) { s_carry_items = 0; s_carry_slots = 0; }
+  __shared__ i64 s_carry_items, s_carry_bk;
+  if (threadIdx.x == 0) { s_carry_items = 0; s_carry_bk = 0; }
   __syncthreads();
   for (int b0 = 0; b0 < p.B; b0 += blockDim.x) {
     const int b = b0 + threadIdx.x;
-    i64 items = 0, slots = 0;
+    i64 items = 0, nbk = 0;
+    int shift = 32;
     if (b < p.B) {
       i64 ns = p.seeds_ptr[b + 1] - p.seeds_ptr[b];
       i64 ne = p.edge_ptr[b + 1] - p.edge_ptr[b];
       if (ns < 0 || ne < 0) { raise(p.err, ERRBIT_BAD_INPUT); ns = ns < 0 ? 0 : ns; ne = ne < 0 ? 0 : ne; }
       items = ns + ne;
-      slots = table_slots_for(items);
+      const i64 need = (items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS;
+      nbk = 1;
+      while (nbk < need && nbk < PT_MAX_BUCKETS) { nbk <<= 1; --shift; }
     }
-    i64 tot_items, tot_slots;
+    i64 tot_items, tot_bk;
     i64 ei = block_exclusive_scan(items, s_scan, &tot_items);
     __syncthreads();
-    i64 es = block_exclusive_scan(slots, s_scan, &tot_slots);
+    i64 eb = block_exclusive_scan(nbk, s_scan, &tot_bk);
     if (b < p.B) {
       p.item_ptr[b] = s_carry_items + ei;
-      p.table_ptr[b] = s_carry_slots + es;
+      p.bucket_ptr[b] = s_carry_bk + eb;
+      p.bucket_shift[b] = shift;
     }
     __syncthreads();
-    if (threadIdx.x == 0) { s_carry_items += tot_items; s_carry_slots += tot_slots; }
+    if (threadIdx.x == 0) { s_carry_items += tot_items; s_carry_bk += tot_bk; }
     __syncthreads();
   }
   if (threadIdx.x == 0) {
-    i64 n_items = s_carry_items, n_slots = s_carry_slots;
-    if (p.direct_bound > 0) n_slots = (p.direct_bound * p.B + 1) / 2;  // 64-bit words to clear
+    i64 n_items = s_carry_items;
     i64 n_seeds = p.seeds_ptr[p.B], n_edges = p.edge_ptr[p.B];
-    if (n_items > p.S_max + p.E_max || n_slots > p.slots_cap || n_seeds > p.S_max ||
-        n_edges > p.E_max || n_seeds < 0 || n_edges < 0) {
+    if (n_items > p.S_max + p.E_max || n_seeds > p.S_max || n_edges > p.E_max || n_seeds < 0 ||
+        n_edges < 0 || s_carry_bk > p.buckets_cap) {
       raise(p.err, ERRBIT_CAPACITY);
-      n_items = 0; n_slots = 0; n_seeds = 0; n_edges = 0;  // later kernels become no-ops
+      n_items = 0; n_seeds = 0; n_edges = 0;  // later kernels become no-ops
     }
     p.item_ptr[p.B] = n_items;
-    p.table_ptr[p.B] = n_slots;
+    p.bucket_ptr[p.B] = s_carry_bk;
     p.hdr->n_items = n_items;
-    p.hdr->n_slots = n_slots;
     p.hdr->n_edges = n_items == 0 ? 0 : n_edges;
     p.hdr->n_seeds = n_items == 0 ? 0 : n_seeds;
     p.hdr->n_tiles = (n_items + RL_TILE - 1) / RL_TILE;
+    p.hdr->n_buckets = n_items == 0 ? 0 : s_carry_bk;
   }
 }
 
-// tables <- empty, per-tile counters <- 0
-__global__ void relabel_clear_kernel(const RelabelParams p) {
-  const i64 tid = (i64)blockIdx.x * blockDim.x + threadIdx.x, nth = (i64)gridDim.x * blockDim.x;
-  const i64 n = p.hdr->n_slots;
-  ulonglong2* t2 = reinterpret_cast<ulonglong2*>(p.table);  // 256-byte aligned base
-  for (i64 i = tid; i < (n >> 1); i += nth) t2[i] = make_ulonglong2(SLOT_EMPTY, SLOT_EMPTY);
-  if ((n & 1) && tid == 0) p.table[n - 1] = SLOT_EMPTY;
-  const i64 nt = p.hdr->n_tiles + 1;
-  for (i64 i = tid; i < nt; i += nth) p.tile_count[i] = 0;
-}
+// ---------------------------------------------------------------- global-memory table of one bucket
+// Slot = id:32 | smallest index:32 (atomicMin on the whole word: the id half is
+// equal for all contenders).  Used by a dedupe CTA for a bucket whose ids do
+// not fit its shared table.  The hash differs from the one that chose the
+// bucket (all ids of a bucket share that one's leading bits).
+__device__ __forceinline__ u32 rehash(u32 key) { return hash32(key * 0x9E3779B1u + 0x7F4A7C15u); }
 
-struct Item {
-  int b;
-  u32 key;
-  u32 idx;      // index inside the minibatch's item list
-  i64 src;      // seed slot (seeds) or edge index (rows) in the caller's arrays
-  bool is_seed;
-  bool ok;
-};
-
-// `b_hint` = minibatch of an item at or before g: the binary search runs once
-// per warp, the walk below is a no-op except at minibatch boundaries.
-__device__ __forceinline__ Item fetch_item(const RelabelParams& p, i64 g, int b_hint) {
-  Item it;
-  it.b = b_hint;
-  while (g >= p.item_ptr[it.b + 1]) ++it.b;
-  const i64 off = g - p.item_ptr[it.b];
-  const i64 s0 = p.seeds_ptr[it.b];
-  const i64 ns = p.seeds_ptr[it.b + 1] - s0;
-  it.is_seed = off < ns;
-  it.src = it.is_seed ? s0 + off : p.edge_ptr[it.b] + (off - ns);
-  const i64 key = it.is_seed ? p.seeds[it.src] : p.coo_row[it.src];
-  it.ok = key >= 0 && key < 0xFFFFFFFFll;
-  it.key = (u32)key;
-  it.idx = (u32)off;
-  return it;
-}
-
-// Read before claiming: duplicates of a popular id mostly find a smaller index
-// already in place and leave without an atomic, which keeps hot slots from
-// serialising in L2 (claim-first measured 2x slower on a power-law graph).
-// Items are visited in order so that the smallest index tends to arrive first.
-__global__ void __launch_bounds__(RL_THREADS) relabel_insert_kernel(const RelabelParams p) {
-  const i64 n = p.hdr->n_items;
-  for (i64 g = (i64)blockIdx.x * RL_THREADS + threadIdx.x; g < n; g += (i64)gridDim.x * RL_THREADS) {
-    const int b_hint = find_segment(p.item_ptr, p.B, g - (threadIdx.x & 31));  // warp-uniform
-    const Item it = fetch_item(p, g, b_hint);
-    if (!it.ok) { raise(p.err, ERRBIT_BAD_INPUT); continue; }
-    if (p.direct_bound > 0) {
-      if ((i64)it.key >= p.direct_bound) { raise(p.err, ERRBIT_BAD_INPUT); continue; }
-      u32* w = reinterpret_cast<u32*>(p.table) + (i64)it.b * p.direct_bound + it.key;
-      u32 cur;  // read first: later duplicates of a popular id leave without an atomic
-      asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(cur) : "l"(w) : "memory");
-      if (cur > it.idx) atomicMin(w, it.idx);
-      continue;
-    }
-    const i64 base = p.table_ptr[it.b];
-    const u32 slots = (u32)(p.table_ptr[it.b + 1] - base);
-    u64* tab = p.table + base;
-    const u64 packed = ((u64)it.key << 32) | it.idx;
-    u32 pos = __umulhi(hash32(it.key), slots);
-    u32 probes = 0;
-    for (; probes < slots; ++probes) {
-      u64 cur = ld_relaxed(tab + pos);
-      if (cur == SLOT_EMPTY) {
-        cur = atomicCAS(tab + pos, SLOT_EMPTY, packed);
-        if (cur == SLOT_EMPTY) break;
-      }
-      if ((u32)(cur >> 32) == it.key) {
-        if ((u32)cur > it.idx) atomicMin(tab + pos, packed);
-        break;
-      }
-      pos = pos + 1 == slots ? 0 : pos + 1;
-    }
-    if (probes == slots) raise(p.err, ERRBIT_TABLE_FULL);
-  }
-}
-
-// payload (smallest item index) of `key`, or IDX_UNSET if the key is absent.
-// The tables are read-only once the insert pass is over.
-__device__ __forceinline__ u32 lookup_min_index(const u64* __restrict__ tab, u32 slots, u32 key) {
-  u32 pos = __umulhi(hash32(key), slots);
+__device__ __forceinline__ bool gtab_insert(u64* tab, u32 slots, u32 key, u32 idx) {
+  const u64 packed = ((u64)key << 32) | idx;
+  u32 pos = __umulhi(rehash(key), slots);
   for (u32 probes = 0; probes < slots; ++probes) {
-    const u64 cur = __ldg(tab + pos);
+    u64 cur = ld_relaxed(tab + pos);
+    if (cur == SLOT_EMPTY) {
+      cur = atomicCAS(tab + pos, SLOT_EMPTY, packed);
+      if (cur == SLOT_EMPTY) return true;
+    }
+    if ((u32)(cur >> 32) == key) {
+      if ((u32)cur > idx) atomicMin(tab + pos, packed);
+      return true;
+    }
+    pos = pos + 1 == slots ? 0 : pos + 1;
+  }
+  return false;
+}
+
+__device__ __forceinline__ u32 gtab_find(const u64* tab, u32 slots, u32 key) {
+  u32 pos = __umulhi(rehash(key), slots);
+  for (u32 probes = 0; probes < slots; ++probes) {
+    const u64 cur = ld_relaxed(tab + pos);
     if (cur == SLOT_EMPTY) return IDX_UNSET;
     if ((u32)(cur >> 32) == key) return (u32)cur;
     pos = pos + 1 == slots ? 0 : pos + 1;
@@ -209,33 +172,327 @@ __device__ __forceinline__ u32 lookup_min_index(const u64* __restrict__ tab, u32
   return IDX_UNSET;
 }
 
-// Thread per item (consecutive threads, consecutive items).  A CTA's 256
-// items lie inside one 1024-item tile, whose counter collects the number of
-// first occurrences (one atomic per warp).
-__global__ void __launch_bounds__(RL_THREADS) relabel_lookup_kernel(const RelabelParams p) {
+// ---------------------------------------------------------------- a minibatch seen from a kernel
+// Offsets inside a minibatch fit 32 bits, so the per-item arithmetic is 32-bit;
+// the 64-bit bases are loaded once per minibatch and tile.
+struct Segment {
+  i64 ibase;           // first item of the minibatch
+  i64 iend;            // one past its last item
+  const i64* seeds_b;  // its seeds
+  const i64* rows_b;   // its row ids, biased by -ns so that seeds and rows index by item offset
+  u32 ns;              // number of seeds
+  i64 bk0;             // first bucket
+  int nbk, shift;
+};
+
+__device__ __forceinline__ Segment load_segment(const RelabelParams& p, int b) {
+  Segment s;
+  s.ibase = p.item_ptr[b];
+  s.iend = p.item_ptr[b + 1];
+  const i64 s0 = p.seeds_ptr[b];
+  const i64 ns = p.seeds_ptr[b + 1] - s0;
+  s.seeds_b = p.seeds + s0;
+  s.rows_b = p.coo_row + p.edge_ptr[b] - ns;
+  s.ns = (u32)ns;
+  s.bk0 = p.bucket_ptr[b];
+  s.nbk = (int)(p.bucket_ptr[b + 1] - s.bk0);
+  s.shift = p.bucket_shift[b];
+  return s;
+}
+
+__device__ __forceinline__ i64 segment_id(const Segment& s, u32 off) {
+  return __ldg((off < s.ns ? s.seeds_b : s.rows_b) + off);
+}
+
+// Bucket of an id: the leading bits of its hash (shift in [22, 32]; the double
+// shift keeps shift == 32, one bucket, well defined).
+__device__ __forceinline__ u32 bucket_of(u32 key, int shift) {
+  return (hash32(key) >> (shift - 1)) >> 1;
+}
+
+// The ids of up to PT_BATCH items of a segment, PT_THREADS apart, loaded before
+// any is used (PT_BATCH loads in flight per thread); -1 past `lim`.
+#define GSB_LOAD_ID_BATCH(off0, lim)                                 \
+  i64 id[PT_BATCH];                                                  \
+  _Pragma("unroll") for (int u = 0; u < PT_BATCH; ++u) {             \
+    const u32 off = (off0) + (u32)(u * PT_THREADS);                  \
+    id[u] = -1;                                                      \
+    if (off < (lim)) id[u] = segment_id(sg, off);                    \
+  }
+
+// Per-bucket item counts.  A CTA walks tiles of PT_TILE consecutive items; the
+// part of a tile that belongs to one minibatch is histogrammed in shared
+// memory and flushed with one global atomic per non-empty bucket.
+__global__ void __launch_bounds__(PT_THREADS) relabel_pcount_kernel(const RelabelParams p) {
+  __shared__ u32 s_hist[PT_MAX_BUCKETS];
   const i64 n = p.hdr->n_items;
-  const int lane = threadIdx.x & 31;
-  for (i64 g0 = (i64)blockIdx.x * RL_THREADS; g0 < n; g0 += (i64)gridDim.x * RL_THREADS) {
-    const i64 g = g0 + threadIdx.x;
-    bool first = false;
-    if (g < n) {
-      const int b_hint = find_segment(p.item_ptr, p.B, g - lane);
-      const Item it = fetch_item(p, g, b_hint);
-      u32 m = IDX_UNSET;
-      if (it.ok && p.direct_bound > 0) {
-        if ((i64)it.key < p.direct_bound)
-          m = __ldg(reinterpret_cast<const u32*>(p.table) + (i64)it.b * p.direct_bound + it.key);
-        first = m == it.idx;
-      } else if (it.ok) {
-        const i64 base = p.table_ptr[it.b];
-        m = lookup_min_index(p.table + base, (u32)(p.table_ptr[it.b + 1] - base), it.key);
-        if (m == IDX_UNSET) raise(p.err, ERRBIT_KEY_MISSING);
-        first = m == it.idx;
+  for (i64 lo = (i64)blockIdx.x * PT_TILE; lo < n; lo += (i64)gridDim.x * PT_TILE) {
+    const i64 hi = lo + PT_TILE < n ? lo + PT_TILE : n;
+    int b = find_segment(p.item_ptr, p.B, lo);
+    i64 at = lo;
+    while (at < hi) {
+      while (p.item_ptr[b + 1] <= at) ++b;  // minibatch of item `at` (skips empty ones)
+      const Segment sg = load_segment(p, b);
+      const i64 seg_hi = hi < sg.iend ? hi : sg.iend;
+      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) s_hist[k] = 0;
+      __syncthreads();
+      const u32 lim = (u32)(seg_hi - sg.ibase);
+      for (u32 off0 = (u32)(at - sg.ibase) + threadIdx.x; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
+        GSB_LOAD_ID_BATCH(off0, lim)
+#pragma unroll
+        for (int u = 0; u < PT_BATCH; ++u)
+          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.shift)], 1u);
       }
-      p.min_idx[g] = m;
+      __syncthreads();
+      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS)
+        if (s_hist[k]) atomicAdd(p.bucket_start + sg.bk0 + k, s_hist[k]);
+      __syncthreads();
+      at = seg_hi;
     }
-    const unsigned mask = __ballot_sync(0xffffffffu, first);
-    if (lane == 0 && mask) atomicAdd(p.tile_count + g0 / RL_TILE, (u32)__popc(mask));
+  }
+}
+
+// One block: a[0..n] <- exclusive scan of a[0..n), a[n] <- the total.
+__device__ __forceinline__ i64 scan_in_place(u32* a, i64 n, i64* s_scan) {
+  const i64 per = (n + blockDim.x - 1) / blockDim.x;
+  const i64 lo = (i64)threadIdx.x * per, hi = lo + per < n ? lo + per : n;
+  i64 acc = 0;
+  for (i64 i = lo; i < hi; ++i) acc += a[i];
+  i64 total;
+  i64 run = block_exclusive_scan(acc, s_scan, &total);
+  for (i64 i = lo; i < hi; ++i) { const u32 c = a[i]; a[i] = (u32)run; run += c; }
+  if (threadIdx.x == 0) a[n] = (u32)total;
+  return total;
+}
+
+__global__ void relabel_pscan_kernel(const RelabelParams p) {
+  __shared__ i64 s_scan[34];
+  scan_in_place(p.bucket_start, p.hdr->n_buckets, s_scan);
+}
+
+// Writes (id, index) of every item into its bucket's range of `part`.  Per tile
+// and minibatch: shared histogram, one global atomic per non-empty bucket to
+// reserve the tile's run inside the bucket, then every item takes the next
+// free word of its bucket's run.  The ids are read twice (the second read hits
+// L1/L2); the 8-byte stores of a run meet in L2 before they reach DRAM.
+// (Sorting the tile in shared memory first, to write whole runs, measured the
+// same 0.23 ms per 23 M items.)
+__global__ void __launch_bounds__(PT_THREADS) relabel_scatter_kernel(const RelabelParams p) {
+  __shared__ u32 s_hist[PT_MAX_BUCKETS];  // items of the bucket in this tile
+  __shared__ u32 s_next[PT_MAX_BUCKETS];  // next free position of the bucket's run in `part`
+  const i64 n = p.hdr->n_items;
+  for (i64 lo = (i64)blockIdx.x * PT_TILE; lo < n; lo += (i64)gridDim.x * PT_TILE) {
+    const i64 hi = lo + PT_TILE < n ? lo + PT_TILE : n;
+    int b = find_segment(p.item_ptr, p.B, lo);
+    i64 at = lo;
+    while (at < hi) {
+      while (p.item_ptr[b + 1] <= at) ++b;
+      const Segment sg = load_segment(p, b);
+      const i64 seg_hi = hi < sg.iend ? hi : sg.iend;
+      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) s_hist[k] = 0;
+      __syncthreads();
+      const u32 lim = (u32)(seg_hi - sg.ibase);
+      const u32 first = (u32)(at - sg.ibase) + threadIdx.x;
+      for (u32 off0 = first; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
+        GSB_LOAD_ID_BATCH(off0, lim)
+#pragma unroll
+        for (int u = 0; u < PT_BATCH; ++u)
+          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.shift)], 1u);
+      }
+      __syncthreads();
+      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) {
+        const u32 h = s_hist[k];
+        if (h) s_next[k] = p.bucket_start[sg.bk0 + k] + atomicAdd(p.bucket_cursor + sg.bk0 + k, h);
+      }
+      __syncthreads();
+      for (u32 off0 = first; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
+        GSB_LOAD_ID_BATCH(off0, lim)
+#pragma unroll
+        for (int u = 0; u < PT_BATCH; ++u) {
+          const u32 off = off0 + (u32)(u * PT_THREADS);
+          if ((u64)id[u] < p.id_limit) {
+            const u32 dst = atomicAdd(&s_next[bucket_of((u32)id[u], sg.shift)], 1u);
+            p.part[dst] = ((u64)(u32)id[u] << 32) | off;
+          } else if (off < lim) {
+            raise(p.err, ERRBIT_BAD_INPUT);  // negative, or not below the stated bound
+            p.min_idx[sg.ibase + off] = IDX_UNSET;
+          }
+        }
+      }
+      __syncthreads();
+      at = seg_hi;
+    }
+  }
+}
+
+// Shared table of a dedupe CTA: claim the slot of `key` (linear probing) and
+// lower its index; returns the slot, or `tab` when the table is full.
+__device__ __forceinline__ u32 stab_insert(u32* s_key, u32* s_min, u32 tab, u32 key, u32 idx) {
+  const u32 mask = tab - 1;
+  u32 pos = hash32(key) & mask;
+  for (u32 probes = 0; probes < tab; ++probes) {
+    u32 cur = s_key[pos];
+    if (cur == KEY_EMPTY) cur = atomicCAS(&s_key[pos], KEY_EMPTY, key);
+    if (cur == KEY_EMPTY || cur == key) { atomicMin(&s_min[pos], idx); return pos; }
+    pos = (pos + 1) & mask;
+  }
+  return tab;
+}
+
+// CTA per bucket: shared table id -> smallest index, then min_idx for every
+// item of the bucket.  Only the distinct ids have to fit the table, so a hub
+// id repeated thousands of times costs nothing extra.  A bucket of at most
+// DD_BATCH * DD_THREADS items (the normal case) stays in registers between the
+// two phases together with the table slot each item found.
+__global__ void __launch_bounds__(DD_THREADS, 3) relabel_dedupe_kernel(const RelabelParams p) {
+  extern __shared__ __align__(16) unsigned char dd_smem[];
+  u32* s_key = reinterpret_cast<u32*>(dd_smem);
+  u32* s_min = s_key + DD_TAB;
+  __shared__ int s_over;
+  const i64 nb = p.hdr->n_buckets;
+  for (i64 k = blockIdx.x; k < nb; k += gridDim.x) {
+    const u32 start = p.bucket_start[k];
+    const u32 cnt = p.bucket_start[k + 1] - start;
+    if (cnt == 0) continue;  // uniform over the CTA
+    const int b = find_segment(p.bucket_ptr, p.B, k);
+    u32* out = p.min_idx + p.item_ptr[b];
+    const u64* items = p.part + start;
+    // table size: a power of two >= 1.5 * cnt (at most DD_TAB)
+    u32 tab = 1024;
+    while (tab < DD_TAB && 2 * tab < 3 * cnt) tab <<= 1;
+    {
+      uint4* k4 = reinterpret_cast<uint4*>(s_key);
+      uint4* m4 = reinterpret_cast<uint4*>(s_min);
+      const uint4 ones = make_uint4(KEY_EMPTY, KEY_EMPTY, KEY_EMPTY, KEY_EMPTY);
+      for (u32 i = threadIdx.x; i < tab / 4; i += DD_THREADS) { k4[i] = ones; m4[i] = ones; }
+    }
+    if (threadIdx.x == 0) s_over = 0;
+    __syncthreads();
+    if (cnt <= DD_BATCH * DD_THREADS) {
+      u64 it[DD_BATCH];
+      u32 slot[DD_BATCH];
+#pragma unroll
+      for (int u = 0; u < DD_BATCH; ++u) {
+        const u32 i = u * DD_THREADS + threadIdx.x;
+        it[u] = i < cnt ? __ldg(items + i) : ~0ull;
+      }
+#pragma unroll
+      for (int u = 0; u < DD_BATCH; ++u) {
+        slot[u] = 0;
+        if (it[u] == ~0ull) continue;
+        slot[u] = stab_insert(s_key, s_min, tab, (u32)(it[u] >> 32), (u32)it[u]);
+        if (slot[u] == tab) s_over = 1;
+      }
+      __syncthreads();
+      if (!s_over) {
+#pragma unroll
+        for (int u = 0; u < DD_BATCH; ++u)
+          if (it[u] != ~0ull) out[(u32)it[u]] = s_min[slot[u]];
+        __syncthreads();
+        continue;
+      }
+    } else {
+      for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
+        const u64 it = __ldg(items + i);
+        if (stab_insert(s_key, s_min, tab, (u32)(it >> 32), (u32)it) == tab) s_over = 1;
+      }
+      __syncthreads();
+      if (!s_over) {
+        const u32 mask = tab - 1;
+        for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
+          const u64 it = __ldg(items + i);
+          const u32 key = (u32)(it >> 32);
+          u32 pos = hash32(key) & mask;
+          for (u32 probes = 0; s_key[pos] != key && probes < tab; ++probes) pos = (pos + 1) & mask;
+          out[(u32)it] = s_min[pos];
+        }
+        __syncthreads();
+        continue;
+      }
+    }
+    // more distinct ids than the shared table holds: a table in global memory,
+    // owned by this CTA (2 slots per item of the bucket)
+    u64* gt = p.overflow + 2 * (i64)start + 32 * k;
+    const u32 slots = 2 * cnt + 32;
+    for (u32 i = threadIdx.x; i < slots; i += DD_THREADS) gt[i] = SLOT_EMPTY;
+    __syncthreads();
+    for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
+      const u64 it = items[i];
+      if (!gtab_insert(gt, slots, (u32)(it >> 32), (u32)it)) raise(p.err, ERRBIT_TABLE_FULL);
+    }
+    __syncthreads();
+    for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
+      const u64 it = items[i];
+      const u32 m = gtab_find(gt, slots, (u32)(it >> 32));
+      if (m == IDX_UNSET) raise(p.err, ERRBIT_KEY_MISSING);
+      out[(u32)it] = m;
+    }
+    __syncthreads();
+  }
+}
+
+// ---------------------------------------------------------------- count / tiles / rank
+// Tile layout of count and rank: warp w owns 128 consecutive items, lane l
+// handles items w*128 + j*32 + l (j = 0..3), so every load/store instruction
+// of a warp touches 32 consecutive items and ranks follow from warp ballots.
+// A lane follows the minibatch of its items with a cursor that is loaded once
+// per warp and only moves at a minibatch boundary.
+struct ItemCursor {
+  int b;
+  i64 ibase, iend;
+};
+
+__device__ __forceinline__ void cursor_seek(const RelabelParams& p, ItemCursor& c, i64 g) {
+  if (g < c.iend) return;
+  while (g >= p.item_ptr[c.b + 1]) ++c.b;
+  c.ibase = p.item_ptr[c.b];
+  c.iend = p.item_ptr[c.b + 1];
+}
+
+__device__ __forceinline__ ItemCursor cursor_at(const RelabelParams& p, i64 g) {
+  ItemCursor c;
+  c.b = find_segment(p.item_ptr, p.B, g);
+  c.ibase = p.item_ptr[c.b];
+  c.iend = p.item_ptr[c.b + 1];
+  return c;
+}
+
+// Number of first occurrences (min_idx[item] == the item's own index) of every
+// RL_TILE-item tile.
+__global__ void __launch_bounds__(RL_THREADS) relabel_count_kernel(const RelabelParams p) {
+  __shared__ int s_warp[RL_THREADS / 32];
+  const i64 n = p.hdr->n_items;
+  const i64 tile = blockIdx.x;
+  if (tile >= p.hdr->n_tiles) return;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const i64 g_warp = tile * RL_TILE + (i64)wid * (32 * RL_ITEMS);
+  u32 m[RL_ITEMS];
+#pragma unroll
+  for (int j = 0; j < RL_ITEMS; ++j) {
+    const i64 g = g_warp + j * 32 + lane;
+    m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
+  }
+  int firsts = 0;
+  if (g_warp < n) {
+    ItemCursor c = cursor_at(p, g_warp);
+#pragma unroll
+    for (int j = 0; j < RL_ITEMS; ++j) {
+      const i64 g = g_warp + j * 32 + lane;
+      if (g < n) {
+        cursor_seek(p, c, g);
+        firsts += m[j] == (u32)(g - c.ibase);
+      }
+    }
+  }
+#pragma unroll
+  for (int d = 16; d > 0; d >>= 1) firsts += __shfl_xor_sync(0xffffffffu, firsts, d);
+  if (lane == 0) s_warp[wid] = firsts;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int t = 0;
+#pragma unroll
+    for (int w = 0; w < RL_THREADS / 32; ++w) t += s_warp[w];
+    p.tile_count[tile] = (u32)t;
   }
 }
 
@@ -243,23 +500,10 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_lookup_kernel(const Relabe
 // receives the total).
 __global__ void relabel_tiles_kernel(const RelabelParams p) {
   __shared__ i64 s_scan[34];
-  const i64 nt = p.hdr->n_tiles;
-  const i64 per = (nt + blockDim.x - 1) / blockDim.x;
-  const i64 lo = (i64)threadIdx.x * per, hi = lo + per < nt ? lo + per : nt;
-  i64 acc = 0;
-  for (i64 i = lo; i < hi; ++i) acc += p.tile_count[i];
-  i64 total;
-  i64 run = block_exclusive_scan(acc, s_scan, &total);
-  for (i64 i = lo; i < hi; ++i) { const u32 c = p.tile_count[i]; p.tile_count[i] = (u32)run; run += c; }
-  if (threadIdx.x == 0) {
-    p.tile_count[nt] = (u32)total;
-    if (total > p.U_cap || total >= 0x7FFFFFFFll) raise(p.err, ERRBIT_CAPACITY);
-  }
+  const i64 total = scan_in_place(p.tile_count, p.hdr->n_tiles, s_scan);
+  if (threadIdx.x == 0 && (total > p.U_cap || total >= 0x7FFFFFFFll)) raise(p.err, ERRBIT_CAPACITY);
 }
 
-// Tile layout: warp w owns 128 consecutive items, lane l handles items
-// w*128 + j*32 + l (j = 0..3), so every load/store instruction of a warp
-// touches 32 consecutive items and ranks follow from warp ballots.
 __global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelParams p) {
   __shared__ int s_warp[RL_THREADS / 32];
   const i64 n = p.hdr->n_items;
@@ -273,23 +517,32 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelP
   }
   const unsigned lt_mask = (1u << lane) - 1u;
   const i64 g_warp = tile * RL_TILE + (i64)wid * (32 * RL_ITEMS);
-  const int b_warp = g_warp < n ? find_segment(p.item_ptr, p.B, g_warp) : 0;
-  Item it[RL_ITEMS];
-  bool live[RL_ITEMS], first[RL_ITEMS];
-  int before[RL_ITEMS];
-  int warp_firsts = 0;
+  u32 m[RL_ITEMS];
 #pragma unroll
   for (int j = 0; j < RL_ITEMS; ++j) {
     const i64 g = g_warp + j * 32 + lane;
-    live[j] = g < n;
+    m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
+  }
+  bool first[RL_ITEMS];
+  int before[RL_ITEMS], bj[RL_ITEMS];
+  u32 off[RL_ITEMS];
+  int warp_firsts = 0;
+  ItemCursor c = cursor_at(p, g_warp < n ? g_warp : n - 1);
+#pragma unroll
+  for (int j = 0; j < RL_ITEMS; ++j) {
+    const i64 g = g_warp + j * 32 + lane;
     first[j] = false;
-    if (live[j]) {
-      it[j] = fetch_item(p, g, b_warp);
-      first[j] = it[j].ok && __ldg(p.min_idx + g) == it[j].idx;
+    off[j] = IDX_UNSET;
+    bj[j] = c.b;
+    if (g < n) {
+      cursor_seek(p, c, g);
+      bj[j] = c.b;
+      off[j] = (u32)(g - c.ibase);
+      first[j] = m[j] == off[j];
     }
-    const unsigned m = __ballot_sync(0xffffffffu, first[j]);
-    before[j] = warp_firsts + __popc(m & lt_mask);
-    warp_firsts += __popc(m);
+    const unsigned bal = __ballot_sync(0xffffffffu, first[j]);
+    before[j] = warp_firsts + __popc(bal & lt_mask);
+    warp_firsts += __popc(bal);
   }
   if (lane == 0) s_warp[wid] = warp_firsts;
   __syncthreads();
@@ -298,18 +551,22 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelP
   const bool fits = (i64)p.tile_count[tiles] <= p.U_cap;
 #pragma unroll
   for (int j = 0; j < RL_ITEMS; ++j) {
-    if (!live[j]) continue;
+    if (off[j] == IDX_UNSET) continue;
     const i64 g = g_warp + j * 32 + lane;
     const i64 run = wbase + before[j];
-    if (it[j].idx == 0) {
+    if (off[j] == 0) {
       // first item of its minibatch: the running count is the minibatch's
       // offset; empty minibatches directly before it share the same value
-      int b = it[j].b;
+      int b = bj[j];
       p.unique_ptr[b] = run;
       while (b > 0 && p.item_ptr[b - 1] == g) p.unique_ptr[--b] = run;
     }
     if (first[j]) {
-      if (fits) p.unique[run] = (i64)it[j].key;
+      // the id is read only here: one item in three is a repeat
+      const i64 s0 = p.seeds_ptr[bj[j]];
+      const u32 ns = (u32)(p.seeds_ptr[bj[j] + 1] - s0);
+      const i64 id = off[j] < ns ? p.seeds[s0 + off[j]] : p.coo_row[p.edge_ptr[bj[j]] + (off[j] - ns)];
+      if (fits) p.unique[run] = id;
       p.rank[g] = (u32)run;
     }
   }
@@ -321,58 +578,102 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelP
   }
 }
 
-// Thread per edge.  Position of an id = rank[first item carrying it]; for an
-// id seen for the first time on this very edge that is the edge's own item, so
-// two thirds of the gathers of a GraphSAGE layer are in fact coalesced.
+// ---------------------------------------------------------------- emit
+// Thread per edge, four edges (256 apart) per thread with their loads issued
+// together.  Position of an id = rank[first item carrying it]; for an id seen
+// for the first time on this very edge that is the edge's own item, so two
+// thirds of the gathers of a GraphSAGE layer are in fact coalesced.
+struct EdgeCursor {
+  int b;
+  i64 e0, e_end;   // edges of the minibatch
+  i64 s0;          // its first seed slot
+  i64 ubase;       // its first position in `unique`
+  const u32* min_b;   // min_idx of its items
+  const u32* rank_b;  // rank of its items
+  u32 ns;
+};
+
+__device__ __forceinline__ void edge_cursor_load(const RelabelParams& p, EdgeCursor& c) {
+  c.e0 = p.edge_ptr[c.b];
+  c.e_end = p.edge_ptr[c.b + 1];
+  c.s0 = p.seeds_ptr[c.b];
+  c.ns = (u32)(p.seeds_ptr[c.b + 1] - c.s0);
+  c.ubase = p.unique_ptr[c.b];
+  c.min_b = p.min_idx + p.item_ptr[c.b];
+  c.rank_b = p.rank + p.item_ptr[c.b];
+}
+
 __global__ void __launch_bounds__(RL_THREADS) relabel_emit_kernel(const RelabelParams p) {
+  constexpr int EB = 4;
   const i64 n = p.hdr->n_edges;
-  const int lane = threadIdx.x & 31;
-  for (i64 e = (i64)blockIdx.x * RL_THREADS + threadIdx.x; e < n; e += (i64)gridDim.x * RL_THREADS) {
-    int b = find_segment(p.edge_ptr, p.B, e - lane);  // warp-uniform start
-    while (e >= p.edge_ptr[b + 1]) ++b;
-    const i64 ibase = p.item_ptr[b];
-    const i64 s0 = p.seeds_ptr[b], ns = p.seeds_ptr[b + 1] - s0;
-    const i64 ubase = p.unique_ptr[b];
-    const u32 m = __ldg(p.min_idx + ibase + ns + (e - p.edge_ptr[b]));
-    const i64 c = __ldg(p.coo_col + e);
-    i64 r = -1, cc = -1;
-    if (m != IDX_UNSET) r = (i64)__ldg(p.rank + ibase + m) - ubase;
-    if (c >= s0 && c < s0 + ns) {
-      const u32 mc = __ldg(p.min_idx + ibase + (c - s0));
-      if (mc != IDX_UNSET) cc = (i64)__ldg(p.rank + ibase + mc) - ubase;
-    } else {
-      raise(p.err, ERRBIT_BAD_INPUT);  // a column slot outside the edge's own minibatch
+  for (i64 e_cta = (i64)blockIdx.x * (EB * RL_THREADS); e_cta < n; e_cta += (i64)gridDim.x * (EB * RL_THREADS)) {
+    EdgeCursor c;
+    c.b = find_segment(p.edge_ptr, p.B, e_cta);
+    edge_cursor_load(p, c);
+    u32 m[EB], mc[EB];
+    i64 ub[EB];
+    const u32* rb[EB];
+    bool live[EB];
+#pragma unroll
+    for (int u = 0; u < EB; ++u) {
+      const i64 e = e_cta + u * RL_THREADS + threadIdx.x;
+      live[u] = e < n;
+      m[u] = IDX_UNSET; mc[u] = IDX_UNSET;
+      ub[u] = 0; rb[u] = p.rank;
+      if (live[u]) {
+        if (e >= c.e_end) {
+          while (e >= p.edge_ptr[c.b + 1]) ++c.b;
+          edge_cursor_load(p, c);
+        }
+        ub[u] = c.ubase; rb[u] = c.rank_b;
+        m[u] = __ldg(c.min_b + c.ns + (u32)(e - c.e0));
+        const u64 lc = (u64)(__ldg(p.coo_col + e) - c.s0);  // seed slot inside the minibatch
+        if (lc < c.ns) mc[u] = __ldg(c.min_b + lc);
+        else raise(p.err, ERRBIT_BAD_INPUT);  // a column slot outside the edge's own minibatch
+      }
     }
-    p.out_row[e] = r;
-    p.out_col[e] = cc;
+    u32 r[EB], rc[EB];
+#pragma unroll
+    for (int u = 0; u < EB; ++u) {
+      r[u] = m[u] != IDX_UNSET ? __ldg(rb[u] + m[u]) : 0;
+      rc[u] = mc[u] != IDX_UNSET ? __ldg(rb[u] + mc[u]) : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < EB; ++u) {
+      if (!live[u]) continue;
+      const i64 e = e_cta + u * RL_THREADS + threadIdx.x;
+      p.out_row[e] = m[u] != IDX_UNSET ? (i64)r[u] - ub[u] : -1;
+      p.out_col[e] = mc[u] != IDX_UNSET ? (i64)rc[u] - ub[u] : -1;
+    }
   }
 }
 
 struct RelabelLayout {
-  size_t hdr, item_ptr, table_ptr, tile_count, min_idx, rank, table, total;
-  i64 slots_cap, tiles;
+  size_t hdr, item_ptr, bucket_ptr, bucket_shift, tile_count, bucket_start, bucket_cursor, min_idx,
+      rank, part, overflow, total;
+  i64 tiles, buckets_cap;
 };
-
-// Direct-address tables are used when they need no more memory than hashing.
-static bool use_direct(i64 S_max, i64 E_max, i64 B, i64 id_bound) {
-  if (id_bound <= 0 || id_bound >= 0xFFFFFFFFll) return false;
-  const i64 hash_words = (S_max + E_max) * 2 + 32 * (B + 1);          // 64-bit words
-  return (id_bound * B + 1) / 2 <= hash_words;
-}
 
 static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   RelabelLayout L;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-  L.tiles = (S_max + E_max + RL_TILE - 1) / RL_TILE + 1;
-  L.slots_cap = (S_max + E_max) * 2 + 32 * (B + 1);
+  const i64 items = S_max + E_max;
+  L.tiles = (items + RL_TILE - 1) / RL_TILE + 1;
+  // a minibatch of n items has at most max(1, 2n / PT_BUCKET_ITEMS) buckets
+  L.buckets_cap = B + (2 * items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS + 1;
   size_t o = 0;
   L.hdr = o; o = up(o + sizeof(RelabelHeader));
   L.item_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
-  L.table_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
+  L.bucket_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
+  L.bucket_shift = o; o = up(o + sizeof(int) * (size_t)(B + 1));
   L.tile_count = o; o = up(o + sizeof(u32) * (size_t)(L.tiles + 1));
-  L.min_idx = o; o = up(o + sizeof(u32) * (size_t)(S_max + E_max + 4));
-  L.rank = o; o = up(o + sizeof(u32) * (size_t)(S_max + E_max + 4));
-  L.table = o; o = up(o + sizeof(u64) * (size_t)L.slots_cap);
+  L.bucket_start = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
+  L.bucket_cursor = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
+  L.min_idx = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
+  L.rank = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
+  L.part = o; o = up(o + sizeof(u64) * (size_t)(items + 4));
+  // overflow tables: 2 slots per item + 32 per bucket; touched only by buckets that need them
+  L.overflow = o; o = up(o + sizeof(u64) * (size_t)(2 * items + 32 * (L.buckets_cap + 1)));
   L.total = o;
   return L;
 }
@@ -407,26 +708,34 @@ extern "C" int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr,
   p.seeds = (const i64*)seeds; p.seeds_ptr = (const i64*)seeds_ptr; p.coo_row = (const i64*)coo_row;
   p.coo_col = (const i64*)coo_col; p.edge_ptr = (const i64*)edge_ptr; p.B = (int)B;
   p.S_max = S_max; p.E_max = E_max; p.unique = (i64*)unique; p.U_cap = U_cap;
+  p.id_limit = id_bound > 0 && id_bound < 0xFFFFFFFFll ? (u64)id_bound : 0xFFFFFFFFull;
   p.unique_ptr = (i64*)unique_ptr; p.out_row = (i64*)out_row; p.out_col = (i64*)out_col;
   p.hdr = (RelabelHeader*)(ws + L.hdr); p.item_ptr = (i64*)(ws + L.item_ptr);
-  p.table_ptr = (i64*)(ws + L.table_ptr); p.tile_count = (u32*)(ws + L.tile_count);
-  p.min_idx = (u32*)(ws + L.min_idx); p.rank = (u32*)(ws + L.rank);
-  p.table = (u64*)(ws + L.table); p.slots_cap = L.slots_cap; p.tiles_cap = L.tiles; p.err = d_err;
-  p.direct_bound = use_direct(S_max, E_max, B, id_bound) ? id_bound : 0;
+  p.tile_count = (u32*)(ws + L.tile_count); p.min_idx = (u32*)(ws + L.min_idx);
+  p.rank = (u32*)(ws + L.rank); p.err = d_err;
+  p.bucket_ptr = (i64*)(ws + L.bucket_ptr); p.bucket_shift = (int*)(ws + L.bucket_shift);
+  p.bucket_start = (u32*)(ws + L.bucket_start); p.bucket_cursor = (u32*)(ws + L.bucket_cursor);
+  p.part = (u64*)(ws + L.part); p.overflow = (u64*)(ws + L.overflow); p.buckets_cap = L.buckets_cap;
 
   { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
+  // bucket counts and cursors are adjacent: one clear
+  GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_start, 0, L.min_idx - L.bucket_start, st));
   const i64 items_max = S_max + E_max;
   const int wide = 148 * 8;
-  int g_clear = (int)((L.slots_cap / 2 + RL_THREADS - 1) / RL_THREADS); if (g_clear > wide) g_clear = wide; if (g_clear < 1) g_clear = 1;
-  { LaunchScope ls(KID_RL_CLEAR, st); relabel_clear_kernel<<<g_clear, RL_THREADS, 0, st>>>(p); }
-  int g_items = (int)((items_max + RL_THREADS - 1) / RL_THREADS); if (g_items < 1) g_items = 1;
-  if (g_items > 148 * 16) g_items = 148 * 16;
-  { LaunchScope ls(KID_RL_INSERT, st); relabel_insert_kernel<<<g_items, RL_THREADS, 0, st>>>(p); }
-  { LaunchScope ls(KID_RL_LOOKUP, st); relabel_lookup_kernel<<<g_items, RL_THREADS, 0, st>>>(p); }
+  int g_tiles = (int)((items_max + PT_TILE - 1) / PT_TILE); if (g_tiles < 1) g_tiles = 1;
+  if (g_tiles > wide) g_tiles = wide;
+  { LaunchScope ls(KID_RL_PCOUNT, st); relabel_pcount_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
+  { LaunchScope ls(KID_RL_PSCAN, st); relabel_pscan_kernel<<<1, 1024, 0, st>>>(p); }
+  { LaunchScope ls(KID_RL_SCATTER, st); relabel_scatter_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
+  const int g_bk = (int)(L.buckets_cap < 148 * 12 ? L.buckets_cap : 148 * 12);
+  const int dd_smem = 2 * DD_TAB * (int)sizeof(u32);
+  GSB_CUDA_OK(cudaFuncSetAttribute(relabel_dedupe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_smem));
+  { LaunchScope ls(KID_RL_DEDUPE, st); relabel_dedupe_kernel<<<g_bk, DD_THREADS, dd_smem, st>>>(p); }
+  { LaunchScope ls(KID_RL_COUNT, st); relabel_count_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_TILES, st); relabel_tiles_kernel<<<1, 1024, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_SCAN, st); relabel_rank_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   if (out_row && E_max > 0) {
-    int g_edges = (int)((E_max + RL_THREADS - 1) / RL_THREADS);
+    int g_edges = (int)((E_max + 4 * RL_THREADS - 1) / (4 * RL_THREADS));
     if (g_edges > 148 * 16) g_edges = 148 * 16;
     { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<g_edges, RL_THREADS, 0, st>>>(p); }
   }

@@ -179,8 +179,10 @@ GSB_API int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, int 
  * holds LOCAL column slots, i.e. indices into `seeds`).  out_row/out_col may
  * both be NULL (all_nodes only).  S_max/E_max bound seeds_ptr[B]/edge_ptr[B],
  * which are read on the device.  `unique` has capacity U_cap.
- * Limits: node ids < 2^32-1 (id_bound states the exclusive upper bound of the
- * ids), S_max+E_max < 2^31.
+ * id_bound > 0 states the exclusive upper bound of the ids; an id outside
+ * [0, id_bound) -- or outside [0, 2^32-1) when id_bound is 0 -- sets
+ * GSB_ERRBIT_BAD_INPUT and is relabelled to -1.
+ * Limits: node ids < 2^32-1, S_max+E_max < 2^31.
  */
 GSB_API size_t gsb_batch_relabel_workspace_bytes(int64_t S_max, int64_t E_max, int64_t B);
 GSB_API int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B,
