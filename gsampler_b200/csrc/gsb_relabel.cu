@@ -257,9 +257,11 @@ __device__ __forceinline__ i64 scan_in_place(u32* a, i64 n, i64* s_scan) {
   const i64 per = (n + blockDim.x - 1) / blockDim.x;
   const i64 lo = (i64)threadIdx.x * per, hi = lo + per < n ? lo + per : n;
   i64 acc = 0;
+#pragma unroll 8
   for (i64 i = lo; i < hi; ++i) acc += a[i];
   i64 total;
   i64 run = block_exclusive_scan(acc, s_scan, &total);
+#pragma unroll 8
   for (i64 i = lo; i < hi; ++i) { const u32 c = a[i]; a[i] = (u32)run; run += c; }
   if (threadIdx.x == 0) a[n] = (u32)total;
   return total;

@@ -132,6 +132,9 @@ class Graph : public torch::CustomClassHolder {
   // the reference, which composes it from per-layer operators).
   std::vector<torch::Tensor> BatchGraphSAGE(torch::Tensor seeds, torch::Tensor seeds_ptr,
                                             std::vector<int64_t> fanouts);
+  // enqueue only: tensors at capacity + the device-side counts (see graph_more.cc)
+  std::vector<torch::Tensor> BatchGraphSAGEAsync(torch::Tensor seeds, torch::Tensor seeds_ptr,
+                                                 std::vector<int64_t> fanouts);
 
   void CreateSparseFormat(int64_t format);
 

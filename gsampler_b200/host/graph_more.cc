@@ -19,13 +19,16 @@ static const int64_t* P(const torch::Tensor& t) { return t.data_ptr<int64_t>(); 
 // L-layer GraphSAGE super-batch sampler in ONE call: the operator sequence
 // A[:, seeds::ptr] -> individual_sampling(K) -> all_nodes -> to_dgl_block per
 // layer (examples/graphsage/graphsage_e2e.py:37-44 in gSampler) with every
-// intermediate size kept on the device.  Returns 9 tensors per layer
-// (sub_indptr, rows, cols, select, edge_ptr, unique, unique_ptr, block_row,
-// block_col), narrowed to their live sizes, followed by one CPU int64 tensor
-// [3*L] = {S_l, E_l, U_l}.  The single synchronisation is the read of those
-// counts at the end.
-std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Tensor seeds_ptr,
-                                                 std::vector<int64_t> fanouts) {
+// intermediate size kept on the device.
+//
+// BatchGraphSAGEAsync only enqueues the work on the current stream and returns
+// 9 tensors per layer (sub_indptr, rows, cols, select, edge_ptr, unique,
+// unique_ptr, block_row, block_col) at their CAPACITY, followed by one device
+// int64 tensor [3*L + 1] = {S_l, E_l, U_l}..., error word.  The caller reads
+// the counts when it needs them (it can keep several super-batches in flight
+// on different streams) and narrows the tensors itself.
+std::vector<torch::Tensor> Graph::BatchGraphSAGEAsync(torch::Tensor seeds, torch::Tensor seeds_ptr,
+                                                      std::vector<int64_t> fanouts) {
   CreateSparseFormat(kCSC);
   TORCH_CHECK(!csc_->e_ids.has_value(), "BatchGraphSAGE expects a CSC without edge-id indirection");
   CheckIds(seeds, "seeds");
@@ -38,7 +41,6 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
   std::vector<gsb_layer_buffers> bufs((size_t)L);
   std::vector<torch::Tensor> keep;
   int64_t S_cap = S0;
-  const int64_t nnz = csc_->indices.numel();
   for (int l = 0; l < L; ++l) {
     TORCH_CHECK(fanouts[l] >= 1, "fanout must be positive");
     int64_t E_cap = S_cap * fanouts[l];
@@ -57,7 +59,6 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
     b.block_col = mk(E_cap);
     S_cap = S_cap + E_cap;
   }
-  (void)nnz;
   auto counts = torch::zeros({3 * L + 1}, opt);  // last entry: device error word
   const size_t ws_bytes = gsb_graphsage_workspace_bytes(B, L, bufs.data(), fanouts.data());
   auto ws = NewWorkspace(ws_bytes, seeds.device());
@@ -69,13 +70,25 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
                                    (size_t)ws.numel(),
                                    (int*)(counts.data_ptr<int64_t>() + 3 * L), CurrentStream()),
               "graphsage_sample");
-  auto host = counts.cpu();
+  // the workspace is released to the caching allocator here; it stays valid for the
+  // kernels already enqueued because the allocator reuses a block on its own stream only
+  keep.push_back(counts);
+  return keep;
+}
+
+// The synchronous form: narrows the tensors to their live sizes and returns the
+// counts as a CPU int64 tensor [3*L].  Its single synchronisation is the read
+// of those counts at the end.
+std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Tensor seeds_ptr,
+                                                 std::vector<int64_t> fanouts) {
+  auto k = BatchGraphSAGEAsync(seeds, seeds_ptr, fanouts);
+  const int L = (int)fanouts.size();
+  auto host = k.back().cpu();
   const int64_t* c = host.data_ptr<int64_t>();
   CheckDeviceError((int)c[3 * L], "graphsage_sample");
   std::vector<torch::Tensor> out;
   for (int l = 0; l < L; ++l) {
     const int64_t S = c[3 * l], E = c[3 * l + 1], U = c[3 * l + 2];
-    auto& k = keep;
     const size_t o = (size_t)l * 9;
     out.push_back(k[o + 0].narrow(0, 0, S + 1));
     out.push_back(k[o + 1].narrow(0, 0, E));

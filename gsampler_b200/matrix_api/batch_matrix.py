@@ -204,3 +204,39 @@ class BatchMatrix(Matrix):
         synchronisation between layers).  Returns the per-layer tensors of
         ``Graph._CAPI_BatchGraphSAGE``."""
         return self._graph._CAPI_BatchGraphSAGE(seeds, seeds_ptr, list(fanouts))
+
+    def graphsage_async(self, seeds, seeds_ptr, fanouts):
+        """Enqueue the GraphSAGE super-batch sampler on the current CUDA stream and return at
+        once.  ``.wait()`` on the returned object gives what :meth:`graphsage` returns.  A data
+        loader keeps two or three super-batches in flight, each on its own stream, so that the
+        copies and the host work of one overlap the kernels of another."""
+        return GraphSAGEResult(self._graph._CAPI_BatchGraphSAGEAsync(seeds, seeds_ptr, list(fanouts)),
+                               len(fanouts), (seeds, seeds_ptr))
+
+
+class GraphSAGEResult:
+    """Pending result of :meth:`BatchMatrix.graphsage_async`."""
+
+    _NARROW = (0, 1, 2, 3, None, 5, None, 7, 8)   # which count bounds which of a layer's 9 tensors
+
+    def __init__(self, tensors, num_layers, inputs):
+        self._t = tensors
+        self._L = num_layers
+        self._inputs = inputs                      # kept alive until the kernels have run
+        self._host = torch.empty(3 * num_layers + 1, dtype=torch.int64, pin_memory=True)
+        self._host.copy_(tensors[-1], non_blocking=True)
+        self._done = torch.cuda.Event()
+        self._done.record()
+
+    def wait(self):
+        self._done.synchronize()
+        c = self._host.tolist()
+        if c[3 * self._L]:
+            raise RuntimeError("graphsage_sample reported device-side error bits 0x%x" % c[3 * self._L])
+        out = []
+        for l in range(self._L):
+            S, E, U = c[3 * l:3 * l + 3]
+            t = self._t[9 * l:9 * l + 9]
+            out += [t[0][:S + 1], t[1][:E], t[2][:E], t[3][:E], t[4], t[5][:U], t[6], t[7][:E], t[8][:E]]
+        out.append(self._host[:3 * self._L].clone())
+        return out

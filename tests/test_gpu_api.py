@@ -94,6 +94,31 @@ def test_native_graphsage_pipeline_bit_exact(gsb, oracle, rmat, idx_dtype):
                                                     layer["unique"].size]
 
 
+def test_graphsage_async_two_in_flight(gsb, rmat):
+    """The enqueue-only form gives the same tensors as the synchronous one, also with two
+    super-batches in flight on two streams."""
+    indptr, indices = rmat
+    seeds, ptr = _seeds(indptr.size - 1)
+    A = new_graph(gsb, indptr, indices)
+    bm = gsb.BatchMatrix()
+    bm.load_from_matrix(gsb.Matrix(A), False)
+    sd, pd = torch.as_tensor(seeds).cuda(), torch.as_tensor(ptr).cuda()
+    A._CAPI_SetSeed(77)
+    want = [bm.graphsage(sd, pd, [10, 5]) for _ in range(2)]
+    A._CAPI_SetSeed(77)
+    torch.cuda.synchronize()
+    futs = []
+    for i in range(2):
+        with torch.cuda.stream(torch.cuda.Stream()):
+            futs.append(bm.graphsage_async(sd, pd, [10, 5]))
+    got = [f.wait() for f in futs]
+    torch.cuda.synchronize()
+    for w, g in zip(want, got):
+        assert len(w) == len(g)
+        for a, b in zip(w, g):
+            assert torch.equal(a.cpu(), b.cpu())
+
+
 def test_batchmatrix_sampler_matches_oracle(gsb, oracle, rmat):
     """The reference's batch_graphsage_sampler (examples/graphsage/graphsage.py:20-27) written
     against this package's BatchMatrix."""
