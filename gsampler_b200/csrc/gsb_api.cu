@@ -11,20 +11,13 @@ namespace gsb {
 
 static thread_local const char* g_last_cuda_error = "";
 
-__global__ void record_counts_kernel(const i64* seeds_ptr, const i64* unique_ptr, int B,
-                                     i64* counts /* {S, E, U}; E already written */) {
-  if (threadIdx.x == 0 && blockIdx.x == 0) {
-    counts[0] = seeds_ptr[B];
-    counts[2] = unique_ptr[B];
-  }
-}
 
 // ---------------------------------------------------------------- launch accounting
 static const char* const kKernelNames[KID_NUM] = {
     "sample_tile", "sample_probs", "count", "slice_fill", "gather", "expand_indptr",
     "indptr_from_sorted", "relabel_setup", "relabel_pcount", "relabel_pscan", "relabel_scatter",
     "relabel_dedupe", "relabel_count", "relabel_tiles", "relabel_rank", "relabel_emit",
-    "record_counts", "slice_rows", "edge_sum", "edge_op", "list_sample", "walk", "sort", "misc"};
+    "slice_rows", "edge_sum", "edge_op", "list_sample", "walk", "sort", "misc"};
 
 struct TimedLaunch {
   int id, tag;
@@ -158,7 +151,6 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
   // checked on the device (GSB_ERRBIT_CAPACITY).
   if (layers[0].S_cap < S0) return GSB_ERR_INVALID;
 
-  cudaStream_t st = (cudaStream_t)cuda_stream;
   const int64_t* cur_seeds = seeds;
   const int64_t* cur_ptr = seeds_ptr;
   const int64_t* d_S = nullptr;
@@ -171,16 +163,12 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
                              seed, (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
                              d_counts + 3 * l + 1, workspace, ws_a, d_err, cuda_stream);
     if (rc != GSB_OK) return rc;
-    rc = gsb_gather_i64(L.sub_indptr, cur_ptr, B + 1, L.edge_ptr, cuda_stream);
+    // edge_ptr = sub_indptr[seeds_ptr] and the {S, U} counts are produced inside the relabel passes
+    rc = relabel_launch(cur_seeds, cur_ptr, B, S_max, L.rows, L.cols, nullptr, L.sub_indptr,
+                        L.edge_ptr, L.E_cap, id_bound, L.unique, L.S_cap + L.E_cap, L.unique_ptr,
+                        L.block_row, L.block_col, d_counts + 3 * l, (char*)workspace + ws_a,
+                        workspace_bytes - ws_a, d_err, cuda_stream);
     if (rc != GSB_OK) return rc;
-    rc = gsb_batch_relabel(cur_seeds, cur_ptr, B, S_max, L.rows, L.cols, L.edge_ptr, L.E_cap,
-                           id_bound, L.unique, L.S_cap + L.E_cap, L.unique_ptr, L.block_row,
-                           L.block_col, (char*)workspace + ws_a, workspace_bytes - ws_a, d_err,
-                           cuda_stream);
-    if (rc != GSB_OK) return rc;
-    { LaunchScope ls(KID_COUNTS, st);
-    record_counts_kernel<<<1, 32, 0, st>>>((const i64*)cur_ptr, (const i64*)L.unique_ptr, (int)B,
-                                           (i64*)d_counts + 3 * l); }
     cur_seeds = L.unique;
     cur_ptr = L.unique_ptr;
     d_S = L.unique_ptr + B;

@@ -195,6 +195,14 @@ __device__ __forceinline__ i64 load_index<i64>(const void* base, i64 pos) {
   return __ldg((const i64*)base + pos);
 }
 
+// gsb_batch_relabel with two extras for the layered sampler (gsb_relabel.cu)
+int relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B, int64_t S_max,
+                   const int64_t* coo_row, const int64_t* coo_col, const int64_t* edge_ptr,
+                   const int64_t* sub_indptr, int64_t* edge_ptr_out, int64_t E_max, int64_t id_bound,
+                   int64_t* unique, int64_t U_cap, int64_t* unique_ptr, int64_t* out_row,
+                   int64_t* out_col, int64_t* counts_out, void* workspace, size_t workspace_bytes,
+                   int* d_err, void* cuda_stream);
+
 inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 
 // Launch accounting: every kernel launch of the library sits inside a
@@ -203,7 +211,7 @@ inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 enum KernelId {
   KID_SAMPLE = 0, KID_SAMPLE_PROBS, KID_COUNT, KID_SLICE_FILL, KID_GATHER, KID_EXPAND,
   KID_INDPTR_SORTED, KID_RL_SETUP, KID_RL_PCOUNT, KID_RL_PSCAN, KID_RL_SCATTER, KID_RL_DEDUPE,
-  KID_RL_COUNT, KID_RL_TILES, KID_RL_SCAN, KID_RL_EDGES, KID_COUNTS, KID_SLICE_ROWS, KID_EDGE_SUM,
+  KID_RL_COUNT, KID_RL_TILES, KID_RL_SCAN, KID_RL_EDGES, KID_SLICE_ROWS, KID_EDGE_SUM,
   KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT, KID_MISC, KID_NUM
 };
 struct LaunchScope {

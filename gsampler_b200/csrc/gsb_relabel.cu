@@ -63,6 +63,9 @@ struct RelabelParams {
   const i64* coo_row;
   const i64* coo_col;
   const i64* edge_ptr;
+  const i64* sub_indptr;  // non-null: setup derives edge_ptr[b] = sub_indptr[seeds_ptr[b]] first
+  i64* edge_ptr_out;
+  i64* counts_out;        // nullable {S, (unused), U} of the call, written by the rank pass
   int B;
   i64 S_max, E_max;
   u64 id_limit;       // ids must be below this (at most 2^32 - 1)
@@ -98,7 +101,15 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
     int shift = 32;
     if (b < p.B) {
       i64 ns = p.seeds_ptr[b + 1] - p.seeds_ptr[b];
-      i64 ne = p.edge_ptr[b + 1] - p.edge_ptr[b];
+      i64 ne;
+      if (p.sub_indptr) {
+        const i64 e_lo = p.sub_indptr[p.seeds_ptr[b]], e_hi = p.sub_indptr[p.seeds_ptr[b + 1]];
+        p.edge_ptr_out[b] = e_lo;
+        if (b == p.B - 1) p.edge_ptr_out[p.B] = e_hi;
+        ne = e_hi - e_lo;
+      } else {
+        ne = p.edge_ptr[b + 1] - p.edge_ptr[b];
+      }
       if (ns < 0 || ne < 0) { raise(p.err, ERRBIT_BAD_INPUT); ns = ns < 0 ? 0 : ns; ne = ne < 0 ? 0 : ne; }
       items = ns + ne;
       const i64 need = (items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS;
@@ -120,7 +131,8 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
   }
   if (threadIdx.x == 0) {
     i64 n_items = s_carry_items;
-    i64 n_seeds = p.seeds_ptr[p.B], n_edges = p.edge_ptr[p.B];
+    i64 n_seeds = p.seeds_ptr[p.B];
+    i64 n_edges = p.sub_indptr ? p.sub_indptr[n_seeds < 0 ? 0 : n_seeds] : p.edge_ptr[p.B];
     if (n_items > p.S_max + p.E_max || n_seeds > p.S_max || n_edges > p.E_max || n_seeds < 0 ||
         n_edges < 0 || s_carry_bk > p.buckets_cap) {
       raise(p.err, ERRBIT_CAPACITY);
@@ -252,19 +264,31 @@ __global__ void __launch_bounds__(PT_THREADS) relabel_pcount_kernel(const Relabe
   }
 }
 
-// One block: a[0..n] <- exclusive scan of a[0..n), a[n] <- the total.
+// One block: a[0..n] <- exclusive scan of a[0..n), a[n] <- the total.  The
+// array (16-byte aligned) is walked in chunks of four words per thread, so the
+// loads and stores of a warp are contiguous.
 __device__ __forceinline__ i64 scan_in_place(u32* a, i64 n, i64* s_scan) {
-  const i64 per = (n + blockDim.x - 1) / blockDim.x;
-  const i64 lo = (i64)threadIdx.x * per, hi = lo + per < n ? lo + per : n;
-  i64 acc = 0;
-#pragma unroll 8
-  for (i64 i = lo; i < hi; ++i) acc += a[i];
-  i64 total;
-  i64 run = block_exclusive_scan(acc, s_scan, &total);
-#pragma unroll 8
-  for (i64 i = lo; i < hi; ++i) { const u32 c = a[i]; a[i] = (u32)run; run += c; }
-  if (threadIdx.x == 0) a[n] = (u32)total;
-  return total;
+  __shared__ i64 s_carry;
+  if (threadIdx.x == 0) s_carry = 0;
+  __syncthreads();
+  uint4* a4 = reinterpret_cast<uint4*>(a);
+  const i64 chunk = (i64)blockDim.x * 4;
+  for (i64 c0 = 0; c0 < n; c0 += chunk) {
+    const i64 i = c0 + (i64)threadIdx.x * 4;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (i + 3 < n) v = a4[i >> 2];
+    else if (i < n) { v.x = a[i]; if (i + 1 < n) v.y = a[i + 1]; if (i + 2 < n) v.z = a[i + 2]; }
+    i64 total;
+    const i64 run = s_carry + block_exclusive_scan((i64)v.x + v.y + v.z + v.w, s_scan, &total);
+    const uint4 o = make_uint4((u32)run, (u32)(run + v.x), (u32)(run + v.x + v.y), (u32)(run + v.x + v.y + v.z));
+    if (i + 3 < n) a4[i >> 2] = o;
+    else if (i < n) { a[i] = o.x; if (i + 1 < n) a[i + 1] = o.y; if (i + 2 < n) a[i + 2] = o.z; }
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry += total;
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) a[n] = (u32)s_carry;
+  return s_carry;
 }
 
 __global__ void relabel_pscan_kernel(const RelabelParams p) {
@@ -513,8 +537,10 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelP
   const i64 tile = blockIdx.x;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   if (tile >= tiles) {
-    if (tile == 0 && threadIdx.x == 0)  // no items at all: every node list is empty
+    if (tile == 0 && threadIdx.x == 0) {  // no items at all: every node list is empty
       for (int b = 0; b <= p.B; ++b) p.unique_ptr[b] = 0;
+      if (p.counts_out) { p.counts_out[0] = p.seeds_ptr[p.B]; p.counts_out[2] = 0; }
+    }
     return;
   }
   const unsigned lt_mask = (1u << lane) - 1u;
@@ -577,6 +603,7 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelP
     int b = p.B;
     p.unique_ptr[b] = grand;
     while (b > 0 && p.item_ptr[b - 1] == n) p.unique_ptr[--b] = grand;
+    if (p.counts_out) { p.counts_out[0] = p.seeds_ptr[p.B]; p.counts_out[2] = grand; }
   }
 }
 
@@ -695,6 +722,21 @@ extern "C" int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr,
                                  int64_t* unique, int64_t U_cap, int64_t* unique_ptr,
                                  int64_t* out_row, int64_t* out_col, void* workspace,
                                  size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  return gsb::relabel_launch(seeds, seeds_ptr, B, S_max, coo_row, coo_col, edge_ptr, nullptr, nullptr,
+                             E_max, id_bound, unique, U_cap, unique_ptr, out_row, out_col, nullptr,
+                             workspace, workspace_bytes, d_err, cuda_stream);
+}
+
+// `sub_indptr` non-null: edge_ptr is derived on the device (edge_ptr_out[b] =
+// sub_indptr[seeds_ptr[b]]) instead of read; `counts_out` non-null: receives
+// {seeds_ptr[B], -, unique_ptr[B]}.  Both spare the layered sampler a launch.
+int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B, int64_t S_max,
+                        const int64_t* coo_row, const int64_t* coo_col, const int64_t* edge_ptr,
+                        const int64_t* sub_indptr, int64_t* edge_ptr_out, int64_t E_max,
+                        int64_t id_bound, int64_t* unique, int64_t U_cap, int64_t* unique_ptr,
+                        int64_t* out_row, int64_t* out_col, int64_t* counts_out, void* workspace,
+                        size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (sub_indptr) edge_ptr = edge_ptr_out;
   if (B < 1 || S_max < 0 || E_max < 0 || !seeds_ptr || !edge_ptr || !unique_ptr || U_cap < 0)
     return GSB_ERR_INVALID;
   if ((S_max > 0 && !seeds) || (E_max > 0 && !coo_row) || (U_cap > 0 && !unique)) return GSB_ERR_INVALID;
@@ -709,6 +751,7 @@ extern "C" int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr,
   RelabelParams p;
   p.seeds = (const i64*)seeds; p.seeds_ptr = (const i64*)seeds_ptr; p.coo_row = (const i64*)coo_row;
   p.coo_col = (const i64*)coo_col; p.edge_ptr = (const i64*)edge_ptr; p.B = (int)B;
+  p.sub_indptr = (const i64*)sub_indptr; p.edge_ptr_out = (i64*)edge_ptr_out; p.counts_out = (i64*)counts_out;
   p.S_max = S_max; p.E_max = E_max; p.unique = (i64*)unique; p.U_cap = U_cap;
   p.id_limit = id_bound > 0 && id_bound < 0xFFFFFFFFll ? (u64)id_bound : 0xFFFFFFFFull;
   p.unique_ptr = (i64*)unique_ptr; p.out_row = (i64*)out_row; p.out_col = (i64*)out_col;
