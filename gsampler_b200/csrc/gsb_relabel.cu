@@ -18,10 +18,11 @@
 //   scatter : (id, index) pairs grouped by bucket; every tile reserves a run
 //             per bucket, its 8-byte stores meet in L2            (streaming)
 //   dedupe  : CTA per bucket: shared table id -> smallest index, then
-//             min_idx[item] for every item of the bucket; a bucket whose ids
-//             do not fit the shared table falls back to a table in global
-//             memory that the CTA owns                            (streaming
-//             read + one scattered 4-byte store per item)
+//             min_idx[item] for every REPEATED item of the bucket (the scatter
+//             pass preset min_idx[item] = item); a bucket whose ids do not fit
+//             the shared table falls back to a table in global memory that
+//             the CTA owns                                        (streaming
+//             read + one scattered 4-byte store per repeat)
 //   count   : number of first occurrences per 1024-item tile      (streaming)
 //   tiles   : exclusive scan of those counts                      (one block)
 //   rank    : first occurrences get their position in `unique`    (streaming)
@@ -42,11 +43,26 @@ constexpr u32 IDX_UNSET = 0xFFFFFFFFu;
 constexpr int PT_TILE = 8192;          // items per CTA tile of pcount / scatter
 constexpr int PT_THREADS = 512;
 constexpr int PT_BATCH = 8;            // loads in flight per thread
-constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch (power of two)
-constexpr int PT_BUCKET_ITEMS = 3072;  // a minibatch gets pow2ceil(items / this) buckets
+constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
+#ifndef GSB_BUCKET_ITEMS
+#define GSB_BUCKET_ITEMS 3584
+#endif
+#ifndef GSB_DD_TAB
+#define GSB_DD_TAB 8192
+#endif
+#ifndef GSB_DD_MIN_CTAS
+#define GSB_DD_MIN_CTAS 3
+#endif
+#ifndef GSB_RANK_MIN_CTAS
+#define GSB_RANK_MIN_CTAS 8
+#endif
+#ifndef GSB_SCATTER_MIN_CTAS
+#define GSB_SCATTER_MIN_CTAS 1
+#endif
+constexpr int PT_BUCKET_ITEMS = GSB_BUCKET_ITEMS;  // a minibatch gets ceil(items / this) buckets
 constexpr int DD_THREADS = 512;
 constexpr int DD_BATCH = 8;            // items a dedupe thread keeps in registers
-constexpr int DD_TAB = 8192;           // shared-table slots of the dedupe CTA
+constexpr int DD_TAB = GSB_DD_TAB;           // shared-table slots of the dedupe CTA
 constexpr u32 KEY_EMPTY = 0xFFFFFFFFu;
 
 struct RelabelHeader {
@@ -80,7 +96,6 @@ struct RelabelParams {
   u32* min_idx;       // [items] smallest item index carrying the item's id
   u32* rank;          // [items] position in `unique`, valid for first occurrences
   i64* bucket_ptr;    // [B+1] first bucket of minibatch b
-  int* bucket_shift;  // [B] bucket of an id = hash >> shift (32: the single bucket 0)
   u32* bucket_start;  // [buckets+1] counts, then their exclusive scan (positions in `part`)
   u32* bucket_cursor; // [buckets] fill level during the scatter pass
   u64* part;          // [items] id:32 | index:32, grouped by bucket
@@ -98,7 +113,6 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
   for (int b0 = 0; b0 < p.B; b0 += blockDim.x) {
     const int b = b0 + threadIdx.x;
     i64 items = 0, nbk = 0;
-    int shift = 32;
     if (b < p.B) {
       i64 ns = p.seeds_ptr[b + 1] - p.seeds_ptr[b];
       i64 ne;
@@ -113,8 +127,7 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
       if (ns < 0 || ne < 0) { raise(p.err, ERRBIT_BAD_INPUT); ns = ns < 0 ? 0 : ns; ne = ne < 0 ? 0 : ne; }
       items = ns + ne;
       const i64 need = (items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS;
-      nbk = 1;
-      while (nbk < need && nbk < PT_MAX_BUCKETS) { nbk <<= 1; --shift; }
+      nbk = need < 1 ? 1 : (need > PT_MAX_BUCKETS ? PT_MAX_BUCKETS : need);
     }
     i64 tot_items, tot_bk;
     i64 ei = block_exclusive_scan(items, s_scan, &tot_items);
@@ -123,7 +136,6 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
     if (b < p.B) {
       p.item_ptr[b] = s_carry_items + ei;
       p.bucket_ptr[b] = s_carry_bk + eb;
-      p.bucket_shift[b] = shift;
     }
     __syncthreads();
     if (threadIdx.x == 0) { s_carry_items += tot_items; s_carry_bk += tot_bk; }
@@ -194,7 +206,7 @@ struct Segment {
   const i64* rows_b;   // its row ids, biased by -ns so that seeds and rows index by item offset
   u32 ns;              // number of seeds
   i64 bk0;             // first bucket
-  int nbk, shift;
+  int nbk;
 };
 
 __device__ __forceinline__ Segment load_segment(const RelabelParams& p, int b) {
@@ -208,7 +220,6 @@ __device__ __forceinline__ Segment load_segment(const RelabelParams& p, int b) {
   s.ns = (u32)ns;
   s.bk0 = p.bucket_ptr[b];
   s.nbk = (int)(p.bucket_ptr[b + 1] - s.bk0);
-  s.shift = p.bucket_shift[b];
   return s;
 }
 
@@ -216,10 +227,12 @@ __device__ __forceinline__ i64 segment_id(const Segment& s, u32 off) {
   return __ldg((off < s.ns ? s.seeds_b : s.rows_b) + off);
 }
 
-// Bucket of an id: the leading bits of its hash (shift in [22, 32]; the double
-// shift keeps shift == 32, one bucket, well defined).
-__device__ __forceinline__ u32 bucket_of(u32 key, int shift) {
-  return (hash32(key) >> (shift - 1)) >> 1;
+// Bucket of an id: its hash scaled to [0, nbk) -- any bucket count works, so a
+// minibatch gets exactly ceil(items / PT_BUCKET_ITEMS) buckets of near-equal
+// size.  The leading hash bits decide; the shared table inside a bucket uses
+// the trailing ones.
+__device__ __forceinline__ u32 bucket_of(u32 key, int nbk) {
+  return __umulhi(hash32(key), (u32)nbk);
 }
 
 // The ids of up to PT_BATCH items of a segment, PT_THREADS apart, loaded before
@@ -253,7 +266,7 @@ __global__ void __launch_bounds__(PT_THREADS) relabel_pcount_kernel(const Relabe
         GSB_LOAD_ID_BATCH(off0, lim)
 #pragma unroll
         for (int u = 0; u < PT_BATCH; ++u)
-          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.shift)], 1u);
+          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.nbk)], 1u);
       }
       __syncthreads();
       for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS)
@@ -303,7 +316,7 @@ __global__ void relabel_pscan_kernel(const RelabelParams p) {
 // L1/L2); the 8-byte stores of a run meet in L2 before they reach DRAM.
 // (Sorting the tile in shared memory first, to write whole runs, measured the
 // same 0.23 ms per 23 M items.)
-__global__ void __launch_bounds__(PT_THREADS) relabel_scatter_kernel(const RelabelParams p) {
+__global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scatter_kernel(const RelabelParams p) {
   __shared__ u32 s_hist[PT_MAX_BUCKETS];  // items of the bucket in this tile
   __shared__ u32 s_next[PT_MAX_BUCKETS];  // next free position of the bucket's run in `part`
   const i64 n = p.hdr->n_items;
@@ -323,7 +336,7 @@ __global__ void __launch_bounds__(PT_THREADS) relabel_scatter_kernel(const Relab
         GSB_LOAD_ID_BATCH(off0, lim)
 #pragma unroll
         for (int u = 0; u < PT_BATCH; ++u)
-          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.shift)], 1u);
+          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.nbk)], 1u);
       }
       __syncthreads();
       for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) {
@@ -337,8 +350,9 @@ __global__ void __launch_bounds__(PT_THREADS) relabel_scatter_kernel(const Relab
         for (int u = 0; u < PT_BATCH; ++u) {
           const u32 off = off0 + (u32)(u * PT_THREADS);
           if ((u64)id[u] < p.id_limit) {
-            const u32 dst = atomicAdd(&s_next[bucket_of((u32)id[u], sg.shift)], 1u);
+            const u32 dst = atomicAdd(&s_next[bucket_of((u32)id[u], sg.nbk)], 1u);
             p.part[dst] = ((u64)(u32)id[u] << 32) | off;
+            p.min_idx[sg.ibase + off] = off;  // "first occurrence" until the dedupe pass says otherwise
           } else if (off < lim) {
             raise(p.err, ERRBIT_BAD_INPUT);  // negative, or not below the stated bound
             p.min_idx[sg.ibase + off] = IDX_UNSET;
@@ -370,7 +384,7 @@ __device__ __forceinline__ u32 stab_insert(u32* s_key, u32* s_min, u32 tab, u32 
 // id repeated thousands of times costs nothing extra.  A bucket of at most
 // DD_BATCH * DD_THREADS items (the normal case) stays in registers between the
 // two phases together with the table slot each item found.
-__global__ void __launch_bounds__(DD_THREADS, 3) relabel_dedupe_kernel(const RelabelParams p) {
+__global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_kernel(const RelabelParams p) {
   extern __shared__ __align__(16) unsigned char dd_smem[];
   u32* s_key = reinterpret_cast<u32*>(dd_smem);
   u32* s_min = s_key + DD_TAB;
@@ -413,7 +427,10 @@ __global__ void __launch_bounds__(DD_THREADS, 3) relabel_dedupe_kernel(const Rel
       if (!s_over) {
 #pragma unroll
         for (int u = 0; u < DD_BATCH; ++u)
-          if (it[u] != ~0ull) out[(u32)it[u]] = s_min[slot[u]];
+          if (it[u] != ~0ull) {
+            const u32 m = s_min[slot[u]];
+            if (m != (u32)it[u]) out[(u32)it[u]] = m;  // first occurrences were preset by the scatter pass
+          }
         __syncthreads();
         continue;
       }
@@ -430,7 +447,7 @@ __global__ void __launch_bounds__(DD_THREADS, 3) relabel_dedupe_kernel(const Rel
           const u32 key = (u32)(it >> 32);
           u32 pos = hash32(key) & mask;
           for (u32 probes = 0; s_key[pos] != key && probes < tab; ++probes) pos = (pos + 1) & mask;
-          out[(u32)it] = s_min[pos];
+          if (s_min[pos] != (u32)it) out[(u32)it] = s_min[pos];
         }
         __syncthreads();
         continue;
@@ -530,7 +547,7 @@ __global__ void relabel_tiles_kernel(const RelabelParams p) {
   if (threadIdx.x == 0 && (total > p.U_cap || total >= 0x7FFFFFFFll)) raise(p.err, ERRBIT_CAPACITY);
 }
 
-__global__ void __launch_bounds__(RL_THREADS) relabel_rank_kernel(const RelabelParams p) {
+__global__ void __launch_bounds__(RL_THREADS, GSB_RANK_MIN_CTAS) relabel_rank_kernel(const RelabelParams p) {
   __shared__ int s_warp[RL_THREADS / 32];
   const i64 n = p.hdr->n_items;
   const i64 tiles = p.hdr->n_tiles;
@@ -632,8 +649,14 @@ __device__ __forceinline__ void edge_cursor_load(const RelabelParams& p, EdgeCur
   c.rank_b = p.rank + p.item_ptr[c.b];
 }
 
-__global__ void __launch_bounds__(RL_THREADS) relabel_emit_kernel(const RelabelParams p) {
-  constexpr int EB = 4;
+#ifndef GSB_EMIT_EB
+#define GSB_EMIT_EB 2
+#endif
+#ifndef GSB_EMIT_MIN_CTAS
+#define GSB_EMIT_MIN_CTAS 8
+#endif
+__global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_kernel(const RelabelParams p) {
+  constexpr int EB = GSB_EMIT_EB;
   const i64 n = p.hdr->n_edges;
   for (i64 e_cta = (i64)blockIdx.x * (EB * RL_THREADS); e_cta < n; e_cta += (i64)gridDim.x * (EB * RL_THREADS)) {
     EdgeCursor c;
@@ -678,7 +701,7 @@ __global__ void __launch_bounds__(RL_THREADS) relabel_emit_kernel(const RelabelP
 }
 
 struct RelabelLayout {
-  size_t hdr, item_ptr, bucket_ptr, bucket_shift, tile_count, bucket_start, bucket_cursor, min_idx,
+  size_t hdr, item_ptr, bucket_ptr, tile_count, bucket_start, bucket_cursor, min_idx,
       rank, part, overflow, total;
   i64 tiles, buckets_cap;
 };
@@ -688,13 +711,12 @@ static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
   const i64 items = S_max + E_max;
   L.tiles = (items + RL_TILE - 1) / RL_TILE + 1;
-  // a minibatch of n items has at most max(1, 2n / PT_BUCKET_ITEMS) buckets
-  L.buckets_cap = B + (2 * items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS + 1;
+  // a minibatch of n items has ceil(n / PT_BUCKET_ITEMS) buckets, at least one
+  L.buckets_cap = B + (items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS + 1;
   size_t o = 0;
   L.hdr = o; o = up(o + sizeof(RelabelHeader));
   L.item_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
   L.bucket_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
-  L.bucket_shift = o; o = up(o + sizeof(int) * (size_t)(B + 1));
   L.tile_count = o; o = up(o + sizeof(u32) * (size_t)(L.tiles + 1));
   L.bucket_start = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
   L.bucket_cursor = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
@@ -758,7 +780,7 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   p.hdr = (RelabelHeader*)(ws + L.hdr); p.item_ptr = (i64*)(ws + L.item_ptr);
   p.tile_count = (u32*)(ws + L.tile_count); p.min_idx = (u32*)(ws + L.min_idx);
   p.rank = (u32*)(ws + L.rank); p.err = d_err;
-  p.bucket_ptr = (i64*)(ws + L.bucket_ptr); p.bucket_shift = (int*)(ws + L.bucket_shift);
+  p.bucket_ptr = (i64*)(ws + L.bucket_ptr);
   p.bucket_start = (u32*)(ws + L.bucket_start); p.bucket_cursor = (u32*)(ws + L.bucket_cursor);
   p.part = (u64*)(ws + L.part); p.overflow = (u64*)(ws + L.overflow); p.buckets_cap = L.buckets_cap;
 
@@ -780,7 +802,7 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   { LaunchScope ls(KID_RL_TILES, st); relabel_tiles_kernel<<<1, 1024, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_SCAN, st); relabel_rank_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   if (out_row && E_max > 0) {
-    int g_edges = (int)((E_max + 4 * RL_THREADS - 1) / (4 * RL_THREADS));
+    int g_edges = (int)((E_max + GSB_EMIT_EB * RL_THREADS - 1) / (GSB_EMIT_EB * RL_THREADS));
     if (g_edges > 148 * 16) g_edges = 148 * 16;
     { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<g_edges, RL_THREADS, 0, st>>>(p); }
   }
