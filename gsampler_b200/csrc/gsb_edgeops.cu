@@ -153,6 +153,29 @@ __global__ void __launch_bounds__(EO_THREADS) sddmm_coo_kernel(const CooParams p
   }
 }
 
+// out[eid, f] = sum_k lhs[sel_l, off_l(f) * reduce + k] * rhs[sel_r, off_r(f) * reduce + k];
+// warp per (edge, f), lanes over k.
+__global__ void __launch_bounds__(EO_THREADS) sddmm_coo_dot_kernel(const CooParams p, i64 reduce) {
+  const int lane = threadIdx.x & 31;
+  const i64 total = p.nnz * p.out_len;
+  const i64 warp0 = ((i64)blockIdx.x * EO_THREADS + threadIdx.x) >> 5;
+  const i64 nwarps = ((i64)gridDim.x * EO_THREADS) >> 5;
+  for (i64 t = warp0; t < total; t += nwarps) {
+    const i64 ed = t / p.out_len, f = t - ed * p.out_len;
+    const i64 src = __ldg(p.row + ed), dst = __ldg(p.col + ed);
+    const i64 eid = p.e_ids ? __ldg(p.e_ids + ed) : ed;
+    const i64 lo = p.lhs_off ? p.lhs_off[f] : (p.lhs_len == reduce ? 0 : f);
+    const i64 ro = p.rhs_off ? p.rhs_off[f] : (p.rhs_len == reduce ? 0 : f);
+    const float* l = p.lhs + select_target(p.lhs_target, src, eid, dst) * p.lhs_len + lo * reduce;
+    const float* r = p.rhs + select_target(p.rhs_target, src, eid, dst) * p.rhs_len + ro * reduce;
+    float acc = 0.f;
+    for (i64 k = lane; k < reduce; k += 32) acc += __ldg(l + k) * __ldg(r + k);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+    if (lane == 0) p.out[eid * p.out_len + f] = acc;
+  }
+}
+
 // sum-SpMM on an unsorted COO: atomicAdd per (edge, feature).  lhs = node
 // feature of the OTHER endpoint, rhs = edge feature.
 __global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_kernel(const CooParams p) {
@@ -254,6 +277,25 @@ extern "C" int gsb_spmm_coo_sum(const int64_t* row, const int64_t* col, const in
   cudaStream_t st = (cudaStream_t)cuda_stream;
   LaunchScope ls(KID_EDGE_SUM, st);
   spmm_coo_sum_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_sddmm_coo_dot(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                                 int64_t nnz, const float* lhs, int64_t lhs_len, int lhs_target,
+                                 const float* rhs, int64_t rhs_len, int rhs_target,
+                                 const int64_t* lhs_off, const int64_t* rhs_off, int64_t reduce,
+                                 float* out, int64_t out_len, void* cuda_stream) {
+  if (nnz == 0) return GSB_OK;
+  if (!row || !col || !lhs || !rhs || !out || nnz < 0 || reduce < 1 || out_len < 1 ||
+      lhs_len < reduce || rhs_len < reduce || lhs_len % reduce || rhs_len % reduce)
+    return GSB_ERR_INVALID;
+  if (lhs_target < 0 || lhs_target > 2 || rhs_target < 0 || rhs_target > 2) return GSB_ERR_INVALID;
+  CooParams p{(const i64*)row, (const i64*)col, (const i64*)e_ids, nnz, OP_MUL, lhs, lhs_len, lhs_target,
+              rhs, rhs_len, rhs_target, (const i64*)lhs_off, (const i64*)rhs_off, out, out_len, 0};
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  LaunchScope ls(KID_EDGE_OP, st);
+  sddmm_coo_dot_kernel<<<wide_grid(nnz * out_len * 32, EO_THREADS), EO_THREADS, 0, st>>>(p, reduce);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

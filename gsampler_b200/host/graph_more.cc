@@ -267,7 +267,8 @@ int OpCode(const std::string& op) {
   if (op == "div") return OP_DIV;
   if (op == "copy_lhs") return OP_COPY_LHS;
   if (op == "copy_rhs") return OP_COPY_RHS;
-  TORCH_CHECK(false, "unsupported binary op '", op, "' (add, sub, mul, div, copy_lhs, copy_rhs)");
+  TORCH_CHECK(false, "unsupported binary op '", op,
+              "' (add, sub, mul, div, copy_lhs, copy_rhs; dot in SDDMM only)");
 }
 int ReduceCode(const std::string& r) {
   if (r == "sum") return 0;
@@ -353,6 +354,27 @@ void Graph::SDDMM(const std::string& op, OptTensor lhs, OptTensor rhs, torch::Te
   TORCH_CHECK(on_format == kCOO || on_format == kCSC || on_format == kCSR, "SDDMM: bad format");
   CreateSparseFormat(kCOO);
   c10::cuda::CUDAGuard guard(out.device());
+  if (op == "dot") {
+    // contraction over the last feature dimension (src/cuda/functor.h:119-138); the leading
+    // feature dimensions broadcast as for the other ops
+    Feature l = AsFeature(lhs, true, "lhs"), r = AsFeature(rhs, true, "rhs");
+    TORCH_CHECK(!l.shape.empty() && !r.shape.empty() && l.shape.back() == r.shape.back(),
+                "SDDMM dot: operands need equal last dimensions");
+    const int64_t reduce = l.shape.back();
+    Feature lp = l, rp = r;
+    lp.shape.pop_back(); rp.shape.pop_back();
+    lp.len = l.len / reduce; rp.len = r.len / reduce;
+    const Bcast bc = MakeBcast(lp, true, rp, true, out.device());
+    TORCH_CHECK(out.is_cuda() && out.scalar_type() == torch::kFloat32 && out.is_contiguous() &&
+                    out.numel() == num_edges_ * bc.out_len,
+                "SDDMM dot: out must be contiguous float32 [num_edges, ", bc.out_len, "(, 1)]");
+    CheckStatus(gsb_sddmm_coo_dot(P(coo_->row), P(coo_->col), EidPtr(coo_->e_ids), coo_->row.numel(),
+                                  l.ptr, l.len, (int)lhs_target, r.ptr, r.len, (int)rhs_target,
+                                  OffPtr(bc.lhs_off), OffPtr(bc.rhs_off), reduce,
+                                  out.data_ptr<float>(), bc.out_len, CurrentStream()),
+                "sddmm_dot");
+    return;
+  }
   const int code = OpCode(op);
   const Feature l = AsFeature(lhs, UsesLhs(code), "lhs"), r = AsFeature(rhs, UsesRhs(code), "rhs");
   const Bcast bc = MakeBcast(l, UsesLhs(code), r, UsesRhs(code), out.device());

@@ -217,18 +217,22 @@ class BatchMatrix(Matrix):
 class GraphSAGEResult:
     """Pending result of :meth:`BatchMatrix.graphsage_async`."""
 
-    _NARROW = (0, 1, 2, 3, None, 5, None, 7, 8)   # which count bounds which of a layer's 9 tensors
+    _pinned = {}      # free pinned count buffers by length (page-locking memory is slow)
 
     def __init__(self, tensors, num_layers, inputs):
         self._t = tensors
         self._L = num_layers
         self._inputs = inputs                      # kept alive until the kernels have run
-        self._host = torch.empty(3 * num_layers + 1, dtype=torch.int64, pin_memory=True)
+        free = GraphSAGEResult._pinned.setdefault(3 * num_layers + 1, [])
+        self._host = free.pop() if free else torch.empty(3 * num_layers + 1, dtype=torch.int64,
+                                                         pin_memory=True)
         self._host.copy_(tensors[-1], non_blocking=True)
         self._done = torch.cuda.Event()
         self._done.record()
 
     def wait(self):
+        if self._host is None:
+            return self._result
         self._done.synchronize()
         c = self._host.tolist()
         if c[3 * self._L]:
@@ -239,4 +243,7 @@ class GraphSAGEResult:
             t = self._t[9 * l:9 * l + 9]
             out += [t[0][:S + 1], t[1][:E], t[2][:E], t[3][:E], t[4], t[5][:U], t[6], t[7][:E], t[8][:E]]
         out.append(self._host[:3 * self._L].clone())
+        GraphSAGEResult._pinned[3 * self._L + 1].append(self._host)
+        self._host = None
+        self._result = out
         return out

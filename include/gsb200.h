@@ -298,6 +298,16 @@ GSB_API int gsb_sddmm_coo(const int64_t* row, const int64_t* col, const int64_t*
                           int64_t nnz, int op, const float* lhs, int64_t lhs_len, int lhs_target,
                           const float* rhs, int64_t rhs_len, int rhs_target, const int64_t* lhs_off,
                           const int64_t* rhs_off, float* out, int64_t out_len, void* cuda_stream);
+/* The `dot` edge map: out[eid, f] = sum over k < reduce of lhs[sel, off_l(f) * reduce + k] *
+ * rhs[sel, off_r(f) * reduce + k]; features are [n, len] with len a multiple of `reduce`, the
+ * offset tables (NULL = identity, or 0 for an operand of one group) index groups of `reduce`
+ * values.  Replaces the binary::Dot instantiation of SDDMMCOO (src/cuda/functor.h:119-138,
+ * src/cuda/sddmm.cu:23-61,186). */
+GSB_API int gsb_sddmm_coo_dot(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                              int64_t nnz, const float* lhs, int64_t lhs_len, int lhs_target,
+                              const float* rhs, int64_t rhs_len, int rhs_target,
+                              const int64_t* lhs_off, const int64_t* rhs_off, int64_t reduce,
+                              float* out, int64_t out_len, void* cuda_stream);
 
 /* ------------------------------------------------------------------ collective sampling
  * gsb_list_sample: for every segment [range[b], range[b+1]) choose min(K, len)

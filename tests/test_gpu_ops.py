@@ -168,6 +168,21 @@ def test_spmm_sddmm_against_oracle(gsb, oracle, graph):
     assert np.allclose(host(out), ref, **tol)
     out = gsb.ops.gsddmm(m, "add", cuda(u, torch.float32), cuda(u[:, :1].copy(), torch.float32), "u", "v")
     assert np.allclose(host(out), u[indices] + u[col, :1], **tol)
+    # dot over the last feature dimension: plain vectors, multi-head, and one shared operand
+    v = rng.random((n, 40)).astype(np.float32)
+    out = gsb.ops.gsddmm(m, "dot", cuda(v, torch.float32), cuda(v, torch.float32), "u", "v")
+    assert out.shape == (E, 1)
+    assert np.allclose(host(out)[:, 0], (v[indices] * v[col]).sum(-1), rtol=1e-5, atol=1e-5)
+    h = rng.random((n, 3, 8)).astype(np.float32)
+    out = gsb.ops.gsddmm(m, "dot", cuda(h, torch.float32), cuda(h, torch.float32), "u", "v")
+    assert out.shape == (E, 3, 1)
+    assert np.allclose(host(out)[..., 0], (h[indices] * h[col]).sum(-1), rtol=1e-5, atol=1e-5)
+    h1 = rng.random((n, 1, 8)).astype(np.float32)
+    out = gsb.ops.gsddmm(m, "dot", cuda(h, torch.float32), cuda(h1, torch.float32), "v", "u")
+    assert np.allclose(host(out)[..., 0], (h[col] * h1[indices]).sum(-1), rtol=1e-5, atol=1e-5)
+    ew = rng.random((E, 8)).astype(np.float32)
+    out = gsb.ops.gsddmm(m, "dot", cuda(ew, torch.float32), cuda(h1[:, 0].copy(), torch.float32), "e", "v")
+    assert np.allclose(host(out)[:, 0], (ew * h1[col, 0]).sum(-1), rtol=1e-5, atol=1e-5)
 
 
 def test_list_sampling(gsb, oracle):
