@@ -40,9 +40,15 @@ constexpr int RL_ITEMS = 4;
 constexpr int RL_TILE = RL_THREADS * RL_ITEMS;
 constexpr u64 SLOT_EMPTY = ~0ull;
 constexpr u32 IDX_UNSET = 0xFFFFFFFFu;
-constexpr int PT_TILE = 8192;          // items per CTA tile of pcount / scatter
+#ifndef GSB_PT_TILE
+#define GSB_PT_TILE 8192
+#endif
+#ifndef GSB_PT_BATCH
+#define GSB_PT_BATCH 8
+#endif
+constexpr int PT_TILE = GSB_PT_TILE;   // items per CTA tile of pcount / scatter
 constexpr int PT_THREADS = 512;
-constexpr int PT_BATCH = 8;            // loads in flight per thread
+constexpr int PT_BATCH = GSB_PT_BATCH; // loads in flight per thread
 constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
 #ifndef GSB_BUCKET_ITEMS
 #define GSB_BUCKET_ITEMS 3584
@@ -57,7 +63,7 @@ constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
 #define GSB_RANK_MIN_CTAS 8
 #endif
 #ifndef GSB_SCATTER_MIN_CTAS
-#define GSB_SCATTER_MIN_CTAS 1
+#define GSB_SCATTER_MIN_CTAS 2
 #endif
 constexpr int PT_BUCKET_ITEMS = GSB_BUCKET_ITEMS;  // a minibatch gets ceil(items / this) buckets
 constexpr int DD_THREADS = 512;
