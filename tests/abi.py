@@ -116,7 +116,8 @@ def slice_cols(indptr, indices, seeds, col_bptr=None, encoding_size=0):
     return sub, rows, cols, sel, int(err[0])
 
 
-def batch_relabel(seeds, seeds_ptr, coo_row, coo_col, edge_ptr, want_edges=True, U_cap=None):
+def batch_relabel(seeds, seeds_ptr, coo_row, coo_col, edge_ptr, want_edges=True, U_cap=None,
+                  id_bound=0):
     import torch
 
     dev = seeds_ptr.device
@@ -133,7 +134,7 @@ def batch_relabel(seeds, seeds_ptr, coo_row, coo_col, edge_ptr, want_edges=True,
     ws = torch.empty(L.gsb_batch_relabel_workspace_bytes(i64(S), i64(E), i64(B)) + 256,
                      dtype=torch.uint8, device=dev)
     check(L.gsb_batch_relabel(ptr(seeds), ptr(seeds_ptr), i64(B), i64(S), ptr(coo_row),
-                              ptr(coo_col if want_edges else None), ptr(edge_ptr), i64(E), i64(0),
+                              ptr(coo_col if want_edges else None), ptr(edge_ptr), i64(E), i64(id_bound),
                               ptr(unique), i64(U_cap), ptr(uptr), ptr(orow), ptr(ocol), ptr(ws),
                               C.c_size_t(ws.numel()), ptr(err), st), "gsb_batch_relabel")
     torch.cuda.synchronize()

@@ -149,6 +149,44 @@ def test_relabel_reports_bad_ids():
     rows = dev([5, 2 ** 33, -4])
     uq, up, orow, ocol, err = abi.batch_relabel(seeds, dev([0, 3]), rows, dev([0, 1, 2]), dev([0, 3]))
     assert err & 16
+    # a stated bound: ids at or above it are reported and relabelled to -1, the rest is exact
+    rows = dev([5, 9, 2, 10, 7])
+    uq, up, orow, ocol, err = abi.batch_relabel(seeds, dev([0, 3]), rows, dev([0, 0, 1, 2, 2]), dev([0, 5]),
+                                                id_bound=10)
+    assert err & 16
+    assert host(uq).tolist() == [1, 2, 3, 5, 9, 7] and host(orow).tolist() == [3, 4, 1, -1, 5]
+    assert host(ocol).tolist() == [0, 0, 1, 2, 2]
+
+
+@pytest.mark.parametrize("case", ["streamed_buckets", "table_overflow", "hub", "two_big"])
+def test_batch_relabel_large_minibatches(oracle, case):
+    """Minibatches far larger than a sampler produces: buckets too large for the register path
+    (streamed twice), more distinct ids than the shared table holds (CTA-owned table in global
+    memory), and one id repeated hundreds of thousands of times."""
+    rng = np.random.default_rng(len(case))
+    if case == "streamed_buckets":      # 1024 buckets of ~5 000 items
+        sizes, nid = [(1000, 5_200_000)], 3_000_000
+    elif case == "table_overflow":      # 1024 buckets of ~9 300 mostly distinct ids
+        sizes, nid = [(50_000, 9_500_000)], 2 ** 31 - 5
+    elif case == "hub":
+        sizes, nid = [(100, 400_000), (50, 30_000)], 50_000
+    else:
+        sizes, nid = [(20_000, 1_500_000), (0, 0), (30_000, 2_500_000)], 400_000
+    ns = np.array([s for s, _ in sizes]); ne = np.array([e for _, e in sizes])
+    sp = np.concatenate([[0], np.cumsum(ns)]); ep = np.concatenate([[0], np.cumsum(ne)])
+    seeds = rng.integers(0, nid, sp[-1])
+    rows = rng.integers(0, nid, ep[-1])
+    if case == "hub":
+        rows[rng.random(rows.size) < 0.9] = 4242
+    col_local = np.sort(np.concatenate([rng.integers(sp[b], sp[b + 1], ne[b]) if ns[b] else
+                                        np.empty(0, np.int64) for b in range(len(sizes))])).astype(np.int64)
+    uq, up, orow, ocol, err = abi.batch_relabel(dev(seeds), dev(sp), dev(rows), dev(col_local), dev(ep))
+    assert err == 0
+    euq, eup, eorow, eocol = oracle.batch_coo_relabel(seeds, sp, seeds[col_local], rows, ep)
+    assert np.array_equal(host(up), eup)
+    assert np.array_equal(host(uq), euq)
+    assert np.array_equal(host(orow), eorow)
+    assert np.array_equal(host(ocol), eocol)
 
 
 def test_sampler_statistics_vs_reference(oracle):
