@@ -102,6 +102,8 @@ class ClockSampler(threading.Thread):
 # `ncu --set full` capture of the "medium" case summarised under profiles/; the access pattern
 # per unit is the same on the bench workload, so the per-launch traffic is scaled by the units.
 NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 94.3}
+# the same capture summed over all kernels and layers of one super-batch, per sampled edge
+NCU_PATH_DRAM_BYTES_PER_EDGE = 183.1
 
 
 def ncu_traffic(kernel, mean_edges):
@@ -170,6 +172,26 @@ def cpu_reference_run(cfg, indptr_np, indices_np, steps, warmup, minibatches, sa
     desc = "%d steps x %d minibatches of %d seeds, %d layers, oracle %s sampler + batch relabel" % (
         steps, minibatches, cfg["batch"], len(cfg["fanouts"]), sampler)
     return total_edges / total_t, desc, gs_oracle.num_threads(), total_t / steps * 1e3
+
+
+def cpu_sort_indices_run(indptr_np, indices_np, max_edges=20_000_000):
+    """The one CPU routine the reference owns on this path -- SortIndicesCPU, an OpenMP parallel
+    for over columns with a qsort each (src/cpu/sort_indices.cc:27-48 in gSampler, the node2vec
+    preprocessing of a graph kept in host memory) -- timed as restated in oracle/ on the leading
+    columns of the bench graph with their row ids shuffled."""
+    from oracle import gs_oracle
+
+    ncols = int(np.searchsorted(indptr_np, max_edges, side="right")) - 1
+    ncols = max(ncols, 1)
+    ip = np.ascontiguousarray(indptr_np[:ncols + 1])
+    idx = np.random.default_rng(11).permutation(indices_np[:ip[-1]])
+    t0 = time.perf_counter()
+    out = gs_oracle.sort_indices(ip, idx)
+    dt = time.perf_counter() - t0
+    assert out.size == idx.size
+    return {"what": "SortIndicesCPU algorithm (per-column qsort under OpenMP)", "columns": ncols,
+            "edges": int(ip[-1]), "seconds": dt, "edges_per_sec": float(ip[-1]) / dt,
+            "cores": gs_oracle.num_threads()}
 
 
 def run_reference(args, cfg, rank, world):
@@ -345,12 +367,15 @@ def main():
     def e2e_run(first, count):
         edges, nin, nout = 0, 0, 0
         pending = []
+        t_run = time.perf_counter()
         for k in range(count + 1):
             if k < count:
                 pending.append(e2e_submit(first + k))
             if k >= 1:
                 fut, nbytes = pending.pop(0)
                 cnt = fut.wait()[-1]
+                if os.environ.get("GSB_E2E_TRACE"):
+                    sys.stderr.write("e2e step %d done at %.3f ms\n" % (k, (time.perf_counter() - t_run) * 1e3))
                 edges += int(cnt.view(L, 3)[:, 1].sum())
                 nin += nbytes
                 nout += (3 * L + 1) * 8
@@ -362,9 +387,14 @@ def main():
     gc.collect()
     gc.disable()          # a collection inside the ~20 ms timed region would be most of it
     t0 = time.perf_counter()
+    ms0 = torch.cuda.memory_stats(dev) if os.environ.get("GSB_E2E_TRACE") else None
     e2e_edges, h2d, d2h = e2e_run(args.warmup, args.steps)
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3   # host clock around copies, launches and reads
+    if ms0 is not None:
+        ms1 = torch.cuda.memory_stats(dev)
+        for key in ("num_device_alloc", "num_device_free", "num_alloc_retries", "reserved_bytes.all.current"):
+            sys.stderr.write("memstat %s %s -> %s\n" % (key, ms0.get(key), ms1.get(key)))
     gc.enable()
 
     # ---- reduce over ranks: slowest rank's time, summed edges
@@ -430,7 +460,12 @@ def main():
                          "avg_launch_ms": dms / dcnt},
             "roofline_path": {"algorithmic_gb_per_step": path_bytes / args.steps / 1e9,
                               "achieved": path_gbs, "unit": "GB/s", "frac": path_gbs / peak,
-                              "peak_kind": peak_kind},
+                              "peak_kind": peak_kind,
+                              # DRAM traffic (ncu, scaled by edges) over the same time: how busy HBM is
+                              "dram_traffic_gbs": NCU_PATH_DRAM_BYTES_PER_EDGE * (edges / max(world, 1))
+                                                  / (elapsed_ms / 1e3) / 1e9,
+                              "dram_traffic_frac": NCU_PATH_DRAM_BYTES_PER_EDGE * (edges / max(world, 1))
+                                                   / (elapsed_ms / 1e3) / 1e9 / peak},
             "kernels": {"%s[%d]" % k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(by.items())},
             "clocks": clocks.summary(),
         }
@@ -439,7 +474,8 @@ def main():
             eps, desc, cores, _ = cpu_reference_run(cfg, indptr_np, indices_np, steps=3, warmup=1,
                                                     minibatches=4, sampler="ref")
             line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port",
-                                    "sample": desc}
+                                    "sample": desc,
+                                    "reference_cpu_code": cpu_sort_indices_run(indptr_np, indices_np)}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -39,40 +39,54 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGEAsync(torch::Tensor seeds, torch
   TORCH_CHECK(L >= 1 && B >= 1, "need at least one layer and one minibatch");
   auto opt = torch::dtype(torch::kInt64).device(seeds.device());
   std::vector<gsb_layer_buffers> bufs((size_t)L);
-  std::vector<torch::Tensor> keep;
+  // Capacities first, then ONE allocation for the 9 L output arrays, the counts and the
+  // workspace: a call costs the caching allocator a single block of a size that repeats from
+  // call to call, instead of 28 blocks whose best-fit splitting keeps the pool from settling.
+  std::vector<int64_t> sizes;  // int64 words of every output array, in return order
   int64_t S_cap = S0;
   for (int l = 0; l < L; ++l) {
     TORCH_CHECK(fanouts[l] >= 1, "fanout must be positive");
-    int64_t E_cap = S_cap * fanouts[l];
-    gsb_layer_buffers& b = bufs[(size_t)l];
-    b.S_cap = S_cap;
-    b.E_cap = E_cap;
-    auto mk = [&](int64_t n) { keep.push_back(torch::empty({n}, opt)); return keep.back().data_ptr<int64_t>(); };
-    b.sub_indptr = mk(S_cap + 1);
-    b.rows = mk(E_cap);
-    b.cols = mk(E_cap);
-    b.sel = mk(E_cap);
-    b.edge_ptr = mk(B + 1);
-    b.unique = mk(S_cap + E_cap);
-    b.unique_ptr = mk(B + 1);
-    b.block_row = mk(E_cap);
-    b.block_col = mk(E_cap);
+    const int64_t E_cap = S_cap * fanouts[l];
+    bufs[(size_t)l].S_cap = S_cap;
+    bufs[(size_t)l].E_cap = E_cap;
+    for (int64_t n : {S_cap + 1, E_cap, E_cap, E_cap, B + 1, S_cap + E_cap, B + 1, E_cap, E_cap})
+      sizes.push_back(n);
     S_cap = S_cap + E_cap;
   }
-  auto counts = torch::zeros({3 * L + 1}, opt);  // last entry: device error word
+  sizes.push_back(3 * L + 1);  // counts; last entry: device error word
+  auto round32 = [](int64_t words) { return (words + 31) & ~(int64_t)31; };  // 256-byte steps
+  int64_t total_words = 0;
+  for (int64_t n : sizes) total_words += round32(n);
   const size_t ws_bytes = gsb_graphsage_workspace_bytes(B, L, bufs.data(), fanouts.data());
-  auto ws = NewWorkspace(ws_bytes, seeds.device());
+  auto arena = torch::empty({total_words + (int64_t)((ws_bytes + 7) / 8)}, opt);
+  std::vector<torch::Tensor> keep;
+  int64_t at = 0;
+  for (int64_t n : sizes) { keep.push_back(arena.narrow(0, at, n)); at += round32(n); }
+  for (int l = 0; l < L; ++l) {
+    gsb_layer_buffers& b = bufs[(size_t)l];
+    const size_t o = (size_t)l * 9;
+    b.sub_indptr = keep[o + 0].data_ptr<int64_t>();
+    b.rows = keep[o + 1].data_ptr<int64_t>();
+    b.cols = keep[o + 2].data_ptr<int64_t>();
+    b.sel = keep[o + 3].data_ptr<int64_t>();
+    b.edge_ptr = keep[o + 4].data_ptr<int64_t>();
+    b.unique = keep[o + 5].data_ptr<int64_t>();
+    b.unique_ptr = keep[o + 6].data_ptr<int64_t>();
+    b.block_row = keep[o + 7].data_ptr<int64_t>();
+    b.block_col = keep[o + 8].data_ptr<int64_t>();
+  }
+  auto counts = keep.back();
+  counts.zero_();
+  void* ws = arena.data_ptr<int64_t>() + total_words;
   const int dtype = csc_->indices.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
   CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype,
                                    std::max(num_rows_, num_cols_), P(seeds),
                                    P(seeds_ptr), B, S0, L, fanouts.data(), GetSeedU64(),
-                                   bufs.data(), counts.data_ptr<int64_t>(), ws.data_ptr(),
-                                   (size_t)ws.numel(),
+                                   bufs.data(), counts.data_ptr<int64_t>(), ws, ws_bytes,
                                    (int*)(counts.data_ptr<int64_t>() + 3 * L), CurrentStream()),
               "graphsage_sample");
-  // the workspace is released to the caching allocator here; it stays valid for the
-  // kernels already enqueued because the allocator reuses a block on its own stream only
-  keep.push_back(counts);
+  // every returned tensor is a view of the one arena (which therefore lives as long as any
+  // of them); the workspace sits at its end
   return keep;
 }
 
