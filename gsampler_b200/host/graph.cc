@@ -179,6 +179,18 @@ torch::Tensor Graph::MapThroughEids(const c10::optional<torch::Tensor>& e_ids,
   return e_ids.value().index_select(0, select);
 }
 
+// data[index] for a caller-supplied id map: bounds-checked on the device and reported here as an
+// exception (never as a device assert).  The operators that use it synchronise anyway.
+static torch::Tensor CheckedIdGather(const torch::Tensor& data, const torch::Tensor& index,
+                                     const char* what) {
+  CheckIds(data, what);
+  CheckIds(index, "index");
+  CheckAsyncErrors();  // do not blame this call for an older, unreported error
+  auto out = GatherRows(data, index);
+  CheckAsyncErrors();
+  return out;
+}
+
 // ------------------------------------------------------------------ kernels glue
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SampleCompressed(
     const Compressed& src, const c10::optional<torch::Tensor>& seeds, int64_t fanout, bool replace,
@@ -416,7 +428,7 @@ Graph::GraphRelabel(torch::Tensor col_seeds, torch::Tensor row_ids) {
   CreateSparseFormat(kCOO);
   TORCH_CHECK(col_seeds.numel() == num_cols_ || coo_->col.numel() == 0,
               "GraphRelabel: col_seeds must hold one id per column");
-  torch::Tensor coo_row = row_ids.numel() > 0 ? row_ids.index_select(0, coo_->row) : coo_->row;
+  torch::Tensor coo_row = row_ids.numel() > 0 ? CheckedIdGather(row_ids, coo_->row, "row_ids") : coo_->row;
   auto r = RelabelImpl(col_seeds, Ptr2(col_seeds.numel(), col_seeds), coo_row, coo_->col,
                        Ptr2(coo_row.numel(), col_seeds), true);
   return {std::get<0>(r), std::get<2>(r), std::get<3>(r), coo_->e_ids};
@@ -431,7 +443,7 @@ torch::Tensor Graph::GetValidNodes(torch::Tensor col_seeds, torch::Tensor row_id
     CreateSparseFormat(kCOO);
     rows = coo_->row;
   }
-  if (row_ids.numel() > 0) rows = row_ids.index_select(0, rows);
+  if (row_ids.numel() > 0) rows = CheckedIdGather(row_ids, rows, "row_ids");
   auto r = RelabelImpl(col_seeds, Ptr2(col_seeds.numel(), col_seeds), rows, torch::Tensor(),
                        Ptr2(rows.numel(), col_seeds), false);
   return std::get<0>(r);
@@ -575,7 +587,7 @@ Graph::RelabelResult Graph::BatchRelabelImpl(torch::Tensor col_seeds, torch::Ten
   torch::Tensor coo_row = coo_->row;
   if (row_ids.numel() > 0) {
     // encoded row ids: decode back to graph ids (encoding_decoding.cu:99-122)
-    auto enc = row_ids.index_select(0, coo_->row);
+    auto enc = CheckedIdGather(row_ids, coo_->row, "row_ids");
     coo_row = row_encoding_size_ > 0 ? torch::remainder(enc, row_encoding_size_) : enc;
   }
   auto r = RelabelImpl(col_seeds, col_bptr_, coo_row, coo_->col, edge_bptr_, true);

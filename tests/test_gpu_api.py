@@ -210,6 +210,22 @@ def test_graph_accessors_and_formats(gsb, oracle):
     assert counts == [10, 30]
 
 
+def test_short_row_id_map_is_an_exception(gsb, rmat):
+    """A row-id map shorter than the row ids it is indexed with is reported as an exception (the
+    gather is bounds-checked on the device), and the context stays usable."""
+    indptr, indices = rmat
+    A = new_graph(gsb, indptr, indices)
+    seeds = torch.arange(0, 64, device="cuda")
+    sub, _ = A._CAPI_SlicingSampling(1, seeds, 5, False, gsb._CSC, gsb._COO)
+    short_map = torch.arange(0, 10, device="cuda")
+    with pytest.raises(RuntimeError):
+        sub._CAPI_GetValidNodes(seeds, short_map)
+    with pytest.raises(RuntimeError):
+        sub._CAPI_GraphRelabel(seeds, short_map)
+    ok = sub._CAPI_GetValidNodes(seeds, torch.empty(0, dtype=torch.int64, device="cuda"))
+    assert ok.numel() >= 64
+
+
 def test_errors_are_exceptions(gsb):
     A = gsb.Graph(4, 4)
     A._CAPI_LoadCSC(torch.tensor([0, 1, 2, 3, 4]).cuda(), torch.tensor([0, 1, 2, 3]).cuda())
