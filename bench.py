@@ -194,6 +194,47 @@ def cpu_sort_indices_run(indptr_np, indices_np, max_edges=20_000_000):
             "cores": gs_oracle.num_threads()}
 
 
+def reference_gpu_run(cfg, indptr, indices, rank, steps, warmup):
+    """The reference's own CUDA kernels (oracle/_ref/gs_ref.so, built from the reference tree by
+    oracle/build_ref.py) on the same super-batches on this GPU: per layer
+    FusedCSCColSlicingSamplingCUDA, edge_ptr = sub_indptr[seeds_ptr], BatchCOORelabelCUDA once
+    (the reference's Python pipeline runs the relabel twice per layer).  None when the file has
+    not been built."""
+    import torch
+
+    from oracle import build_ref
+
+    ref = build_ref.load()
+    if ref is None or not indptr.is_cuda:
+        return None
+    indices = indices.to(torch.int64)      # the reference's sampling path is int64 only
+    batches = [(s.to(indptr.device), p.to(indptr.device)) for s, p in make_super_batches(cfg, rank)]
+
+    def step(seeds, ptr):
+        edges = 0
+        for K in cfg["fanouts"]:
+            sub_indptr, col, rows, _ = ref.fused_slice_sample(indptr, indices, K, seeds, False, True)
+            uq, up, _, _, _ = ref.batch_coo_relabel(seeds, ptr, seeds[col], rows, sub_indptr[ptr])
+            edges += rows.numel()
+            seeds, ptr = uq, up
+        return edges
+
+    for i in range(warmup):
+        step(*batches[i % len(batches)])
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    edges = 0
+    for i in range(steps):
+        edges += step(*batches[(warmup + i) % len(batches)])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1)
+    return {"value": edges / (ms / 1e3), "unit": "edges/s", "ms_per_step": ms / steps, "steps": steps,
+            "what": "the reference's CUDA kernels compiled unmodified for sm_100a, one relabel per layer, "
+                    "device-resident inputs, CUDA-event time"}
+
+
 def run_reference(args, cfg, rank, world):
     if rank != 0:
         return
@@ -202,6 +243,7 @@ def run_reference(args, cfg, rank, world):
     device = "cuda" if torch.cuda.is_available() else "cpu"
     indptr, indices = make_graph(cfg, device)
     indptr_np, indices_np = indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64)
+    ref_gpu = reference_gpu_run(cfg, indptr, indices, rank, args.steps, args.warmup) if device == "cuda" else None
     del indptr, indices
     eps, desc, cores, ms = cpu_reference_run(cfg, indptr_np, indices_np, args.steps, args.warmup,
                                              minibatches=4, sampler="ref")
@@ -217,6 +259,8 @@ def run_reference(args, cfg, rank, world):
         "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if ref_gpu is not None:
+        line["reference_gpu"] = ref_gpu
     print(json.dumps(line))
 
 
