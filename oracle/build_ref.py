@@ -25,6 +25,8 @@ SOURCES = [
     "src/cuda/fusion/slice_sampling.cu", "src/cuda/batch/slicing.cu",
     "src/cuda/batch/batch_relabel.cu", "src/cuda/fusion/random_walk.cu",
     "src/cuda/fusion/node2vec.cu", "src/cuda/fusion/column_row_slicing.cu",
+    "src/cuda/sampling_probs.cu", "src/cuda/list_sampling.cu", "src/cuda/list_sampling_probs.cu",
+    "src/cuda/batch/list_sampling_probs.cu", "src/cuda/spmm.cu", "src/cuda/sddmm.cu", "src/bcast.cc",
 ]
 
 
@@ -51,7 +53,7 @@ def build(reference="/root/reference", jobs=None, verbose=True):
     cuda = ["--extended-lambda", "--expt-relaxed-constexpr", "-gencode", "arch=compute_100a,code=sm_100a"]
     binding = os.path.join(HERE, "ref_binding.cc")
     units = [(os.path.join(reference, s), os.path.join(OUT, os.path.basename(os.path.dirname(s)) + "_" +
-              os.path.basename(s)[:-3] + ".o")) for s in SOURCES]
+              os.path.splitext(os.path.basename(s))[0] + ".o")) for s in SOURCES]
     units.append((binding, os.path.join(OUT, "ref_binding.o")))
 
     def compile_one(unit):

@@ -12,8 +12,32 @@
 #include "cuda/fusion/slice_sampling.h"
 #include "cuda/graph_ops.h"
 #include "cuda/tensor_ops.h"
+#include "bcast.h"
+#include "graph_storage.h"
+#include "cuda/sddmm.h"
+#include "cuda/spmm.h"
 
 namespace ri = gs::impl;
+
+// SpMM / SDDMM take the reference's graph structs and its broadcast table (src/bcast.cc:24-76),
+// built here the way Graph::SpMM / Graph::SDDMM do (src/graph.cc:320-379).
+static void spmm_csc(const std::string& op, const std::string& reduce, torch::Tensor indptr,
+                     torch::Tensor indices, torch::Tensor ufeat, torch::Tensor efeat, torch::Tensor out,
+                     torch::Tensor argu, torch::Tensor arge) {
+  auto csc = std::make_shared<gs::CSC>(gs::CSC{indptr, indices, torch::nullopt});
+  ri::SpMMCSC(op, reduce, gs::CalcBcastOff(op, ufeat, efeat), csc, ufeat, efeat, out, {argu, arge});
+}
+static void spmm_coo(const std::string& op, const std::string& reduce, torch::Tensor row, torch::Tensor col,
+                     torch::Tensor ufeat, torch::Tensor efeat, torch::Tensor out, int64_t u_target,
+                     torch::Tensor argu, torch::Tensor arge) {
+  auto coo = std::make_shared<gs::COO>(gs::COO{row, col, torch::nullopt, false, false});
+  ri::SpMMCOO(op, reduce, gs::CalcBcastOff(op, ufeat, efeat), coo, ufeat, efeat, out, u_target, {argu, arge});
+}
+static void sddmm_coo(const std::string& op, torch::Tensor row, torch::Tensor col, torch::Tensor lhs,
+                      torch::Tensor rhs, torch::Tensor out, int64_t lhs_target, int64_t rhs_target) {
+  auto coo = std::make_shared<gs::COO>(gs::COO{row, col, torch::nullopt, false, false});
+  ri::SDDMMCOO(op, gs::CalcBcastOff(op, lhs, rhs), coo, lhs, rhs, out, (int)lhs_target, (int)rhs_target);
+}
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("slice_cols", &ri::OnIndptrSlicingCUDA);                         // src/cuda/slicing.cu:100-181
@@ -28,4 +52,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("node2vec", &ri::fusion::FusedNode2VecCUDA);                     // src/cuda/fusion/node2vec.cu:20-162
   m.def("col_row_slicing", &ri::fusion::CSCColRowSlicingCUDA);           // src/cuda/fusion/column_row_slicing.cu:154-216
   m.def("batch_col_row_slicing", &ri::fusion::BatchCSCColRowSlicingCUDA);  // :266-362
+  m.def("sample_cols_probs", &ri::CSCColSamplingProbsCUDA);               // src/cuda/sampling_probs.cu:23-281
+  m.def("list_sampling", &ri::ListSamplingCUDA);                          // src/cuda/list_sampling.cu:20-73
+  m.def("list_sampling_probs", &ri::ListSamplingProbsCUDA);               // src/cuda/list_sampling_probs.cu:11-89
+  m.def("batch_list_sampling_probs", &ri::batch::BatchListSamplingProbsCUDA);  // src/cuda/batch/list_sampling_probs.cu:29-107
+  m.def("spmm_csc", &spmm_csc);                                           // src/cuda/spmm.cu:253-348
+  m.def("spmm_coo", &spmm_coo);                                           // src/cuda/spmm.cu:170-250
+  m.def("sddmm_coo", &sddmm_coo);                                         // src/cuda/sddmm.cu:120-200
 }
