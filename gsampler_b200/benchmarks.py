@@ -89,7 +89,28 @@ def ladies(steps=10, warmup=3):
         layer_fn(m, batches[warmup + i], [K, K])
     timed = pipeline.timing_collect()
     pipeline.timing_enable(False)
+    # the same layers through the single native call per layer
+    def native_fn(A, seeds, fanouts):
+        edges = 0
+        for k in fanouts:
+            blk, seeds, _ = A.ladies_layer(seeds, k)
+            edges += blk.num_edges()
+        return edges
+
+    for i in range(warmup):
+        native_fn(m, batches[i], [K, K])
+    torch.cuda.synchronize()
+    e0, e1 = _events()
+    e0.record()
+    n_edges = 0
+    for i in range(steps):
+        n_edges += native_fn(m, batches[warmup + i], [K, K])
+    e1.record()
+    torch.cuda.synchronize()
+    native_ms = e0.elapsed_time(e1)
     print(json.dumps({"metric": "ladies_block_edges_per_sec", "value": edges / (ms / 1e3), "unit": "edges/s",
+                      "native_layer_call": {"value": n_edges / (native_ms / 1e3), "ms_per_step": native_ms / steps,
+                                            "edges_per_step": n_edges / steps},
                       "ms_per_step": ms / steps, "steps": steps, "edges_per_step": edges / steps,
                       "config": {"workload": "LADIES 2 layers x %d nodes, %d seeds, %d nodes / %d edges fp32 w"
                                  % (K, nseeds, n, int(indptr[-1]))},

@@ -132,6 +132,8 @@ class Graph : public torch::CustomClassHolder {
   // the reference, which composes it from per-layer operators).
   std::vector<torch::Tensor> BatchGraphSAGE(torch::Tensor seeds, torch::Tensor seeds_ptr,
                                             std::vector<int64_t> fanouts);
+  // one whole LADIES layer (slice, row weights, collective sampling, renormalisation, block)
+  std::vector<torch::Tensor> LadiesLayer(torch::Tensor seeds, int64_t K, torch::Tensor w);
   // enqueue only: tensors at capacity + the device-side counts (see graph_more.cc)
   std::vector<torch::Tensor> BatchGraphSAGEAsync(torch::Tensor seeds, torch::Tensor seeds_ptr,
                                                  std::vector<int64_t> fanouts);

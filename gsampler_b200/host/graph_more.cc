@@ -472,6 +472,123 @@ void Graph::FusedUOPV(const std::string& op, OptTensor lhs1, OptTensor rhs1, tor
   SDDMM(op, lhs2, rhs2, out2, 0, 2, on_format);
 }
 
+// {0, n} on the device (a one-segment offset array)
+static torch::Tensor OneSegment(int64_t n, const torch::Device& dev) {
+  auto t = torch::empty({2}, torch::dtype(torch::kInt64).pinned_memory(true));
+  t.data_ptr<int64_t>()[0] = 0;
+  t.data_ptr<int64_t>()[1] = n;
+  return t.to(dev, /*non_blocking=*/true);
+}
+
+// ------------------------------------------------------------------ whole LADIES layer
+// One layer of the layer-wise (LADIES) sampler of gSampler's examples/ladies/ladies.py:7-21 in a
+// single call:
+//   subA = A[:, seeds];  p[r] = sum over the slice of w^2 per row r;  K rows by weight p
+//   (collective sampling without replacement);  keep their edges;  w <- w / p[row];
+//   w <- w / (column sum of w);  node list = first-occurrence unique of [seeds, rows];  block.
+// The operator sequence is the one the Matrix API composes from Slicing / SpMM / ListSampling /
+// row Slicing / SDDMM / GetValidNodes / GraphRelabel; doing it here leaves two host read-backs
+// (the slice size and the kept-edge count, both needed to size outputs) instead of one per
+// operator, and no Python between the launches.  Returns {node list, block rows, block cols,
+// edge weights, selected row ids, edge positions in this graph, p of the selected rows}.
+std::vector<torch::Tensor> Graph::LadiesLayer(torch::Tensor seeds, int64_t K, torch::Tensor w) {
+  CreateSparseFormat(kCSC);
+  TORCH_CHECK(!csc_->e_ids.has_value(), "LadiesLayer expects a CSC without edge-id indirection");
+  CheckIds(seeds, "seeds");
+  TORCH_CHECK(K >= 1, "K must be positive");
+  TORCH_CHECK(w.is_cuda() && w.scalar_type() == torch::kFloat32 && w.is_contiguous() &&
+                  w.numel() == csc_->indices.numel(),
+              "LadiesLayer: weights must be a contiguous float32 CUDA tensor with one entry per edge");
+  c10::cuda::CUDAGuard guard(seeds.device());
+  const auto dev = seeds.device();
+  auto i64 = torch::dtype(torch::kInt64).device(dev);
+  auto f32 = torch::dtype(torch::kFloat32).device(dev);
+  const int64_t S = seeds.numel(), R = num_rows_;
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(dev));
+  int* d_err = err.data_ptr<int>();
+  void* st = CurrentStream();
+  const int idt = IdxDtype(csc_->indices);
+
+  // 1. column slice (the one size that must come back before anything can be allocated)
+  auto sub_indptr = torch::empty({S + 1}, i64);
+  {
+    auto ws = NewWorkspace(gsb_slice_cols_workspace_bytes(S), dev);
+    CheckStatus(gsb_slice_cols_count(P(csc_->indptr), P(seeds), S, PM(sub_indptr), ws.data_ptr(),
+                                     (size_t)ws.numel(), d_err, st),
+                "slice_cols_count");
+  }
+  const int64_t Es = sub_indptr.narrow(0, S, 1).item<int64_t>();
+  auto rows = torch::empty({Es}, i64), cols = torch::empty({Es}, i64), sel = torch::empty({Es}, i64);
+  CheckStatus(gsb_slice_cols_fill(P(csc_->indptr), csc_->indices.data_ptr(), idt, P(seeds), S,
+                                  P(sub_indptr), Es, PM(rows), PM(cols), PM(sel), nullptr, 0, 0, st),
+              "slice_cols_fill");
+  auto ws_e = torch::empty({Es}, f32);
+  CheckStatus(gsb_gather_rows(w.data_ptr(), 4, w.numel(), P(sel), Es, ws_e.data_ptr(), d_err, st), "gather");
+
+  // 2. p[r] = sum of w^2 over the slice's entries in row r
+  auto prob = torch::zeros({R}, f32);
+  if (Es > 0)
+    CheckStatus(gsb_spmm_coo_sum(P(rows), P(cols), nullptr, Es, OP_SQUARE_RHS, /*u_target=*/2, nullptr, 1,
+                                 ws_e.data_ptr<float>(), 1, nullptr, nullptr, prob.data_ptr<float>(), 1, st),
+                "row sums");
+
+  // 3. K of the R rows by weight p, without replacement
+  const int64_t Ksel = std::min(K, R);
+  auto range = OneSegment(R, dev);
+  auto picked = torch::empty({Ksel}, i64), picked_ptr = torch::empty({2}, i64);
+  {
+    auto ws = NewWorkspace(gsb_list_sample_workspace_bytes(R, 1), dev);
+    CheckStatus(gsb_list_sample(prob.data_ptr<float>(), P(range), 1, R, K, ListSamplingSeed(),
+                                NextListStream(), PM(picked), PM(picked_ptr), ws.data_ptr(),
+                                (size_t)ws.numel(), d_err, st),
+                "list_sample");
+  }
+
+  // 4. keep the slice's entries whose row was picked (ordered compaction over the slice's
+  //    edges, which stay in column order); row id -> position among the picked
+  auto new_row = torch::empty({Es}, i64), seg = torch::empty({Es}, i64), sel2 = torch::empty({Es}, i64);
+  auto kept = torch::zeros({1}, i64);
+  {
+    auto ws = NewWorkspace(gsb_coo_filter_workspace_bytes(Es, R), dev);
+    CheckStatus(gsb_coo_filter(P(rows), P(cols), Es, P(picked), Ksel, R, PM(new_row), PM(seg), PM(sel2),
+                               PM(kept), ws.data_ptr(), (size_t)ws.numel(), d_err, st),
+                "coo_filter");
+  }
+  const int64_t E2 = kept.item<int64_t>();
+  CheckDeviceError(err.item<int>(), "LadiesLayer");
+  new_row = new_row.narrow(0, 0, E2); seg = seg.narrow(0, 0, E2); sel2 = sel2.narrow(0, 0, E2);
+
+  // 5. w / p[row], then / column sum (division as multiplication by the reciprocal, like the
+  //    Matrix API's div: python/gs/ops/sddmm.py:23-25)
+  auto w2 = torch::empty({E2}, f32), p_sel = torch::empty({Ksel}, f32);
+  CheckStatus(gsb_gather_rows(ws_e.data_ptr(), 4, Es, P(sel2), E2, w2.data_ptr(), d_err, st), "gather");
+  CheckStatus(gsb_gather_rows(prob.data_ptr(), 4, R, P(picked), Ksel, p_sel.data_ptr(), d_err, st), "gather");
+  auto inv_p = p_sel.reciprocal();
+  auto w3 = torch::empty({E2}, f32), w4 = torch::empty({E2}, f32);
+  auto colsum = torch::zeros({S}, f32);
+  if (E2 > 0) {
+    CheckStatus(gsb_sddmm_coo(P(new_row), P(seg), nullptr, E2, OP_MUL, w2.data_ptr<float>(), 1, 1,
+                              inv_p.data_ptr<float>(), 1, 0, nullptr, nullptr, w3.data_ptr<float>(), 1, st),
+                "sddmm");
+    CheckStatus(gsb_spmm_coo_sum(P(new_row), P(seg), nullptr, E2, OP_COPY_RHS, /*u_target=*/0, nullptr, 1,
+                                 w3.data_ptr<float>(), 1, nullptr, nullptr, colsum.data_ptr<float>(), 1, st),
+                "column sums");
+    auto inv_c = colsum.reciprocal();
+    CheckStatus(gsb_sddmm_coo(P(new_row), P(seg), nullptr, E2, OP_MUL, w3.data_ptr<float>(), 1, 1,
+                              inv_c.data_ptr<float>(), 1, 2, nullptr, nullptr, w4.data_ptr<float>(), 1, st),
+                "sddmm");
+  }
+
+  // 6. node list and block: first-occurrence unique of [seeds, picked[new_row]]
+  auto rows_global = torch::empty({E2}, i64), edge_pos = torch::empty({E2}, i64);
+  CheckStatus(gsb_gather_rows(picked.data_ptr(), 8, Ksel, P(new_row), E2, rows_global.data_ptr(), d_err, st),
+              "gather");
+  CheckStatus(gsb_gather_rows(sel.data_ptr(), 8, Es, P(sel2), E2, edge_pos.data_ptr(), d_err, st), "gather");
+  auto r = RelabelImpl(seeds, OneSegment(S, dev), rows_global, seg, OneSegment(E2, dev), true);
+  CheckDeviceError(err.item<int>(), "LadiesLayer");
+  return {std::get<0>(r), std::get<2>(r), std::get<3>(r), w4, picked, edge_pos, p_sel};
+}
+
 // ------------------------------------------------------------------ batch row slicing
 // src/batch_graph.cc:144-157
 Graph::GraphAndIndex Graph::BatchRowSlicing(torch::Tensor row_ids, torch::Tensor row_bptr) {

@@ -216,6 +216,21 @@ class Matrix(object):
         assign_edata = {key: self.edata[key] for key in prefetch_edata}
         return assign_block(block, e_ids, assign_edata, unique_tensor)
 
+    def ladies_layer(self, seeds, num_pick, weight_key="w"):
+        """One layer of the layer-wise (LADIES) sampler in a single native call: the operator
+        sequence of gSampler's examples/ladies/ladies.py:7-21 (``A[:, seeds]``, row weights
+        ``sum(w**2)``, collective sampling of ``num_pick`` rows, ``w / p[row]``, ``w / column
+        sum``, ``all_nodes``, ``to_dgl_block``).  Returns ``(block, next_seeds, picked_rows)``; the
+        block carries the renormalised weights as ``edata[weight_key]`` and the positions of its
+        edges in this matrix as ``edata["_ID"]``."""
+        nodes, brow, bcol, w, picked, edge_pos, _ = self._graph._CAPI_LadiesLayer(
+            seeds, int(num_pick), self.edata[weight_key])
+        block = create_block_from_coo(brow, bcol, num_src=nodes.numel(), num_dst=seeds.numel())
+        block.edata[weight_key] = w
+        block.edata["_ID"] = edge_pos
+        block.srcdata["_ID"] = nodes
+        return block, nodes, picked
+
     def all_nodes(self) -> torch.Tensor:
         return self._graph._CAPI_GetValidNodes(self.col_ndata.get("_ID", self.null_tensor),
                                                self.row_ndata.get("_ID", self.null_tensor))

@@ -326,6 +326,43 @@ def test_ladies_sampler_layer(gsb, oracle):
     assert np.array_equal(np.sort(host(nodes)), np.sort(frontier))
 
 
+def test_ladies_layer_native_call(gsb, oracle):
+    """The same layer through the single native call (Matrix.ladies_layer): every stage is
+    recomputed on the host from the rows the GPU picked; the kept edges stay in column order."""
+    rng = np.random.default_rng(19)
+    indptr, indices = rand_csc(rng, 5000, 50, heavy=5)
+    n, E = indptr.size - 1, indices.size
+    w = (rng.random(E) + 0.05).astype(np.float32)
+    m = gsb.Matrix(new_graph(gsb, indptr, indices))
+    m.edata["w"] = cuda(w, torch.float32)
+    torch.ops.gs_ops._CAPI_SetListSamplingSeed(3)
+    seeds = rng.permutation(n)[:200].astype(np.int64)
+    K = 600
+    block, nodes, picked = m.ladies_layer(cuda(seeds), K)
+    picked = host(picked)
+    sip, srows, scols, ssel = oracle.slice_cols(indptr, indices, seeds)
+    p_ref = oracle.edge_sum(srows, scols, w[ssel], 0, n, square=True)
+    assert picked.size == K and np.unique(picked).size == K and np.all(p_ref[picked] > 0)
+    assert np.all(np.diff(picked) > 0)                      # ascending, like _CAPI_ListSamplingWithProbs
+    spec = oracle.list_sample_probs_spec(p_ref, K, seed=3, stream=0)
+    assert np.intersect1d(picked, spec).size >= K - 2        # same draw up to fp32 summation order of p
+    mask = np.isin(srows, picked)
+    pos = np.full(n, -1)
+    pos[picked] = np.arange(K)
+    kept_rows, kept_cols = srows[mask], scols[mask]
+    assert np.array_equal(host(block.edata["_ID"]), ssel[mask])
+    w1 = w[ssel][mask] / p_ref[kept_rows]
+    colsum = np.bincount(kept_cols, weights=w1, minlength=seeds.size)
+    assert np.allclose(host(block.edata["w"]), w1 / colsum[kept_cols], rtol=5e-5, atol=1e-7)
+    frontier, nrow, ncol = oracle.relabel(seeds, kept_rows, kept_cols)
+    assert np.array_equal(host(nodes), frontier) and np.array_equal(host(block.srcdata["_ID"]), frontier)
+    assert np.array_equal(host(block.row), nrow) and np.array_equal(host(block.col), ncol)
+    assert block.num_src == frontier.size and block.num_dst == seeds.size
+    # a second layer on the new frontier runs, and K larger than the row count is clamped
+    block2, nodes2, picked2 = m.ladies_layer(nodes, 10 ** 7)
+    assert picked2.numel() == n and block2.num_dst == nodes.numel()
+
+
 def test_node2vec_sampler_api(gsb, oracle, graph):
     """examples/node2vec/node2vec.py:10-29 of the reference on this package's Matrix."""
     indptr, indices = graph
