@@ -5,10 +5,9 @@
 //
 // Membership is a direct-address map (one 32-bit word per possible id, built
 // per call in the workspace): no probing, one L2-resident load per entry.
-// A warp owns a segment (column): pass 1 counts the survivors per segment and
-// turns the counts into offsets (chained tile prefix); pass 2 rewrites the
-// survivors in order using warp ballots, so the output keeps the operand's
-// entry order inside every segment.
+// Both the CSC and the COO form are edge-parallel ordered compactions (tile
+// scan + chained tile prefix), so the output keeps the operand's entry order
+// and the cost does not depend on how the entries are spread over segments.
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -32,77 +31,98 @@ __global__ void map_build_kernel(const i64* __restrict__ ids, i64 R, u32* map, i
   }
 }
 
-// Tile = RS_WARPS segments per iteration is too coarse for the chained prefix,
-// so a CTA owns RS_THREADS consecutive segments: warps stride over them to
-// count, then one scan + tile prefix yields the offsets of all of them.
-template <typename IndexT>
+// Slicing across a CSC (CSR) is EDGE-parallel: a CTA takes a tile of 1024 consecutive
+// entries (four per thread), whatever segments they belong to, so a few very long segments
+// cost the same as many short ones.  Entries are already in segment order, hence an ordered
+// compaction over all entries (tile scan + chained tile prefix) IS the segment-major output,
+// and the output offset of a segment is the number of kept entries before its first entry.
+// Pass 1 (FILL = false) writes those offsets, pass 2 the kept entries.
+constexpr int AC_PER_THREAD = 4;
+constexpr int AC_TILE = RS_THREADS * AC_PER_THREAD;
+
+// largest s in [lo, hi] with indptr[s] <= e
+__device__ __forceinline__ i64 segment_in_range(const i64* __restrict__ indptr, i64 lo, i64 hi, i64 e) {
+  while (lo < hi) {
+    const i64 mid = (lo + hi + 1) >> 1;
+    if (__ldg(indptr + mid) <= e) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+template <typename IndexT, bool FILL>
 __global__ void __launch_bounds__(RS_THREADS)
-across_count_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 nseg,
-                    const u32* __restrict__ map, i64 id_bound, i64* __restrict__ out_indptr,
-                    u64* status, int* ticket, int* err) {
+across_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 nseg, i64 nnz_max,
+              const u32* __restrict__ map, i64 id_bound, i64* __restrict__ out_indptr,
+              i64* __restrict__ out_ids, i64* __restrict__ out_seg, i64* __restrict__ out_sel,
+              u64* status, int* ticket, int* err) {
   __shared__ i64 s_scan[34];
-  __shared__ int s_cnt[RS_THREADS];
   __shared__ int s_tile;
-  __shared__ i64 s_base;
+  __shared__ i64 s_base, s_lo, s_hi;
   if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
   __syncthreads();
   const int tile = s_tile;
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const i64 seg0 = (i64)tile * RS_THREADS;
-  for (int k = wid; k < RS_THREADS; k += RS_WARPS) {
-    const i64 seg = seg0 + k;
-    int cnt = 0;
-    if (seg < nseg) {
-      const i64 st = __ldg(indptr + seg), en = __ldg(indptr + seg + 1);
-      for (i64 e = st + lane; e < en; e += 32) {
-        const i64 id = load_index<IndexT>(indices, e);
-        if (id >= 0 && id < id_bound && __ldg(map + id) != MAP_ABSENT) ++cnt;
-      }
-#pragma unroll
-      for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
-    }
-    if (lane == 0) s_cnt[k] = cnt;
+  i64 nnz = nseg > 0 ? indptr[nseg] : 0;
+  if (nnz > nnz_max || nnz < 0) {
+    if (tile == 0 && threadIdx.x == 0) raise(err, ERRBIT_CAPACITY);
+    nnz = 0;
   }
-  __syncthreads();
+  const i64 tiles = nnz == 0 ? 1 : (nnz + AC_TILE - 1) / AC_TILE;
+  if (tile >= tiles) return;
+  const i64 e0 = (i64)tile * AC_TILE;
+  const i64 e_last = e0 + AC_TILE - 1 < nnz - 1 ? e0 + AC_TILE - 1 : nnz - 1;
+  if (threadIdx.x < 2 && nnz > 0) {
+    const i64 s = find_segment(indptr, (int)nseg, threadIdx.x == 0 ? e0 : e_last);
+    if (threadIdx.x == 0) s_lo = s; else s_hi = s;
+  }
+  // four consecutive entries per thread
+  const i64 first = e0 + (i64)threadIdx.x * AC_PER_THREAD;
+  u32 pos[AC_PER_THREAD];
+  int kept = 0;
+#pragma unroll
+  for (int j = 0; j < AC_PER_THREAD; ++j) {
+    const i64 e = first + j;
+    pos[j] = MAP_ABSENT;
+    if (e < nnz) {
+      const i64 id = load_index<IndexT>(indices, e);
+      if (id >= 0 && id < id_bound) pos[j] = __ldg(map + id);
+    }
+    kept += pos[j] != MAP_ABSENT;
+  }
   i64 total;
-  const i64 loff = block_exclusive_scan((i64)s_cnt[threadIdx.x], s_scan, &total);
+  const i64 loff = block_exclusive_scan((i64)kept, s_scan, &total);  // also orders s_lo / s_hi
   if (threadIdx.x < 32) {
-    i64 base = chained_exclusive_prefix(status, tile, total, err);
+    const i64 base = chained_exclusive_prefix(status, tile, total, err);
     if (threadIdx.x == 0) s_base = base;
   }
   __syncthreads();
-  const i64 seg = seg0 + threadIdx.x;
-  if (seg < nseg) out_indptr[seg] = s_base + loff;
-  if (seg == nseg - 1 || (nseg == 0 && seg == 0)) out_indptr[nseg] = s_base + total;
-}
-
-template <typename IndexT>
-__global__ void __launch_bounds__(RS_THREADS)
-across_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 nseg,
-                   const u32* __restrict__ map, i64 id_bound, const i64* __restrict__ out_indptr,
-                   i64* __restrict__ out_ids, i64* __restrict__ out_seg, i64* __restrict__ out_sel) {
-  const int lane = threadIdx.x & 31;
-  const i64 warp0 = ((i64)blockIdx.x * RS_THREADS + threadIdx.x) >> 5;
-  const i64 nwarps = ((i64)gridDim.x * RS_THREADS) >> 5;
-  for (i64 seg = warp0; seg < nseg; seg += nwarps) {
-    const i64 st = __ldg(indptr + seg), en = __ldg(indptr + seg + 1);
-    i64 o = out_indptr[seg];
-    for (i64 e0 = st; e0 < en; e0 += 32) {
-      const i64 e = e0 + lane;
-      u32 pos = MAP_ABSENT;
-      if (e < en) {
-        const i64 id = load_index<IndexT>(indices, e);
-        if (id >= 0 && id < id_bound) pos = __ldg(map + id);
+  i64 run = s_base + loff;  // kept entries before this thread's first entry
+  if (first < nnz) {
+    i64 seg = segment_in_range(indptr, s_lo, s_hi, first);
+    i64 seg_end = __ldg(indptr + seg + 1);
+#pragma unroll
+    for (int j = 0; j < AC_PER_THREAD; ++j) {
+      const i64 e = first + j;
+      if (e >= nnz) break;
+      while (e >= seg_end) { ++seg; seg_end = __ldg(indptr + seg + 1); }  // skips empty segments
+      if (!FILL) {
+        if (__ldg(indptr + seg) == e) {  // first entry of its segment: the segment's output offset
+          i64 s = seg;
+          out_indptr[s] = run;
+          while (s > 0 && __ldg(indptr + s - 1) == e) out_indptr[--s] = run;  // empty ones before it
+        }
+      } else if (pos[j] != MAP_ABSENT) {
+        out_ids[run] = (i64)pos[j];
+        out_sel[run] = e;
+        if (out_seg) out_seg[run] = seg;
       }
-      const unsigned keep = __ballot_sync(0xffffffffu, pos != MAP_ABSENT);
-      if (pos != MAP_ABSENT) {
-        const i64 w = o + __popc(keep & ((1u << lane) - 1u));
-        out_ids[w] = (i64)pos;
-        out_sel[w] = e;
-        if (out_seg) out_seg[w] = seg;
-      }
-      o += __popc(keep);
+      run += pos[j] != MAP_ABSENT;
     }
+  }
+  if (!FILL && tile == tiles - 1 && threadIdx.x == 0) {
+    const i64 grand = s_base + total;  // everything kept; also the offset of trailing empty segments
+    i64 s = nseg;
+    out_indptr[s] = grand;
+    while (s > 0 && indptr[s - 1] == nnz) out_indptr[--s] = grand;
   }
 }
 
@@ -333,62 +353,65 @@ static ColRowLayout colrow_layout(i64 S, i64 R, i64 B) {
 
 using namespace gsb;
 
-extern "C" size_t gsb_slice_across_workspace_bytes(int64_t nseg, int64_t id_bound) {
-  if (nseg < 0 || id_bound < 0) return 0;
-  return across_layout(nseg, id_bound).total;
+extern "C" size_t gsb_slice_across_workspace_bytes(int64_t nnz_max, int64_t id_bound) {
+  if (nnz_max < 0 || id_bound < 0) return 0;
+  return across_layout((nnz_max + AC_PER_THREAD - 1) / AC_PER_THREAD, id_bound).total;
+}
+
+template <bool FILL>
+static int launch_across(const int64_t* indptr, const void* indices, int indices_dtype, int64_t nseg,
+                         int64_t nnz_max, int64_t id_bound, int64_t* out_indptr, int64_t* out_ids,
+                         int64_t* out_seg, int64_t* out_sel, char* ws, const AcrossLayout& L, int* d_err,
+                         cudaStream_t st) {
+  const int tiles = nnz_max == 0 ? 1 : ceil_div_i(nnz_max, AC_TILE);
+  LaunchScope ls(KID_SLICE_ROWS, st);
+  if (indices_dtype == GSB_I32)
+    across_kernel<int, FILL><<<tiles, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.map), id_bound, (i64*)out_indptr,
+        (i64*)out_ids, (i64*)out_seg, (i64*)out_sel, (u64*)(ws + L.status), (int*)(ws + L.ticket), d_err);
+  else
+    across_kernel<i64, FILL><<<tiles, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.map), id_bound, (i64*)out_indptr,
+        (i64*)out_ids, (i64*)out_seg, (i64*)out_sel, (u64*)(ws + L.status), (int*)(ws + L.ticket), d_err);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
 }
 
 extern "C" int gsb_slice_across_count(const int64_t* indptr, const void* indices, int indices_dtype,
-                                      int64_t nseg, const int64_t* ids, int64_t R, int64_t id_bound,
-                                      int64_t* out_indptr, void* workspace, size_t workspace_bytes,
-                                      int* d_err, void* cuda_stream) {
-  if (!indptr || !out_indptr || nseg < 0 || R < 0 || id_bound < 0 || (R > 0 && !ids))
+                                      int64_t nseg, int64_t nnz_max, const int64_t* ids, int64_t R,
+                                      int64_t id_bound, int64_t* out_indptr, void* workspace,
+                                      size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (!indptr || !out_indptr || nseg < 0 || nnz_max < 0 || R < 0 || id_bound < 0 || (R > 0 && !ids) ||
+      (nnz_max > 0 && !indices))
     return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   if (R >= 0xFFFFFFFFll || id_bound > (1ll << 33)) return GSB_ERR_UNSUPPORTED;
-  const AcrossLayout L = across_layout(nseg, id_bound);
+  const AcrossLayout L = across_layout((nnz_max + AC_PER_THREAD - 1) / AC_PER_THREAD, id_bound);
   if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
   int rc = build_map(ws, L, (const i64*)ids, R, id_bound, d_err, st);
   if (rc != GSB_OK) return rc;
-  const int tiles = nseg == 0 ? 1 : ceil_div_i(nseg, RS_THREADS);
-  LaunchScope ls(KID_SLICE_ROWS, st);
-  if (indices_dtype == GSB_I32)
-    across_count_kernel<int><<<tiles, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, nseg, (const u32*)(ws + L.map), id_bound, (i64*)out_indptr,
-        (u64*)(ws + L.status), (int*)(ws + L.ticket), d_err);
-  else
-    across_count_kernel<i64><<<tiles, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, nseg, (const u32*)(ws + L.map), id_bound, (i64*)out_indptr,
-        (u64*)(ws + L.status), (int*)(ws + L.ticket), d_err);
-  GSB_CUDA_OK(cudaGetLastError());
-  return GSB_OK;
+  return launch_across<false>(indptr, indices, indices_dtype, nseg, nnz_max, id_bound, out_indptr, nullptr,
+                              nullptr, nullptr, ws, L, d_err, st);
 }
 
 extern "C" int gsb_slice_across_fill(const int64_t* indptr, const void* indices, int indices_dtype,
-                                     int64_t nseg, int64_t id_bound, const int64_t* out_indptr,
+                                     int64_t nseg, int64_t nnz_max, int64_t id_bound,
                                      int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
-                                     const void* workspace, void* cuda_stream) {
-  if (nseg == 0) return GSB_OK;
-  if (!indptr || !indices || !out_indptr || !out_ids || !out_sel || !workspace || nseg < 0)
+                                     void* workspace, size_t workspace_bytes, int* d_err,
+                                     void* cuda_stream) {
+  if (nseg == 0 || nnz_max == 0) return GSB_OK;
+  if (!indptr || !indices || !out_ids || !out_sel || !workspace || nseg < 0 || nnz_max < 0)
     return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
-  const AcrossLayout L = across_layout(nseg, id_bound);
+  const AcrossLayout L = across_layout((nnz_max + AC_PER_THREAD - 1) / AC_PER_THREAD, id_bound);
+  if (workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
-  i64 g = (nseg + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
-  const u32* map = (const u32*)((const char*)workspace + L.map);
-  LaunchScope ls(KID_SLICE_ROWS, st);
-  if (indices_dtype == GSB_I32)
-    across_fill_kernel<int><<<(int)g, RS_THREADS, 0, st>>>((const i64*)indptr, indices, nseg, map,
-                                                           id_bound, (const i64*)out_indptr,
-                                                           (i64*)out_ids, (i64*)out_seg, (i64*)out_sel);
-  else
-    across_fill_kernel<i64><<<(int)g, RS_THREADS, 0, st>>>((const i64*)indptr, indices, nseg, map,
-                                                           id_bound, (const i64*)out_indptr,
-                                                           (i64*)out_ids, (i64*)out_seg, (i64*)out_sel);
-  GSB_CUDA_OK(cudaGetLastError());
-  return GSB_OK;
+  char* ws = (char*)workspace;
+  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.map, st));  // ticket + status again; the map stays
+  return launch_across<true>(indptr, indices, indices_dtype, nseg, nnz_max, id_bound, nullptr, out_ids,
+                             out_seg, out_sel, ws, L, d_err, st);
 }
 
 extern "C" size_t gsb_coo_filter_workspace_bytes(int64_t nnz, int64_t id_bound) {

@@ -138,20 +138,23 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sl
   auto opt = I64(src.indptr);
   auto sub_indptr = torch::empty({nseg + 1}, opt);
   auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(ids.device()));
-  auto ws = NewWorkspace(gsb_slice_across_workspace_bytes(nseg, id_bound), ids.device());
+  const int64_t nnz_max = src.indices.numel();
+  auto ws = NewWorkspace(gsb_slice_across_workspace_bytes(nnz_max, id_bound), ids.device());
   CheckStatus(gsb_slice_across_count(P(src.indptr), src.indices.data_ptr(), IdxDtype(src.indices),
-                                     nseg, P(ids), ids.numel(), id_bound, PM(sub_indptr),
+                                     nseg, nnz_max, P(ids), ids.numel(), id_bound, PM(sub_indptr),
                                      ws.data_ptr(), (size_t)ws.numel(), err.data_ptr<int>(),
                                      CurrentStream()),
               "slice_across_count");
   const int64_t E = sub_indptr.narrow(0, nseg, 1).item<int64_t>();
   CheckDeviceError(err.item<int>(), "slice_across_count");
   auto out_ids = torch::empty({E}, opt), seg = torch::empty({E}, opt), sel = torch::empty({E}, opt);
-  if (E > 0)
+  if (E > 0) {
     CheckStatus(gsb_slice_across_fill(P(src.indptr), src.indices.data_ptr(), IdxDtype(src.indices),
-                                    nseg, id_bound, P(sub_indptr), PM(out_ids), PM(seg), PM(sel),
-                                    ws.data_ptr(), CurrentStream()),
-              "slice_across_fill");
+                                      nseg, nnz_max, id_bound, PM(out_ids), PM(seg), PM(sel),
+                                      ws.data_ptr(), (size_t)ws.numel(), err.data_ptr<int>(),
+                                      CurrentStream()),
+                "slice_across_fill");
+  }
   return {sub_indptr, out_ids, seg, sel};
 }
 

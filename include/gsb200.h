@@ -224,19 +224,21 @@ GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nke
  * entry order inside every segment preserved.  Replaces OnIndicesSlicingCUDA
  * (src/cuda/slicing.cu:184-308), reached from Graph::Slicing axis=0 on CSC
  * (src/graph.cc:116-119) and Graph::BatchRowSlicing (src/batch_graph.cc:144-157).
+ * Both passes walk the entries, not the segments (cost independent of the
+ * degree distribution); nnz_max bounds indptr[nseg], which is read on the device.
  * count: out_indptr[nseg+1]; builds the membership map in the workspace.
  * fill : out_ids / out_seg (nullable) / out_sel [E], E = out_indptr[nseg]
  *        (host value); must be given the workspace of the matching count call.
  * id_bound = exclusive upper bound of the ids stored in `indices`. */
-GSB_API size_t gsb_slice_across_workspace_bytes(int64_t nseg, int64_t id_bound);
+GSB_API size_t gsb_slice_across_workspace_bytes(int64_t nnz_max, int64_t id_bound);
 GSB_API int gsb_slice_across_count(const int64_t* indptr, const void* indices, int indices_dtype,
-                                   int64_t nseg, const int64_t* ids, int64_t R, int64_t id_bound,
-                                   int64_t* out_indptr, void* workspace, size_t workspace_bytes,
-                                   int* d_err, void* cuda_stream);
+                                   int64_t nseg, int64_t nnz_max, const int64_t* ids, int64_t R,
+                                   int64_t id_bound, int64_t* out_indptr, void* workspace,
+                                   size_t workspace_bytes, int* d_err, void* cuda_stream);
 GSB_API int gsb_slice_across_fill(const int64_t* indptr, const void* indices, int indices_dtype,
-                                  int64_t nseg, int64_t id_bound, const int64_t* out_indptr,
-                                  int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
-                                  const void* workspace, void* cuda_stream);
+                                  int64_t nseg, int64_t nnz_max, int64_t id_bound, int64_t* out_ids,
+                                  int64_t* out_seg, int64_t* out_sel, void* workspace,
+                                  size_t workspace_bytes, int* d_err, void* cuda_stream);
 /* Column AND row selection per minibatch (induced sub-matrices): minibatch b
  * keeps, of the columns cols[col_ptr[b]..col_ptr[b+1]), the entries whose row
  * id occurs in rows[row_ptr[b]..row_ptr[b+1]).  out_ids = position of the row
