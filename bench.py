@@ -272,7 +272,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("GSB_WORKLOAD", "cfg2"), choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--streams", type=int, default=int(os.environ.get("GSB_STREAMS", "3")),
+    ap.add_argument("--streams", type=int, default=int(os.environ.get("GSB_STREAMS", "2")),
                     help="independent super-batches in flight (each on its own CUDA stream)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
