@@ -103,7 +103,7 @@ class ClockSampler(threading.Thread):
 # per unit is the same on the bench workload, so the per-launch traffic is scaled by the units.
 NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 94.3}
 # the same capture summed over all kernels and layers of one super-batch, per sampled edge
-NCU_PATH_DRAM_BYTES_PER_EDGE = 183.1
+NCU_PATH_DRAM_BYTES_PER_EDGE = 183.8
 
 
 def ncu_traffic(kernel, mean_edges):
