@@ -6,6 +6,7 @@ repository root holds the headline one):
     python -m gsampler_b200.benchmarks node2vec   # 1 M walkers x 80 steps, p=2, q=0.5,
                                                   # 2 449 029 nodes / 123.7 M edges
     python -m gsampler_b200.benchmarks gather     # feature fetch: 4 M rows of 100 fp32 out of 2 449 029
+    python -m gsampler_b200.benchmarks cfg5       # the same on the full 111 M nodes / 3.2 G edges (14 GB)
     python -m gsampler_b200.benchmarks cfg5s      # GraphSAGE [15,10,5] on an int32-index R-MAT-like
                                                   # power-law graph, 11.1 M nodes / 320 M edges
 
@@ -182,15 +183,27 @@ def gather(steps=10, warmup=3, rows=4000000, width=100):
                       "config": {"workload": "%d rows x %d fp32 out of %d" % (rows, width, n)}, **out}))
 
 
-def cfg5s(steps=6, warmup=3):
+def cfg5(steps=6, warmup=3):
+    """The full-size configuration: 111 059 956 nodes / about 3.2 G directed edges."""
+    cfg5s(steps, warmup, n=111059956, e=3200000000, large=True)
+
+
+def cfg5s(steps=6, warmup=3, n=11105996, e=320000000, large=False):
     dev = torch.device("cuda")
-    n, e, batch, sb = 11105996, 320000000, 1024, 64
-    indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=100000, seed=9, device=dev,
-                                         index_dtype=torch.int32)
+    batch, sb = 1024, 64
+    t_gen = time.time()
+    if large:
+        indptr, indices = synth.powerlaw_csc_large(n, e, exponent=2.1, max_degree=100000, seed=9, device=dev)
+    else:
+        indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=100000, seed=9, device=dev,
+                                             index_dtype=torch.int32)
+    torch.cuda.synchronize()
+    t_gen = time.time() - t_gen
+    torch.cuda.empty_cache()
     fan = [15, 10, 5]
-    gen = torch.Generator()
+    gen = torch.Generator(device=dev)
     gen.manual_seed(3)
-    seeds_all = torch.randperm(n, generator=gen)[:batch * sb * (steps + warmup)].to(dev)
+    seeds_all = torch.randperm(n, generator=gen, device=dev)[:batch * sb * (steps + warmup)].contiguous()
     ptr = (torch.arange(sb + 1, dtype=torch.int64) * batch).to(dev)
     probe = pipeline.GraphSAGESampler(indptr, indices, sb, batch * sb, fan)
     probe.sample(seeds_all[:batch * sb], ptr)
@@ -219,11 +232,12 @@ def cfg5s(steps=6, warmup=3):
                       "config": {"workload": "GraphSAGE [15,10,5], %d x %d seeds, %d nodes / %d edges, int32 indices"
                                  % (sb, batch, n, int(indptr[-1])),
                                  "graph_gb": (indices.numel() * 4 + indptr.numel() * 8) / 1e9,
+                                 "graph_build_s": t_gen,
                                  "mean_SEU_per_layer": c.double().mean(0).tolist()}}))
 
 
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "node2vec"
     t0 = time.time()
-    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s, "gather": gather}[which]()
+    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s, "cfg5": cfg5, "gather": gather}[which]()
     print("# %s finished in %.1f s" % (which, time.time() - t0), file=sys.stderr)

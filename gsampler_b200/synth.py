@@ -116,3 +116,68 @@ def seed_batches(num_seeds: int, num_nodes: int, batch: int, seed: int, device="
     if ptr[-1] == ptr[-2] and ptr.numel() > 2:
         ptr = ptr[:-1]
     return seeds.to(device), ptr.to(device)
+
+
+def powerlaw_csc_large(num_nodes: int, num_directed_edges: int, exponent: float = 2.1,
+                       max_degree: int = 100000, seed: int = 0, device="cuda", chunk: int = 1 << 28):
+    """Memory-lean variant of :func:`powerlaw_csc` for billions of edges (int32 indices, int64
+    offsets): same construction -- power-law stub counts, uniform partners, no self-loops, no
+    duplicate pairs, symmetric -- but the CSC is assembled from two sorts of the undirected
+    pairs instead of a sort of all directed edges.  For a column c the neighbours below c are
+    the ``lo`` ends of the pairs with ``hi == c`` and the neighbours above c are the ``hi`` ends
+    of the pairs with ``lo == c``; listing the first group (sorted by lo) before the second
+    (sorted by hi) gives a sorted column without any further sort.  The number of edges is
+    close to, not exactly, ``num_directed_edges`` (duplicates are dropped, the surplus is thinned
+    at random).  Returns (indptr int64, indices int32)."""
+    assert num_nodes < (1 << 31)
+    dev = torch.device(device)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(seed)
+    target = num_directed_edges // 2
+    want = int(target * 1.03) + 16
+    u = torch.rand(num_nodes, generator=gen, device=dev, dtype=torch.float64)
+    raw = (1.0 - u).clamp_min_(1e-12).pow_(-1.0 / (exponent - 1.0)).clamp_max_(float(max_degree))
+    del u
+    scale = want / float(raw.sum())
+    for _ in range(8):
+        scale *= want / float((raw * scale).clamp_max(float(max_degree)).sum())
+    deg = torch.floor((raw * scale).clamp_max_(float(max_degree)) +
+                      torch.rand(num_nodes, generator=gen, device=dev, dtype=torch.float64)).to(torch.int64)
+    del raw
+    src = torch.repeat_interleave(torch.arange(num_nodes, device=dev, dtype=torch.int32), deg)
+    del deg
+    dst = torch.randint(0, num_nodes, (src.numel(),), generator=gen, device=dev, dtype=torch.int32)
+    lo, hi = torch.minimum(src, dst), torch.maximum(src, dst)
+    del src, dst
+    keep = lo != hi
+    key = lo[keep].to(torch.int64) * num_nodes + hi[keep]
+    del lo, hi, keep
+    key = torch.unique_consecutive(torch.sort(key).values)
+    if key.numel() > target:
+        thin = torch.rand(key.numel(), generator=gen, device=dev) < (target / key.numel())
+        key = key[thin]
+        del thin
+    m = key.numel()
+    lo = torch.div(key, num_nodes, rounding_mode="floor").to(torch.int32)   # sorted by (lo, hi)
+    hi = (key - lo.to(torch.int64) * num_nodes).to(torch.int32)
+    key2 = torch.sort(hi.to(torch.int64) * num_nodes + lo).values           # sorted by (hi, lo)
+    del key
+    hi2 = torch.div(key2, num_nodes, rounding_mode="floor").to(torch.int32)
+    lo2 = (key2 - hi2.to(torch.int64) * num_nodes).to(torch.int32)
+    del key2
+    cnt_lo = torch.bincount(lo, minlength=num_nodes)     # neighbours above c
+    cnt_hi = torch.bincount(hi2, minlength=num_nodes)    # neighbours below c
+    indptr = torch.zeros(num_nodes + 1, dtype=torch.int64, device=dev)
+    indptr[1:] = torch.cumsum(cnt_lo + cnt_hi, 0)
+    start_lo = torch.cumsum(cnt_lo, 0) - cnt_lo
+    start_hi = torch.cumsum(cnt_hi, 0) - cnt_hi
+    indices = torch.empty(2 * m, dtype=torch.int32, device=dev)
+    for a in range(0, m, chunk):
+        b = min(a + chunk, m)
+        j = torch.arange(a, b, device=dev)
+        c = hi2[a:b].to(torch.int64)                      # below-c group first
+        indices[indptr[c] + (j - start_hi[c])] = lo2[a:b]
+        c = lo[a:b].to(torch.int64)                       # then the above-c group
+        indices[indptr[c] + cnt_hi[c] + (j - start_lo[c])] = hi[a:b]
+        del j, c
+    return indptr, indices
