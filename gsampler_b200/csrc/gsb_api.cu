@@ -153,7 +153,9 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
 
   const int64_t* cur_seeds = seeds;
   const int64_t* cur_ptr = seeds_ptr;
-  const int64_t* d_S = nullptr;
+  // the live seed count is read on the device for every layer (seeds_ptr[B] for the first one),
+  // so S0 is only an upper bound: a recorded CUDA graph can be replayed on a shorter super-batch
+  const int64_t* d_S = seeds_ptr + B;
   for (int l = 0; l < num_layers; ++l) {
     const gsb_layer_buffers& L = layers[l];
     const int64_t S_max = l == 0 ? S0 : L.S_cap;

@@ -362,7 +362,9 @@ GSB_API int gsb_node2vec(const int64_t* indptr, const void* indices, int indices
  * (e.g. measured on a warm-up step) are allowed, an overflow then raises
  * GSB_ERRBIT_CAPACITY and the affected layers come back empty.
  * After the call (and a stream sync) each layer's counts are in d_counts[3*l
- * .. 3*l+2] = {S_l, E_l, U_l}.
+ * .. 3*l+2] = {S_l, E_l, U_l}.  S0 is an upper bound of the seed count; the
+ * live count is seeds_ptr[B], read on the device, so the same launch sequence
+ * (e.g. a recorded CUDA graph) serves shorter super-batches too.
  */
 typedef struct {
   int64_t S_cap, E_cap;   /* capacities in elements: seeds / edges of this layer      */

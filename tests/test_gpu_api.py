@@ -94,6 +94,32 @@ def test_native_graphsage_pipeline_bit_exact(gsb, oracle, rmat, idx_dtype):
                                                     layer["unique"].size]
 
 
+def test_preallocated_sampler_cuda_graph_replay(gsb, oracle, rmat):
+    """The pre-allocated pipeline recorded into a CUDA graph and replayed on a full and on a
+    shorter super-batch: bit-exact against the oracle both times."""
+    indptr, indices = rmat
+    n = indptr.size - 1
+    rng = np.random.default_rng(12)
+    smp = gsb.GraphSAGESampler(torch.as_tensor(indptr).cuda(), torch.as_tensor(indices).cuda(), 4, 2048,
+                               [10, 5], seed=321)
+    smp.capture()
+    for sizes in ([512, 512, 512, 512], [300, 0, 77, 0]):
+        ptr = np.concatenate([[0], np.cumsum(sizes)]).astype(np.int64)
+        seeds = rng.permutation(n)[:ptr[-1]].astype(np.int64)
+        smp.replay(torch.as_tensor(seeds).cuda(), torch.as_tensor(ptr).cuda())
+        counts = smp.counts()
+        want = oracle.graphsage_batch(indptr, indices, seeds, ptr, [10, 5], seed=321)
+        for l, layer in enumerate(want):
+            S, E, U = counts[l]
+            assert (S, E, U) == (layer["seeds"].size, layer["rows"].size, layer["unique"].size)
+            L = smp.layers[l]
+            assert np.array_equal(host(L["rows"][:E]), layer["rows"])
+            assert np.array_equal(host(L["unique"][:U]), layer["unique"])
+            assert np.array_equal(host(L["block_row"][:E]), layer["block_row"])
+            assert np.array_equal(host(L["block_col"][:E]), layer["block_col"])
+    assert smp.replayed_launches > 0
+
+
 def test_graphsage_async_two_in_flight(gsb, rmat):
     """The enqueue-only form gives the same tensors as the synchronous one, also with two
     super-batches in flight on two streams."""
