@@ -2,12 +2,14 @@
 //
 // Without replacement: every edge e of a column gets the key log2(u_e)/p_e
 // (the logarithm of the A-Res key u^(1/p)); the K largest keys win.  A warp
-// owns a column.  Keys are never stored: u_e is draw e of the column slot's
-// counter-based stream, so each pass simply recomputes them.  The K-th largest
-// key is found by a 4-pass radix select (8 bits per pass, per-warp histogram in
-// shared memory); a last pass writes the winners in column order, ties on the
-// threshold key going to the lowest positions.  No scratch proportional to the
-// degrees, no sort, no limit of 32 on K.
+// owns a column.  u_e is draw e of the column slot's counter-based stream, so a
+// key can be recomputed at any time: columns of up to WP_CACHE entries compute
+// their keys once into the warp's shared-memory cache, longer ones recompute
+// them in every pass and need no scratch proportional to the degree.  The K-th
+// largest key is found by a 4-pass radix select (8 bits per pass, per-warp
+// histogram in shared memory); a last pass writes the winners in column order,
+// ties on the threshold key going to the lowest positions.  No sort, no limit
+// of 32 on K.
 //
 // With replacement: K independent draws from the column's distribution by
 // streaming the running sum through the warp (no materialised CDF).
@@ -18,6 +20,7 @@ namespace gsb {
 constexpr int WP_WARPS = 4;
 constexpr int WP_THREADS = WP_WARPS * 32;
 constexpr int WP_MAX_K = 1024;
+constexpr int WP_CACHE = 1024;  // keys a warp caches (4 KB of shared memory per warp)
 
 struct ProbParams {
   const i64* indptr;
@@ -58,6 +61,7 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   u32* hist = s_dyn + wid * 256;
   float* targets = reinterpret_cast<float*>(s_dyn + WP_WARPS * 256) + wid * p.K;
+  u32* kcache = s_dyn + WP_WARPS * 256 + WP_WARPS * p.K + wid * WP_CACHE;
   i64 S = p.S_max;
   if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
   const int K = p.K;
@@ -80,18 +84,76 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
     }
     if (!p.replace) {
       // ---- radix select of the K-th largest key
+      const bool cached = deg <= WP_CACHE;
+      if (cached) {
+        for (i64 e0 = (i64)lane * 4; e0 < deg; e0 += 128) {
+          const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (e0 + j < deg) kcache[e0 + j] = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
+        }
+        __syncwarp();
+      }
+      // Short column, small K: K rounds of "largest remaining key" (ties to the lowest
+      // position) instead of the radix select -- a few hundred instead of about a thousand
+      // warp instructions for a typical column.  Same winners, written in column order.
+      const int nchunk = (int)((deg + 31) >> 5);
+      if (cached && K * (nchunk * 6 + 40) < 4 * (nchunk * 8 + 120)) {
+        u32 taken = 0;  // bit i: entry lane + 32 i of this column is a winner
+        for (int r = 0; r < K; ++r) {
+          u32 bk = 0;
+          int bp = -1;
+          for (int i = 0; i < nchunk; ++i) {
+            const int e = lane + (i << 5);
+            if (e < (int)deg && !((taken >> i) & 1u)) {
+              const u32 k = kcache[e];
+              if (bp < 0 || k > bk) { bk = k; bp = e; }
+            }
+          }
+          // warp argmax of (key, lowest position); lanes with nothing left offer 0
+          u64 best = bp < 0 ? 0ull : (((u64)bk + 1ull) << 32) | (u64)(0xFFFFFFFFu - (u32)bp);
+#pragma unroll
+          for (int d = 16; d > 0; d >>= 1) {
+            const u64 o = __shfl_xor_sync(0xffffffffu, best, d);
+            best = o > best ? o : best;
+          }
+          const int win = (int)(0xFFFFFFFFu - (u32)best);
+          if ((win & 31) == lane) taken |= 1u << (win >> 5);
+        }
+        i64 o = out_start;
+        for (int i = 0; i < nchunk; ++i) {
+          const bool take = (taken >> i) & 1u;
+          const unsigned bal = __ballot_sync(0xffffffffu, take);
+          if (take) {
+            const i64 e = in_start + lane + (i << 5);
+            const i64 w = o + __popc(bal & ((1u << lane) - 1u));
+            p.out_rows[w] = load_index<IndexT>(p.indices, e);
+            p.out_sel[w] = e;
+            if (p.out_cols) p.out_cols[w] = slot;
+          }
+          o += __popc(bal);
+        }
+        continue;
+      }
       u32 prefix = 0, prefix_mask = 0;
       u32 remaining = (u32)K;  // rank (1 = largest) still to locate inside the prefix class
       for (int shift = 24; shift >= 0; shift -= 8) {
         for (int i = lane; i < 256; i += 32) hist[i] = 0;
         __syncwarp();
-        for (i64 e0 = (i64)lane * 4; e0 < deg; e0 += 128) {
-          const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+        if (cached) {
+          for (int e = lane; e < (int)deg; e += 32) {
+            const u32 key = kcache[e];
+            if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+          }
+        } else {
+          for (i64 e0 = (i64)lane * 4; e0 < deg; e0 += 128) {
+            const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            if (e0 + j < deg) {
-              const u32 key = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
-              if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+            for (int j = 0; j < 4; ++j) {
+              if (e0 + j < deg) {
+                const u32 key = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
+                if ((key & prefix_mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+              }
             }
           }
         }
@@ -133,7 +195,13 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
         const i64 e0 = base + (i64)lane * 4;
         u32 keys[4];
         int ntie = 0;
-        if (e0 < deg) {
+        if (e0 < deg && cached) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            keys[j] = e0 + j < deg ? kcache[e0 + j] : 0u;
+            if (e0 + j < deg && keys[j] == thr) ++ntie;
+          }
+        } else if (e0 < deg) {
           const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
@@ -282,7 +350,8 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   p.E_cap = E_cap; p.err = d_err;
   i64 blocks = (S_max + WP_WARPS - 1) / WP_WARPS;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  const size_t smem = sizeof(u32) * WP_WARPS * 256 + sizeof(float) * WP_WARPS * (size_t)K;
+  const size_t smem = sizeof(u32) * WP_WARPS * 256 + sizeof(float) * WP_WARPS * (size_t)K +
+                      sizeof(u32) * WP_WARPS * WP_CACHE;
   LaunchScope ls(KID_SAMPLE_PROBS, st);
   if (indices_dtype == GSB_I32)
     sample_probs_kernel<int><<<(int)blocks, WP_THREADS, smem, st>>>(p);
