@@ -212,7 +212,7 @@ enum KernelId {
   KID_SAMPLE = 0, KID_SAMPLE_PROBS, KID_COUNT, KID_SLICE_FILL, KID_GATHER, KID_EXPAND,
   KID_INDPTR_SORTED, KID_RL_SETUP, KID_RL_PCOUNT, KID_RL_PSCAN, KID_RL_SCATTER, KID_RL_DEDUPE,
   KID_RL_COUNT, KID_RL_TILES, KID_RL_SCAN, KID_RL_EDGES, KID_SLICE_ROWS, KID_EDGE_SUM,
-  KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT, KID_MISC, KID_NUM
+  KID_EDGE_OP, KID_LIST_SAMPLE, KID_WALK, KID_SORT, KID_SAMPLE_PROBS_SHORT, KID_SAMPLE_PROBS_LONG, KID_MISC, KID_NUM
 };
 struct LaunchScope {
   LaunchScope(int id, cudaStream_t st);
@@ -226,9 +226,19 @@ void set_timing_tag(int tag);
 // Offsets of a slice/sample in one pass (defined in gsb_slice.cu): sub_indptr =
 // exclusive scan of the per-column pick counts, optional device total.
 size_t count_workspace_bytes(i64 S_max);
+// optional by-products of the count pass: first entry / length of every column slot, and a
+// list (unordered) of the slots whose column has at least list_min_deg entries and a non-zero
+// pick count; *list_n must be zero before the launch
+struct CountExtra {
+  i64* start = nullptr;
+  u32* deg = nullptr;
+  i64* list = nullptr;
+  int* list_n = nullptr;
+  i64 list_min_deg = 0;
+};
 int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
                  int replace, i64* sub_indptr, i64* d_total, void* workspace, int* d_err,
-                 cudaStream_t st);
+                 cudaStream_t st, const CountExtra& extra = CountExtra());
 
 #define GSB_CUDA_OK(expr)                          \
   do {                                             \

@@ -39,6 +39,11 @@ struct ProbParams {
   i64* out_sel;
   i64 E_cap;
   int* err;
+  int thread_path;       // columns of at most WT_MAX_DEG entries are handled by the thread kernel
+  const i64* slot_start;  // [S] first entry of the slot's column   } by-products of
+  const u32* slot_deg;    // [S] its length                          } the count pass
+  const i64* list;        // slots the warp kernel has to process (unordered)
+  const int* list_n;
 };
 
 __device__ __forceinline__ u32 orderable(float f) {
@@ -55,6 +60,199 @@ __device__ __forceinline__ u32 ares_key(u32 draw, float p) {
   return o == 0u ? 1u : o;
 }
 
+// Short columns (K < degree <= WT_MAX_DEG) with a small K: THREAD per column.  The thread
+// streams its column once, keeping the K largest keys seen so far in a shared-memory array
+// (transposed: bank = thread); a new key replaces the current smallest only when it is
+// strictly larger, and among equal smallest keys the one at the highest position leaves, so
+// the winners are the K largest keys with ties going to the lowest positions -- the same set
+// the warp kernel selects.  About 30 instructions per entry instead of a warp's several
+// hundred per column.  Longer columns and larger K stay with the warp kernel.
+constexpr int WT_THREADS = 128;
+constexpr int WT_MAX_DEG = 256;
+constexpr int WT_MAX_K = 32;
+
+template <typename IndexT>
+__global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const ProbParams p) {
+  extern __shared__ u32 s_top[];  // keys[K][WT_THREADS], then positions[K][WT_THREADS]
+  const int K = p.K;
+  u32* tkey = s_top + threadIdx.x;
+  u32* tpos = s_top + K * WT_THREADS + threadIdx.x;
+  i64 S = p.S_max;
+  if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
+  for (i64 slot = (i64)blockIdx.x * WT_THREADS + threadIdx.x; slot < S; slot += (i64)gridDim.x * WT_THREADS) {
+    const i64 in_start = p.slot_start[slot];
+    const i64 deg = (i64)p.slot_deg[slot];
+    if (deg == 0 || deg > WT_MAX_DEG) continue;  // nothing to do / the warp kernel's column
+    const i64 out_start = p.sub_indptr[slot];
+    if (out_start + (deg < K ? deg : K) > p.E_cap) { raise(p.err, ERRBIT_CAPACITY); continue; }
+    if (deg <= K) {  // the whole column
+      for (i64 k = 0; k < deg; ++k) {
+        p.out_rows[out_start + k] = load_index<IndexT>(p.indices, in_start + k);
+        p.out_sel[out_start + k] = in_start + k;
+        if (p.out_cols) p.out_cols[out_start + k] = slot;
+      }
+      continue;
+    }
+    const float* pr = p.probs + in_start;
+    const int d = (int)deg;
+    u32 kmin = 0, pmin = 0;
+    int imin = 0;
+    Philox4 blk;
+    for (int e = 0; e < d; ++e) {
+      if ((e & 3) == 0) blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e >> 2));
+      const u32 key = ares_key(pick_word(blk, e & 3), __ldg(pr + e));
+      if (e < K) {
+        tkey[e * WT_THREADS] = key;
+        tpos[e * WT_THREADS] = (u32)e;
+        if (e == 0 || key <= kmin) { kmin = key; pmin = (u32)e; imin = e; }  // <=: later position leaves first
+      } else if (key > kmin) {
+        tkey[imin * WT_THREADS] = key;
+        tpos[imin * WT_THREADS] = (u32)e;
+        // new smallest: least key, the highest position among equals
+        kmin = tkey[0]; pmin = tpos[0]; imin = 0;
+        for (int j = 1; j < K; ++j) {
+          const u32 kj = tkey[j * WT_THREADS], pj = tpos[j * WT_THREADS];
+          if (kj < kmin || (kj == kmin && pj > pmin)) { kmin = kj; pmin = pj; imin = j; }
+        }
+      }
+    }
+    // winners in column order: repeatedly take the smallest remaining position
+    u32 last = 0;
+    for (int k = 0; k < K; ++k) {
+      u32 best = 0xFFFFFFFFu;
+      for (int j = 0; j < K; ++j) {
+        const u32 pj = tpos[j * WT_THREADS];
+        if (pj < best && (k == 0 || pj > last)) best = pj;
+      }
+      last = best;
+      const i64 e = in_start + best;
+      p.out_rows[out_start + k] = load_index<IndexT>(p.indices, e);
+      p.out_sel[out_start + k] = e;
+      if (p.out_cols) p.out_cols[out_start + k] = slot;
+    }
+  }
+}
+
+// Very long columns (more than WB_MIN_DEG entries): one CTA per column, same radix select and
+// ordered emit as the warp kernel but with the histogram shared by 256 threads and block scans
+// for the tie ranks and output offsets.  Keeps a hub column from being the tail of the launch.
+constexpr int WB_THREADS = 256;
+constexpr int WB_MIN_DEG = 4096;
+
+template <typename IndexT>
+__global__ void __launch_bounds__(WB_THREADS) sample_probs_block_kernel(const ProbParams p) {
+  __shared__ u32 s_hist[256];
+  __shared__ i64 s_scan[34];
+  __shared__ u32 s_digit, s_above;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  i64 S = p.S_max;
+  if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
+  const int K = p.K;
+  const i64 n_listed = *p.list_n;
+  for (i64 w = blockIdx.x; w < n_listed; w += gridDim.x) {
+    const i64 slot = p.list[w];
+    if (slot >= S) continue;
+    const i64 in_start = p.slot_start[slot];
+    const i64 deg = (i64)p.slot_deg[slot];
+    if (deg <= WB_MIN_DEG || deg <= K) continue;  // the warp kernel's column
+    const i64 out_start = p.sub_indptr[slot];
+    if (out_start + K > p.E_cap) { if (threadIdx.x == 0) raise(p.err, ERRBIT_CAPACITY); continue; }
+    const float* pr = p.probs + in_start;
+    u32 prefix = 0, prefix_mask = 0;
+    u32 remaining = (u32)K;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      s_hist[threadIdx.x] = 0;
+      __syncthreads();
+      for (i64 e0 = (i64)threadIdx.x * 4; e0 < deg; e0 += WB_THREADS * 4) {
+        const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (e0 + j < deg) {
+            const u32 key = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
+            if ((key & prefix_mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
+          }
+        }
+      }
+      __syncthreads();
+      if (wid == 0) {  // walk the buckets from the top: lane owns 8 buckets
+        u32 mine = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mine += s_hist[255 - (lane * 8 + j)];
+        u32 inc = mine;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          u32 t = __shfl_up_sync(0xffffffffu, inc, d);
+          if (lane >= d) inc += t;
+        }
+        const u32 exc = inc - mine;
+        const unsigned hit = __ballot_sync(0xffffffffu, inc >= remaining);
+        const int owner = __ffs(hit) - 1;
+        if (lane == owner) {
+          u32 run = exc;
+          for (int j = 0; j < 8; ++j) {
+            const u32 h = s_hist[255 - (lane * 8 + j)];
+            if (run + h >= remaining) { s_digit = 255u - (u32)(lane * 8 + j); s_above = run; break; }
+            run += h;
+          }
+        }
+      }
+      __syncthreads();
+      remaining -= s_above;
+      prefix |= s_digit << shift;
+      prefix_mask |= 255u << shift;
+      __syncthreads();
+    }
+    const u32 thr = prefix;
+    i64 ties_left = remaining;  // keys equal to the threshold still to take, lowest positions first
+    i64 written = 0;
+    for (i64 base = 0; base < deg; base += WB_THREADS * 4) {
+      const i64 e0 = base + (i64)threadIdx.x * 4;
+      u32 keys[4];
+      int ntie = 0;
+      if (e0 < deg) {
+        const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          keys[j] = e0 + j < deg ? ares_key(pick_word(blk, j), __ldg(pr + e0 + j)) : 0u;
+          if (e0 + j < deg && keys[j] == thr) ++ntie;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) keys[j] = 0u;
+      }
+      i64 chunk_ties;
+      i64 tie_rank = block_exclusive_scan((i64)ntie, s_scan, &chunk_ties);
+      __syncthreads();
+      bool take[4];
+      int ntake = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        take[j] = false;
+        if (e0 + j < deg) {
+          if (keys[j] > thr) take[j] = true;
+          else if (keys[j] == thr) { take[j] = tie_rank < ties_left; ++tie_rank; }
+        }
+        ntake += take[j] ? 1 : 0;
+      }
+      i64 chunk_take;
+      i64 o = out_start + written + block_exclusive_scan((i64)ntake, s_scan, &chunk_take);
+      __syncthreads();
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (take[j]) {
+          p.out_rows[o] = load_index<IndexT>(p.indices, in_start + e0 + j);
+          p.out_sel[o] = in_start + e0 + j;
+          if (p.out_cols) p.out_cols[o] = slot;
+          ++o;
+        }
+      }
+      written += chunk_take;
+      ties_left -= chunk_ties < ties_left ? chunk_ties : ties_left;
+    }
+    __syncthreads();
+  }
+}
+
 template <typename IndexT>
 __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbParams p) {
   extern __shared__ u32 s_dyn[];
@@ -65,10 +263,13 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
   i64 S = p.S_max;
   if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
   const int K = p.K;
-  for (i64 slot = (i64)blockIdx.x * WP_WARPS + wid; slot < S; slot += (i64)gridDim.x * WP_WARPS) {
-    const i64 c = p.seeds ? p.seeds[slot] : slot;
-    const i64 in_start = __ldg(p.indptr + c);
-    const i64 deg = __ldg(p.indptr + c + 1) - in_start;
+  const i64 n_listed = *p.list_n;
+  for (i64 w = (i64)blockIdx.x * WP_WARPS + wid; w < n_listed; w += (i64)gridDim.x * WP_WARPS) {
+    const i64 slot = p.list[w];
+    if (slot >= S) continue;
+    const i64 in_start = p.slot_start[slot];
+    const i64 deg = (i64)p.slot_deg[slot];
+    if (!p.replace && deg > WB_MIN_DEG && deg > K) continue;  // the block kernel's column
     const i64 out_start = p.sub_indptr[slot];
     const i64 cnt = p.sub_indptr[slot + 1] - out_start;
     if (cnt == 0) continue;
@@ -318,9 +519,26 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
 
 using namespace gsb;
 
+struct ProbLayout {
+  size_t count, start, deg, list, list_n, total;
+};
+
+static ProbLayout prob_layout(i64 S_max) {
+  ProbLayout L;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  size_t o = 0;
+  L.count = o; o = up(o + count_workspace_bytes(S_max));
+  L.start = o; o = up(o + sizeof(i64) * (size_t)(S_max + 1));
+  L.deg = o; o = up(o + sizeof(u32) * (size_t)(S_max + 1));
+  L.list = o; o = up(o + sizeof(i64) * (size_t)(S_max + 1));
+  L.list_n = o; o = up(o + 256);
+  L.total = o;
+  return L;
+}
+
 extern "C" size_t gsb_sample_cols_probs_workspace_bytes(int64_t S_max, int64_t K) {
   if (S_max < 0 || K < 1) return 0;
-  return count_workspace_bytes(S_max);
+  return prob_layout(S_max).total;
 }
 
 extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices, int indices_dtype,
@@ -338,8 +556,17 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   if (!workspace || workspace_bytes < gsb_sample_cols_probs_workspace_bytes(S_max, K))
     return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
+  const ProbLayout L = prob_layout(S_max);
+  char* ws = (char*)workspace;
+  const bool thread_path = !replace && K <= WT_MAX_K;
+  CountExtra extra;
+  extra.start = (i64*)(ws + L.start); extra.deg = (u32*)(ws + L.deg);
+  extra.list = (i64*)(ws + L.list); extra.list_n = (int*)(ws + L.list_n);
+  extra.list_min_deg = thread_path ? WT_MAX_DEG + 1 : 0;  // what is left for the warp kernel
+  GSB_CUDA_OK(cudaMemsetAsync(ws + L.list_n, 0, 256, st));
   int rc = launch_count((const i64*)indptr, (const i64*)seeds, S_max, (const i64*)d_S, K,
-                        replace ? 1 : 0, (i64*)sub_indptr, (i64*)d_num_edges, workspace, d_err, st);
+                        replace ? 1 : 0, (i64*)sub_indptr, (i64*)d_num_edges, ws + L.count, d_err, st,
+                        extra);
   if (rc != GSB_OK) return rc;
   if (S_max == 0) return GSB_OK;
   ProbParams p;
@@ -348,15 +575,36 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   p.seed = seed; p.stream = stream; p.sub_indptr = (const i64*)sub_indptr;
   p.out_rows = (i64*)out_rows; p.out_cols = (i64*)out_cols; p.out_sel = (i64*)out_sel;
   p.E_cap = E_cap; p.err = d_err;
+  p.thread_path = thread_path ? 1 : 0;
+  p.slot_start = extra.start; p.slot_deg = extra.deg; p.list = extra.list; p.list_n = extra.list_n;
+  if (p.thread_path) {
+    i64 tb = (S_max + WT_THREADS - 1) / WT_THREADS;
+    if (tb > 148 * 16) tb = 148 * 16;
+    const size_t tsmem = sizeof(u32) * 2 * (size_t)K * WT_THREADS;
+    LaunchScope ls(KID_SAMPLE_PROBS_SHORT, st);
+    if (indices_dtype == GSB_I32)
+      sample_probs_thread_kernel<int><<<(int)tb, WT_THREADS, tsmem, st>>>(p);
+    else
+      sample_probs_thread_kernel<i64><<<(int)tb, WT_THREADS, tsmem, st>>>(p);
+  }
   i64 blocks = (S_max + WP_WARPS - 1) / WP_WARPS;
   if (blocks > 148 * 16) blocks = 148 * 16;
   const size_t smem = sizeof(u32) * WP_WARPS * 256 + sizeof(float) * WP_WARPS * (size_t)K +
                       sizeof(u32) * WP_WARPS * WP_CACHE;
-  LaunchScope ls(KID_SAMPLE_PROBS, st);
-  if (indices_dtype == GSB_I32)
-    sample_probs_kernel<int><<<(int)blocks, WP_THREADS, smem, st>>>(p);
-  else
-    sample_probs_kernel<i64><<<(int)blocks, WP_THREADS, smem, st>>>(p);
+  {
+    LaunchScope ls(KID_SAMPLE_PROBS, st);
+    if (indices_dtype == GSB_I32)
+      sample_probs_kernel<int><<<(int)blocks, WP_THREADS, smem, st>>>(p);
+    else
+      sample_probs_kernel<i64><<<(int)blocks, WP_THREADS, smem, st>>>(p);
+  }
+  if (!replace) {
+    LaunchScope ls2(KID_SAMPLE_PROBS_LONG, st);
+    if (indices_dtype == GSB_I32)
+      sample_probs_block_kernel<int><<<148 * 2, WB_THREADS, 0, st>>>(p);
+    else
+      sample_probs_block_kernel<i64><<<148 * 2, WB_THREADS, 0, st>>>(p);
+  }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

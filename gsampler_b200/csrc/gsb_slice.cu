@@ -17,7 +17,7 @@ constexpr int SLICE_THREADS = 256;
 __global__ void __launch_bounds__(SLICE_THREADS)
 count_kernel(const i64* __restrict__ indptr, const i64* __restrict__ seeds, i64 S_max,
              const i64* __restrict__ d_S, i64 K, int replace, i64* __restrict__ sub_indptr,
-             i64* __restrict__ d_total, u64* status, int* ticket, int* err) {
+             i64* __restrict__ d_total, u64* status, int* ticket, int* err, const CountExtra x) {
   __shared__ i64 s_scan[34];
   __shared__ int s_tile;
   __shared__ i64 s_base;
@@ -30,10 +30,21 @@ count_kernel(const i64* __restrict__ indptr, const i64* __restrict__ seeds, i64 
   if (tile >= tiles) return;
   const i64 slot = (i64)tile * SLICE_THREADS + threadIdx.x;
   i64 cnt = 0;
+  bool listed = false;
   if (slot < S) {
     const i64 c = seeds ? seeds[slot] : slot;
-    const i64 deg = __ldg(indptr + c + 1) - __ldg(indptr + c);
+    const i64 st = __ldg(indptr + c);
+    const i64 deg = __ldg(indptr + c + 1) - st;
     cnt = K == 0 ? deg : (replace ? (deg == 0 ? 0 : K) : (deg < K ? deg : K));
+    if (x.start) { x.start[slot] = st; x.deg[slot] = deg > 0xFFFFFFFFll ? 0xFFFFFFFFu : (u32)deg; }
+    listed = x.list && cnt > 0 && deg >= x.list_min_deg;
+  }
+  if (x.list) {  // columns of at least list_min_deg entries, in no particular order
+    const unsigned bal = __ballot_sync(0xffffffffu, listed);
+    int base = 0;
+    if ((threadIdx.x & 31) == 0 && bal) base = atomicAdd(x.list_n, __popc(bal));
+    base = __shfl_sync(0xffffffffu, base, 0);
+    if (listed) x.list[base + __popc(bal & ((1u << (threadIdx.x & 31)) - 1u))] = slot;
   }
   i64 total;
   const i64 loff = block_exclusive_scan(cnt, s_scan, &total);
@@ -55,13 +66,13 @@ size_t count_workspace_bytes(i64 S_max) {
 
 int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
                  int replace, i64* sub_indptr, i64* d_total, void* workspace, int* d_err,
-                 cudaStream_t st) {
+                 cudaStream_t st, const CountExtra& extra) {
   const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, SLICE_THREADS);
   GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
   LaunchScope ls(KID_COUNT, st);
   count_kernel<<<tiles, SLICE_THREADS, 0, st>>>(indptr, seeds, S_max, d_S, K, replace, sub_indptr,
                                                 d_total, (u64*)((char*)workspace + 256),
-                                                (int*)workspace, d_err);
+                                                (int*)workspace, d_err, extra);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

@@ -252,3 +252,32 @@ def test_weighted_sampling_invariants_and_statistics(oracle, graph):
                                          8, True, 21, 0, probs=dev(w, torch.float32))
     cnt = np.bincount(host(rows), minlength=deg)
     assert rows.numel() == 32000 and stats.chisquare(cnt, 32000 * w.astype(np.float64) / w.astype(np.float64).sum()).pvalue > 0.01
+
+
+@pytest.mark.parametrize("K", [1, 7, 32, 40])
+def test_weighted_sampling_bit_exact_on_every_kernel_path(oracle, K):
+    """Short columns (thread per column), medium ones (warp, cached or recomputed keys) and a hub
+    (CTA per column) draw the same winners as the oracle; columns with fewer positive weights
+    than K fill up with zero-weight entries from the lowest positions."""
+    rng = np.random.default_rng(100 + K)
+    degs = np.concatenate([rng.integers(0, 60, 300), rng.integers(200, 1500, 12), [6000, 9000, 257, 256, K, K + 1]])
+    indptr = np.concatenate([[0], np.cumsum(degs)]).astype(np.int64)
+    n = degs.size
+    indices = rng.integers(0, n, indptr[-1]).astype(np.int64)
+    probs = (rng.random(indptr[-1]) + 0.05).astype(np.float32)
+    probs[rng.random(probs.size) < 0.2] = 0.0
+    z = int(np.flatnonzero(degs == 9000)[0])
+    probs[indptr[z]:indptr[z + 1]] = 0.0                  # a hub with no positive weight at all
+    probs[indptr[z] + 4321] = 1.0                          # ... except one entry
+    seeds = rng.permutation(n)
+    want = oracle.sample_probs_spec(indptr, indices, probs, seeds, K, False, seed=9, stream=2)
+    sub, rows, cols, sel, err = abi.sample_cols(dev(indptr), dev(indices), dev(seeds), K, False, 9, 2,
+                                                probs=dev(probs, torch.float32))
+    assert err == 0
+    sub, rows, cols, sel = map(host, (sub, rows, cols, sel))
+    assert np.array_equal(sub, want[0]) and np.array_equal(cols, want[2])
+    assert np.array_equal(rows, indices[sel])
+    # the library writes a column's winners in column order, the oracle in its own: same SET
+    col_of = np.repeat(np.arange(seeds.size), np.diff(sub))
+    assert np.all(np.diff(sel)[np.diff(col_of) == 0] > 0)
+    assert np.array_equal(sel, want[3][np.lexsort((want[3], col_of))])
