@@ -34,6 +34,7 @@ struct ListParams {
   i64* out_idx;        // [<= B*K]
   i64* out_range;      // [B+1]
   u64* status; int* ticket;
+  int* done;           // CTAs that finished the current round
   int* err;
 };
 
@@ -77,38 +78,68 @@ __global__ void list_setup_kernel(const ListParams p) {
   }
 }
 
-__global__ void __launch_bounds__(LS_THREADS) list_keys_kernel(const ListParams p) {
-  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
-  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS)
-    p.keys[i] = list_key(p, i);
-}
-
-__global__ void __launch_bounds__(LS_THREADS) list_hist_kernel(const ListParams p, int shift) {
-  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
-  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS) {
-    const int b = find_segment(p.range, p.B, i);
-    const SegState s = p.state[b];
-    if (s.take_all) continue;
-    const u32 k = p.keys[i];
-    if ((k & s.mask) == s.prefix) atomicAdd(p.hist + b * 256 + ((k >> shift) & 255u), 1u);
-  }
-}
-
-// block per segment: locate the bucket that holds the `remaining`-th largest key
-__global__ void list_pick_kernel(const ListParams p, int shift) {
-  const int b = blockIdx.x;
+// One radix-select round for all segments: histogram of the current digit over the keys that
+// still match their segment's prefix, then -- in the CTA that finishes last -- the choice of the
+// digit that holds the wanted rank.  A CTA whose 256 items lie in one segment (always, for a
+// single list) histograms in shared memory and flushes 256 counters.  The first round also
+// computes and stores the keys.  "Last CTA" is decided by a counter after a __threadfence(): no
+// CTA waits for another.
+__global__ void __launch_bounds__(LS_THREADS) list_round_kernel(const ListParams p, int shift, int first) {
   __shared__ u32 s_h[256];
-  s_h[threadIdx.x] = p.hist[b * 256 + threadIdx.x];
-  p.hist[b * 256 + threadIdx.x] = 0;  // ready for the next pass
+  __shared__ int s_last;
+  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  for (i64 base = (i64)blockIdx.x * LS_THREADS; base < n; base += (i64)gridDim.x * LS_THREADS) {
+    const i64 i = base + threadIdx.x;
+    const i64 last_i = base + LS_THREADS - 1 < n - 1 ? base + LS_THREADS - 1 : n - 1;
+    const int b_lo = find_segment(p.range, p.B, base), b_hi = find_segment(p.range, p.B, last_i);
+    const bool one_segment = b_lo == b_hi;  // uniform over the CTA
+    if (one_segment) { s_h[threadIdx.x & 255] = 0; __syncthreads(); }
+    if (i < n) {
+      const int b = one_segment ? b_lo : find_segment(p.range, p.B, i);
+      u32 k;
+      if (first) { k = list_key(p, i); p.keys[i] = k; } else { k = p.keys[i]; }
+      const SegState s = p.state[b];
+      if (!s.take_all && (k & s.mask) == s.prefix) {
+        const u32 d = (k >> shift) & 255u;
+        if (one_segment) atomicAdd(&s_h[d], 1u); else atomicAdd(p.hist + b * 256 + d, 1u);
+      }
+    }
+    if (one_segment) {
+      __syncthreads();
+      if (threadIdx.x < 256 && s_h[threadIdx.x]) atomicAdd(p.hist + b_lo * 256 + threadIdx.x, s_h[threadIdx.x]);
+      __syncthreads();
+    }
+  }
+  __threadfence();
   __syncthreads();
-  if (threadIdx.x == 0) {
+  if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  // warp per segment: locate the bucket that holds the `remaining`-th largest key
+  for (int b = wid; b < p.B; b += LS_THREADS / 32) {
     SegState s = p.state[b];
-    if (!s.take_all) {
-      u32 run = 0;
-      int d = 255;
-      for (; d > 0; --d) {
-        if (run + s_h[d] >= s.remaining) break;
-        run += s_h[d];
+    volatile u32* h = p.hist + b * 256;
+    u32 cnt[8], mine = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { cnt[j] = h[255 - (lane * 8 + j)]; h[255 - (lane * 8 + j)] = 0; mine += cnt[j]; }
+    if (s.take_all) continue;  // warp-uniform
+    u32 inc = mine;
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      u32 t = __shfl_up_sync(0xffffffffu, inc, d);
+      if (lane >= d) inc += t;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, inc >= s.remaining);
+    const int owner = hit ? __ffs(hit) - 1 : 31;
+    if (lane == owner) {
+      u32 run = inc - mine;
+      int d = 0;
+      for (int j = 0; j < 8; ++j) {
+        d = 255 - (lane * 8 + j);
+        if (run + cnt[j] >= s.remaining || d == 0) break;
+        run += cnt[j];
       }
       s.remaining -= run;
       s.prefix |= (u32)d << shift;
@@ -116,6 +147,7 @@ __global__ void list_pick_kernel(const ListParams p, int shift) {
       p.state[b] = s;
     }
   }
+  if (threadIdx.x == 0) *p.done = 0;
 }
 
 // exclusive prefixes (over ALL items, segment starts are subtracted later) of
@@ -260,15 +292,15 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
   p.stream = stream; p.keys = (u32*)(ws + L.keys); p.hist = (u32*)(ws + L.hist);
   p.state = (SegState*)(ws + L.state); p.pre_gt = (u32*)(ws + L.pre_gt);
   p.pre_eq = (u32*)(ws + L.pre_eq); p.out_idx = (i64*)out_idx; p.out_range = (i64*)out_range;
-  p.status = (u64*)(ws + L.status); p.ticket = (int*)(ws + L.ticket); p.err = d_err;
+  p.status = (u64*)(ws + L.status); p.ticket = (int*)(ws + L.ticket); p.done = p.ticket + 16;
+  p.err = d_err;
   GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.keys, st));  // ticket, status, histograms
   i64 g = (R + LS_THREADS - 1) / LS_THREADS; if (g > 148 * 8) g = 148 * 8; if (g < 1) g = 1;
   { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
   if (R > 0 && K > 0) {
-    { LaunchScope ls(KID_LIST_SAMPLE, st); list_keys_kernel<<<(int)g, LS_THREADS, 0, st>>>(p); }
     for (int shift = 24; shift >= 0; shift -= 8) {
-      { LaunchScope ls(KID_LIST_SAMPLE, st); list_hist_kernel<<<(int)g, LS_THREADS, 0, st>>>(p, shift); }
-      { LaunchScope ls(KID_LIST_SAMPLE, st); list_pick_kernel<<<(int)B, 256, 0, st>>>(p, shift); }
+      LaunchScope ls(KID_LIST_SAMPLE, st);
+      list_round_kernel<<<(int)g, LS_THREADS, 0, st>>>(p, shift, shift == 24 ? 1 : 0);
     }
     { LaunchScope ls(KID_LIST_SAMPLE, st); list_scan_kernel<<<(int)L.tiles, LS_THREADS, 0, st>>>(p); }
     { LaunchScope ls(KID_LIST_SAMPLE, st); list_emit_kernel<<<(int)g, LS_THREADS, 0, st>>>(p); }
