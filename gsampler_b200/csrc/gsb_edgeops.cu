@@ -88,6 +88,48 @@ __global__ void __launch_bounds__(EO_THREADS) spmm_scalar_kernel(const SpmmParam
   }
 }
 
+// Scalar sum per segment, the samplers' case.  Same arithmetic as the kernel above (lanes stride
+// over the segment, then a butterfly), but a warp takes 32 consecutive segments at a time: their
+// bounds arrive with one coalesced load instead of 32 dependent ones, the edge loads of
+// neighbouring segments fall into the same lines, and the 32 results leave with one coalesced
+// read-modify-write.  Short segments (a whole graph's columns) are latency-bound otherwise.
+template <typename IndexT>
+__global__ void __launch_bounds__(EO_THREADS) spmm_scalar_sum_kernel(const SpmmParams p) {
+  const int lane = threadIdx.x & 31;
+  const i64 warp0 = ((i64)blockIdx.x * EO_THREADS + threadIdx.x) >> 5;
+  const i64 nwarps = ((i64)gridDim.x * EO_THREADS) >> 5;
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  const float* __restrict__ uf = p.u;
+  const float* __restrict__ ef = p.e;
+  const i64* __restrict__ eids = p.e_ids;
+  for (i64 seg0 = warp0 * 32; seg0 < p.nseg; seg0 += nwarps * 32) {
+    const i64 mine = seg0 + lane;
+    const i64 my_st = mine < p.nseg ? __ldg(p.indptr + mine) : 0;
+    const i64 my_en = mine < p.nseg ? __ldg(p.indptr + mine + 1) : 0;
+    const int live = p.nseg - seg0 < 32 ? (int)(p.nseg - seg0) : 32;
+    float res = 0.f;
+    for (int j = 0; j < live; ++j) {
+      const i64 st = __shfl_sync(0xffffffffu, my_st, j), en = __shfl_sync(0xffffffffu, my_en, j);
+      float acc = 0.f;
+      if (p.op == OP_COPY_RHS && !eids && p.e_len == 1) {
+        for (i64 i = st + lane; i < en; i += 32) acc += __ldg(ef + i);
+      } else {
+        for (i64 i = st + lane; i < en; i += 32) {
+          const i64 cid = ul ? load_index<IndexT>(p.indices, i) : 0;
+          const i64 eid = eids ? __ldg(eids + i) : i;
+          const float l = ul ? __ldg(uf + cid * p.u_len) : 0.f;
+          const float r = ur ? __ldg(ef + eid * p.e_len) : 0.f;
+          acc += apply_op(p.op, l, r);
+        }
+      }
+#pragma unroll
+      for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, d);
+      if (lane == j) res = acc;
+    }
+    if (mine < p.nseg) p.out[mine] += res;  // the caller zero-fills `out` (accumulate semantics)
+  }
+}
+
 // Feature vectors: warp per segment, lanes over the feature dimension.
 template <typename IndexT>
 __global__ void __launch_bounds__(EO_THREADS) spmm_vector_kernel(const SpmmParams p) {
@@ -195,6 +237,70 @@ __global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_kernel(const CooParam
   }
 }
 
+// Scalar features on both sides (the samplers' case): no index arithmetic per element, and only
+// the endpoint arrays the operands actually select are read.
+__global__ void __launch_bounds__(EO_THREADS) sddmm_coo_scalar_kernel(const CooParams p) {
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  const bool need_row = (ul && p.lhs_target == 0) || (ur && p.rhs_target == 0);
+  const bool need_col = (ul && p.lhs_target == 2) || (ur && p.rhs_target == 2);
+  const i64* __restrict__ row = p.row;
+  const i64* __restrict__ col = p.col;
+  const i64* __restrict__ eids = p.e_ids;
+  const float* __restrict__ lhs = p.lhs;
+  const float* __restrict__ rhs = p.rhs;
+  float* __restrict__ out = p.out;
+  const i64 step = (i64)gridDim.x * EO_THREADS;
+#pragma unroll 4
+  for (i64 ed = (i64)blockIdx.x * EO_THREADS + threadIdx.x; ed < p.nnz; ed += step) {
+    const i64 src = need_row ? __ldg(row + ed) : 0, dst = need_col ? __ldg(col + ed) : 0;
+    const i64 eid = eids ? __ldg(eids + ed) : ed;
+    const float l = ul ? __ldg(lhs + select_target(p.lhs_target, src, eid, dst)) : 0.f;
+    const float r = ur ? __ldg(rhs + select_target(p.rhs_target, src, eid, dst)) : 0.f;
+    out[eid] = apply_op(p.op, l, r);
+  }
+}
+
+// Scalar sum over an unsorted COO.  Neighbouring edges that reduce into the same node (always,
+// when the COO is in the order of the reduced side) are summed inside the warp first, so that one
+// atomic per run reaches memory instead of one per edge.
+__global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_scalar_kernel(const CooParams p) {
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  const int lane = threadIdx.x & 31;
+  const i64* __restrict__ red = p.out_target == 2 ? p.col : p.row;   // reduced side
+  const i64* __restrict__ feat = p.out_target == 2 ? p.row : p.col;  // feature side
+  const i64* __restrict__ eids = p.e_ids;
+  const float* __restrict__ lhs = p.lhs;
+  const float* __restrict__ rhs = p.rhs;
+  const i64 step = (i64)gridDim.x * EO_THREADS;
+  const i64 rounded = (p.nnz + 31) & ~(i64)31;  // whole warps stay in the loop for the shuffles
+  for (i64 ed = (i64)blockIdx.x * EO_THREADS + threadIdx.x; ed < rounded; ed += step) {
+    const bool live = ed < p.nnz;
+    i64 dst = -1 - lane;  // distinct per lane: a dead lane joins no run
+    float v = 0.f;
+    if (live) {
+      dst = __ldg(red + ed);
+      const i64 eid = eids ? __ldg(eids + ed) : ed;
+      const float l = ul ? __ldg(lhs + __ldg(feat + ed)) : 0.f;
+      const float r = ur ? __ldg(rhs + eid) : 0.f;
+      v = apply_op(p.op, l, r);
+    }
+    const i64 prev = __shfl_up_sync(0xffffffffu, dst, 1);
+    const bool head = lane == 0 || prev != dst;
+    if (__any_sync(0xffffffffu, !head)) {
+      // runs of equal targets: suffix sums inside each run, the head holds the run's total
+      const unsigned heads = __ballot_sync(0xffffffffu, head);
+      const unsigned above = lane == 31 ? 0u : heads >> (lane + 1);
+      const int run_end = above ? lane + __ffs(above) - 1 : 31;  // last lane of this lane's run
+#pragma unroll
+      for (int d = 1; d < 32; d <<= 1) {
+        const float o = __shfl_down_sync(0xffffffffu, v, d);
+        if (lane + d <= run_end) v += o;
+      }
+    }
+    if (live && head) atomicAdd(p.out + dst, v);
+  }
+}
+
 static int wide_grid(i64 work_items, int per_block) {
   i64 g = (work_items + per_block - 1) / per_block;
   if (g > 148 * 16) g = 148 * 16;
@@ -223,7 +329,12 @@ extern "C" int gsb_spmm_segmented(const int64_t* indptr, const void* indices, in
   const int grid = wide_grid(nseg, EO_THREADS / 32);
   LaunchScope ls(KID_EDGE_SUM, st);
   const bool scalar = out_len == 1;
-  if (indices_dtype == GSB_I32) {
+  const bool scalar_sum = scalar && reduce == RED_SUM && !u_off && !e_off;
+  if (scalar_sum) {
+    const int g32 = wide_grid((nseg + 31) / 32, EO_THREADS / 32);
+    if (indices_dtype == GSB_I32) spmm_scalar_sum_kernel<int><<<g32, EO_THREADS, 0, st>>>(p);
+    else spmm_scalar_sum_kernel<i64><<<g32, EO_THREADS, 0, st>>>(p);
+  } else if (indices_dtype == GSB_I32) {
     if (scalar) spmm_scalar_kernel<int><<<grid, EO_THREADS, 0, st>>>(p);
     else spmm_vector_kernel<int><<<grid, EO_THREADS, 0, st>>>(p);
   } else {
@@ -257,7 +368,11 @@ extern "C" int gsb_sddmm_coo(const int64_t* row, const int64_t* col, const int64
               rhs, rhs_len, rhs_target, (const i64*)lhs_off, (const i64*)rhs_off, out, out_len, 0};
   cudaStream_t st = (cudaStream_t)cuda_stream;
   LaunchScope ls(KID_EDGE_OP, st);
-  sddmm_coo_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  if (out_len == 1 && (!op_uses_lhs(op) || lhs_len == 1) && (!op_uses_rhs(op) || rhs_len == 1) &&
+      !lhs_off && !rhs_off)
+    sddmm_coo_scalar_kernel<<<wide_grid(nnz, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  else
+    sddmm_coo_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }
@@ -276,7 +391,11 @@ extern "C" int gsb_spmm_coo_sum(const int64_t* row, const int64_t* col, const in
               (const i64*)u_off, (const i64*)e_off, out, out_len, u_target == 0 ? 2 : 0};
   cudaStream_t st = (cudaStream_t)cuda_stream;
   LaunchScope ls(KID_EDGE_SUM, st);
-  spmm_coo_sum_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  if (out_len == 1 && (!op_uses_lhs(op) || u_len == 1) && (!op_uses_rhs(op) || e_len == 1) &&
+      !u_off && !e_off)
+    spmm_coo_sum_scalar_kernel<<<wide_grid(nnz, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  else
+    spmm_coo_sum_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

@@ -5,10 +5,11 @@
 // Weighted selection without replacement = the K largest A-Res keys
 // log2(u_i)/p_i (u_i = draw 0 of element i's counter-based stream); uniform
 // selection = the K largest raw draws.  Instead of sorting all R keys, the
-// K-th largest key of every segment is located by a 4-pass radix select over
-// 32-bit orderable keys (per-segment 256-bin histograms), and one ordered
-// compaction emits the winners in ascending index order; ties on the threshold
-// key go to the lowest indices.  Everything is sized by R, nothing by K.
+// K-th largest key of every segment is located by a 4-round radix select over
+// 32-bit orderable keys (per-segment 256-bin histograms, one launch per round),
+// and one scan-and-emit pass writes the winners in ascending index order; ties
+// on the threshold key go to the lowest indices.  Everything is sized by R,
+// nothing by K: 6 launches per call.
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -29,8 +30,8 @@ struct ListParams {
   u32* keys;           // [R]
   u32* hist;           // [B*256]
   SegState* state;     // [B]
-  u32* pre_gt;         // [R+1]
-  u32* pre_eq;         // [R+1]
+  u32* eq_total;       // [B] keys equal to the final threshold
+  i64* seg_base;       // [B] winners before the segment's first item: above << 31 | equal
   i64* out_idx;        // [<= B*K]
   i64* out_range;      // [B+1]
   u64* status; int* ticket;
@@ -78,39 +79,73 @@ __global__ void list_setup_kernel(const ListParams p) {
   }
 }
 
+constexpr int LS_TILE = LS_THREADS * 4;  // items per CTA step: four consecutive keys per thread
+
+__device__ __forceinline__ void list_flush(const ListParams& p, u32* s_h, int b) {
+  __syncthreads();
+  if (b >= 0 && s_h[threadIdx.x]) atomicAdd(p.hist + b * 256 + threadIdx.x, s_h[threadIdx.x]);
+  s_h[threadIdx.x] = 0;
+  __syncthreads();
+}
+
 // One radix-select round for all segments: histogram of the current digit over the keys that
 // still match their segment's prefix, then -- in the CTA that finishes last -- the choice of the
-// digit that holds the wanted rank.  A CTA whose 256 items lie in one segment (always, for a
-// single list) histograms in shared memory and flushes 256 counters.  The first round also
-// computes and stores the keys.  "Last CTA" is decided by a counter after a __threadfence(): no
-// CTA waits for another.
+// digit that holds the wanted rank.  Every CTA owns one contiguous run of items and keeps its
+// histogram in shared memory for as long as the run stays inside one segment (always, for a
+// single list), so a round costs one flush of at most 256 counters per CTA, not one per tile.
+// The first round also computes and stores the keys; the last one leaves, per segment, how many
+// keys equal the threshold and the global counts of winners before the segment's first item
+// (what the emit pass subtracts).  "Last CTA" is decided by a counter after a __threadfence():
+// no CTA waits for another.
 __global__ void __launch_bounds__(LS_THREADS) list_round_kernel(const ListParams p, int shift, int first) {
   __shared__ u32 s_h[256];
+  __shared__ i64 s_scan[34];
+  __shared__ i64 s_carry;
   __shared__ int s_last;
   const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  for (i64 base = (i64)blockIdx.x * LS_THREADS; base < n; base += (i64)gridDim.x * LS_THREADS) {
-    const i64 i = base + threadIdx.x;
-    const i64 last_i = base + LS_THREADS - 1 < n - 1 ? base + LS_THREADS - 1 : n - 1;
+  const i64 per = (((n + gridDim.x - 1) / gridDim.x) + LS_TILE - 1) / LS_TILE * LS_TILE;
+  const i64 c0 = (i64)blockIdx.x * per, c1 = c0 + per < n ? c0 + per : n;
+  s_h[threadIdx.x] = 0;
+  int cur_b = -1;  // the segment whose counts sit in s_h
+  const bool spread = first && p.probs;  // weighted keys crowd into a few top digits
+  for (i64 base = c0; base < c1; base += LS_TILE) {
+    const i64 last_i = base + LS_TILE - 1 < c1 - 1 ? base + LS_TILE - 1 : c1 - 1;
     const int b_lo = find_segment(p.range, p.B, base), b_hi = find_segment(p.range, p.B, last_i);
     const bool one_segment = b_lo == b_hi;  // uniform over the CTA
-    if (one_segment) { s_h[threadIdx.x & 255] = 0; __syncthreads(); }
-    if (i < n) {
-      const int b = one_segment ? b_lo : find_segment(p.range, p.B, i);
-      u32 k;
-      if (first) { k = list_key(p, i); p.keys[i] = k; } else { k = p.keys[i]; }
-      const SegState s = p.state[b];
-      if (!s.take_all && (k & s.mask) == s.prefix) {
-        const u32 d = (k >> shift) & 255u;
-        if (one_segment) atomicAdd(&s_h[d], 1u); else atomicAdd(p.hist + b * 256 + d, 1u);
+    if (one_segment && b_lo != cur_b) { list_flush(p, s_h, cur_b); cur_b = b_lo; }
+    const i64 i0 = base + (i64)threadIdx.x * 4;
+    u32 k[4] = {0u, 0u, 0u, 0u};
+    if (first) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) if (i0 + j < c1) k[j] = list_key(p, i0 + j);
+      if (i0 + 3 < c1) *reinterpret_cast<uint4*>(p.keys + i0) = make_uint4(k[0], k[1], k[2], k[3]);
+      else for (int j = 0; j < 4; ++j) if (i0 + j < c1) p.keys[i0 + j] = k[j];
+    } else if (i0 + 3 < c1) {
+      const uint4 v = *reinterpret_cast<const uint4*>(p.keys + i0);
+      k[0] = v.x; k[1] = v.y; k[2] = v.z; k[3] = v.w;
+    } else {
+      for (int j = 0; j < 4; ++j) if (i0 + j < c1) k[j] = p.keys[i0 + j];
+    }
+    SegState s = p.state[b_lo];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      int b = b_lo;
+      bool in = i0 + j < c1;
+      if (in && !one_segment) { b = find_segment(p.range, p.B, i0 + j); s = p.state[b]; }
+      in = in && !s.take_all && (k[j] & s.mask) == s.prefix;
+      const u32 d = (k[j] >> shift) & 255u;
+      if (!one_segment) {
+        if (in) atomicAdd(p.hist + b * 256 + d, 1u);
+      } else if (spread) {  // one shared-memory add per distinct digit of the warp
+        const unsigned same = __match_any_sync(0xffffffffu, in ? d : 256u + (u32)lane);
+        if (in && lane == __ffs(same) - 1) atomicAdd(&s_h[d], (u32)__popc(same));
+      } else if (in) {
+        atomicAdd(&s_h[d], 1u);
       }
     }
-    if (one_segment) {
-      __syncthreads();
-      if (threadIdx.x < 256 && s_h[threadIdx.x]) atomicAdd(p.hist + b_lo * 256 + threadIdx.x, s_h[threadIdx.x]);
-      __syncthreads();
-    }
   }
+  list_flush(p, s_h, cur_b);
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) s_last = atomicAdd(p.done, 1) == (int)gridDim.x - 1;
@@ -135,8 +170,8 @@ __global__ void __launch_bounds__(LS_THREADS) list_round_kernel(const ListParams
     const int owner = hit ? __ffs(hit) - 1 : 31;
     if (lane == owner) {
       u32 run = inc - mine;
-      int d = 0;
-      for (int j = 0; j < 8; ++j) {
+      int d = 0, j = 0;
+      for (; j < 8; ++j) {
         d = 255 - (lane * 8 + j);
         if (run + cnt[j] >= s.remaining || d == 0) break;
         run += cnt[j];
@@ -145,14 +180,37 @@ __global__ void __launch_bounds__(LS_THREADS) list_round_kernel(const ListParams
       s.prefix |= (u32)d << shift;
       s.mask |= 255u << shift;
       p.state[b] = s;
+      if (shift == 0) p.eq_total[b] = cnt[j < 8 ? j : 7];
     }
   }
-  if (threadIdx.x == 0) *p.done = 0;
+  if (threadIdx.x == 0) { *p.done = 0; s_carry = 0; }
+  if (shift != 0) return;
+  __syncthreads();
+  // winners (above the threshold | equal to it) before each segment's first item, packed
+  for (int b0 = 0; b0 < p.B; b0 += LS_THREADS) {
+    const int b = b0 + threadIdx.x;
+    i64 packed = 0;
+    if (b < p.B) {
+      const SegState s = p.state[b];
+      i64 len = p.range[b + 1] - p.range[b];
+      if (len < 0) len = 0;
+      if (s.take_all) packed = len << 31;
+      else packed = (((len < p.K ? len : p.K) - (i64)s.remaining) << 31) | (i64)p.eq_total[b];
+    }
+    i64 tot;
+    const i64 ex = block_exclusive_scan(packed, s_scan, &tot);
+    if (b < p.B) p.seg_base[b] = s_carry + ex;
+    __syncthreads();
+    if (threadIdx.x == 0) s_carry += tot;
+    __syncthreads();
+  }
 }
 
-// exclusive prefixes (over ALL items, segment starts are subtracted later) of
-// "key above the segment threshold" and "key equal to it"
-__global__ void __launch_bounds__(LS_THREADS) list_scan_kernel(const ListParams p) {
+// Ordered emit: a chained scan over tiles of 1024 keys counts the winners before every item
+// (keys above the segment's threshold, and keys equal to it); a winner's output position is its
+// segment's offset plus its rank inside the segment, ties on the threshold going to the lowest
+// indices.  Only winners are written.
+__global__ void __launch_bounds__(LS_THREADS) list_emit_kernel(const ListParams p) {
   __shared__ i64 s_scan[34];
   __shared__ int s_tile;
   __shared__ i64 s_base;
@@ -160,45 +218,53 @@ __global__ void __launch_bounds__(LS_THREADS) list_scan_kernel(const ListParams 
   __syncthreads();
   const int tile = s_tile;
   const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
-  const i64 tiles = n / LS_THREADS + 1;  // one spare slot so that pre_*[n] is written
+  const i64 tiles = (n + LS_TILE - 1) / LS_TILE;
   if (tile >= tiles) return;
-  const i64 i = (i64)tile * LS_THREADS + threadIdx.x;
-  i64 packed = 0;  // gt count in the high 31 bits, eq count in the low 31
-  if (i < n) {
-    const int b = find_segment(p.range, p.B, i);
-    const SegState s = p.state[b];
-    const u32 k = p.keys[i];
-    if (s.take_all || k > s.prefix) packed = 1ll << 31;
-    else if (k == s.prefix) packed = 1;
+  const i64 base = (i64)tile * LS_TILE;
+  const i64 i0 = base + (i64)threadIdx.x * 4;
+  const i64 last_i = base + LS_TILE - 1 < n - 1 ? base + LS_TILE - 1 : n - 1;
+  const int b_lo = find_segment(p.range, p.B, base), b_hi = find_segment(p.range, p.B, last_i);
+  const bool one_segment = b_lo == b_hi;
+  u32 k[4] = {0u, 0u, 0u, 0u};
+  if (i0 + 3 < n) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p.keys + i0);
+    k[0] = v.x; k[1] = v.y; k[2] = v.z; k[3] = v.w;
+  } else {
+    for (int j = 0; j < 4; ++j) if (i0 + j < n) k[j] = p.keys[i0 + j];
+  }
+  int seg[4];
+  bool gt[4], eq[4];
+  i64 packed = 0;
+  SegState s = p.state[b_lo];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    seg[j] = b_lo; gt[j] = false; eq[j] = false;
+    if (i0 + j < n) {
+      if (!one_segment) { seg[j] = find_segment(p.range, p.B, i0 + j); s = p.state[seg[j]]; }
+      gt[j] = s.take_all || k[j] > s.prefix;
+      eq[j] = !s.take_all && k[j] == s.prefix;
+      packed += gt[j] ? (1ll << 31) : (eq[j] ? 1 : 0);
+    }
   }
   i64 total;
   const i64 loff = block_exclusive_scan(packed, s_scan, &total);
   if (threadIdx.x < 32) {
-    i64 base = chained_exclusive_prefix(p.status, tile, total, p.err);
-    if (threadIdx.x == 0) s_base = base;
+    i64 b = chained_exclusive_prefix(p.status, tile, total, p.err);
+    if (threadIdx.x == 0) s_base = b;
   }
   __syncthreads();
-  if (i <= n) {
-    const i64 v = s_base + loff;
-    p.pre_gt[i] = (u32)(v >> 31);
-    p.pre_eq[i] = (u32)(v & 0x7FFFFFFF);
-  }
-}
-
-__global__ void __launch_bounds__(LS_THREADS) list_emit_kernel(const ListParams p) {
-  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
-  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS) {
-    const int b = find_segment(p.range, p.B, i);
-    const SegState s = p.state[b];
-    const i64 r0 = p.range[b];
-    const u32 gt_before = p.pre_gt[i] - p.pre_gt[r0];
-    const u32 eq_before = p.pre_eq[i] - p.pre_eq[r0];
-    const u32 k = p.keys[i];
-    const bool gt = s.take_all || k > s.prefix;
-    const bool eq = !s.take_all && k == s.prefix;
-    if (gt || (eq && eq_before < s.remaining)) {
-      const u32 eq_taken = eq_before < s.remaining ? eq_before : s.remaining;
-      p.out_idx[p.out_range[b] + gt_before + (s.take_all ? 0u : eq_taken)] = i;
+  i64 run = s_base + loff;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (gt[j] || eq[j]) {
+      if (!one_segment || j == 0) s = p.state[seg[j]];
+      const i64 rel = run - p.seg_base[seg[j]];  // winners of this segment before this item
+      const u32 gt_before = (u32)(rel >> 31), eq_before = (u32)(rel & 0x7FFFFFFF);
+      if (gt[j] || eq_before < s.remaining) {
+        const u32 eq_taken = s.take_all ? 0u : (eq_before < s.remaining ? eq_before : s.remaining);
+        p.out_idx[p.out_range[seg[j]] + gt_before + eq_taken] = i0 + j;
+      }
+      run += gt[j] ? (1ll << 31) : 1;
     }
   }
 }
@@ -245,22 +311,22 @@ __global__ void list_replace_cdf_kernel(const double* __restrict__ cdf, i64 n, i
 }
 
 struct ListLayout {
-  size_t ticket, status, keys, hist, state, pre_gt, pre_eq, total;
+  size_t ticket, status, keys, hist, state, eq_total, seg_base, total;
   i64 tiles;
 };
 
 static ListLayout list_layout(i64 R, i64 B) {
   ListLayout L;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-  L.tiles = R / LS_THREADS + 2;
+  L.tiles = R / (LS_THREADS * 4) + 2;
   size_t o = 0;
   L.ticket = o; o = up(o + 256);
   L.status = o; o = up(o + sizeof(u64) * (size_t)L.tiles);
   L.hist = o; o = up(o + sizeof(u32) * 256 * (size_t)(B > 0 ? B : 1));
   L.keys = o; o = up(o + sizeof(u32) * (size_t)(R + 1));
   L.state = o; o = up(o + sizeof(SegState) * (size_t)(B > 0 ? B : 1));
-  L.pre_gt = o; o = up(o + sizeof(u32) * (size_t)(R + 2));
-  L.pre_eq = o; o = up(o + sizeof(u32) * (size_t)(R + 2));
+  L.eq_total = o; o = up(o + sizeof(u32) * (size_t)(B > 0 ? B : 1));
+  L.seg_base = o; o = up(o + sizeof(i64) * (size_t)(B > 0 ? B : 1));
   // the with-replacement path reuses the region as a double CDF
   size_t cdf = up(sizeof(double) * (size_t)(R + 1));
   L.total = o > cdf ? o : cdf;
@@ -290,20 +356,19 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
   ListParams p;
   p.probs = probs; p.range = (const i64*)range; p.B = (int)B; p.R = R; p.K = K; p.seed = seed;
   p.stream = stream; p.keys = (u32*)(ws + L.keys); p.hist = (u32*)(ws + L.hist);
-  p.state = (SegState*)(ws + L.state); p.pre_gt = (u32*)(ws + L.pre_gt);
-  p.pre_eq = (u32*)(ws + L.pre_eq); p.out_idx = (i64*)out_idx; p.out_range = (i64*)out_range;
+  p.state = (SegState*)(ws + L.state); p.eq_total = (u32*)(ws + L.eq_total);
+  p.seg_base = (i64*)(ws + L.seg_base); p.out_idx = (i64*)out_idx; p.out_range = (i64*)out_range;
   p.status = (u64*)(ws + L.status); p.ticket = (int*)(ws + L.ticket); p.done = p.ticket + 16;
   p.err = d_err;
   GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.keys, st));  // ticket, status, histograms
-  i64 g = (R + LS_THREADS - 1) / LS_THREADS; if (g > 148 * 8) g = 148 * 8; if (g < 1) g = 1;
+  i64 g = (R + LS_TILE - 1) / LS_TILE; if (g > 148 * 4) g = 148 * 4; if (g < 1) g = 1;
   { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
   if (R > 0 && K > 0) {
     for (int shift = 24; shift >= 0; shift -= 8) {
       LaunchScope ls(KID_LIST_SAMPLE, st);
       list_round_kernel<<<(int)g, LS_THREADS, 0, st>>>(p, shift, shift == 24 ? 1 : 0);
     }
-    { LaunchScope ls(KID_LIST_SAMPLE, st); list_scan_kernel<<<(int)L.tiles, LS_THREADS, 0, st>>>(p); }
-    { LaunchScope ls(KID_LIST_SAMPLE, st); list_emit_kernel<<<(int)g, LS_THREADS, 0, st>>>(p); }
+    { LaunchScope ls(KID_LIST_SAMPLE, st); list_emit_kernel<<<(int)L.tiles, LS_THREADS, 0, st>>>(p); }
   }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;

@@ -44,6 +44,8 @@ struct ProbParams {
   const u32* slot_deg;    // [S] its length                          } the count pass
   const i64* list;        // slots the warp kernel has to process (unordered)
   const int* list_n;
+  i64* long_list;  // filled by the warp kernel: the columns it leaves to the CTA kernel
+  int* long_n;
 };
 
 __device__ __forceinline__ u32 orderable(float f) {
@@ -68,7 +70,10 @@ __device__ __forceinline__ u32 ares_key(u32 draw, float p) {
 // the warp kernel selects.  About 30 instructions per entry instead of a warp's several
 // hundred per column.  Longer columns and larger K stay with the warp kernel.
 constexpr int WT_THREADS = 128;
-constexpr int WT_MAX_DEG = 256;
+#ifndef GSB_WT_MAX_DEG
+#define GSB_WT_MAX_DEG 128
+#endif
+constexpr int WT_MAX_DEG = GSB_WT_MAX_DEG;
 constexpr int WT_MAX_K = 32;
 
 template <typename IndexT>
@@ -148,13 +153,12 @@ __global__ void __launch_bounds__(WB_THREADS) sample_probs_block_kernel(const Pr
   i64 S = p.S_max;
   if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
   const int K = p.K;
-  const i64 n_listed = *p.list_n;
+  const i64 n_listed = *p.long_n;
   for (i64 w = blockIdx.x; w < n_listed; w += gridDim.x) {
-    const i64 slot = p.list[w];
+    const i64 slot = p.long_list[w];
     if (slot >= S) continue;
     const i64 in_start = p.slot_start[slot];
     const i64 deg = (i64)p.slot_deg[slot];
-    if (deg <= WB_MIN_DEG || deg <= K) continue;  // the warp kernel's column
     const i64 out_start = p.sub_indptr[slot];
     if (out_start + K > p.E_cap) { if (threadIdx.x == 0) raise(p.err, ERRBIT_CAPACITY); continue; }
     const float* pr = p.probs + in_start;
@@ -269,7 +273,10 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
     if (slot >= S) continue;
     const i64 in_start = p.slot_start[slot];
     const i64 deg = (i64)p.slot_deg[slot];
-    if (!p.replace && deg > WB_MIN_DEG && deg > K) continue;  // the block kernel's column
+    if (!p.replace && deg > WB_MIN_DEG && deg > K) {  // the block kernel's column
+      if (lane == 0) p.long_list[atomicAdd(p.long_n, 1)] = slot;
+      continue;
+    }
     const i64 out_start = p.sub_indptr[slot];
     const i64 cnt = p.sub_indptr[slot + 1] - out_start;
     if (cnt == 0) continue;
@@ -520,7 +527,7 @@ __global__ void __launch_bounds__(WP_THREADS) sample_probs_kernel(const ProbPara
 using namespace gsb;
 
 struct ProbLayout {
-  size_t count, start, deg, list, list_n, total;
+  size_t count, start, deg, list, long_list, list_n, total;
 };
 
 static ProbLayout prob_layout(i64 S_max) {
@@ -531,6 +538,7 @@ static ProbLayout prob_layout(i64 S_max) {
   L.start = o; o = up(o + sizeof(i64) * (size_t)(S_max + 1));
   L.deg = o; o = up(o + sizeof(u32) * (size_t)(S_max + 1));
   L.list = o; o = up(o + sizeof(i64) * (size_t)(S_max + 1));
+  L.long_list = o; o = up(o + sizeof(i64) * (size_t)(S_max + 1));
   L.list_n = o; o = up(o + 256);
   L.total = o;
   return L;
@@ -577,6 +585,7 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   p.E_cap = E_cap; p.err = d_err;
   p.thread_path = thread_path ? 1 : 0;
   p.slot_start = extra.start; p.slot_deg = extra.deg; p.list = extra.list; p.list_n = extra.list_n;
+  p.long_list = (i64*)(ws + L.long_list); p.long_n = (int*)(ws + L.list_n) + 16;
   if (p.thread_path) {
     i64 tb = (S_max + WT_THREADS - 1) / WT_THREADS;
     if (tb > 148 * 16) tb = 148 * 16;
