@@ -249,14 +249,29 @@ __global__ void __launch_bounds__(EO_THREADS) sddmm_coo_scalar_kernel(const CooP
   const float* __restrict__ lhs = p.lhs;
   const float* __restrict__ rhs = p.rhs;
   float* __restrict__ out = p.out;
-  const i64 step = (i64)gridDim.x * EO_THREADS;
-#pragma unroll 4
-  for (i64 ed = (i64)blockIdx.x * EO_THREADS + threadIdx.x; ed < p.nnz; ed += step) {
-    const i64 src = need_row ? __ldg(row + ed) : 0, dst = need_col ? __ldg(col + ed) : 0;
-    const i64 eid = eids ? __ldg(eids + ed) : ed;
-    const float l = ul ? __ldg(lhs + select_target(p.lhs_target, src, eid, dst)) : 0.f;
-    const float r = ur ? __ldg(rhs + select_target(p.rhs_target, src, eid, dst)) : 0.f;
-    out[eid] = apply_op(p.op, l, r);
+  // four independent, coalesced edges per thread and step: the loads of all four are in flight
+  // before the first gather is needed
+  const i64 step = (i64)gridDim.x * EO_THREADS * 4;
+  for (i64 base = (i64)blockIdx.x * EO_THREADS * 4 + threadIdx.x; base < p.nnz; base += step) {
+    i64 src[4], dst[4], eid[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const i64 ed = base + k * EO_THREADS;
+      const bool in = ed < p.nnz;
+      src[k] = need_row && in ? __ldg(row + ed) : 0;
+      dst[k] = need_col && in ? __ldg(col + ed) : 0;
+      eid[k] = eids && in ? __ldg(eids + ed) : ed;
+    }
+    float l[4], r[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool in = base + k * EO_THREADS < p.nnz;
+      l[k] = ul && in ? __ldg(lhs + select_target(p.lhs_target, src[k], eid[k], dst[k])) : 0.f;
+      r[k] = ur && in ? __ldg(rhs + select_target(p.rhs_target, src[k], eid[k], dst[k])) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (base + k * EO_THREADS < p.nnz) out[eid[k]] = apply_op(p.op, l[k], r[k]);
   }
 }
 
@@ -271,33 +286,42 @@ __global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_scalar_kernel(const C
   const i64* __restrict__ eids = p.e_ids;
   const float* __restrict__ lhs = p.lhs;
   const float* __restrict__ rhs = p.rhs;
-  const i64 step = (i64)gridDim.x * EO_THREADS;
-  const i64 rounded = (p.nnz + 31) & ~(i64)31;  // whole warps stay in the loop for the shuffles
-  for (i64 ed = (i64)blockIdx.x * EO_THREADS + threadIdx.x; ed < rounded; ed += step) {
-    const bool live = ed < p.nnz;
-    i64 dst = -1 - lane;  // distinct per lane: a dead lane joins no run
-    float v = 0.f;
-    if (live) {
-      dst = __ldg(red + ed);
-      const i64 eid = eids ? __ldg(eids + ed) : ed;
-      const float l = ul ? __ldg(lhs + __ldg(feat + ed)) : 0.f;
-      const float r = ur ? __ldg(rhs + eid) : 0.f;
-      v = apply_op(p.op, l, r);
-    }
-    const i64 prev = __shfl_up_sync(0xffffffffu, dst, 1);
-    const bool head = lane == 0 || prev != dst;
-    if (__any_sync(0xffffffffu, !head)) {
-      // runs of equal targets: suffix sums inside each run, the head holds the run's total
-      const unsigned heads = __ballot_sync(0xffffffffu, head);
-      const unsigned above = lane == 31 ? 0u : heads >> (lane + 1);
-      const int run_end = above ? lane + __ffs(above) - 1 : 31;  // last lane of this lane's run
+  const i64 step = (i64)gridDim.x * EO_THREADS * 4;
+  // whole CTAs stay in the loop (the shuffles need full warps); four coalesced groups per step
+  for (i64 base = (i64)blockIdx.x * EO_THREADS * 4; base < p.nnz; base += step) {
+    i64 dst[4];
+    float v[4];
 #pragma unroll
-      for (int d = 1; d < 32; d <<= 1) {
-        const float o = __shfl_down_sync(0xffffffffu, v, d);
-        if (lane + d <= run_end) v += o;
+    for (int k = 0; k < 4; ++k) {
+      const i64 ed = base + k * EO_THREADS + threadIdx.x;
+      dst[k] = -1 - lane;  // distinct per lane: a dead lane joins no run
+      v[k] = 0.f;
+      if (ed < p.nnz) {
+        dst[k] = __ldg(red + ed);
+        const i64 eid = eids ? __ldg(eids + ed) : ed;
+        const float l = ul ? __ldg(lhs + __ldg(feat + ed)) : 0.f;
+        const float r = ur ? __ldg(rhs + eid) : 0.f;
+        v[k] = apply_op(p.op, l, r);
       }
     }
-    if (live && head) atomicAdd(p.out + dst, v);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const i64 prev = __shfl_up_sync(0xffffffffu, dst[k], 1);
+      const bool head = lane == 0 || prev != dst[k];
+      float acc = v[k];
+      if (__any_sync(0xffffffffu, !head)) {
+        // runs of equal targets: suffix sums inside each run, the head holds the run's total
+        const unsigned heads = __ballot_sync(0xffffffffu, head);
+        const unsigned above = lane == 31 ? 0u : heads >> (lane + 1);
+        const int run_end = above ? lane + __ffs(above) - 1 : 31;  // last lane of this lane's run
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+          const float o = __shfl_down_sync(0xffffffffu, acc, d);
+          if (lane + d <= run_end) acc += o;
+        }
+      }
+      if (dst[k] >= 0 && head) atomicAdd(p.out + dst[k], acc);
+    }
   }
 }
 
@@ -370,7 +394,7 @@ extern "C" int gsb_sddmm_coo(const int64_t* row, const int64_t* col, const int64
   LaunchScope ls(KID_EDGE_OP, st);
   if (out_len == 1 && (!op_uses_lhs(op) || lhs_len == 1) && (!op_uses_rhs(op) || rhs_len == 1) &&
       !lhs_off && !rhs_off)
-    sddmm_coo_scalar_kernel<<<wide_grid(nnz, EO_THREADS), EO_THREADS, 0, st>>>(p);
+    sddmm_coo_scalar_kernel<<<wide_grid(nnz, EO_THREADS * 4), EO_THREADS, 0, st>>>(p);
   else
     sddmm_coo_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
   GSB_CUDA_OK(cudaGetLastError());
@@ -393,7 +417,7 @@ extern "C" int gsb_spmm_coo_sum(const int64_t* row, const int64_t* col, const in
   LaunchScope ls(KID_EDGE_SUM, st);
   if (out_len == 1 && (!op_uses_lhs(op) || u_len == 1) && (!op_uses_rhs(op) || e_len == 1) &&
       !u_off && !e_off)
-    spmm_coo_sum_scalar_kernel<<<wide_grid(nnz, EO_THREADS), EO_THREADS, 0, st>>>(p);
+    spmm_coo_sum_scalar_kernel<<<wide_grid(nnz, EO_THREADS * 4), EO_THREADS, 0, st>>>(p);
   else
     spmm_coo_sum_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
   GSB_CUDA_OK(cudaGetLastError());

@@ -49,18 +49,42 @@ __device__ __forceinline__ i64 segment_in_range(const i64* __restrict__ indptr, 
   return lo;
 }
 
-template <typename IndexT, bool FILL>
+// bits[w] bit j = (map[32 w + j] present): the membership test of the counting pass, small enough
+// (one bit per possible id) to stay in L1 where the 32-bit map only fits L2
+__global__ void bits_build_kernel(const u32* __restrict__ map, i64 id_bound, u32* __restrict__ bits) {
+  const i64 rounded = (id_bound + 31) & ~(i64)31;
+  for (i64 i = (i64)blockIdx.x * blockDim.x + threadIdx.x; i < rounded; i += (i64)gridDim.x * blockDim.x) {
+    const unsigned present = __ballot_sync(0xffffffffu, i < id_bound && map[i] != MAP_ABSENT);
+    if ((threadIdx.x & 31) == 0) bits[i >> 5] = present;
+  }
+}
+
+// tile_seg[t] = segment of entry t * AC_TILE (the last segment for tiles past the end).  One
+// thread per tile: the 20-odd dependent loads of a binary search over the whole indptr are hidden
+// by the other searches here, where inside the tile kernels they were each tile's critical path.
+__global__ void tile_segment_kernel(const i64* __restrict__ indptr, i64 nseg, i64 n_tiles,
+                                    i64* __restrict__ tile_seg) {
+  const i64 t = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tiles || nseg <= 0) return;
+  const i64 e = t * AC_TILE, nnz = indptr[nseg];
+  tile_seg[t] = e < nnz ? (i64)find_segment(indptr, (int)nseg, e) : nseg - 1;
+}
+
+// Pass 1: membership of every entry (bitmap test), one byte per thread saying which of its four
+// entries stay, the thread's exclusive offset inside its tile (16 bits) and the tile's total.
+// The tiles' exclusive prefixes come from a separate one-CTA scan (tile_scan_kernel): with over
+// 10^5 tiles a chained look-back was the critical path of this pass (its prefix moves at most 32
+// tiles per memory round trip).  No segment logic here: the segments' output offsets follow from
+// these arrays (across_offsets_kernel), and so do the output positions of pass 2, which therefore
+// needs neither a scan nor a barrier.
+template <typename IndexT>
 __global__ void __launch_bounds__(RS_THREADS)
-across_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 nseg, i64 nnz_max,
-              const u32* __restrict__ map, i64 id_bound, i64* __restrict__ out_indptr,
-              i64* __restrict__ out_ids, i64* __restrict__ out_seg, i64* __restrict__ out_sel,
-              u64* status, int* ticket, int* err) {
+across_mark_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 nseg,
+                   i64 nnz_max, const u32* __restrict__ bits, i64 id_bound,
+                   unsigned char* __restrict__ nib, unsigned short* __restrict__ toff,
+                   u32* __restrict__ tile_total, int* err) {
   __shared__ i64 s_scan[34];
-  __shared__ int s_tile;
-  __shared__ i64 s_base, s_lo, s_hi;
-  if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
-  __syncthreads();
-  const int tile = s_tile;
+  const i64 tile = blockIdx.x;
   i64 nnz = nseg > 0 ? indptr[nseg] : 0;
   if (nnz > nnz_max || nnz < 0) {
     if (tile == 0 && threadIdx.x == 0) raise(err, ERRBIT_CAPACITY);
@@ -68,65 +92,104 @@ across_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, 
   }
   const i64 tiles = nnz == 0 ? 1 : (nnz + AC_TILE - 1) / AC_TILE;
   if (tile >= tiles) return;
-  const i64 e0 = (i64)tile * AC_TILE;
-  const i64 e_last = e0 + AC_TILE - 1 < nnz - 1 ? e0 + AC_TILE - 1 : nnz - 1;
-  if (threadIdx.x < 2 && nnz > 0) {
-    const i64 s = find_segment(indptr, (int)nseg, threadIdx.x == 0 ? e0 : e_last);
-    if (threadIdx.x == 0) s_lo = s; else s_hi = s;
-  }
-  // four consecutive entries per thread
-  const i64 first = e0 + (i64)threadIdx.x * AC_PER_THREAD;
-  u32 pos[AC_PER_THREAD];
-  int kept = 0;
+  const i64 first = tile * AC_TILE + (i64)threadIdx.x * AC_PER_THREAD;
+  unsigned keep = 0;  // bit j: entry first + j stays
 #pragma unroll
   for (int j = 0; j < AC_PER_THREAD; ++j) {
     const i64 e = first + j;
-    pos[j] = MAP_ABSENT;
     if (e < nnz) {
       const i64 id = load_index<IndexT>(indices, e);
-      if (id >= 0 && id < id_bound) pos[j] = __ldg(map + id);
+      if (id >= 0 && id < id_bound && ((__ldg(bits + (id >> 5)) >> (id & 31)) & 1u)) keep |= 1u << j;
     }
-    kept += pos[j] != MAP_ABSENT;
   }
   i64 total;
-  const i64 loff = block_exclusive_scan((i64)kept, s_scan, &total);  // also orders s_lo / s_hi
-  if (threadIdx.x < 32) {
-    const i64 base = chained_exclusive_prefix(status, tile, total, err);
-    if (threadIdx.x == 0) s_base = base;
-  }
-  __syncthreads();
-  i64 run = s_base + loff;  // kept entries before this thread's first entry
-  if (first < nnz) {
-    i64 seg = segment_in_range(indptr, s_lo, s_hi, first);
-    i64 seg_end = __ldg(indptr + seg + 1);
-#pragma unroll
-    for (int j = 0; j < AC_PER_THREAD; ++j) {
-      const i64 e = first + j;
-      if (e >= nnz) break;
-      while (e >= seg_end) { ++seg; seg_end = __ldg(indptr + seg + 1); }  // skips empty segments
-      if (!FILL) {
-        if (__ldg(indptr + seg) == e) {  // first entry of its segment: the segment's output offset
-          i64 s = seg;
-          out_indptr[s] = run;
-          while (s > 0 && __ldg(indptr + s - 1) == e) out_indptr[--s] = run;  // empty ones before it
-        }
-      } else if (pos[j] != MAP_ABSENT) {
-        out_ids[run] = (i64)pos[j];
-        out_sel[run] = e;
-        if (out_seg) out_seg[run] = seg;
-      }
-      run += pos[j] != MAP_ABSENT;
-    }
-  }
-  if (!FILL && tile == tiles - 1 && threadIdx.x == 0) {
-    const i64 grand = s_base + total;  // everything kept; also the offset of trailing empty segments
-    i64 s = nseg;
-    out_indptr[s] = grand;
-    while (s > 0 && indptr[s - 1] == nnz) out_indptr[--s] = grand;
+  const i64 loff = block_exclusive_scan((i64)__popc(keep), s_scan, &total);
+  nib[tile * RS_THREADS + threadIdx.x] = (unsigned char)keep;
+  toff[tile * RS_THREADS + threadIdx.x] = (unsigned short)loff;
+  if (threadIdx.x == 0) tile_total[tile] = (u32)total;
+}
+
+// tile_base[t] = sum of tile_total[0..t), tile_base[tiles] = everything; one CTA, every thread a
+// contiguous run of tiles
+__global__ void __launch_bounds__(1024)
+tile_scan_kernel(const i64* __restrict__ indptr, i64 nseg, i64 nnz_max,
+                 const u32* __restrict__ tile_total, i64* __restrict__ tile_base) {
+  __shared__ i64 s_scan[34];
+  i64 nnz = nseg > 0 ? indptr[nseg] : 0;
+  if (nnz > nnz_max || nnz < 0) nnz = 0;
+  const i64 tiles = nnz == 0 ? 1 : (nnz + AC_TILE - 1) / AC_TILE;
+  const i64 per = (tiles + 1023) / 1024;
+  const i64 lo = (i64)threadIdx.x * per, hi = lo + per < tiles ? lo + per : tiles;
+  i64 sum = 0;
+  for (i64 t = lo; t < hi; ++t) sum += tile_total[t];
+  i64 grand;
+  i64 run = block_exclusive_scan(sum, s_scan, &grand);
+  for (i64 t = lo; t < hi; ++t) { tile_base[t] = run; run += tile_total[t]; }
+  if (threadIdx.x == 0) tile_base[tiles] = grand;
+}
+
+// kept entries before entry e (e < nnz)
+__device__ __forceinline__ i64 across_kept_before(i64 e, const unsigned char* __restrict__ nib,
+                                                  const unsigned short* __restrict__ toff,
+                                                  const i64* __restrict__ tile_base) {
+  const i64 t = e / AC_PER_THREAD;  // tile * RS_THREADS + thread
+  const unsigned below = (1u << (unsigned)(e % AC_PER_THREAD)) - 1u;
+  return tile_base[e / AC_TILE] + (i64)toff[t] + __popc((unsigned)nib[t] & below);
+}
+
+// out_indptr[s] = kept entries before the first entry of segment s; thread per segment
+__global__ void across_offsets_kernel(const i64* __restrict__ indptr, i64 nseg, i64 nnz_max,
+                                      const unsigned char* __restrict__ nib,
+                                      const unsigned short* __restrict__ toff,
+                                      const i64* __restrict__ tile_base, i64* __restrict__ out_indptr) {
+  i64 nnz = nseg > 0 ? indptr[nseg] : 0;
+  if (nnz > nnz_max || nnz < 0) nnz = 0;
+  const i64 tiles = nnz == 0 ? 1 : (nnz + AC_TILE - 1) / AC_TILE;
+  for (i64 s = (i64)blockIdx.x * blockDim.x + threadIdx.x; s <= nseg; s += (i64)gridDim.x * blockDim.x) {
+    const i64 e = indptr[s];
+    out_indptr[s] = e >= nnz || e < 0 ? tile_base[tiles] : across_kept_before(e, nib, toff, tile_base);
   }
 }
 
-// COO filter: keep edge e iff key[e] is in the set; ordered compaction.
+// Pass 2: every thread writes the kept ones of its four entries; the segment of an entry is
+// looked up only when the caller wants the COO form (out_seg).
+template <typename IndexT>
+__global__ void __launch_bounds__(RS_THREADS)
+across_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 nseg,
+                   i64 nnz_max, const u32* __restrict__ map, const unsigned char* __restrict__ nib,
+                   const unsigned short* __restrict__ toff, const i64* __restrict__ tile_base,
+                   const i64* __restrict__ tile_seg, i64* __restrict__ out_ids,
+                   i64* __restrict__ out_seg, i64* __restrict__ out_sel) {
+  const i64 nnz = nseg > 0 ? indptr[nseg] : 0;
+  if (nnz > nnz_max || nnz < 0) return;
+  const i64 tile = blockIdx.x;
+  const i64 t = tile * RS_THREADS + threadIdx.x;
+  const i64 first = t * AC_PER_THREAD;
+  if (first >= nnz) return;
+  const unsigned keep = nib[t];
+  if (!keep) return;
+  i64 run = tile_base[tile] + (i64)toff[t];
+  i64 seg = 0, seg_end = 0;
+  if (out_seg) {
+    seg = segment_in_range(indptr, tile_seg[tile], tile_seg[tile + 1], first);
+    seg_end = __ldg(indptr + seg + 1);
+  }
+#pragma unroll
+  for (int j = 0; j < AC_PER_THREAD; ++j) {
+    if (!((keep >> j) & 1u)) continue;
+    const i64 e = first + j;
+    out_ids[run] = (i64)__ldg(map + load_index<IndexT>(indices, e));
+    out_sel[run] = e;
+    if (out_seg) {
+      while (e >= seg_end) { ++seg; seg_end = __ldg(indptr + seg + 1); }  // skips empty segments
+      out_seg[run] = seg;
+    }
+    ++run;
+  }
+}
+
+// COO filter: keep edge e iff key[e] is in the set; ordered compaction over tiles of 1024 edges
+// (four consecutive edges per thread).
 __global__ void __launch_bounds__(RS_THREADS)
 coo_filter_kernel(const i64* __restrict__ key, const i64* __restrict__ other, i64 nnz,
                   const u32* __restrict__ map, i64 id_bound, i64* __restrict__ out_key,
@@ -138,41 +201,61 @@ coo_filter_kernel(const i64* __restrict__ key, const i64* __restrict__ other, i6
   if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
   __syncthreads();
   const int tile = s_tile;
-  const i64 e = (i64)tile * RS_THREADS + threadIdx.x;
-  u32 pos = MAP_ABSENT;
-  if (e < nnz) {
-    const i64 id = key[e];
-    if (id >= 0 && id < id_bound) pos = __ldg(map + id);
+  const i64 tiles = nnz == 0 ? 1 : (nnz + AC_TILE - 1) / AC_TILE;
+  if (tile >= tiles) return;
+  const i64 first = (i64)tile * AC_TILE + (i64)threadIdx.x * AC_PER_THREAD;
+  u32 pos[AC_PER_THREAD];
+  int kept = 0;
+#pragma unroll
+  for (int j = 0; j < AC_PER_THREAD; ++j) {
+    pos[j] = MAP_ABSENT;
+    if (first + j < nnz) {
+      const i64 id = key[first + j];
+      if (id >= 0 && id < id_bound) pos[j] = __ldg(map + id);
+    }
+    kept += pos[j] != MAP_ABSENT;
   }
   i64 total;
-  const i64 loff = block_exclusive_scan(pos != MAP_ABSENT ? 1 : 0, s_scan, &total);
+  const i64 loff = block_exclusive_scan((i64)kept, s_scan, &total);
   if (threadIdx.x < 32) {
     i64 base = chained_exclusive_prefix(status, tile, total, err);
     if (threadIdx.x == 0) s_base = base;
   }
   __syncthreads();
-  if (pos != MAP_ABSENT) {
-    const i64 w = s_base + loff;
-    out_key[w] = (i64)pos;
-    out_other[w] = other[e];
-    out_sel[w] = e;
+  i64 w = s_base + loff;
+#pragma unroll
+  for (int j = 0; j < AC_PER_THREAD; ++j) {
+    if (pos[j] != MAP_ABSENT) {
+      out_key[w] = (i64)pos[j];
+      out_other[w] = other[first + j];
+      out_sel[w] = first + j;
+      ++w;
+    }
   }
-  if ((e == nnz - 1) || (nnz == 0 && e == 0)) *d_count = s_base + total;
+  if (tile == tiles - 1 && threadIdx.x == 0) *d_count = s_base + total;
 }
 
 struct AcrossLayout {
-  size_t ticket, status, map, total;
+  size_t ticket, status, map, bits, nib, toff, tile_total, tile_base, tile_seg, total;
   i64 tiles;
 };
 
-static AcrossLayout across_layout(i64 units, i64 id_bound) {
+// `entries` = most entries the operand can hold; with_mask adds what the two-pass CSC form hands
+// from its first pass to its second
+static AcrossLayout across_layout(i64 entries, i64 id_bound, bool with_mask) {
   AcrossLayout L;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-  L.tiles = (units + RS_THREADS - 1) / RS_THREADS + 1;
+  L.tiles = (entries + AC_TILE - 1) / AC_TILE + 1;
   size_t o = 0;
   L.ticket = o; o = up(o + 256);
   L.status = o; o = up(o + sizeof(u64) * (size_t)L.tiles);
   L.map = o; o = up(o + sizeof(u32) * (size_t)(id_bound > 0 ? id_bound : 1));
+  L.bits = o; if (with_mask) o = up(o + sizeof(u32) * (size_t)(id_bound / 32 + 1));
+  L.nib = o; if (with_mask) o = up(o + (size_t)L.tiles * RS_THREADS);
+  L.toff = o; if (with_mask) o = up(o + sizeof(unsigned short) * (size_t)L.tiles * RS_THREADS);
+  L.tile_total = o; if (with_mask) o = up(o + sizeof(u32) * (size_t)L.tiles);
+  L.tile_base = o; if (with_mask) o = up(o + sizeof(i64) * (size_t)(L.tiles + 1));
+  L.tile_seg = o; if (with_mask) o = up(o + sizeof(i64) * (size_t)(L.tiles + 1));
   L.total = o;
   return L;
 }
@@ -355,26 +438,7 @@ using namespace gsb;
 
 extern "C" size_t gsb_slice_across_workspace_bytes(int64_t nnz_max, int64_t id_bound) {
   if (nnz_max < 0 || id_bound < 0) return 0;
-  return across_layout((nnz_max + AC_PER_THREAD - 1) / AC_PER_THREAD, id_bound).total;
-}
-
-template <bool FILL>
-static int launch_across(const int64_t* indptr, const void* indices, int indices_dtype, int64_t nseg,
-                         int64_t nnz_max, int64_t id_bound, int64_t* out_indptr, int64_t* out_ids,
-                         int64_t* out_seg, int64_t* out_sel, char* ws, const AcrossLayout& L, int* d_err,
-                         cudaStream_t st) {
-  const int tiles = nnz_max == 0 ? 1 : ceil_div_i(nnz_max, AC_TILE);
-  LaunchScope ls(KID_SLICE_ROWS, st);
-  if (indices_dtype == GSB_I32)
-    across_kernel<int, FILL><<<tiles, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.map), id_bound, (i64*)out_indptr,
-        (i64*)out_ids, (i64*)out_seg, (i64*)out_sel, (u64*)(ws + L.status), (int*)(ws + L.ticket), d_err);
-  else
-    across_kernel<i64, FILL><<<tiles, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.map), id_bound, (i64*)out_indptr,
-        (i64*)out_ids, (i64*)out_seg, (i64*)out_sel, (u64*)(ws + L.status), (int*)(ws + L.ticket), d_err);
-  GSB_CUDA_OK(cudaGetLastError());
-  return GSB_OK;
+  return across_layout(nnz_max, id_bound, true).total;
 }
 
 extern "C" int gsb_slice_across_count(const int64_t* indptr, const void* indices, int indices_dtype,
@@ -386,14 +450,44 @@ extern "C" int gsb_slice_across_count(const int64_t* indptr, const void* indices
     return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   if (R >= 0xFFFFFFFFll || id_bound > (1ll << 33)) return GSB_ERR_UNSUPPORTED;
-  const AcrossLayout L = across_layout((nnz_max + AC_PER_THREAD - 1) / AC_PER_THREAD, id_bound);
+  const AcrossLayout L = across_layout(nnz_max, id_bound, true);
   if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
   int rc = build_map(ws, L, (const i64*)ids, R, id_bound, d_err, st);
   if (rc != GSB_OK) return rc;
-  return launch_across<false>(indptr, indices, indices_dtype, nseg, nnz_max, id_bound, out_indptr, nullptr,
-                              nullptr, nullptr, ws, L, d_err, st);
+  {
+    i64 g = (id_bound + 255) / 256; if (g > 148 * 16) g = 148 * 16; if (g < 1) g = 1;
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    bits_build_kernel<<<(int)g, 256, 0, st>>>((const u32*)(ws + L.map), id_bound, (u32*)(ws + L.bits));
+  }
+  const int tiles = nnz_max == 0 ? 1 : ceil_div_i(nnz_max, AC_TILE);
+  {
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    if (indices_dtype == GSB_I32)
+      across_mark_kernel<int><<<tiles, RS_THREADS, 0, st>>>(
+          (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.bits), id_bound,
+          (unsigned char*)(ws + L.nib), (unsigned short*)(ws + L.toff), (u32*)(ws + L.tile_total), d_err);
+    else
+      across_mark_kernel<i64><<<tiles, RS_THREADS, 0, st>>>(
+          (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.bits), id_bound,
+          (unsigned char*)(ws + L.nib), (unsigned short*)(ws + L.toff), (u32*)(ws + L.tile_total), d_err);
+  }
+  {
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    tile_scan_kernel<<<1, 1024, 0, st>>>((const i64*)indptr, nseg, nnz_max, (const u32*)(ws + L.tile_total),
+                                         (i64*)(ws + L.tile_base));
+  }
+  {
+    i64 g = (nseg + 256) / 256; if (g > 148 * 16) g = 148 * 16;
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    across_offsets_kernel<<<(int)g, 256, 0, st>>>((const i64*)indptr, nseg, nnz_max,
+                                                 (const unsigned char*)(ws + L.nib),
+                                                 (const unsigned short*)(ws + L.toff),
+                                                 (const i64*)(ws + L.tile_base), (i64*)out_indptr);
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
 }
 
 extern "C" int gsb_slice_across_fill(const int64_t* indptr, const void* indices, int indices_dtype,
@@ -401,22 +495,42 @@ extern "C" int gsb_slice_across_fill(const int64_t* indptr, const void* indices,
                                      int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
                                      void* workspace, size_t workspace_bytes, int* d_err,
                                      void* cuda_stream) {
+  (void)d_err;
   if (nseg == 0 || nnz_max == 0) return GSB_OK;
   if (!indptr || !indices || !out_ids || !out_sel || !workspace || nseg < 0 || nnz_max < 0)
     return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
-  const AcrossLayout L = across_layout((nnz_max + AC_PER_THREAD - 1) / AC_PER_THREAD, id_bound);
+  const AcrossLayout L = across_layout(nnz_max, id_bound, true);
   if (workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
-  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.map, st));  // ticket + status again; the map stays
-  return launch_across<true>(indptr, indices, indices_dtype, nseg, nnz_max, id_bound, nullptr, out_ids,
-                             out_seg, out_sel, ws, L, d_err, st);
+  const int tiles = ceil_div_i(nnz_max, AC_TILE);
+  if (out_seg) {
+    const i64 n_tiles = (i64)tiles + 1;
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    tile_segment_kernel<<<(int)((n_tiles + 255) / 256), 256, 0, st>>>((const i64*)indptr, nseg, n_tiles,
+                                                                      (i64*)(ws + L.tile_seg));
+  }
+  LaunchScope ls(KID_SLICE_ROWS, st);
+  if (indices_dtype == GSB_I32)
+    across_fill_kernel<int><<<tiles, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.map),
+        (const unsigned char*)(ws + L.nib), (const unsigned short*)(ws + L.toff),
+        (const i64*)(ws + L.tile_base), (const i64*)(ws + L.tile_seg), (i64*)out_ids, (i64*)out_seg,
+        (i64*)out_sel);
+  else
+    across_fill_kernel<i64><<<tiles, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, nseg, nnz_max, (const u32*)(ws + L.map),
+        (const unsigned char*)(ws + L.nib), (const unsigned short*)(ws + L.toff),
+        (const i64*)(ws + L.tile_base), (const i64*)(ws + L.tile_seg), (i64*)out_ids, (i64*)out_seg,
+        (i64*)out_sel);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
 }
 
 extern "C" size_t gsb_coo_filter_workspace_bytes(int64_t nnz, int64_t id_bound) {
   if (nnz < 0 || id_bound < 0) return 0;
-  return across_layout(nnz, id_bound).total;
+  return across_layout(nnz, id_bound, false).total;
 }
 
 extern "C" int gsb_coo_filter(const int64_t* key, const int64_t* other, int64_t nnz,
@@ -427,13 +541,13 @@ extern "C" int gsb_coo_filter(const int64_t* key, const int64_t* other, int64_t 
   if (nnz < 0 || R < 0 || id_bound < 0 || !d_count || (R > 0 && !ids)) return GSB_ERR_INVALID;
   if (nnz > 0 && (!key || !other || !out_key || !out_other || !out_sel)) return GSB_ERR_INVALID;
   if (R >= 0xFFFFFFFFll || id_bound > (1ll << 33)) return GSB_ERR_UNSUPPORTED;
-  const AcrossLayout L = across_layout(nnz, id_bound);
+  const AcrossLayout L = across_layout(nnz, id_bound, false);
   if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
   int rc = build_map(ws, L, (const i64*)ids, R, id_bound, d_err, st);
   if (rc != GSB_OK) return rc;
-  const int tiles = nnz == 0 ? 1 : ceil_div_i(nnz, RS_THREADS);
+  const int tiles = nnz == 0 ? 1 : ceil_div_i(nnz, AC_TILE);
   LaunchScope ls(KID_SLICE_ROWS, st);
   coo_filter_kernel<<<tiles, RS_THREADS, 0, st>>>(
       (const i64*)key, (const i64*)other, nnz, (const u32*)(ws + L.map), id_bound, (i64*)out_key,

@@ -282,7 +282,8 @@ Graph::GraphAndIndex Graph::Slicing(torch::Tensor seeds, int64_t axis, int64_t o
       std::tie(sub_indptr, ids, seg, select) = SliceCompressed(src, seeds, c10::nullopt, 0);
     } else {
       std::tie(sub_indptr, ids, seg, select) =
-          SliceAcross(src, seeds, is_csc ? num_cols_ : num_rows_, is_csc ? num_rows_ : num_cols_);
+          SliceAcross(src, seeds, is_csc ? num_cols_ : num_rows_, is_csc ? num_rows_ : num_cols_,
+                      (output_format & kCOO) != 0);
     }
     if (output_format & on_format) {
       auto c = std::make_shared<Compressed>(Compressed{sub_indptr, ids, c10::nullopt});

@@ -153,8 +153,9 @@ class Graph : public torch::CustomClassHolder {
       int64_t encoding_size);
   // row slicing of a CSC operand / column slicing of a CSR operand: keep the
   // entries whose id is in `ids`, relabelled to their position in `ids`
+  // (`want_seg`: also the segment of every kept entry, i.e. the COO form)
   std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> SliceAcross(
-      const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound);
+      const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound, bool want_seg);
   void ReduceImpl(int opcode, const std::string& reduce, OptTensor ufeat, OptTensor efeat,
                   torch::Tensor out, OptTensor argu, OptTensor arge, int64_t u_target,
                   int64_t on_format, const char* who);

@@ -132,7 +132,7 @@ static int IdxDtype(const torch::Tensor& t) {
 
 // ------------------------------------------------------------------ slicing across / on COO
 std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceAcross(
-    const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound) {
+    const Compressed& src, torch::Tensor ids, int64_t nseg, int64_t id_bound, bool want_seg) {
   c10::cuda::CUDAGuard guard(ComputeDevice(src.indptr));
   CheckIds(ids, "ids");
   auto opt = I64(src.indptr);
@@ -147,10 +147,10 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sl
               "slice_across_count");
   const int64_t E = sub_indptr.narrow(0, nseg, 1).item<int64_t>();
   CheckDeviceError(err.item<int>(), "slice_across_count");
-  auto out_ids = torch::empty({E}, opt), seg = torch::empty({E}, opt), sel = torch::empty({E}, opt);
+  auto out_ids = torch::empty({E}, opt), seg = torch::empty({want_seg ? E : 0}, opt), sel = torch::empty({E}, opt);
   if (E > 0) {
     CheckStatus(gsb_slice_across_fill(P(src.indptr), src.indices.data_ptr(), IdxDtype(src.indices),
-                                      nseg, nnz_max, id_bound, PM(out_ids), PM(seg), PM(sel),
+                                      nseg, nnz_max, id_bound, PM(out_ids), want_seg ? PM(seg) : nullptr, PM(sel),
                                       ws.data_ptr(), (size_t)ws.numel(), err.data_ptr<int>(),
                                       CurrentStream()),
                 "slice_across_fill");

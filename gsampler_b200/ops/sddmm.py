@@ -27,7 +27,8 @@ def _prepare(num_edges, op, lhs_data, rhs_data):
     ref = lhs if use_l else rhs
     l_shp = lhs.shape if use_l else (0,)
     r_shp = rhs.shape if use_r else (0,)
-    out = torch.zeros((num_edges,) + broadcast_shape(op, l_shp[1:], r_shp[1:]), dtype=ref.dtype,
+    # every edge's entry is written exactly once, so no zero fill
+    out = torch.empty((num_edges,) + broadcast_shape(op, l_shp[1:], r_shp[1:]), dtype=ref.dtype,
                       device=ref.device)
     squeeze = (scalar_l or not use_l) and (scalar_r or not use_r)
     return op, lhs, rhs, out, squeeze
