@@ -3,13 +3,14 @@
 // the with-replacement draws for a single segment.
 //
 // Weighted selection without replacement = the K largest A-Res keys
-// log2(u_i)/p_i (u_i = draw 0 of element i's counter-based stream); uniform
-// selection = the K largest raw draws.  Instead of sorting all R keys, the
-// K-th largest key of every segment is located by a 4-round radix select over
-// 32-bit orderable keys (per-segment 256-bin histograms, one launch per round),
-// and one scan-and-emit pass writes the winners in ascending index order; ties
-// on the threshold key go to the lowest indices.  Everything is sized by R,
-// nothing by K: 6 launches per call.
+// log2(u_i)/p_i (u_i = draw 0 of element i's counter-based stream).  Instead
+// of sorting all R keys, the K-th largest key of every segment is located by a
+// 4-round radix select over 32-bit orderable keys (per-segment 256-bin
+// histograms, one launch per round), and one scan-and-emit pass writes the
+// winners in ascending index order; ties on the threshold key go to the lowest
+// indices.  Everything is sized by R, nothing by K: 6 launches per call.
+// Uniform selection without replacement is one reservoir pass (Algorithm R with
+// an atomic max per slot), picks in slot order.
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -269,6 +270,34 @@ __global__ void __launch_bounds__(LS_THREADS) list_emit_kernel(const ListParams 
   }
 }
 
+// Uniform selection without replacement: reservoir sampling (Algorithm R) evaluated in
+// parallel, the reference's scheme (list_sampling.cu:47-64).  Candidate j of a segment (j counted
+// from the segment's start) owns slot j if j < K; otherwise it draws num = floor(u * (j + 1)) and
+// claims slot num when num < K.  Sequentially a slot ends with the last candidate that drew it,
+// i.e. the largest index: an atomic max, whatever the order of execution.  `out_idx` must be zero
+// before the launch; picks come out in slot order.
+__global__ void __launch_bounds__(LS_THREADS) list_reservoir_kernel(const ListParams p) {
+  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
+  if (p.B == 1 && blockIdx.x == 0 && threadIdx.x == 0) {  // a single list has no set-up launch
+    i64 len = p.range[1] - p.range[0];
+    if (len < 0) { raise(p.err, ERRBIT_BAD_INPUT); len = 0; }
+    if (p.range[1] > p.R) raise(p.err, ERRBIT_CAPACITY);
+    p.out_range[0] = 0;
+    p.out_range[1] = len < p.K ? len : p.K;
+  }
+  for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS) {
+    const int b = p.B == 1 ? 0 : find_segment(p.range, p.B, i);
+    const i64 r0 = p.range[b], j = i - r0, len = p.range[b + 1] - r0;
+    if (j < 0) continue;  // an item before the first segment
+    long long* out = reinterpret_cast<long long*>(p.out_idx) + (p.B == 1 ? 0 : p.out_range[b]);
+    if (len <= p.K) { out[j] = i; continue; }
+    if (j < p.K) { atomicMax(out + j, (long long)i); continue; }
+    const u32 d = stream_block(p.seed, p.stream, (u64)i, 0).x;
+    const u64 num = ((u64)d * (u64)(j + 1)) >> 32;
+    if (num < (u64)p.K) atomicMax(out + num, (long long)i);
+  }
+}
+
 // K draws with replacement from one segment [0, n): uniform, or by inverse CDF
 __global__ void list_replace_uniform_kernel(i64 n, i64 K, u64 seed, u32 stream, i64* out) {
   for (i64 k = (i64)blockIdx.x * blockDim.x + threadIdx.x; k < K; k += (i64)gridDim.x * blockDim.x) {
@@ -350,7 +379,7 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
     return GSB_ERR_INVALID;
   if (R >= (1ll << 31) || B >= (1ll << 22)) return GSB_ERR_UNSUPPORTED;
   const ListLayout L = list_layout(R, B);
-  if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
+  if (probs && (!workspace || workspace_bytes < L.total)) return GSB_ERR_WORKSPACE;  // uniform: no scratch
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
   ListParams p;
@@ -360,6 +389,18 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
   p.seg_base = (i64*)(ws + L.seg_base); p.out_idx = (i64*)out_idx; p.out_range = (i64*)out_range;
   p.status = (u64*)(ws + L.status); p.ticket = (int*)(ws + L.ticket); p.done = p.ticket + 16;
   p.err = d_err;
+  if (!probs) {  // uniform: one reservoir pass, no keys
+    const i64 cap = R < B * K ? R : B * K;  // most picks there can be
+    if (cap > 0) GSB_CUDA_OK(cudaMemsetAsync(out_idx, 0, sizeof(i64) * (size_t)cap, st));
+    if (B > 1 || R == 0 || K == 0) { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
+    if (R > 0 && K > 0) {
+      i64 gr = (R + LS_THREADS - 1) / LS_THREADS; if (gr > 148 * 16) gr = 148 * 16;
+      LaunchScope ls(KID_LIST_SAMPLE, st);
+      list_reservoir_kernel<<<(int)gr, LS_THREADS, 0, st>>>(p);
+    }
+    GSB_CUDA_OK(cudaGetLastError());
+    return GSB_OK;
+  }
   GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.keys, st));  // ticket, status, histograms
   i64 g = (R + LS_TILE - 1) / LS_TILE; if (g > 148 * 4) g = 148 * 4; if (g < 1) g = 1;
   { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }

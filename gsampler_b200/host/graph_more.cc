@@ -654,16 +654,24 @@ Graph::GraphAndIndex Graph::BatchColRowSlcing(torch::Tensor col, torch::Tensor c
 }
 
 // ------------------------------------------------------------------ gs_ops
+static torch::Tensor& AsyncErrorWord(const torch::Device& dev);
+
+// `single_list`: the caller built `range` = [0, R] itself, so the number of picks is known on the
+// host (min(K, R)) and nothing is read back; device-side errors go to the per-device word that
+// CheckAsyncErrors reports.
 static std::tuple<torch::Tensor, torch::Tensor> ListSampleImpl(const c10::optional<torch::Tensor>& probs,
                                                                torch::Tensor range, int64_t R,
-                                                               int64_t K, const torch::Device& dev) {
+                                                               int64_t K, const torch::Device& dev,
+                                                               bool single_list = false) {
   c10::cuda::CUDAGuard guard(dev);
   const int64_t B = range.numel() - 1;
   auto opt = torch::dtype(torch::kInt64).device(dev);
   auto out_range = torch::empty({B + 1}, opt);
   auto out_idx = torch::empty({std::min(B * K, R)}, opt);
-  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(dev));
-  auto ws = NewWorkspace(gsb_list_sample_workspace_bytes(R, B), dev);
+  auto err = single_list ? AsyncErrorWord(dev)
+                         : torch::zeros({1}, torch::dtype(torch::kInt32).device(dev));
+  // the uniform reservoir pass needs no scratch
+  auto ws = NewWorkspace(probs.has_value() ? gsb_list_sample_workspace_bytes(R, B) : 256, dev);
   const float* pp = nullptr;
   if (probs.has_value()) {
     const auto& pr = probs.value();
@@ -675,6 +683,7 @@ static std::tuple<torch::Tensor, torch::Tensor> ListSampleImpl(const c10::option
                               PM(out_idx), PM(out_range), ws.data_ptr(), (size_t)ws.numel(),
                               err.data_ptr<int>(), CurrentStream()),
               "list_sample");
+  if (single_list) return {out_idx, out_range};
   const int64_t total = out_range.narrow(0, B, 1).item<int64_t>();
   CheckDeviceError(err.item<int>(), "list_sample");
   return {out_idx.narrow(0, 0, total), out_range};
@@ -706,7 +715,8 @@ static torch::Device CurrentCudaDevice() { return torch::Device(torch::kCUDA, c1
 torch::Tensor ListSampling(int64_t num_items, int64_t num_picks, bool replace) {
   const auto dev = CurrentCudaDevice();
   if (replace) return ListReplaceImpl(c10::nullopt, num_items, num_picks, dev);
-  return std::get<0>(ListSampleImpl(c10::nullopt, Range2(num_items, dev), num_items, num_picks, dev));
+  return std::get<0>(ListSampleImpl(c10::nullopt, Range2(num_items, dev), num_items, num_picks, dev,
+                                    /*single_list=*/true));
 }
 
 // src/tensor_ops.cc:10-13
@@ -715,7 +725,7 @@ torch::Tensor ListSamplingProbs(torch::Tensor probs, int64_t num_picks, bool rep
   probs = probs.contiguous();
   if (replace) return ListReplaceImpl(probs, probs.numel(), num_picks, probs.device());
   return std::get<0>(ListSampleImpl(probs, Range2(probs.numel(), probs.device()), probs.numel(),
-                                    num_picks, probs.device()));
+                                    num_picks, probs.device(), /*single_list=*/true));
 }
 
 // src/tensor_ops.cc:15-19
@@ -770,7 +780,7 @@ void CheckAsyncErrors() {
   auto& w = AsyncErrorWord(dev);
   const int bits = w.item<int>();
   if (bits) w.zero_();
-  CheckDeviceError(bits, "an earlier sync-free operator (row gather)");
+  CheckDeviceError(bits, "an earlier sync-free operator (row gather, single-list sampling)");
 }
 
 // out[i, ...] = data[index[i], ...].  `data` lives on the GPU or in page-locked

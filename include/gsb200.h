@@ -315,8 +315,9 @@ GSB_API int gsb_sddmm_coo_dot(const int64_t* row, const int64_t* col, const int6
  * gsb_list_sample: for every segment [range[b], range[b+1]) choose min(K, len)
  * candidates without replacement -- uniformly (probs NULL) or with weights
  * probs[R] (A-Res keys; weight <= 0 is chosen last) -- and write their
- * positions in ascending order to out_idx; out_range[B+1] = offsets of the
- * picks.  R bounds range[B].  Replaces ListSampling / ListSamplingProbs /
+ * positions to out_idx (weighted: ascending; uniform: reservoir slot order, as
+ * the reference's ListSampling); out_range[B+1] = offsets of the picks.  R
+ * bounds range[B]; out_idx holds min(R, B * K) entries.  Replaces ListSampling / ListSamplingProbs /
  * BatchListSamplingProbs without replacement (src/cuda/list_sampling.cu:20-73,
  * src/cuda/list_sampling_probs.cu:11-89, src/cuda/batch/list_sampling_probs.cu:29-107),
  * which return the same set in descending-key order.

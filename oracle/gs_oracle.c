@@ -615,22 +615,33 @@ static int cmp_i64_asc(const void* a, const void* b) {
  * all keys descending and keeping the first K (list_sampling_probs.cu:47-77).
  * The picks are returned in ASCENDING INDEX order (the reference returns them
  * in descending key order, i.e. a random order; nothing downstream depends on
- * it).  probs == NULL selects uniformly: key = the raw 32-bit draw.
+ * it).
+ * probs == NULL selects uniformly by reservoir sampling (Algorithm R), as the
+ * reference does (list_sampling.cu:47-64): the first K candidates fill the K
+ * slots, candidate j >= K draws num = floor(u * (j + 1)) and, when num < K,
+ * replaces slot num; processed in order, a slot ends up with the LAST (largest)
+ * candidate that drew it, which is what the reference's AtomicMax computes in
+ * parallel.  Picks are returned in slot order.
  * returns the number of picks written (min(K, n)). */
 GO_API i64 go_list_sample_probs_spec(const float* probs, i64 begin, i64 end, i64 K, u64 seed,
                                      u32 stream, i64* out_idx) {
   i64 n = end - begin;
   if (n <= K) { for (i64 i = 0; i < n; ++i) out_idx[i] = begin + i; return n; }
+  if (!probs) {
+    for (i64 j = 0; j < K; ++j) out_idx[j] = begin + j;
+    for (i64 j = K; j < n; ++j) {
+      u32 d = spec_draw(seed, stream, (u64)(begin + j), 0);
+      u64 num = ((u64)d * (u64)(j + 1)) >> 32;
+      if (num < (u64)K) out_idx[num] = begin + j;
+    }
+    return K;
+  }
   kv_t* kv = (kv_t*)malloc(sizeof(kv_t) * (size_t)n);
   for (i64 i = 0; i < n; ++i) {
     u32 d = spec_draw(seed, stream, (u64)(begin + i), 0);
-    if (probs) {
-      double u = ((double)d + 1.0) * (1.0 / 4294967296.0);
-      double p = probs[begin + i];
-      kv[i].key = p > 0 ? log2(u) / p : -INFINITY;
-    } else {
-      kv[i].key = (double)d;
-    }
+    double u = ((double)d + 1.0) * (1.0 / 4294967296.0);
+    double p = probs[begin + i];
+    kv[i].key = p > 0 ? log2(u) / p : -INFINITY;
     kv[i].idx = begin + i;
   }
   qsort(kv, (size_t)n, sizeof(kv_t), cmp_kv_desc);

@@ -230,6 +230,19 @@ def test_list_sampling(gsb, oracle):
     # with replacement, weighted
     got = host(ops._CAPI_ListSamplingWithProbs(cuda(w, torch.float32), 16000, True))
     assert stats.chisquare(np.bincount(got, minlength=8), 16000 * w64 / w64.sum()).pvalue > 0.01
+    # uniform reservoir: 3 of 12 in 6000 independent segments -- distinct picks inside every
+    # segment, bit-exact with the oracle, every item equally likely
+    rp = np.arange(6001) * 12
+    ops._CAPI_SetListSamplingSeed(9)
+    idx, optr = ops._CAPI_BatchListSampling(3, False, cuda(rp))
+    idx, optr = host(idx), host(optr)
+    assert optr.tolist() == (np.arange(6001) * 3).tolist()
+    want, _ = oracle.list_sample_probs_spec(None, 3, seed=9, stream=0, range_ptr=rp, n=int(rp[-1]))
+    assert np.array_equal(idx, want)
+    picks = idx.reshape(6000, 3)
+    assert np.all(picks // 12 == np.arange(6000)[:, None])
+    assert np.all(np.sort(picks, axis=1)[:, 1:] != np.sort(picks, axis=1)[:, :-1])
+    assert stats.chisquare(np.bincount(idx % 12, minlength=12)).pvalue > 0.01
 
 
 def test_walks_bit_exact(gsb, oracle, graph):
