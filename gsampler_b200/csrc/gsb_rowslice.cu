@@ -359,8 +359,16 @@ colrow_count_kernel(const i64* __restrict__ indptr, const void* __restrict__ ind
         u32 slots;
         const u64* tab = rowtab_of(table, row_ptr, find_segment(col_ptr, B, seg), &slots);
         const i64 st = __ldg(indptr + c), en = __ldg(indptr + c + 1);
-        for (i64 e = st + lane; e < en; e += 32)
-          if (rowtab_find(tab, slots, load_index<IndexT>(indices, e)) != MAP_ABSENT) ++cnt;
+        // four independent look-ups per lane and step: a long column is a chain of dependent
+        // loads (index, then table probes), and one warp walks it alone
+        for (i64 e0 = st + lane; e0 < en; e0 += 128) {
+          i64 id[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) id[k] = e0 + 32 * k < en ? load_index<IndexT>(indices, e0 + 32 * k) : -1;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            if (e0 + 32 * k < en && rowtab_find(tab, slots, id[k]) != MAP_ABSENT) ++cnt;
+        }
 #pragma unroll
         for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
       }
@@ -398,18 +406,28 @@ colrow_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indi
     const u64* tab = rowtab_of(const_cast<u64*>(table), row_ptr, find_segment(col_ptr, B, seg), &slots);
     const i64 st = __ldg(indptr + c), en = __ldg(indptr + c + 1);
     i64 o = out_indptr[seg];
-    for (i64 e0 = st; e0 < en; e0 += 32) {
-      const i64 e = e0 + lane;
-      u32 pos = MAP_ABSENT;
-      if (e < en) pos = rowtab_find(tab, slots, load_index<IndexT>(indices, e));
-      const unsigned keep = __ballot_sync(0xffffffffu, pos != MAP_ABSENT);
-      if (pos != MAP_ABSENT) {
-        const i64 w = o + __popc(keep & ((1u << lane) - 1u));
-        out_ids[w] = (i64)pos;
-        out_sel[w] = e;
-        if (out_seg) out_seg[w] = seg;
+    for (i64 e0 = st; e0 < en; e0 += 128) {  // four chunks of 32 entries in flight
+      i64 id[4];
+      u32 pos[4];
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const i64 e = e0 + 32 * k + lane;
+        id[k] = e < en ? load_index<IndexT>(indices, e) : -1;
       }
-      o += __popc(keep);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        pos[k] = e0 + 32 * k + lane < en ? rowtab_find(tab, slots, id[k]) : MAP_ABSENT;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const unsigned keep = __ballot_sync(0xffffffffu, pos[k] != MAP_ABSENT);
+        if (pos[k] != MAP_ABSENT) {
+          const i64 w = o + __popc(keep & ((1u << lane) - 1u));
+          out_ids[w] = (i64)pos[k];
+          out_sel[w] = e0 + 32 * k + lane;
+          if (out_seg) out_seg[w] = seg;
+        }
+        o += __popc(keep);
+      }
     }
   }
 }
