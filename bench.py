@@ -411,15 +411,12 @@ def main():
     def e2e_run(first, count):
         edges, nin, nout = 0, 0, 0
         pending = []
-        t_run = time.perf_counter()
         for k in range(count + 1):
             if k < count:
                 pending.append(e2e_submit(first + k))
             if k >= 1:
                 fut, nbytes = pending.pop(0)
                 cnt = fut.wait()[-1]
-                if os.environ.get("GSB_E2E_TRACE"):
-                    sys.stderr.write("e2e step %d done at %.3f ms\n" % (k, (time.perf_counter() - t_run) * 1e3))
                 edges += int(cnt.view(L, 3)[:, 1].sum())
                 nin += nbytes
                 nout += (3 * L + 1) * 8
@@ -431,14 +428,9 @@ def main():
     gc.collect()
     gc.disable()          # a collection inside the ~20 ms timed region would be most of it
     t0 = time.perf_counter()
-    ms0 = torch.cuda.memory_stats(dev) if os.environ.get("GSB_E2E_TRACE") else None
     e2e_edges, h2d, d2h = e2e_run(args.warmup, args.steps)
     torch.cuda.synchronize()
     e2e_ms = (time.perf_counter() - t0) * 1e3   # host clock around copies, launches and reads
-    if ms0 is not None:
-        ms1 = torch.cuda.memory_stats(dev)
-        for key in ("num_device_alloc", "num_device_free", "num_alloc_retries", "reserved_bytes.all.current"):
-            sys.stderr.write("memstat %s %s -> %s\n" % (key, ms0.get(key), ms1.get(key)))
     gc.enable()
 
     # ---- reduce over ranks: slowest rank's time, summed edges

@@ -331,121 +331,162 @@ __device__ __forceinline__ u32 rowtab_find(const u64* __restrict__ tab, u32 slot
   return MAP_ABSENT;
 }
 
-// CTA = RS_THREADS consecutive column slots; a warp walks one column at a time.
-template <typename IndexT>
-__global__ void __launch_bounds__(RS_THREADS)
-colrow_count_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 num_cols,
-                    const i64* __restrict__ cols, const i64* __restrict__ col_ptr,
-                    const i64* __restrict__ row_ptr, int B, u64* table, i64* __restrict__ out_indptr,
-                    u64* status, int* ticket, int* err) {
-  __shared__ i64 s_scan[34];
-  __shared__ int s_cnt[RS_THREADS];
-  __shared__ int s_tile;
-  __shared__ i64 s_base;
-  if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
-  __syncthreads();
-  const int tile = s_tile;
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const i64 nseg = col_ptr[B];
-  const i64 seg0 = (i64)tile * RS_THREADS;
-  for (int k = wid; k < RS_THREADS; k += RS_WARPS) {
-    const i64 seg = seg0 + k;
-    int cnt = 0;
-    if (seg < nseg) {
-      const i64 c = cols[seg];
-      if (c < 0 || c >= num_cols) {
-        if (lane == 0) raise(err, ERRBIT_BAD_INPUT);
-      } else {
-        u32 slots;
-        const u64* tab = rowtab_of(table, row_ptr, find_segment(col_ptr, B, seg), &slots);
-        const i64 st = __ldg(indptr + c), en = __ldg(indptr + c + 1);
-        // four independent look-ups per lane and step: a long column is a chain of dependent
-        // loads (index, then table probes), and one warp walks it alone
-        for (i64 e0 = st + lane; e0 < en; e0 += 128) {
-          i64 id[4];
-#pragma unroll
-          for (int k = 0; k < 4; ++k) id[k] = e0 + 32 * k < en ? load_index<IndexT>(indices, e0 + 32 * k) : -1;
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            if (e0 + 32 * k < en && rowtab_find(tab, slots, id[k]) != MAP_ABSENT) ++cnt;
-        }
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, d);
-      }
-    }
-    if (lane == 0) s_cnt[k] = cnt;
-  }
-  __syncthreads();
-  i64 total;
-  const i64 loff = block_exclusive_scan((i64)s_cnt[threadIdx.x], s_scan, &total);
-  if (threadIdx.x < 32) {
-    i64 base = chained_exclusive_prefix(status, tile, total, err);
-    if (threadIdx.x == 0) s_base = base;
-  }
-  __syncthreads();
-  const i64 seg = seg0 + threadIdx.x;
-  if (seg < nseg) out_indptr[seg] = s_base + loff;
-  if (seg == nseg - 1 || (nseg == 0 && seg == 0)) out_indptr[nseg] = s_base + total;
+// Fused column + row slicing works on PARTS of columns: a column of `deg` entries is cut into
+// ceil(deg / part_len) parts, part_len = max(CR_PART, total entries / CR_EXTRA_PARTS), so the
+// number of parts is at most S + CR_EXTRA_PARTS whatever the degrees are, and a warp never walks
+// more than part_len entries: one very long column costs the same as many short ones.
+//   deg    : length of every selected column (ids checked) + their sum       thread / column
+//   parts  : vptr = exclusive scan of the columns' part counts               one CTA
+//   count  : kept entries of every part                                      warp / part
+//   offsets: voff = exclusive scan of those; out_indptr[seg] = voff[vptr[seg]]   one CTA
+//   fill   : ordered emit of every part from voff[part]                      warp / part
+constexpr i64 CR_PART = 1024;
+constexpr i64 CR_EXTRA_PARTS = 1 << 19;
+
+__device__ __forceinline__ i64 colrow_part_len(i64 total_entries) {
+  const i64 by_budget = (total_entries + CR_EXTRA_PARTS - 1) / CR_EXTRA_PARTS;
+  const i64 len = by_budget > CR_PART ? by_budget : CR_PART;
+  return (len + 127) & ~(i64)127;  // whole steps of 4 x 32 entries
 }
 
-template <typename IndexT>
+__global__ void colrow_deg_kernel(const i64* __restrict__ indptr, i64 num_cols,
+                                  const i64* __restrict__ cols, const i64* __restrict__ col_ptr, int B,
+                                  i64 S, i64* __restrict__ deg, unsigned long long* total, int* err) {
+  __shared__ i64 s_scan[34];
+  const i64 nseg = col_ptr[B] < S ? col_ptr[B] : S;
+  const i64 seg = (i64)blockIdx.x * blockDim.x + threadIdx.x;
+  i64 d = 0;
+  if (seg < nseg) {
+    const i64 c = cols[seg];
+    if (c < 0 || c >= num_cols) raise(err, ERRBIT_BAD_INPUT);
+    else d = __ldg(indptr + c + 1) - __ldg(indptr + c);
+    deg[seg] = d;
+  }
+  i64 block_total;
+  block_exclusive_scan(d, s_scan, &block_total);
+  if (threadIdx.x == 0 && block_total) atomicAdd(total, (unsigned long long)block_total);
+}
+
+// out[i] = sum of f(i') for i' < i, out[n] = everything; one CTA of 1024 threads, a contiguous run
+// of elements per thread
+template <typename F>
+__device__ __forceinline__ void cta_exclusive_scan(i64 n, F value, i64* __restrict__ out, i64* s_scan) {
+  const i64 per = (n + 1023) / 1024;
+  const i64 lo = (i64)threadIdx.x * per < n ? (i64)threadIdx.x * per : n;
+  const i64 hi = lo + per < n ? lo + per : n;
+  i64 sum = 0;
+  for (i64 i = lo; i < hi; ++i) sum += value(i);
+  i64 grand;
+  i64 run = block_exclusive_scan(sum, s_scan, &grand);
+  for (i64 i = lo; i < hi; ++i) { out[i] = run; run += value(i); }
+  if (threadIdx.x == 0) out[n] = grand;
+}
+
+__global__ void __launch_bounds__(1024)
+colrow_parts_kernel(const i64* __restrict__ col_ptr, int B, i64 S, const i64* __restrict__ deg,
+                    const unsigned long long* __restrict__ total, i64* __restrict__ vptr) {
+  __shared__ i64 s_scan[34];
+  const i64 nseg = col_ptr[B] < S ? col_ptr[B] : S;
+  const i64 part = colrow_part_len((i64)*total);
+  cta_exclusive_scan(nseg, [&](i64 s) { const i64 d = deg[s]; return d == 0 ? (i64)1 : (d + part - 1) / part; },
+                     vptr, s_scan);
+}
+
+// warp per part; FILL = false counts the kept entries, FILL = true writes them from voff[part]
+template <typename IndexT, bool FILL>
 __global__ void __launch_bounds__(RS_THREADS)
-colrow_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices, i64 num_cols,
+colrow_part_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices,
                    const i64* __restrict__ cols, const i64* __restrict__ col_ptr,
-                   const i64* __restrict__ row_ptr, int B, const u64* __restrict__ table,
-                   const i64* __restrict__ out_indptr, i64* __restrict__ out_ids,
-                   i64* __restrict__ out_seg, i64* __restrict__ out_sel) {
+                   const i64* __restrict__ row_ptr, int B, i64 S, const u64* __restrict__ table,
+                   const i64* __restrict__ deg, const unsigned long long* __restrict__ total,
+                   const i64* __restrict__ vptr, u32* __restrict__ vcnt, const i64* __restrict__ voff,
+                   i64* __restrict__ out_ids, i64* __restrict__ out_seg, i64* __restrict__ out_sel) {
   const int lane = threadIdx.x & 31;
-  const i64 nseg = col_ptr[B];
+  const i64 nseg = col_ptr[B] < S ? col_ptr[B] : S;
+  if (nseg <= 0) return;
+  const i64 V = vptr[nseg];
+  const i64 part = colrow_part_len((i64)*total);
   const i64 warp0 = ((i64)blockIdx.x * RS_THREADS + threadIdx.x) >> 5;
   const i64 nwarps = ((i64)gridDim.x * RS_THREADS) >> 5;
-  for (i64 seg = warp0; seg < nseg; seg += nwarps) {
-    const i64 c = cols[seg];
-    if (c < 0 || c >= num_cols) continue;
-    u32 slots;
-    const u64* tab = rowtab_of(const_cast<u64*>(table), row_ptr, find_segment(col_ptr, B, seg), &slots);
-    const i64 st = __ldg(indptr + c), en = __ldg(indptr + c + 1);
-    i64 o = out_indptr[seg];
-    for (i64 e0 = st; e0 < en; e0 += 128) {  // four chunks of 32 entries in flight
-      i64 id[4];
-      u32 pos[4];
+  for (i64 v = warp0; v < V; v += nwarps) {
+    // the column of part v: largest seg with vptr[seg] <= v
+    i64 lo = 0, hi = nseg;
+    while (hi - lo > 1) { const i64 mid = (lo + hi) >> 1; if (__ldg(vptr + mid) <= v) lo = mid; else hi = mid; }
+    const i64 seg = lo;
+    const i64 d = deg[seg];
+    int cnt = 0;
+    if (d > 0) {
+      const i64 c = cols[seg];
+      u32 slots;
+      const u64* tab = rowtab_of(const_cast<u64*>(table), row_ptr, find_segment(col_ptr, B, seg), &slots);
+      const i64 col_start = __ldg(indptr + c);
+      const i64 st = col_start + (v - __ldg(vptr + seg)) * part;
+      const i64 en = st + part < col_start + d ? st + part : col_start + d;
+      i64 o = FILL ? voff[v] : 0;
+      for (i64 e0 = st; e0 < en; e0 += 128) {  // four chunks of 32 entries in flight
+        i64 id[4];
+        u32 pos[4];
 #pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const i64 e = e0 + 32 * k + lane;
-        id[k] = e < en ? load_index<IndexT>(indices, e) : -1;
-      }
-#pragma unroll
-      for (int k = 0; k < 4; ++k)
-        pos[k] = e0 + 32 * k + lane < en ? rowtab_find(tab, slots, id[k]) : MAP_ABSENT;
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        const unsigned keep = __ballot_sync(0xffffffffu, pos[k] != MAP_ABSENT);
-        if (pos[k] != MAP_ABSENT) {
-          const i64 w = o + __popc(keep & ((1u << lane) - 1u));
-          out_ids[w] = (i64)pos[k];
-          out_sel[w] = e0 + 32 * k + lane;
-          if (out_seg) out_seg[w] = seg;
+        for (int k = 0; k < 4; ++k) {
+          const i64 e = e0 + 32 * k + lane;
+          id[k] = e < en ? load_index<IndexT>(indices, e) : -1;
         }
-        o += __popc(keep);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) pos[k] = id[k] >= 0 ? rowtab_find(tab, slots, id[k]) : MAP_ABSENT;
+        if (!FILL) {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) cnt += pos[k] != MAP_ABSENT;
+        } else {
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            const unsigned keep = __ballot_sync(0xffffffffu, pos[k] != MAP_ABSENT);
+            if (pos[k] != MAP_ABSENT) {
+              const i64 w = o + __popc(keep & ((1u << lane) - 1u));
+              out_ids[w] = (i64)pos[k];
+              out_sel[w] = e0 + 32 * k + lane;
+              if (out_seg) out_seg[w] = seg;
+            }
+            o += __popc(keep);
+          }
+        }
       }
     }
+    if (!FILL) {
+#pragma unroll
+      for (int dd = 16; dd > 0; dd >>= 1) cnt += __shfl_xor_sync(0xffffffffu, cnt, dd);
+      if (lane == 0) vcnt[v] = (u32)cnt;
+    }
   }
+}
+
+__global__ void __launch_bounds__(1024)
+colrow_offsets_kernel(const i64* __restrict__ col_ptr, int B, i64 S, const i64* __restrict__ vptr,
+                      const u32* __restrict__ vcnt, i64* __restrict__ voff, i64* __restrict__ out_indptr) {
+  __shared__ i64 s_scan[34];
+  const i64 nseg = col_ptr[B] < S ? col_ptr[B] : S;
+  const i64 V = nseg > 0 ? vptr[nseg] : 0;
+  cta_exclusive_scan(V, [&](i64 v) { return (i64)vcnt[v]; }, voff, s_scan);
+  __syncthreads();  // voff is this CTA's own global writes
+  for (i64 s = threadIdx.x; s <= nseg; s += 1024) out_indptr[s] = voff[s < nseg ? vptr[s] : V];
 }
 
 struct ColRowLayout {
-  size_t ticket, status, table, total;
-  i64 tiles, slots;
+  size_t total_entries, table, deg, vptr, vcnt, voff, total;
+  i64 slots, parts;
 };
 
 static ColRowLayout colrow_layout(i64 S, i64 R, i64 B) {
   ColRowLayout L;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-  L.tiles = (S + RS_THREADS - 1) / RS_THREADS + 1;
   L.slots = 2 * R + 32 * (B + 1);
+  L.parts = S + CR_EXTRA_PARTS + 1;
   size_t o = 0;
-  L.ticket = o; o = up(o + 256);
-  L.status = o; o = up(o + sizeof(u64) * (size_t)L.tiles);
+  L.total_entries = o; o = up(o + 256);
   L.table = o; o = up(o + sizeof(u64) * (size_t)L.slots);
+  L.deg = o; o = up(o + sizeof(i64) * (size_t)(S + 1));
+  L.vptr = o; o = up(o + sizeof(i64) * (size_t)(S + 1));
+  L.vcnt = o; o = up(o + sizeof(u32) * (size_t)L.parts);
+  L.voff = o; o = up(o + sizeof(i64) * (size_t)(L.parts + 1));
   L.total = o;
   return L;
 }
@@ -595,7 +636,7 @@ extern "C" int gsb_slice_cols_rows_count(const int64_t* indptr, const void* indi
   if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
-  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.table, st));                               // ticket + status
+  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.table, st));                                     // entry total
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.table, 0xFF, sizeof(u64) * (size_t)L.slots, st));  // empty slots
   if (R > 0) {
     i64 g = (R + 255) / 256; if (g > 148 * 16) g = 148 * 16;
@@ -603,18 +644,38 @@ extern "C" int gsb_slice_cols_rows_count(const int64_t* indptr, const void* indi
     rowtab_insert_kernel<<<(int)g, 256, 0, st>>>((const i64*)rows, (const i64*)row_ptr, (int)B,
                                                  (u64*)(ws + L.table), d_err);
   }
-  const int tiles = S == 0 ? 1 : ceil_div_i(S, RS_THREADS);
-  LaunchScope ls(KID_SLICE_ROWS, st);
-  if (indices_dtype == GSB_I32)
-    colrow_count_kernel<int><<<tiles, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
-        (const i64*)row_ptr, (int)B, (u64*)(ws + L.table), (i64*)out_indptr, (u64*)(ws + L.status),
-        (int*)(ws + L.ticket), d_err);
-  else
-    colrow_count_kernel<i64><<<tiles, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
-        (const i64*)row_ptr, (int)B, (u64*)(ws + L.table), (i64*)out_indptr, (u64*)(ws + L.status),
-        (int*)(ws + L.ticket), d_err);
+  i64* deg = (i64*)(ws + L.deg);
+  i64* vptr = (i64*)(ws + L.vptr);
+  unsigned long long* total = (unsigned long long*)(ws + L.total_entries);
+  {
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    colrow_deg_kernel<<<S == 0 ? 1 : ceil_div_i(S, 256), 256, 0, st>>>(
+        (const i64*)indptr, num_cols, (const i64*)cols, (const i64*)col_ptr, (int)B, S, deg, total, d_err);
+  }
+  {
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    colrow_parts_kernel<<<1, 1024, 0, st>>>((const i64*)col_ptr, (int)B, S, deg, total, vptr);
+  }
+  if (S > 0) {
+    i64 g = (L.parts + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    if (indices_dtype == GSB_I32)
+      colrow_part_kernel<int, false><<<(int)g, RS_THREADS, 0, st>>>(
+          (const i64*)indptr, indices, (const i64*)cols, (const i64*)col_ptr, (const i64*)row_ptr, (int)B,
+          S, (const u64*)(ws + L.table), deg, total, vptr, (u32*)(ws + L.vcnt), nullptr, nullptr,
+          nullptr, nullptr);
+    else
+      colrow_part_kernel<i64, false><<<(int)g, RS_THREADS, 0, st>>>(
+          (const i64*)indptr, indices, (const i64*)cols, (const i64*)col_ptr, (const i64*)row_ptr, (int)B,
+          S, (const u64*)(ws + L.table), deg, total, vptr, (u32*)(ws + L.vcnt), nullptr, nullptr,
+          nullptr, nullptr);
+  }
+  {
+    LaunchScope ls(KID_SLICE_ROWS, st);
+    colrow_offsets_kernel<<<1, 1024, 0, st>>>((const i64*)col_ptr, (int)B, S, vptr,
+                                              (const u32*)(ws + L.vcnt), (i64*)(ws + L.voff),
+                                              (i64*)out_indptr);
+  }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }
@@ -625,6 +686,7 @@ extern "C" int gsb_slice_cols_rows_fill(const int64_t* indptr, const void* indic
                                         int64_t R, int64_t B, const int64_t* out_indptr,
                                         int64_t* out_ids, int64_t* out_seg, int64_t* out_sel,
                                         const void* workspace, void* cuda_stream) {
+  (void)num_cols;
   if (S == 0) return GSB_OK;
   if (!indptr || !indices || !cols || !col_ptr || !row_ptr || !out_indptr || !out_ids || !out_sel ||
       !workspace || S < 0 || B < 1)
@@ -632,18 +694,20 @@ extern "C" int gsb_slice_cols_rows_fill(const int64_t* indptr, const void* indic
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   const ColRowLayout L = colrow_layout(S, R, B);
   cudaStream_t st = (cudaStream_t)cuda_stream;
-  i64 g = (S + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
-  const u64* table = (const u64*)((const char*)workspace + L.table);
+  const char* ws = (const char*)workspace;
+  i64 g = (L.parts + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
   LaunchScope ls(KID_SLICE_ROWS, st);
   if (indices_dtype == GSB_I32)
-    colrow_fill_kernel<int><<<(int)g, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
-        (const i64*)row_ptr, (int)B, table, (const i64*)out_indptr, (i64*)out_ids, (i64*)out_seg,
+    colrow_part_kernel<int, true><<<(int)g, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, (const i64*)cols, (const i64*)col_ptr, (const i64*)row_ptr, (int)B, S,
+        (const u64*)(ws + L.table), (const i64*)(ws + L.deg), (const unsigned long long*)(ws + L.total_entries),
+        (const i64*)(ws + L.vptr), nullptr, (const i64*)(ws + L.voff), (i64*)out_ids, (i64*)out_seg,
         (i64*)out_sel);
   else
-    colrow_fill_kernel<i64><<<(int)g, RS_THREADS, 0, st>>>(
-        (const i64*)indptr, indices, num_cols, (const i64*)cols, (const i64*)col_ptr,
-        (const i64*)row_ptr, (int)B, table, (const i64*)out_indptr, (i64*)out_ids, (i64*)out_seg,
+    colrow_part_kernel<i64, true><<<(int)g, RS_THREADS, 0, st>>>(
+        (const i64*)indptr, indices, (const i64*)cols, (const i64*)col_ptr, (const i64*)row_ptr, (int)B, S,
+        (const u64*)(ws + L.table), (const i64*)(ws + L.deg), (const unsigned long long*)(ws + L.total_entries),
+        (const i64*)(ws + L.vptr), nullptr, (const i64*)(ws + L.voff), (i64*)out_ids, (i64*)out_seg,
         (i64*)out_sel);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
