@@ -77,6 +77,28 @@ int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S,
   return GSB_OK;
 }
 
+// largest i in [0, n) with ptr[i] <= x, searched by a whole warp: 32 probes per round, so a
+// search over 10^6 offsets is 4 dependent loads instead of 20
+__device__ __forceinline__ i64 warp_find_segment(const i64* __restrict__ ptr, i64 n, i64 x) {
+  const int lane = threadIdx.x & 31;
+  i64 lo = 0, hi = n;  // answer in [lo, hi)
+  while (hi - lo > 1) {
+    const i64 stride = (hi - lo + 31) / 32;
+    const i64 probe = lo + (i64)lane * stride;
+    const bool le = probe < hi && __ldg(ptr + probe) <= x;
+    const int k = __popc(__ballot_sync(0xffffffffu, le));  // probes are monotone: the first k hold
+    const i64 nlo = lo + (i64)(k > 0 ? k - 1 : 0) * stride;
+    hi = nlo + stride < hi ? nlo + stride : hi;
+    lo = nlo;
+  }
+  return lo;
+}
+
+// CTA per tile of 1024 output entries: two warps locate the tile's first and last column slot,
+// every thread then searches only between those for each of its four entries.
+constexpr int SF_PER_THREAD = 4;
+constexpr int SF_TILE = SLICE_THREADS * SF_PER_THREAD;
+
 template <typename IndexT>
 __global__ void __launch_bounds__(SLICE_THREADS)
 slice_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices,
@@ -84,21 +106,36 @@ slice_fill_kernel(const i64* __restrict__ indptr, const void* __restrict__ indic
                   i64* __restrict__ out_rows, i64* __restrict__ out_cols,
                   i64* __restrict__ out_sel, const i64* __restrict__ col_bptr, int B,
                   i64 encoding_size) {
-  for (i64 e = (i64)blockIdx.x * SLICE_THREADS + threadIdx.x; e < E;
-       e += (i64)gridDim.x * SLICE_THREADS) {
-    // column slot = last i with sub_indptr[i] <= e
-    i64 lo = 0, hi = S;
-    while (hi - lo > 1) {
-      i64 mid = (lo + hi) >> 1;
-      if (__ldg(sub_indptr + mid) <= e) lo = mid; else hi = mid;
+  __shared__ i64 s_lo, s_hi;
+  const i64 tiles = (E + SF_TILE - 1) / SF_TILE;
+  for (i64 tile = blockIdx.x; tile < tiles; tile += gridDim.x) {
+    const i64 e0 = tile * SF_TILE;
+    const i64 e_last = e0 + SF_TILE - 1 < E - 1 ? e0 + SF_TILE - 1 : E - 1;
+    __syncthreads();  // the previous tile's readers of s_lo / s_hi
+    if (threadIdx.x < 64) {
+      const i64 s = warp_find_segment(sub_indptr, S, threadIdx.x < 32 ? e0 : e_last);
+      if (threadIdx.x == 0) s_lo = s;
+      if (threadIdx.x == 32) s_hi = s;
     }
-    const i64 c = seeds[lo];
-    const i64 pos = __ldg(indptr + c) + (e - __ldg(sub_indptr + lo));
-    i64 row = load_index<IndexT>(indices, pos);
-    if (encoding_size > 0 && col_bptr) row += (i64)find_segment(col_bptr, B, lo) * encoding_size;
-    out_rows[e] = row;
-    out_sel[e] = pos;
-    if (out_cols) out_cols[e] = lo;
+    __syncthreads();
+    // entry e0 + k * 256 + thread: neighbouring lanes read and write neighbouring words
+    const i64 t_lo = s_lo, t_hi = s_hi;
+#pragma unroll
+    for (int k = 0; k < SF_PER_THREAD; ++k) {
+      const i64 e = e0 + k * SLICE_THREADS + threadIdx.x;
+      if (e >= E) break;
+      i64 lo = t_lo, hi = t_hi;  // column slot of e: largest i in [lo, hi] with sub_indptr[i] <= e
+      while (lo < hi) {
+        const i64 mid = (lo + hi + 1) >> 1;
+        if (__ldg(sub_indptr + mid) <= e) lo = mid; else hi = mid - 1;
+      }
+      const i64 pos = __ldg(indptr + seeds[lo]) + (e - __ldg(sub_indptr + lo));
+      i64 row = load_index<IndexT>(indices, pos);
+      if (encoding_size > 0 && col_bptr) row += (i64)find_segment(col_bptr, B, lo) * encoding_size;
+      out_rows[e] = row;
+      out_sel[e] = pos;
+      if (out_cols) out_cols[e] = lo;
+    }
   }
 }
 
@@ -207,7 +244,7 @@ extern "C" int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, i
     return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   cudaStream_t st = (cudaStream_t)cuda_stream;
-  i64 blocks = (E + SLICE_THREADS - 1) / SLICE_THREADS;
+  i64 blocks = (E + SF_TILE - 1) / SF_TILE;
   if (blocks > 148 * 64) blocks = 148 * 64;
   LaunchScope ls(KID_SLICE_FILL, st);
   if (indices_dtype == GSB_I32)
