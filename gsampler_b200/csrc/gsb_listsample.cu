@@ -65,7 +65,7 @@ __global__ void list_setup_kernel(const ListParams p) {
       i64 len = p.range[b + 1] - p.range[b];
       if (len < 0) { raise(p.err, ERRBIT_BAD_INPUT); len = 0; }
       take = len < p.K ? len : p.K;
-      p.state[b] = SegState{0u, 0u, (u32)take, len <= p.K ? 1u : 0u};
+      if (p.state) p.state[b] = SegState{0u, 0u, (u32)take, len <= p.K ? 1u : 0u};  // null: uniform path
     }
     i64 tot;
     const i64 ex = block_exclusive_scan(take, s_scan, &tot);
@@ -389,7 +389,9 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
   p.seg_base = (i64*)(ws + L.seg_base); p.out_idx = (i64*)out_idx; p.out_range = (i64*)out_range;
   p.status = (u64*)(ws + L.status); p.ticket = (int*)(ws + L.ticket); p.done = p.ticket + 16;
   p.err = d_err;
-  if (!probs) {  // uniform: one reservoir pass, no keys
+  if (!probs) {  // uniform: one reservoir pass, no keys, nothing in the workspace (it may be absent)
+    p.keys = nullptr; p.hist = nullptr; p.state = nullptr; p.eq_total = nullptr; p.seg_base = nullptr;
+    p.status = nullptr; p.ticket = nullptr; p.done = nullptr;
     const i64 cap = R < B * K ? R : B * K;  // most picks there can be
     if (cap > 0) GSB_CUDA_OK(cudaMemsetAsync(out_idx, 0, sizeof(i64) * (size_t)cap, st));
     if (B > 1 || R == 0 || K == 0) { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }

@@ -767,11 +767,12 @@ torch::Tensor IndexSearch(torch::Tensor origin_data, torch::Tensor keys) {
 // at the next synchronising call rather than at the launch.
 static torch::Tensor& AsyncErrorWord(const torch::Device& dev) {
   static std::mutex mu;
-  static std::map<int, torch::Tensor> words;
+  // never destroyed: a static destructor would free device memory after the CUDA context is gone
+  static auto* words = new std::map<int, torch::Tensor>();
   std::lock_guard<std::mutex> lock(mu);
-  auto it = words.find(dev.index());
-  if (it == words.end())
-    it = words.emplace(dev.index(), torch::zeros({1}, torch::dtype(torch::kInt32).device(dev))).first;
+  auto it = words->find(dev.index());
+  if (it == words->end())
+    it = words->emplace(dev.index(), torch::zeros({1}, torch::dtype(torch::kInt32).device(dev))).first;
   return it->second;
 }
 
