@@ -58,9 +58,41 @@ def test_row_slicing_on_csc(gsb, oracle, graph, idx_dtype):
     assert np.array_equal(host(sub._CAPI_GetCOORows()), eids)
     assert np.array_equal(host(sub._CAPI_GetCOOCols()), oracle.csc2coo(eip))
     assert (sub._CAPI_GetNumRows(), sub._CAPI_GetNumCols(), sub._CAPI_GetNumEdges()) == (700, 3000, eids.size)
+    # the CSC-only form (no segment of the kept entries is produced)
+    sub2, sel2 = A._CAPI_Slicing(cuda(rows), 0, gsb._CSC, gsb._CSC)
+    assert np.array_equal(host(sub2._CAPI_GetCSCIndptr()), eip)
+    assert np.array_equal(host(sub2._CAPI_GetCSCIndices()), eids)
+    assert np.array_equal(host(sel2), esel)
     # empty selection
     sub, sel = A._CAPI_Slicing(cuda(np.empty(0, np.int64)), 0, gsb._CSC, gsb._CSC)
     assert sel.numel() == 0 and not host(sub._CAPI_GetCSCIndptr()).any()
+
+
+def test_row_slicing_over_thousands_of_tiles(gsb, oracle):
+    """2.4 M entries = 2300 tiles of 1024: every thread of the one-CTA tile scan owns several tiles,
+    columns start anywhere inside a tile, runs of empty columns cross tile borders."""
+    rng = np.random.default_rng(33)
+    n = 200000
+    indptr, indices = rand_csc(rng, n, 12, heavy=20)
+    rows = rng.permutation(n)[:n // 3].astype(np.int64)
+    A = new_graph(gsb, indptr, indices)
+    eip, eids, esel = oracle.slice_rows(indptr, indices, rows)
+    for fmt in (gsb._CSC, gsb._CSC + gsb._COO):
+        sub, sel = A._CAPI_Slicing(cuda(rows), 0, gsb._CSC, fmt)
+        assert np.array_equal(host(sub._CAPI_GetCSCIndptr()), eip)
+        assert np.array_equal(host(sub._CAPI_GetCSCIndices()), eids)
+        assert np.array_equal(host(sel), esel)
+    assert np.array_equal(host(sub._CAPI_GetCOOCols()), oracle.csc2coo(eip))
+    # column slice of the same graph: the tile search of the fill pass over 150 000 column slots
+    seeds = rng.integers(0, n, 150000).astype(np.int64)
+    sub, sel = A._CAPI_Slicing(cuda(seeds), 1, gsb._CSC, gsb._CSC + gsb._COO)
+    deg = np.diff(indptr)[seeds]
+    want_ptr = np.concatenate([[0], np.cumsum(deg)])
+    want_sel = np.concatenate([np.arange(indptr[c], indptr[c + 1]) for c in seeds] + [np.empty(0, np.int64)])
+    assert np.array_equal(host(sub._CAPI_GetCSCIndptr()), want_ptr)
+    assert np.array_equal(host(sel), want_sel)
+    assert np.array_equal(host(sub._CAPI_GetCSCIndices()), indices[want_sel])
+    assert np.array_equal(host(sub._CAPI_GetCOOCols()), np.repeat(np.arange(seeds.size), deg))
 
 
 @pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
