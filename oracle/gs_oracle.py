@@ -269,8 +269,9 @@ def edge_op_node(idx, e, node, op):
 
 # --------------------------------------------------------------------------- list sampling
 def list_sample_probs_spec(probs, K, seed=0, stream=0, range_ptr=None, n=None):
-    """K of the candidates of every segment without replacement, ascending index order.
-    ``probs`` None -> uniform over ``n`` candidates."""
+    """K of the candidates of every segment without replacement: weighted (A-Res keys) in
+    ascending index order; ``probs`` None -> uniform over ``n`` candidates by reservoir sampling,
+    in slot order (list_sampling.cu:47-64)."""
     if probs is not None:
         probs = _f32(probs)
         n = probs.size
