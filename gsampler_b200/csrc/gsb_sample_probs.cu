@@ -138,17 +138,44 @@ __global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const P
   }
 }
 
+// In-place bitonic sort, descending, of a[0..n) in shared memory (n a power of two) by the CTA.
+template <typename T>
+__device__ __forceinline__ void cta_sort_desc(T* a, int n) {
+  for (int k = 2; k <= n; k <<= 1) {
+    for (int j = k >> 1; j > 0; j >>= 1) {
+      for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int o = i ^ j;
+        if (o > i) {
+          const T x = a[i], y = a[o];
+          if (((i & k) == 0) ? (x < y) : (x > y)) { a[i] = y; a[o] = x; }
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
 // Very long columns (more than WB_MIN_DEG entries): one CTA per column, same radix select and
 // ordered emit as the warp kernel but with the histogram shared by 256 threads and block scans
 // for the tie ranks and output offsets.  Keeps a hub column from being the tail of the launch.
+// That is five passes over the column (keys are recomputed, not stored).  For K <= 256 two passes
+// usually do: pass A leaves every thread's largest key, and the K-th largest of those 256 values
+// is a lower bound L of the K-th largest key overall (K different entries reach it); pass B
+// collects the entries with key >= L -- about K of them -- into shared memory, where a sort by
+// (key descending, position ascending) gives exactly the winners of the radix select, ties
+// included.  More than WB_CAND candidates (many equal keys, e.g. zero weights) -> the five-pass form.
 constexpr int WB_THREADS = 256;
 constexpr int WB_MIN_DEG = 4096;
+constexpr int WB_CAND = 2048;
 
 template <typename IndexT>
 __global__ void __launch_bounds__(WB_THREADS) sample_probs_block_kernel(const ProbParams p) {
   __shared__ u32 s_hist[256];
   __shared__ i64 s_scan[34];
   __shared__ u32 s_digit, s_above;
+  __shared__ u32 s_top[WB_THREADS];
+  __shared__ u64 s_cand[WB_CAND];
+  __shared__ int s_ncand;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   i64 S = p.S_max;
   if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
@@ -162,6 +189,67 @@ __global__ void __launch_bounds__(WB_THREADS) sample_probs_block_kernel(const Pr
     const i64 out_start = p.sub_indptr[slot];
     if (out_start + K > p.E_cap) { if (threadIdx.x == 0) raise(p.err, ERRBIT_CAPACITY); continue; }
     const float* pr = p.probs + in_start;
+    bool done = false;
+    if (K <= WB_THREADS) {
+      u32 mine = 0;  // pass A: this thread's largest key
+      for (i64 e0 = (i64)threadIdx.x * 4; e0 < deg; e0 += WB_THREADS * 4) {
+        const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (e0 + j < deg) {
+            const u32 key = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
+            mine = key > mine ? key : mine;
+          }
+        }
+      }
+      __syncthreads();  // the previous column's readers of s_top / s_cand
+      s_top[threadIdx.x] = mine;
+      if (threadIdx.x == 0) s_ncand = 0;
+      __syncthreads();
+      cta_sort_desc(s_top, WB_THREADS);
+      const u32 bound = s_top[K - 1];
+      if (bound > 0u) {  // pass B: the entries that can still win (0 = weights <= 0 are in play)
+        for (i64 e0 = (i64)threadIdx.x * 4; e0 < deg; e0 += WB_THREADS * 4) {
+          const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            if (e0 + j < deg) {
+              const u32 key = ares_key(pick_word(blk, j), __ldg(pr + e0 + j));
+              if (key >= bound) {
+                const int at = atomicAdd(&s_ncand, 1);
+                if (at < WB_CAND) s_cand[at] = ((u64)key << 32) | (u64)(~(u32)(e0 + j));  // ~pos: low position first
+              }
+            }
+          }
+        }
+      }
+      __syncthreads();
+      const int ncand = s_ncand;
+      if (bound > 0u && ncand <= WB_CAND) {  // ncand >= K: K threads' maxima reach the bound
+        int n2 = 2;
+        while (n2 < ncand) n2 <<= 1;
+        for (int i = ncand + threadIdx.x; i < n2; i += WB_THREADS) s_cand[i] = 0ull;
+        __syncthreads();
+        cta_sort_desc(s_cand, n2);
+        // the first K are the winners; emit them in column order (sort ~pos descending)
+        int k2 = 2;
+        while (k2 < K) k2 <<= 1;
+        const u32 inv = threadIdx.x < K ? (u32)s_cand[threadIdx.x] : 0u;
+        __syncthreads();
+        s_top[threadIdx.x] = inv;
+        __syncthreads();
+        cta_sort_desc(s_top, k2);
+        if (threadIdx.x < K) {
+          const i64 e = in_start + (i64)(~s_top[threadIdx.x]);
+          p.out_rows[out_start + threadIdx.x] = load_index<IndexT>(p.indices, e);
+          p.out_sel[out_start + threadIdx.x] = e;
+          if (p.out_cols) p.out_cols[out_start + threadIdx.x] = slot;
+        }
+        done = true;
+      }
+    }
+    __syncthreads();
+    if (done) continue;
     u32 prefix = 0, prefix_mask = 0;
     u32 remaining = (u32)K;
     for (int shift = 24; shift >= 0; shift -= 8) {
