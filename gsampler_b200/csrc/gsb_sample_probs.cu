@@ -102,10 +102,21 @@ __global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const P
     const int d = (int)deg;
     u32 kmin = 0, pmin = 0;
     int imin = 0;
-    Philox4 blk;
-    for (int e = 0; e < d; ++e) {
-      if ((e & 3) == 0) blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e >> 2));
-      const u32 key = ares_key(pick_word(blk, e & 3), __ldg(pr + e));
+    // eight keys at a time: the two Philox blocks and the eight log2/divide chains are independent
+    // of each other, so they overlap; the top-K update below stays in entry order
+    for (int e0 = 0; e0 < d; e0 += 8) {
+      const Philox4 b0 = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
+      Philox4 b1 = b0;
+      if (e0 + 4 < d) b1 = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2) + 1u);
+      u32 keys[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        keys[j] = e0 + j < d ? ares_key(pick_word(j < 4 ? b0 : b1, j & 3), __ldg(pr + e0 + j)) : 0u;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+      const int e = e0 + j;
+      if (e >= d) break;
+      const u32 key = keys[j];
       if (e < K) {
         tkey[e * WT_THREADS] = key;
         tpos[e * WT_THREADS] = (u32)e;
@@ -115,10 +126,11 @@ __global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const P
         tpos[imin * WT_THREADS] = (u32)e;
         // new smallest: least key, the highest position among equals
         kmin = tkey[0]; pmin = tpos[0]; imin = 0;
-        for (int j = 1; j < K; ++j) {
-          const u32 kj = tkey[j * WT_THREADS], pj = tpos[j * WT_THREADS];
-          if (kj < kmin || (kj == kmin && pj > pmin)) { kmin = kj; pmin = pj; imin = j; }
+        for (int t = 1; t < K; ++t) {
+          const u32 kt = tkey[t * WT_THREADS], pt = tpos[t * WT_THREADS];
+          if (kt < kmin || (kt == kmin && pt > pmin)) { kmin = kt; pmin = pt; imin = t; }
         }
+      }
       }
     }
     // winners in column order: repeatedly take the smallest remaining position
