@@ -325,9 +325,14 @@ __global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_scalar_kernel(const C
   }
 }
 
+// grid cap in CTAs per SM for the streaming edge kernels: 123.7 M edges, cap 16 / 64: SDDMM 0.63 / 0.57 ms,
+// COO sums 0.78 / 0.73 ms (more, shorter CTAs even out the tail and the atomics' hot rows)
+#ifndef GSB_WIDE_GRID
+#define GSB_WIDE_GRID 64
+#endif
 static int wide_grid(i64 work_items, int per_block) {
   i64 g = (work_items + per_block - 1) / per_block;
-  if (g > 148 * 16) g = 148 * 16;
+  if (g > 148 * GSB_WIDE_GRID) g = 148 * GSB_WIDE_GRID;
   return g < 1 ? 1 : (int)g;
 }
 
