@@ -50,6 +50,18 @@ constexpr int PT_TILE = GSB_PT_TILE;   // items per CTA tile of pcount / scatter
 constexpr int PT_THREADS = 512;
 constexpr int PT_BATCH = GSB_PT_BATCH; // loads in flight per thread
 constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
+// grid caps in CTAs per SM: tile kernels (pcount, scatter), the bucket kernel (dedupe) and emit.  One
+// CTA per tile / bucket up to 64 per SM lets the hardware scheduler even out the tail (layer 3 of
+// cfg2: 2800 tiles, 6400 buckets; caps of 8 and 12 left CTAs with 2 or 3 tiles each): -1.2 % per step.
+#ifndef GSB_RL_WIDE
+#define GSB_RL_WIDE 64
+#endif
+#ifndef GSB_RL_BK
+#define GSB_RL_BK 64
+#endif
+#ifndef GSB_RL_EMIT
+#define GSB_RL_EMIT 16
+#endif
 #ifndef GSB_BUCKET_ITEMS
 #define GSB_BUCKET_ITEMS 3584
 #endif
@@ -794,13 +806,13 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   // bucket counts and cursors are adjacent: one clear
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_start, 0, L.min_idx - L.bucket_start, st));
   const i64 items_max = S_max + E_max;
-  const int wide = 148 * 8;
+  const int wide = 148 * GSB_RL_WIDE;
   int g_tiles = (int)((items_max + PT_TILE - 1) / PT_TILE); if (g_tiles < 1) g_tiles = 1;
   if (g_tiles > wide) g_tiles = wide;
   { LaunchScope ls(KID_RL_PCOUNT, st); relabel_pcount_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_PSCAN, st); relabel_pscan_kernel<<<1, 1024, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_SCATTER, st); relabel_scatter_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
-  const int g_bk = (int)(L.buckets_cap < 148 * 12 ? L.buckets_cap : 148 * 12);
+  const int g_bk = (int)(L.buckets_cap < 148 * GSB_RL_BK ? L.buckets_cap : 148 * GSB_RL_BK);
   const int dd_smem = 2 * DD_TAB * (int)sizeof(u32);
   GSB_CUDA_OK(cudaFuncSetAttribute(relabel_dedupe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_smem));
   { LaunchScope ls(KID_RL_DEDUPE, st); relabel_dedupe_kernel<<<g_bk, DD_THREADS, dd_smem, st>>>(p); }
@@ -809,7 +821,7 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   { LaunchScope ls(KID_RL_SCAN, st); relabel_rank_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   if (out_row && E_max > 0) {
     int g_edges = (int)((E_max + GSB_EMIT_EB * RL_THREADS - 1) / (GSB_EMIT_EB * RL_THREADS));
-    if (g_edges > 148 * 16) g_edges = 148 * 16;
+    if (g_edges > 148 * GSB_RL_EMIT) g_edges = 148 * GSB_RL_EMIT;
     { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<g_edges, RL_THREADS, 0, st>>>(p); }
   }
   GSB_CUDA_OK(cudaGetLastError());
