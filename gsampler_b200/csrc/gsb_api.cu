@@ -62,6 +62,18 @@ LaunchScope::~LaunchScope() {
 
 void set_timing_tag(int tag) { g_timing_tag = tag; }
 
+int sm_count() {
+  constexpr int MAX_DEV = 64;
+  static std::atomic<int> cached[MAX_DEV];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= MAX_DEV) return 148;
+  int n = cached[dev].load(std::memory_order_relaxed);
+  if (n > 0) return n;
+  if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n < 1) return 148;
+  cached[dev].store(n, std::memory_order_relaxed);
+  return n;
+}
+
 }  // namespace gsb
 
 using namespace gsb;
@@ -136,7 +148,7 @@ extern "C" size_t gsb_graphsage_workspace_bytes(int64_t B, int num_layers,
 }
 
 extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, int indices_dtype,
-                                    int64_t id_bound, const int64_t* seeds,
+                                    int64_t num_cols, int64_t id_bound, const int64_t* seeds,
                                     const int64_t* seeds_ptr, int64_t B, int64_t S0,
                                     int num_layers, const int64_t* fanouts, uint64_t seed,
                                     const gsb_layer_buffers* layers, int64_t* d_counts,
@@ -162,7 +174,7 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
     const int64_t S_max = l == 0 ? S0 : L.S_cap;
     set_timing_tag(l);
     const size_t ws_a = align256(gsb_sample_cols_workspace_bytes(L.S_cap, fanouts[l]));
-    int rc = gsb_sample_cols(indptr, indices, indices_dtype, cur_seeds, S_max, d_S, fanouts[l], 0,
+    int rc = gsb_sample_cols(indptr, indices, indices_dtype, num_cols, cur_seeds, S_max, d_S, fanouts[l], 0,
                              seed, (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
                              d_counts + 3 * l + 1, workspace, ws_a, d_err, cuda_stream);
     if (rc != GSB_OK) return rc;

@@ -205,6 +205,10 @@ int relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B, in
 
 inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 
+// Number of SMs of the current device (queried once per device and cached); grid caps are
+// stated in CTAs per SM times this.
+int sm_count();
+
 // Launch accounting: every kernel launch of the library sits inside a
 // LaunchScope, which counts it and, when timing is enabled
 // (gsb_timing_enable), brackets it with CUDA events on the launching stream.
@@ -236,7 +240,7 @@ struct CountExtra {
   int* list_n = nullptr;
   i64 list_min_deg = 0;
 };
-int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
+int launch_count(const i64* indptr, i64 num_cols, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
                  int replace, i64* sub_indptr, i64* d_total, void* workspace, int* d_err,
                  cudaStream_t st, const CountExtra& extra = CountExtra());
 

@@ -325,6 +325,69 @@ __global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_scalar_kernel(const C
   }
 }
 
+// Two u-op-v edge maps over one COO: out1[eid, f] = op(lhs1[row, .], rhs1[col, .]) and
+// out2[eid, f] = op(lhs2[row, .], rhs2[col, .]).  The endpoints of an edge (and its id) are read
+// once for both maps; with scalar operands four coalesced edges per thread are in flight.
+struct PairParams {
+  const i64* row; const i64* col; const i64* e_ids; i64 nnz;
+  int op;
+  const float* lhs1; const float* rhs1; float* out1;
+  const float* lhs2; const float* rhs2; float* out2;
+  i64 lhs_len, rhs_len;
+  const i64* lhs_off; const i64* rhs_off;
+  i64 out_len;
+};
+
+__global__ void __launch_bounds__(EO_THREADS) u_op_v_pair_scalar_kernel(const PairParams p) {
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  const i64* __restrict__ row = p.row;
+  const i64* __restrict__ col = p.col;
+  const i64* __restrict__ eids = p.e_ids;
+  const i64 step = (i64)gridDim.x * EO_THREADS * 4;
+  for (i64 base = (i64)blockIdx.x * EO_THREADS * 4 + threadIdx.x; base < p.nnz; base += step) {
+    i64 src[4], dst[4], eid[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const i64 ed = base + k * EO_THREADS;
+      const bool in = ed < p.nnz;
+      src[k] = ul && in ? __ldg(row + ed) : 0;
+      dst[k] = ur && in ? __ldg(col + ed) : 0;
+      eid[k] = eids && in ? __ldg(eids + ed) : ed;
+    }
+    float l1[4], r1[4], l2[4], r2[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const bool in = base + k * EO_THREADS < p.nnz;
+      l1[k] = ul && in ? __ldg(p.lhs1 + src[k]) : 0.f;
+      r1[k] = ur && in ? __ldg(p.rhs1 + dst[k]) : 0.f;
+      l2[k] = ul && in ? __ldg(p.lhs2 + src[k]) : 0.f;
+      r2[k] = ur && in ? __ldg(p.rhs2 + dst[k]) : 0.f;
+    }
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+      if (base + k * EO_THREADS < p.nnz) {
+        p.out1[eid[k]] = apply_op(p.op, l1[k], r1[k]);
+        p.out2[eid[k]] = apply_op(p.op, l2[k], r2[k]);
+      }
+  }
+}
+
+__global__ void __launch_bounds__(EO_THREADS) u_op_v_pair_kernel(const PairParams p) {
+  const i64 total = p.nnz * p.out_len;
+  const bool ul = op_uses_lhs(p.op), ur = op_uses_rhs(p.op);
+  for (i64 t = (i64)blockIdx.x * EO_THREADS + threadIdx.x; t < total; t += (i64)gridDim.x * EO_THREADS) {
+    const i64 ed = t / p.out_len, f = t - ed * p.out_len;
+    const i64 src = __ldg(p.row + ed), dst = __ldg(p.col + ed);
+    const i64 eid = p.e_ids ? __ldg(p.e_ids + ed) : ed;
+    const i64 lo = src * p.lhs_len + (p.lhs_off ? p.lhs_off[f] : (p.lhs_len == 1 ? 0 : f));
+    const i64 ro = dst * p.rhs_len + (p.rhs_off ? p.rhs_off[f] : (p.rhs_len == 1 ? 0 : f));
+    const float l1 = ul ? __ldg(p.lhs1 + lo) : 0.f, r1 = ur ? __ldg(p.rhs1 + ro) : 0.f;
+    const float l2 = ul ? __ldg(p.lhs2 + lo) : 0.f, r2 = ur ? __ldg(p.rhs2 + ro) : 0.f;
+    p.out1[eid * p.out_len + f] = apply_op(p.op, l1, r1);
+    p.out2[eid * p.out_len + f] = apply_op(p.op, l2, r2);
+  }
+}
+
 // grid cap in CTAs per SM for the streaming edge kernels: 123.7 M edges, cap 16 / 64: SDDMM 0.63 / 0.57 ms,
 // COO sums 0.78 / 0.73 ms (more, shorter CTAs even out the tail and the atomics' hot rows)
 #ifndef GSB_WIDE_GRID
@@ -332,7 +395,7 @@ __global__ void __launch_bounds__(EO_THREADS) spmm_coo_sum_scalar_kernel(const C
 #endif
 static int wide_grid(i64 work_items, int per_block) {
   i64 g = (work_items + per_block - 1) / per_block;
-  if (g > 148 * GSB_WIDE_GRID) g = 148 * GSB_WIDE_GRID;
+  if (g > sm_count() * GSB_WIDE_GRID) g = sm_count() * GSB_WIDE_GRID;
   return g < 1 ? 1 : (int)g;
 }
 
@@ -402,6 +465,28 @@ extern "C" int gsb_sddmm_coo(const int64_t* row, const int64_t* col, const int64
     sddmm_coo_scalar_kernel<<<wide_grid(nnz, EO_THREADS * 4), EO_THREADS, 0, st>>>(p);
   else
     sddmm_coo_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_u_op_v_pair(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                               int64_t nnz, int op, const float* lhs1, const float* rhs1, float* out1,
+                               const float* lhs2, const float* rhs2, float* out2, int64_t lhs_len,
+                               int64_t rhs_len, const int64_t* lhs_off, const int64_t* rhs_off,
+                               int64_t out_len, void* cuda_stream) {
+  if (nnz == 0) return GSB_OK;
+  int rc = check_coo(row, col, nnz, op, lhs1, lhs_len, rhs1, rhs_len, out1, out_len);
+  if (rc == GSB_OK) rc = check_coo(row, col, nnz, op, lhs2, lhs_len, rhs2, rhs_len, out2, out_len);
+  if (rc != GSB_OK) return rc;
+  PairParams p{(const i64*)row, (const i64*)col, (const i64*)e_ids, nnz, op, lhs1, rhs1, out1,
+               lhs2, rhs2, out2, lhs_len, rhs_len, (const i64*)lhs_off, (const i64*)rhs_off, out_len};
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  LaunchScope ls(KID_EDGE_OP, st);
+  if (out_len == 1 && (!op_uses_lhs(op) || lhs_len == 1) && (!op_uses_rhs(op) || rhs_len == 1) &&
+      !lhs_off && !rhs_off)
+    u_op_v_pair_scalar_kernel<<<wide_grid(nnz, EO_THREADS * 4), EO_THREADS, 0, st>>>(p);
+  else
+    u_op_v_pair_kernel<<<wide_grid(nnz * out_len, EO_THREADS), EO_THREADS, 0, st>>>(p);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

@@ -396,7 +396,7 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
     if (cap > 0) GSB_CUDA_OK(cudaMemsetAsync(out_idx, 0, sizeof(i64) * (size_t)cap, st));
     if (B > 1 || R == 0 || K == 0) { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
     if (R > 0 && K > 0) {
-      i64 gr = (R + LS_THREADS - 1) / LS_THREADS; if (gr > 148 * 16) gr = 148 * 16;
+      i64 gr = (R + LS_THREADS - 1) / LS_THREADS; if (gr > sm_count() * 16) gr = sm_count() * 16;
       LaunchScope ls(KID_LIST_SAMPLE, st);
       list_reservoir_kernel<<<(int)gr, LS_THREADS, 0, st>>>(p);
     }
@@ -404,7 +404,7 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
     return GSB_OK;
   }
   GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.keys, st));  // ticket, status, histograms
-  i64 g = (R + LS_TILE - 1) / LS_TILE; if (g > 148 * 4) g = 148 * 4; if (g < 1) g = 1;
+  i64 g = (R + LS_TILE - 1) / LS_TILE; if (g > sm_count() * 4) g = sm_count() * 4; if (g < 1) g = 1;
   { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
   if (R > 0 && K > 0) {
     for (int shift = 24; shift >= 0; shift -= 8) {
@@ -423,7 +423,7 @@ extern "C" int gsb_list_sample_replace(const float* probs, int64_t n, int64_t K,
   if (K == 0) return GSB_OK;
   if (n < 1 || K < 0 || !out_idx) return GSB_ERR_INVALID;
   cudaStream_t st = (cudaStream_t)cuda_stream;
-  i64 g = (K + 255) / 256; if (g > 148 * 8) g = 148 * 8;
+  i64 g = (K + 255) / 256; if (g > sm_count() * 8) g = sm_count() * 8;
   if (!probs) {
     LaunchScope ls(KID_LIST_SAMPLE, st);
     list_replace_uniform_kernel<<<(int)g, 256, 0, st>>>(n, K, seed, stream, (i64*)out_idx);

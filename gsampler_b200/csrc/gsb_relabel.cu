@@ -806,13 +806,13 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   // bucket counts and cursors are adjacent: one clear
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_start, 0, L.min_idx - L.bucket_start, st));
   const i64 items_max = S_max + E_max;
-  const int wide = 148 * GSB_RL_WIDE;
+  const int wide = sm_count() * GSB_RL_WIDE;
   int g_tiles = (int)((items_max + PT_TILE - 1) / PT_TILE); if (g_tiles < 1) g_tiles = 1;
   if (g_tiles > wide) g_tiles = wide;
   { LaunchScope ls(KID_RL_PCOUNT, st); relabel_pcount_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_PSCAN, st); relabel_pscan_kernel<<<1, 1024, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_SCATTER, st); relabel_scatter_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
-  const int g_bk = (int)(L.buckets_cap < 148 * GSB_RL_BK ? L.buckets_cap : 148 * GSB_RL_BK);
+  const int g_bk = (int)(L.buckets_cap < sm_count() * GSB_RL_BK ? L.buckets_cap : sm_count() * GSB_RL_BK);
   const int dd_smem = 2 * DD_TAB * (int)sizeof(u32);
   GSB_CUDA_OK(cudaFuncSetAttribute(relabel_dedupe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_smem));
   { LaunchScope ls(KID_RL_DEDUPE, st); relabel_dedupe_kernel<<<g_bk, DD_THREADS, dd_smem, st>>>(p); }
@@ -821,7 +821,7 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   { LaunchScope ls(KID_RL_SCAN, st); relabel_rank_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   if (out_row && E_max > 0) {
     int g_edges = (int)((E_max + GSB_EMIT_EB * RL_THREADS - 1) / (GSB_EMIT_EB * RL_THREADS));
-    if (g_edges > 148 * GSB_RL_EMIT) g_edges = 148 * GSB_RL_EMIT;
+    if (g_edges > sm_count() * GSB_RL_EMIT) g_edges = sm_count() * GSB_RL_EMIT;
     { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<g_edges, RL_THREADS, 0, st>>>(p); }
   }
   GSB_CUDA_OK(cudaGetLastError());

@@ -263,10 +263,10 @@ static AcrossLayout across_layout(i64 entries, i64 id_bound, bool with_mask) {
 static int build_map(char* ws, const AcrossLayout& L, const i64* ids, i64 R, i64 id_bound,
                      int* d_err, cudaStream_t st) {
   GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.map, st));  // ticket + status
-  i64 g = (id_bound + 255) / 256; if (g > 148 * 16) g = 148 * 16; if (g < 1) g = 1;
+  i64 g = (id_bound + 255) / 256; if (g > sm_count() * 16) g = sm_count() * 16; if (g < 1) g = 1;
   { LaunchScope ls(KID_SLICE_ROWS, st); map_fill_kernel<<<(int)g, 256, 0, st>>>((u32*)(ws + L.map), id_bound); }
   if (R > 0) {
-    g = (R + 255) / 256; if (g > 148 * 16) g = 148 * 16;
+    g = (R + 255) / 256; if (g > sm_count() * 16) g = sm_count() * 16;
     LaunchScope ls(KID_SLICE_ROWS, st);
     map_build_kernel<<<(int)g, 256, 0, st>>>(ids, R, (u32*)(ws + L.map), id_bound, d_err);
   }
@@ -516,7 +516,7 @@ extern "C" int gsb_slice_across_count(const int64_t* indptr, const void* indices
   int rc = build_map(ws, L, (const i64*)ids, R, id_bound, d_err, st);
   if (rc != GSB_OK) return rc;
   {
-    i64 g = (id_bound + 255) / 256; if (g > 148 * 16) g = 148 * 16; if (g < 1) g = 1;
+    i64 g = (id_bound + 255) / 256; if (g > sm_count() * 16) g = sm_count() * 16; if (g < 1) g = 1;
     LaunchScope ls(KID_SLICE_ROWS, st);
     bits_build_kernel<<<(int)g, 256, 0, st>>>((const u32*)(ws + L.map), id_bound, (u32*)(ws + L.bits));
   }
@@ -538,7 +538,7 @@ extern "C" int gsb_slice_across_count(const int64_t* indptr, const void* indices
                                          (i64*)(ws + L.tile_base));
   }
   {
-    i64 g = (nseg + 256) / 256; if (g > 148 * 16) g = 148 * 16;
+    i64 g = (nseg + 256) / 256; if (g > sm_count() * 16) g = sm_count() * 16;
     LaunchScope ls(KID_SLICE_ROWS, st);
     across_offsets_kernel<<<(int)g, 256, 0, st>>>((const i64*)indptr, nseg, nnz_max,
                                                  (const unsigned char*)(ws + L.nib),
@@ -639,7 +639,7 @@ extern "C" int gsb_slice_cols_rows_count(const int64_t* indptr, const void* indi
   GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.table, st));                                     // entry total
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.table, 0xFF, sizeof(u64) * (size_t)L.slots, st));  // empty slots
   if (R > 0) {
-    i64 g = (R + 255) / 256; if (g > 148 * 16) g = 148 * 16;
+    i64 g = (R + 255) / 256; if (g > sm_count() * 16) g = sm_count() * 16;
     LaunchScope ls(KID_SLICE_ROWS, st);
     rowtab_insert_kernel<<<(int)g, 256, 0, st>>>((const i64*)rows, (const i64*)row_ptr, (int)B,
                                                  (u64*)(ws + L.table), d_err);
@@ -657,7 +657,7 @@ extern "C" int gsb_slice_cols_rows_count(const int64_t* indptr, const void* indi
     colrow_parts_kernel<<<1, 1024, 0, st>>>((const i64*)col_ptr, (int)B, S, deg, total, vptr);
   }
   if (S > 0) {
-    i64 g = (L.parts + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
+    i64 g = (L.parts + RS_WARPS - 1) / RS_WARPS; if (g > sm_count() * 16) g = sm_count() * 16;
     LaunchScope ls(KID_SLICE_ROWS, st);
     if (indices_dtype == GSB_I32)
       colrow_part_kernel<int, false><<<(int)g, RS_THREADS, 0, st>>>(
@@ -695,7 +695,7 @@ extern "C" int gsb_slice_cols_rows_fill(const int64_t* indptr, const void* indic
   const ColRowLayout L = colrow_layout(S, R, B);
   cudaStream_t st = (cudaStream_t)cuda_stream;
   const char* ws = (const char*)workspace;
-  i64 g = (L.parts + RS_WARPS - 1) / RS_WARPS; if (g > 148 * 16) g = 148 * 16;
+  i64 g = (L.parts + RS_WARPS - 1) / RS_WARPS; if (g > sm_count() * 16) g = sm_count() * 16;
   LaunchScope ls(KID_SLICE_ROWS, st);
   if (indices_dtype == GSB_I32)
     colrow_part_kernel<int, true><<<(int)g, RS_THREADS, 0, st>>>(

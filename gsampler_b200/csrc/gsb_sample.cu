@@ -8,6 +8,8 @@
 // positions into shared memory.  Phase 3 (thread per OUTPUT edge) gathers the
 // row ids and writes the three output arrays fully coalesced: consecutive
 // threads write consecutive output elements, whatever the degree skew.
+#include <atomic>
+
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -23,6 +25,7 @@ constexpr int SAMPLE_MAX_TILE_EDGES = 8192;  // picks staged in shared memory pe
 struct SampleParams {
   const i64* indptr;
   const void* indices;
+  i64 num_cols;      // columns of the graph: a seed outside [0, num_cols) is reported, never read
   const i64* seeds;  // nullable
   i64 S_max;
   const i64* d_S;    // nullable
@@ -78,8 +81,15 @@ sample_tile_kernel(const SampleParams p) {
   int cnt = 0;
   if (valid) {
     const i64 c = p.seeds ? p.seeds[slot] : slot;
-    in_start = __ldg(p.indptr + c);
-    const i64 d = __ldg(p.indptr + c + 1) - in_start;
+    i64 d = 0;
+    if ((u64)c < (u64)p.num_cols) {
+      in_start = __ldg(p.indptr + c);
+      d = __ldg(p.indptr + c + 1) - in_start;
+    }
+    if ((u64)c >= (u64)p.num_cols || d < 0 || d > 0xFFFFFFFFll) {  // bad seed / offsets: an empty column
+      raise(p.err, ERRBIT_BAD_INPUT);
+      d = 0;
+    }
     deg = (u32)d;
     cnt = p.replace ? (d == 0 ? 0 : K) : (d < (i64)K ? (int)d : K);
     s_in_start[lc] = in_start;
@@ -169,12 +179,13 @@ extern "C" size_t gsb_sample_cols_workspace_bytes(int64_t S_max, int64_t K) {
 }
 
 extern "C" int gsb_sample_cols(const int64_t* indptr, const void* indices, int indices_dtype,
-                               const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K,
+                               int64_t num_cols, const int64_t* seeds, int64_t S_max,
+                               const int64_t* d_S, int64_t K,
                                int replace, uint64_t seed, uint32_t stream, int64_t* sub_indptr,
                                int64_t* out_rows, int64_t* out_cols, int64_t* out_sel,
                                int64_t E_cap, int64_t* d_num_edges, void* workspace,
                                size_t workspace_bytes, int* d_err, void* cuda_stream) {
-  if (!indptr || !indices || !sub_indptr || S_max < 0 || E_cap < 0) return GSB_ERR_INVALID;
+  if (!indptr || !indices || !sub_indptr || S_max < 0 || E_cap < 0 || num_cols < 0) return GSB_ERR_INVALID;
   if (E_cap > 0 && (!out_rows || !out_sel)) return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   if (K < 1) return GSB_ERR_INVALID;
@@ -186,7 +197,7 @@ extern "C" int gsb_sample_cols(const int64_t* indptr, const void* indices, int i
   const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, tc);
   GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
   SampleParams p;
-  p.indptr = (const i64*)indptr; p.indices = indices; p.seeds = (const i64*)seeds;
+  p.indptr = (const i64*)indptr; p.indices = indices; p.num_cols = num_cols; p.seeds = (const i64*)seeds;
   p.S_max = S_max; p.d_S = (const i64*)d_S; p.K = (int)K; p.replace = replace ? 1 : 0;
   p.seed = seed; p.stream = stream; p.sub_indptr = (i64*)sub_indptr; p.out_rows = (i64*)out_rows;
   p.out_cols = (i64*)out_cols; p.out_sel = (i64*)out_sel; p.E_cap = E_cap;
@@ -225,7 +236,8 @@ static __device__ __align__(256) unsigned char g_noalloc_scratch[NOALLOC_SCRATCH
 
 namespace {
 constexpr int NOALLOC_MAX_DEVICES = 64;
-void* g_noalloc_ptr[NOALLOC_MAX_DEVICES] = {nullptr};  // device address of the array, per device
+// device address of the array, per device; written once per device, read by any host thread
+std::atomic<void*> g_noalloc_ptr[NOALLOC_MAX_DEVICES];
 }  // namespace
 
 extern "C" int64_t gsb_sample_cols_noalloc_max_columns(int64_t K) {
@@ -234,7 +246,8 @@ extern "C" int64_t gsb_sample_cols_noalloc_max_columns(int64_t K) {
 }
 
 extern "C" int gsb_sample_cols_noalloc(const int64_t* indptr, const void* indices,
-                                       int indices_dtype, const int64_t* seeds, int64_t S_max,
+                                       int indices_dtype, int64_t num_cols, const int64_t* seeds,
+                                       int64_t S_max,
                                        const int64_t* d_S, int64_t K, int replace, uint64_t seed,
                                        uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
                                        int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
@@ -246,17 +259,19 @@ extern "C" int gsb_sample_cols_noalloc(const int64_t* indptr, const void* indice
   int dev = -1;
   GSB_CUDA_OK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= NOALLOC_MAX_DEVICES) return GSB_ERR_UNSUPPORTED;
-  if (!g_noalloc_ptr[dev]) {
+  void* scratch = g_noalloc_ptr[dev].load(std::memory_order_acquire);
+  if (!scratch) {
     // first call on this device: resolve the array's DEVICE address.  In host
     // code the symbol's name is only a handle; passing it to a kernel would
     // hand the kernel a host address.
     void* p = nullptr;
     if (cudaGetSymbolAddress(&p, g_noalloc_scratch) != cudaSuccess || !p) return GSB_ERR_CUDA;
-    g_noalloc_ptr[dev] = p;
+    g_noalloc_ptr[dev].store(p, std::memory_order_release);  // every thread resolves the same address
+    scratch = p;
   }
   // the scratch keeps the previous call's ticket and status words;
   // gsb_sample_cols zeroes the part it uses on the stream before the launch
-  return gsb_sample_cols(indptr, indices, indices_dtype, seeds, S_max, d_S, K, replace, seed, stream,
+  return gsb_sample_cols(indptr, indices, indices_dtype, num_cols, seeds, S_max, d_S, K, replace, seed, stream,
                          sub_indptr, out_rows, out_cols, out_sel, E_cap, d_num_edges,
-                         g_noalloc_ptr[dev], NOALLOC_SCRATCH_BYTES, d_err, cuda_stream);
+                         scratch, NOALLOC_SCRATCH_BYTES, d_err, cuda_stream);
 }

@@ -659,13 +659,14 @@ extern "C" size_t gsb_sample_cols_probs_workspace_bytes(int64_t S_max, int64_t K
 }
 
 extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices, int indices_dtype,
-                                     const float* probs, const int64_t* seeds, int64_t S_max,
+                                     int64_t num_cols, const float* probs, const int64_t* seeds,
+                                     int64_t S_max,
                                      const int64_t* d_S, int64_t K, int replace, uint64_t seed,
                                      uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
                                      int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
                                      int64_t* d_num_edges, void* workspace, size_t workspace_bytes,
                                      int* d_err, void* cuda_stream) {
-  if (!indptr || !indices || !probs || !sub_indptr || S_max < 0 || E_cap < 0 || K < 1)
+  if (!indptr || !indices || !probs || !sub_indptr || S_max < 0 || E_cap < 0 || K < 1 || num_cols < 0)
     return GSB_ERR_INVALID;
   if (E_cap > 0 && (!out_rows || !out_sel)) return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
@@ -681,7 +682,7 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   extra.list = (i64*)(ws + L.list); extra.list_n = (int*)(ws + L.list_n);
   extra.list_min_deg = thread_path ? WT_MAX_DEG + 1 : 0;  // what is left for the warp kernel
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.list_n, 0, 256, st));
-  int rc = launch_count((const i64*)indptr, (const i64*)seeds, S_max, (const i64*)d_S, K,
+  int rc = launch_count((const i64*)indptr, num_cols, (const i64*)seeds, S_max, (const i64*)d_S, K,
                         replace ? 1 : 0, (i64*)sub_indptr, (i64*)d_num_edges, ws + L.count, d_err, st,
                         extra);
   if (rc != GSB_OK) return rc;
@@ -697,7 +698,7 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   p.long_list = (i64*)(ws + L.long_list); p.long_n = (int*)(ws + L.list_n) + 16;
   if (p.thread_path) {
     i64 tb = (S_max + WT_THREADS - 1) / WT_THREADS;
-    if (tb > 148 * 16) tb = 148 * 16;
+    if (tb > sm_count() * 16) tb = sm_count() * 16;
     const size_t tsmem = sizeof(u32) * 2 * (size_t)K * WT_THREADS;
     LaunchScope ls(KID_SAMPLE_PROBS_SHORT, st);
     if (indices_dtype == GSB_I32)
@@ -706,7 +707,7 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
       sample_probs_thread_kernel<i64><<<(int)tb, WT_THREADS, tsmem, st>>>(p);
   }
   i64 blocks = (S_max + WP_WARPS - 1) / WP_WARPS;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   const size_t smem = sizeof(u32) * WP_WARPS * 256 + sizeof(float) * WP_WARPS * (size_t)K +
                       sizeof(u32) * WP_WARPS * WP_CACHE;
   {
@@ -719,9 +720,9 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   if (!replace) {
     LaunchScope ls2(KID_SAMPLE_PROBS_LONG, st);
     if (indices_dtype == GSB_I32)
-      sample_probs_block_kernel<int><<<148 * GSB_WB_CTAS_PER_SM, WB_THREADS, 0, st>>>(p);
+      sample_probs_block_kernel<int><<<sm_count() * GSB_WB_CTAS_PER_SM, WB_THREADS, 0, st>>>(p);
     else
-      sample_probs_block_kernel<i64><<<148 * GSB_WB_CTAS_PER_SM, WB_THREADS, 0, st>>>(p);
+      sample_probs_block_kernel<i64><<<sm_count() * GSB_WB_CTAS_PER_SM, WB_THREADS, 0, st>>>(p);
   }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;

@@ -15,7 +15,7 @@ constexpr int SLICE_THREADS = 256;
 // Pick count of one column: K == 0 -> the whole column; otherwise min(deg, K)
 // without replacement, K (0 for an empty column) with replacement.
 __global__ void __launch_bounds__(SLICE_THREADS)
-count_kernel(const i64* __restrict__ indptr, const i64* __restrict__ seeds, i64 S_max,
+count_kernel(const i64* __restrict__ indptr, i64 num_cols, const i64* __restrict__ seeds, i64 S_max,
              const i64* __restrict__ d_S, i64 K, int replace, i64* __restrict__ sub_indptr,
              i64* __restrict__ d_total, u64* status, int* ticket, int* err, const CountExtra x) {
   __shared__ i64 s_scan[34];
@@ -33,8 +33,15 @@ count_kernel(const i64* __restrict__ indptr, const i64* __restrict__ seeds, i64 
   bool listed = false;
   if (slot < S) {
     const i64 c = seeds ? seeds[slot] : slot;
-    const i64 st = __ldg(indptr + c);
-    const i64 deg = __ldg(indptr + c + 1) - st;
+    i64 st = 0, deg = 0;
+    if ((u64)c < (u64)num_cols) {
+      st = __ldg(indptr + c);
+      deg = __ldg(indptr + c + 1) - st;
+    }
+    if ((u64)c >= (u64)num_cols || deg < 0) {  // bad seed / offsets: reported, counted as empty
+      raise(err, ERRBIT_BAD_INPUT);
+      deg = 0;
+    }
     cnt = K == 0 ? deg : (replace ? (deg == 0 ? 0 : K) : (deg < K ? deg : K));
     if (x.start) { x.start[slot] = st; x.deg[slot] = deg > 0xFFFFFFFFll ? 0xFFFFFFFFu : (u32)deg; }
     listed = x.list && cnt > 0 && deg >= x.list_min_deg;
@@ -64,13 +71,13 @@ size_t count_workspace_bytes(i64 S_max) {
   return 256 + (size_t)((S_max + SLICE_THREADS - 1) / SLICE_THREADS + 1) * sizeof(u64);
 }
 
-int launch_count(const i64* indptr, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
+int launch_count(const i64* indptr, i64 num_cols, const i64* seeds, i64 S_max, const i64* d_S, i64 K,
                  int replace, i64* sub_indptr, i64* d_total, void* workspace, int* d_err,
                  cudaStream_t st, const CountExtra& extra) {
   const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, SLICE_THREADS);
   GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
   LaunchScope ls(KID_COUNT, st);
-  count_kernel<<<tiles, SLICE_THREADS, 0, st>>>(indptr, seeds, S_max, d_S, K, replace, sub_indptr,
+  count_kernel<<<tiles, SLICE_THREADS, 0, st>>>(indptr, num_cols, seeds, S_max, d_S, K, replace, sub_indptr,
                                                 d_total, (u64*)((char*)workspace + 256),
                                                 (int*)workspace, d_err, extra);
   GSB_CUDA_OK(cudaGetLastError());
@@ -200,7 +207,7 @@ extern "C" int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nn
   if (nnz == 0) return GSB_OK;
   if (!indptr || !out || nseg <= 0 || nnz < 0) return GSB_ERR_INVALID;
   i64 blocks = (nnz + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > sm_count() * 32) blocks = sm_count() * 32;
   LaunchScope ls(KID_EXPAND, (cudaStream_t)cuda_stream);
   expand_indptr_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)indptr, nseg, nnz, (i64*)out);
@@ -212,7 +219,7 @@ extern "C" int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t 
                                       int64_t* indptr, void* cuda_stream) {
   if (!indptr || nkeys < 0 || nnz < 0 || (nnz > 0 && !keys)) return GSB_ERR_INVALID;
   i64 blocks = (nkeys + 1 + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > sm_count() * 32) blocks = sm_count() * 32;
   LaunchScope ls(KID_INDPTR_SORTED, (cudaStream_t)cuda_stream);
   indptr_from_sorted_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)keys, nnz, nkeys, (i64*)indptr);
@@ -225,12 +232,12 @@ extern "C" size_t gsb_slice_cols_workspace_bytes(int64_t S) {
   return count_workspace_bytes(S);
 }
 
-extern "C" int gsb_slice_cols_count(const int64_t* indptr, const int64_t* seeds, int64_t S,
-                                    int64_t* sub_indptr, void* workspace, size_t workspace_bytes,
-                                    int* d_err, void* cuda_stream) {
-  if (!indptr || !sub_indptr || S < 0 || (S > 0 && !seeds)) return GSB_ERR_INVALID;
+extern "C" int gsb_slice_cols_count(const int64_t* indptr, int64_t num_cols, const int64_t* seeds,
+                                    int64_t S, int64_t* sub_indptr, void* workspace,
+                                    size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (!indptr || !sub_indptr || S < 0 || num_cols < 0 || (S > 0 && !seeds)) return GSB_ERR_INVALID;
   if (!workspace || workspace_bytes < gsb_slice_cols_workspace_bytes(S)) return GSB_ERR_WORKSPACE;
-  return launch_count((const i64*)indptr, (const i64*)seeds, S, nullptr, 0, 0, (i64*)sub_indptr,
+  return launch_count((const i64*)indptr, num_cols, (const i64*)seeds, S, nullptr, 0, 0, (i64*)sub_indptr,
                       nullptr, workspace, d_err, (cudaStream_t)cuda_stream);
 }
 
@@ -245,7 +252,7 @@ extern "C" int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, i
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   i64 blocks = (E + SF_TILE - 1) / SF_TILE;
-  if (blocks > 148 * 64) blocks = 148 * 64;
+  if (blocks > sm_count() * 64) blocks = sm_count() * 64;
   LaunchScope ls(KID_SLICE_FILL, st);
   if (indices_dtype == GSB_I32)
     slice_fill_kernel<int><<<(int)blocks, SLICE_THREADS, 0, st>>>(
@@ -264,7 +271,7 @@ extern "C" int gsb_gather_i64(const int64_t* src, const int64_t* idx, int64_t n,
   if (n == 0) return GSB_OK;
   if (!src || !idx || !out || n < 0) return GSB_ERR_INVALID;
   i64 blocks = (n + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > sm_count() * 32) blocks = sm_count() * 32;
   LaunchScope ls(KID_GATHER, (cudaStream_t)cuda_stream);
   gather_i64_kernel<<<(int)blocks, 256, 0, (cudaStream_t)cuda_stream>>>(
       (const i64*)src, (const i64*)idx, n, (i64*)out);
@@ -277,7 +284,7 @@ static void launch_gather_rows(const void* src, i64 row_bytes, i64 src_rows, con
                                void* out, int* d_err, cudaStream_t st) {
   const i64 cpr = row_bytes / (i64)sizeof(VecT);
   i64 blocks = (n * cpr + 255) / 256;
-  if (blocks > 148 * 32) blocks = 148 * 32;
+  if (blocks > sm_count() * 32) blocks = sm_count() * 32;
   gather_rows_kernel<VecT><<<(int)blocks, 256, 0, st>>>((const VecT*)src, cpr, src_rows, idx, n,
                                                         (VecT*)out, d_err);
 }

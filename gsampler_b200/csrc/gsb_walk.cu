@@ -31,6 +31,9 @@ random_walk_kernel(const i64* __restrict__ indptr, const void* __restrict__ indi
         const i64 st = __ldg(indptr + cur);
         const i64 deg = __ldg(indptr + cur + 1) - st;
         if (deg > 0) pick = load_index<IndexT>(indices, st + (i64)__umulhi(rng.next(), (u32)deg));
+        // a row id that is not a column (more rows than columns) ends the walk instead of
+        // indexing the offsets out of bounds
+        if (pick >= num_nodes) { raise(err, ERRBIT_BAD_INPUT); pick = -1; }
       }
       out[(i64)(s + 1) * N + w] = pick;
       cur = pick;
@@ -103,6 +106,7 @@ node2vec_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices
           }
           if (pick < 0) raise(err, ERRBIT_LOOKBACK_TIMEOUT);
         }
+        if (pick >= num_nodes) { raise(err, ERRBIT_BAD_INPUT); pick = -1; }
       }
       out[(i64)(s + 1) * N + w] = pick;
       last = cur;
@@ -113,7 +117,7 @@ node2vec_kernel(const i64* __restrict__ indptr, const void* __restrict__ indices
 
 static int walk_grid(i64 N) {
   i64 blocks = (N + WALK_THREADS - 1) / WALK_THREADS;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > sm_count() * 16) blocks = sm_count() * 16;
   return blocks < 1 ? 1 : (int)blocks;
 }
 

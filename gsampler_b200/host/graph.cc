@@ -56,6 +56,17 @@ static void CheckGraphIndptr(const torch::Tensor& t, const char* name) {
   TORCH_CHECK(t.is_contiguous(), name, " must be contiguous");
 }
 
+// Checked once at load time (one synchronisation): the offsets start at 0, never decrease, end at
+// the number of entries and have one entry per segment plus one -- what every kernel relies on.
+static void CheckOffsets(const torch::Tensor& indptr, int64_t nseg, int64_t nnz, const char* what) {
+  TORCH_CHECK(indptr.numel() == nseg + 1, what, ": indptr has ", indptr.numel(), " entries, the graph has ",
+              nseg, " segments (expected ", nseg + 1, ")");
+  const bool ok = nseg == 0 ? indptr[0].item<int64_t>() == nnz
+                            : (indptr[0].item<int64_t>() == 0 && indptr[nseg].item<int64_t>() == nnz &&
+                               (indptr.narrow(0, 1, nseg) >= indptr.narrow(0, 0, nseg)).all().item<bool>());
+  TORCH_CHECK(ok, what, ": indptr must start at 0, be non-decreasing and end at the number of entries (", nnz, ")");
+}
+
 static int IndicesDtype(const torch::Tensor& indices) {
   TORCH_CHECK((indices.is_cuda() || indices.is_pinned()) && indices.is_contiguous(),
               "indices must be contiguous, on a GPU or in pinned host memory");
@@ -86,12 +97,14 @@ static torch::Tensor AsI64(const torch::Tensor& t) {
 void Graph::LoadCSC(torch::Tensor indptr, torch::Tensor indices) {
   CheckGraphIndptr(indptr, "indptr");
   IndicesDtype(indices);
+  CheckOffsets(indptr, num_cols_, indices.numel(), "LoadCSC");
   csc_ = std::make_shared<Compressed>(Compressed{indptr, indices, c10::nullopt});
   num_edges_ = indices.numel();
 }
 void Graph::LoadCSR(torch::Tensor indptr, torch::Tensor indices) {
   CheckGraphIndptr(indptr, "indptr");
   IndicesDtype(indices);
+  CheckOffsets(indptr, num_rows_, indices.numel(), "LoadCSR");
   csr_ = std::make_shared<Compressed>(Compressed{indptr, indices, c10::nullopt});
   num_edges_ = indices.numel();
 }
@@ -215,7 +228,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sa
     auto ws = NewWorkspace(gsb_sample_cols_probs_workspace_bytes(S, fanout), ComputeDevice(src.indptr));
     CheckStatus(gsb_sample_cols_probs(
                     P(src.indptr), src.indices.data_ptr(), IndicesDtype(src.indices),
-                    pr.data_ptr<float>(), seeds.has_value() ? P(seeds.value()) : nullptr, S, nullptr,
+                    src.indptr.numel() - 1, pr.data_ptr<float>(), seeds.has_value() ? P(seeds.value()) : nullptr, S, nullptr,
                     fanout, replace, seed_, stream, PM(sub_indptr), PM(rows), PM(cols), PM(sel),
                     E_cap, PM(scal), ws.data_ptr(), (size_t)ws.numel(),
                     (int*)(PM(scal) + 1), CurrentStream()),
@@ -223,7 +236,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sa
   } else {
     auto ws = NewWorkspace(gsb_sample_cols_workspace_bytes(S, fanout), ComputeDevice(src.indptr));
     CheckStatus(gsb_sample_cols(P(src.indptr), src.indices.data_ptr(), IndicesDtype(src.indices),
-                                seeds.has_value() ? P(seeds.value()) : nullptr, S, nullptr, fanout,
+                                src.indptr.numel() - 1, seeds.has_value() ? P(seeds.value()) : nullptr, S, nullptr, fanout,
                                 replace, seed_, stream, PM(sub_indptr), PM(rows), PM(cols), PM(sel),
                                 E_cap, PM(scal), ws.data_ptr(), (size_t)ws.numel(),
                                 (int*)(PM(scal) + 1), CurrentStream()),
@@ -245,7 +258,7 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> Graph::Sl
   auto sub_indptr = torch::empty({S + 1}, opt);
   auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(seeds.device()));
   auto ws = NewWorkspace(gsb_slice_cols_workspace_bytes(S), seeds.device());
-  CheckStatus(gsb_slice_cols_count(P(src.indptr), P(seeds), S, PM(sub_indptr), ws.data_ptr(),
+  CheckStatus(gsb_slice_cols_count(P(src.indptr), src.indptr.numel() - 1, P(seeds), S, PM(sub_indptr), ws.data_ptr(),
                                    (size_t)ws.numel(), err.data_ptr<int>(), CurrentStream()),
               "slice_cols_count");
   const int64_t E = sub_indptr.narrow(0, S, 1).item<int64_t>();  // sizes the outputs

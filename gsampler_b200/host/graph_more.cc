@@ -79,7 +79,7 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGEAsync(torch::Tensor seeds, torch
   counts.zero_();
   void* ws = arena.data_ptr<int64_t>() + total_words;
   const int dtype = csc_->indices.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
-  CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype,
+  CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype, num_cols_,
                                    std::max(num_rows_, num_cols_), P(seeds),
                                    P(seeds_ptr), B, S0, L, fanouts.data(), GetSeedU64(),
                                    bufs.data(), counts.data_ptr<int64_t>(), ws, ws_bytes,
@@ -224,19 +224,23 @@ Graph::GraphAndIndex Graph::Compact(int64_t axis) {
   return {ret, frontiers};
 }
 
+static torch::Tensor& AsyncErrorWord(const torch::Device& dev);
+
 // ------------------------------------------------------------------ walks
 // src/graph.cc:310-317.  The buffer is step-major [(L+1), N]; like the
 // reference it is returned REINTERPRETED as [N, L+1] (a reshape, no transpose).
+// The calls do not synchronise: a start node or row id that is not a column, or a rejection loop
+// that ran out, ends the walk with -1 and raises a bit in the per-device word that
+// _CAPI_CheckAsyncErrors reports.
 torch::Tensor Graph::RandomWalk(torch::Tensor seeds, int64_t walk_length) {
   TORCH_CHECK(csc_, "RandomWalk needs the CSC format");
   c10::cuda::CUDAGuard guard(seeds.device());
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(seeds.device()));
   CheckStatus(gsb_random_walk(P(csc_->indptr), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
                               num_cols_, P(seeds), N, walk_length, seed_, NextStream(), PM(out),
-                              err.data_ptr<int>(), CurrentStream()),
+                              AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "random_walk");
   return out.reshape({N, -1});
 }
@@ -247,28 +251,32 @@ torch::Tensor Graph::Node2Vec(torch::Tensor seeds, int64_t walk_length, double p
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(seeds.device()));
   CheckStatus(gsb_node2vec(P(csc_->indptr), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
                            num_cols_, P(seeds), N, walk_length, p, q, seed_, NextStream(), PM(out),
-                           err.data_ptr<int>(), CurrentStream()),
+                           AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "node2vec");
   return out.reshape({N, -1});
 }
 
-// src/graph.cc:610-629.  Once-per-graph preprocessing: one library sort of the
-// (column, row) pairs (the reference calls CUB's segmented sort here).
+// src/graph.cc:610-629.  Once-per-graph preprocessing: every column sorted in place by this
+// library's per-segment sort (the reference calls CUB's segmented radix sort into a copy).
 void Graph::SortCSCIndices() {
   TORCH_CHECK(csc_, "SortCSCIndices needs the CSC format");
   TORCH_CHECK(!csc_->e_ids.has_value(), "SortCSCIndices: the CSC carries edge ids");
   const int64_t nnz = csc_->indices.numel();
   if (nnz == 0) return;
-  auto seg = torch::empty({nnz}, I64(csc_->indptr));
-  CheckStatus(gsb_expand_indptr(P(csc_->indptr), num_cols_, nnz, PM(seg), CurrentStream()),
-              "expand_indptr");
-  const int64_t span = std::max<int64_t>(num_rows_, 1);
-  auto key = seg * span + csc_->indices.to(torch::kInt64);
-  auto sorted = std::get<0>(key.sort());
-  csc_->indices = (sorted - seg * span).to(csc_->indices.scalar_type());
+  TORCH_CHECK(csc_->indices.is_cuda() && csc_->indptr.is_cuda(), "SortCSCIndices: the graph must be on the GPU");
+  c10::cuda::CUDAGuard guard(csc_->indices.device());
+  const int dt = IdxDtype(csc_->indices);
+  auto ws = torch::empty({(int64_t)gsb_sort_segments_workspace_bytes(num_cols_, nnz, dt)},
+                         torch::dtype(torch::kUInt8).device(csc_->indices.device()));
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(csc_->indices.device()));
+  // a graph loaded from the caller's tensors shares them: sort a private copy
+  csc_->indices = csc_->indices.clone();
+  CheckStatus(gsb_sort_segments(P(csc_->indptr), csc_->indices.data_ptr(), dt, num_cols_, nnz,
+                                ws.data_ptr(), (size_t)ws.numel(), err.data_ptr<int>(), CurrentStream()),
+              "sort_segments");
+  TORCH_CHECK(err.item<int>() == 0, "SortCSCIndices: column offsets are not monotone");
   coo_.reset();
   csr_.reset();
 }
@@ -468,11 +476,27 @@ void Graph::FusedEDivUSum(const std::string&, const std::string& reduce, OptTens
   ReduceImpl(OP_RDIV, reduce, ufeat, efeat, out, argu, arge, u_target, on_format, "FusedEDivUSum");
 }
 
-// src/graph.cc:341-356: two u-op-v edge maps over the same graph
+// src/graph.cc:341-356: two u-op-v edge maps over the same graph, one pass over the edges
 void Graph::FusedUOPV(const std::string& op, OptTensor lhs1, OptTensor rhs1, torch::Tensor out1,
                       OptTensor lhs2, OptTensor rhs2, torch::Tensor out2, int64_t on_format) {
-  SDDMM(op, lhs1, rhs1, out1, 0, 2, on_format);
-  SDDMM(op, lhs2, rhs2, out2, 0, 2, on_format);
+  if (num_edges_ <= 0) return;
+  TORCH_CHECK(on_format == kCOO || on_format == kCSC, "FusedUOPV: CSC or COO format only");
+  CreateSparseFormat(kCOO);   // the CSC flavour of the reference only differs in how it finds the endpoints
+  c10::cuda::CUDAGuard guard(out1.device());
+  const int code = OpCode(op);
+  const Feature l1 = AsFeature(lhs1, UsesLhs(code), "lhs1"), r1 = AsFeature(rhs1, UsesRhs(code), "rhs1");
+  const Feature l2 = AsFeature(lhs2, UsesLhs(code), "lhs2"), r2 = AsFeature(rhs2, UsesRhs(code), "rhs2");
+  TORCH_CHECK(l1.shape == l2.shape && r1.shape == r2.shape, "FusedUOPV: both operand pairs need equal shapes");
+  const Bcast bc = MakeBcast(l1, UsesLhs(code), r1, UsesRhs(code), out1.device());
+  for (const torch::Tensor* o : {&out1, &out2})
+    TORCH_CHECK(o->is_cuda() && o->scalar_type() == torch::kFloat32 && o->is_contiguous() &&
+                    o->numel() == num_edges_ * bc.out_len,
+                "FusedUOPV: outputs must be contiguous float32 [num_edges, ", bc.out_len, "]");
+  CheckStatus(gsb_u_op_v_pair(P(coo_->row), P(coo_->col), EidPtr(coo_->e_ids), coo_->row.numel(), code,
+                              l1.ptr, r1.ptr, out1.data_ptr<float>(), l2.ptr, r2.ptr,
+                              out2.data_ptr<float>(), l1.len, r1.len, OffPtr(bc.lhs_off),
+                              OffPtr(bc.rhs_off), bc.out_len, CurrentStream()),
+              "u_op_v_pair");
 }
 
 // {0, n} on the device (a one-segment offset array)
@@ -516,7 +540,7 @@ std::vector<torch::Tensor> Graph::LadiesLayer(torch::Tensor seeds, int64_t K, to
   auto sub_indptr = torch::empty({S + 1}, i64);
   {
     auto ws = NewWorkspace(gsb_slice_cols_workspace_bytes(S), dev);
-    CheckStatus(gsb_slice_cols_count(P(csc_->indptr), P(seeds), S, PM(sub_indptr), ws.data_ptr(),
+    CheckStatus(gsb_slice_cols_count(P(csc_->indptr), num_cols_, P(seeds), S, PM(sub_indptr), ws.data_ptr(),
                                      (size_t)ws.numel(), d_err, st),
                 "slice_cols_count");
   }
@@ -654,7 +678,6 @@ Graph::GraphAndIndex Graph::BatchColRowSlcing(torch::Tensor col, torch::Tensor c
 }
 
 // ------------------------------------------------------------------ gs_ops
-static torch::Tensor& AsyncErrorWord(const torch::Device& dev);
 
 // `single_list`: the caller built `range` = [0, R] itself, so the number of picks is known on the
 // host (min(K, R)) and nothing is read back; device-side errors go to the per-device word that
@@ -781,7 +804,7 @@ void CheckAsyncErrors() {
   auto& w = AsyncErrorWord(dev);
   const int bits = w.item<int>();
   if (bits) w.zero_();
-  CheckDeviceError(bits, "an earlier sync-free operator (row gather, single-list sampling)");
+  CheckDeviceError(bits, "an earlier sync-free operator (row gather, single-list sampling, walks)");
 }
 
 // out[i, ...] = data[index[i], ...].  `data` lives on the GPU or in page-locked

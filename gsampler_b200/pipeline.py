@@ -138,7 +138,7 @@ class GraphSAGESampler(object):
         counts = self._counts if counts_out is None else counts_out
         rc = cabi().gsb_graphsage_sample(
             C.c_void_p(self.indptr.data_ptr()), C.c_void_p(self.indices.data_ptr()), self._dtype,
-            C.c_int64(self.num_nodes), C.c_void_p(seeds.data_ptr()), C.c_void_p(seeds_ptr.data_ptr()),
+            C.c_int64(self.indptr.numel() - 1), C.c_int64(self.num_nodes), C.c_void_p(seeds.data_ptr()), C.c_void_p(seeds_ptr.data_ptr()),
             C.c_int64(self.B), C.c_int64(seeds.numel()), self.L, self._fan, C.c_uint64(self.seed),
             self._bufs, C.c_void_p(counts.data_ptr()), C.c_void_p(self._ws.data_ptr()),
             C.c_size_t(self._ws.numel()), C.c_void_p(self._err.data_ptr()),

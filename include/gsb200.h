@@ -87,7 +87,9 @@ GSB_API int gsb_timing_collect(int max_entries, const char** names, int* tags, d
  * Graph::Sampling on CSC (src/graph.cc:182-244 -> src/cuda/sampling.cu:103-172)
  * when `seeds` is NULL (column i of the operand is column slot i).
  *
- *  indptr[ncols+1] int64, indices[nnz] (int32|int64), device.
+ *  indptr[num_cols+1] int64, indices[nnz] (int32|int64), device.  A seed outside
+ *  [0, num_cols), or a column whose offsets decrease, sets GSB_ERRBIT_BAD_INPUT
+ *  and counts as an empty column; `indptr` is not read for it.
  *  seeds[S_max] int64 device or NULL.  d_S: optional device int64 holding the
  *  live number of column slots (<= S_max); NULL means S_max.
  *  K fanout (1..8192).  replace: 0 = min(deg,K) distinct edges per column,
@@ -101,7 +103,8 @@ GSB_API int gsb_timing_collect(int max_entries, const char** names, int* tags, d
  */
 GSB_API size_t gsb_sample_cols_workspace_bytes(int64_t S_max, int64_t K);
 GSB_API int gsb_sample_cols(const int64_t* indptr, const void* indices, int indices_dtype,
-                            const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K,
+                            int64_t num_cols, const int64_t* seeds, int64_t S_max,
+                            const int64_t* d_S, int64_t K,
                             int replace, uint64_t seed, uint32_t stream, int64_t* sub_indptr,
                             int64_t* out_rows, int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
                             int64_t* d_num_edges, void* workspace, size_t workspace_bytes,
@@ -117,9 +120,10 @@ GSB_API int gsb_sample_cols(const int64_t* indptr, const void* indices, int indi
  * inside the library, 512 KB + 264 B per GPU that loads it, so the call accepts
  * at most gsb_sample_cols_noalloc_max_columns(K) column slots (65 536 tiles:
  * 16 777 216 slots for K <= 32) and returns GSB_ERR_SCRATCH_LIMIT beyond that.
- * The first call on each device looks up the array's device address (the
- * device must be current); make that first call before starting any stream
- * capture.  All calls on a device share the one array: it still holds the
+ * The first call on each device looks up the array's device address; make that
+ * first call before starting any stream capture.  On EVERY call the device that
+ * owns `cuda_stream` and the buffers must be the calling thread's current
+ * device: the array is chosen by cudaGetDevice().  All calls on a device share the one array: it still holds the
  * previous call's words when a call starts (the used part is zeroed on the
  * stream before the launch), and two calls that overlap on the GPU -- different
  * streams, or a second host thread -- race on it.  Same arguments and results
@@ -127,7 +131,8 @@ GSB_API int gsb_sample_cols(const int64_t* indptr, const void* indices, int indi
  * routine is called while launch timing (gsb_timing_enable) is off. */
 GSB_API int64_t gsb_sample_cols_noalloc_max_columns(int64_t K);
 GSB_API int gsb_sample_cols_noalloc(const int64_t* indptr, const void* indices, int indices_dtype,
-                                    const int64_t* seeds, int64_t S_max, const int64_t* d_S,
+                                    int64_t num_cols, const int64_t* seeds, int64_t S_max,
+                                    const int64_t* d_S,
                                     int64_t K, int replace, uint64_t seed, uint32_t stream,
                                     int64_t* sub_indptr, int64_t* out_rows, int64_t* out_cols,
                                     int64_t* out_sel, int64_t E_cap, int64_t* d_num_edges,
@@ -139,7 +144,8 @@ GSB_API int gsb_sample_cols_noalloc(const int64_t* indptr, const void* indices, 
  * with `indices`.  Same outputs as gsb_sample_cols.  K <= 1024. */
 GSB_API size_t gsb_sample_cols_probs_workspace_bytes(int64_t S_max, int64_t K);
 GSB_API int gsb_sample_cols_probs(const int64_t* indptr, const void* indices, int indices_dtype,
-                                  const float* probs, const int64_t* seeds, int64_t S_max,
+                                  int64_t num_cols, const float* probs, const int64_t* seeds,
+                                  int64_t S_max,
                                   const int64_t* d_S, int64_t K, int replace, uint64_t seed,
                                   uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
                                   int64_t* out_cols, int64_t* out_sel, int64_t E_cap,
@@ -151,14 +157,15 @@ GSB_API int gsb_sample_cols_probs(const int64_t* indptr, const void* indices, in
  * Graph::BatchColSlicing (src/graph.cc:90-179, src/batch_graph.cc:13-104 ->
  * src/cuda/slicing.cu:121-181, src/cuda/batch/slicing.cu:40-120).
  * Two calls because the edge count sizes the outputs:
- *   count: sub_indptr[S+1] = exclusive scan of the seeds' degrees.
+ *   count: sub_indptr[S+1] = exclusive scan of the seeds' degrees (a seed outside
+ *          [0, num_cols) sets GSB_ERRBIT_BAD_INPUT and counts as an empty column).
  *   fill : out_rows/out_cols/out_sel[E] with E = sub_indptr[S] (host value).
  * col_bptr[B+1] + encoding_size > 0 add b*encoding_size to the row ids of
  * minibatch b (the reference's `encoding` mode); pass NULL/0 otherwise. */
 GSB_API size_t gsb_slice_cols_workspace_bytes(int64_t S);
-GSB_API int gsb_slice_cols_count(const int64_t* indptr, const int64_t* seeds, int64_t S,
-                                 int64_t* sub_indptr, void* workspace, size_t workspace_bytes,
-                                 int* d_err, void* cuda_stream);
+GSB_API int gsb_slice_cols_count(const int64_t* indptr, int64_t num_cols, const int64_t* seeds,
+                                 int64_t S, int64_t* sub_indptr, void* workspace,
+                                 size_t workspace_bytes, int* d_err, void* cuda_stream);
 GSB_API int gsb_slice_cols_fill(const int64_t* indptr, const void* indices, int indices_dtype,
                                 const int64_t* seeds, int64_t S, const int64_t* sub_indptr,
                                 int64_t E, int64_t* out_rows, int64_t* out_cols, int64_t* out_sel,
@@ -217,6 +224,17 @@ GSB_API int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nnz, 
  * col_sorted branch of COO2CSCCUDA (src/cuda/format_transform.cu:121-142). */
 GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nkeys,
                                    int64_t* indptr, void* cuda_stream);
+
+/* ------------------------------------------------------------------ per-segment sort
+ * Sorts the ids of every segment of a CSC / CSR ascending, in place (node2vec's membership
+ * search needs sorted columns).  Replaces SortIndicesCUDA (src/cuda/sort_indices.cu:11-37, one
+ * CUB segmented radix sort) and SortIndicesCPU (src/cpu/sort_indices.cc:27-48), reached from
+ * Graph::SortCSCIndices (src/graph.cc:610-629).  nnz bounds indptr[nseg]; the workspace holds two
+ * work lists and a scratch copy used by segments above 4096 entries only. */
+GSB_API size_t gsb_sort_segments_workspace_bytes(int64_t nseg, int64_t nnz, int indices_dtype);
+GSB_API int gsb_sort_segments(const int64_t* indptr, void* indices, int indices_dtype, int64_t nseg,
+                              int64_t nnz, void* workspace, size_t workspace_bytes, int* d_err,
+                              void* cuda_stream);
 
 /* ------------------------------------------------------------------ slicing across
  * Keep the entries of a CSC (CSR) whose row (column) id is in `ids[R]`, each
@@ -311,6 +329,16 @@ GSB_API int gsb_sddmm_coo_dot(const int64_t* row, const int64_t* col, const int6
                               const int64_t* lhs_off, const int64_t* rhs_off, int64_t reduce,
                               float* out, int64_t out_len, void* cuda_stream);
 
+/* Two u-op-v edge maps over one COO in one pass: out1[eid, :] = op(lhs1[row, :], rhs1[col, :]) and
+ * out2[eid, :] = op(lhs2[row, :], rhs2[col, :]); both pairs share shapes and broadcast tables.
+ * Replaces FUSED_COO_U_OP_V / FUSED_CSC_U_OP_V (src/cuda/fusion/fused_coo_u_op_v.cu:21-137,
+ * src/cuda/fusion/fused_csc_u_op_v.cu:21-150), reached from Graph::FusedUOPV (src/graph.cc:341-356). */
+GSB_API int gsb_u_op_v_pair(const int64_t* row, const int64_t* col, const int64_t* e_ids,
+                            int64_t nnz, int op, const float* lhs1, const float* rhs1, float* out1,
+                            const float* lhs2, const float* rhs2, float* out2, int64_t lhs_len,
+                            int64_t rhs_len, const int64_t* lhs_off, const int64_t* rhs_off,
+                            int64_t out_len, void* cuda_stream);
+
 /* ------------------------------------------------------------------ collective sampling
  * gsb_list_sample: for every segment [range[b], range[b+1]) choose min(K, len)
  * candidates without replacement -- uniformly (probs NULL) or with weights
@@ -366,6 +394,9 @@ GSB_API int gsb_node2vec(const int64_t* indptr, const void* indices, int indices
  * .. 3*l+2] = {S_l, E_l, U_l}.  S0 is an upper bound of the seed count; the
  * live count is seeds_ptr[B], read on the device, so the same launch sequence
  * (e.g. a recorded CUDA graph) serves shorter super-batches too.
+ * num_cols = columns of the graph (every layer's seeds are checked against it:
+ * on a graph with more rows than columns a sampled row id may not be a valid
+ * column); id_bound = exclusive bound of the row ids, for the relabel stage.
  */
 typedef struct {
   int64_t S_cap, E_cap;   /* capacities in elements: seeds / edges of this layer      */
@@ -384,7 +415,8 @@ GSB_API size_t gsb_graphsage_workspace_bytes(int64_t B, int num_layers,
                                              const gsb_layer_buffers* layers,
                                              const int64_t* fanouts);
 GSB_API int gsb_graphsage_sample(const int64_t* indptr, const void* indices, int indices_dtype,
-                                 int64_t id_bound, const int64_t* seeds, const int64_t* seeds_ptr,
+                                 int64_t num_cols, int64_t id_bound, const int64_t* seeds,
+                                 const int64_t* seeds_ptr,
                                  int64_t B, int64_t S0, int num_layers, const int64_t* fanouts,
                                  uint64_t seed, const gsb_layer_buffers* layers,
                                  int64_t* d_counts, void* workspace, size_t workspace_bytes,

@@ -27,15 +27,47 @@ SOURCES = [
     "src/cuda/fusion/node2vec.cu", "src/cuda/fusion/column_row_slicing.cu",
     "src/cuda/sampling_probs.cu", "src/cuda/list_sampling.cu", "src/cuda/list_sampling_probs.cu",
     "src/cuda/batch/list_sampling_probs.cu", "src/cuda/spmm.cu", "src/cuda/sddmm.cu", "src/bcast.cc",
+    "src/cuda/sort_indices.cu", "src/cuda/fusion/fused_coo_u_op_v.cu", "src/cuda/fusion/fused_csc_u_op_v.cu",
+    "src/cuda/fusion/fused_coo_e_square_sum.cu", "src/cuda/fusion/fused_csc_e_square_sum.cu",
+    "src/cuda/fusion/fused_coo_e_div_u_sum.cu", "src/cuda/fusion/fused_csc_e_div_u_sum.cu",
 ]
+
+
+def reference_dir():
+    """The gSampler source tree: $GSAMPLER_REFERENCE, else a checkout named ``reference`` beside
+    this repository; None when neither exists."""
+    cand = os.environ.get("GSAMPLER_REFERENCE") or os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")
+    return cand if os.path.isdir(os.path.join(cand, "src", "cuda")) else None
+
+
+def python_dir():
+    """Where stage_python() puts the reference's Python package."""
+    return os.path.join(OUT, "python")
+
+
+def stage_python(reference=None):
+    """Copies the reference's own Python layer (python/gs: Matrix, BatchMatrix, gs.jit.compile with
+    its fx tracer and passes, gs.ops) UNMODIFIED into oracle/_ref/python/gs, next to gs_ref.so and
+    with the same standing: made by this recipe, git-ignored, test infrastructure only.  The tests
+    import it over this repository's libraries to check that it runs on them as it stands."""
+    reference = reference or reference_dir()
+    src = os.path.join(reference or "", "python", "gs")
+    if not os.path.isdir(src):
+        return None
+    dst = os.path.join(python_dir(), "gs")
+    if os.path.isdir(dst):
+        shutil.rmtree(dst)
+    shutil.copytree(src, dst, ignore=shutil.ignore_patterns("__pycache__", "*.so"))
+    return dst
 
 
 def lib_path():
     return os.path.join(OUT, "gs_ref.so")
 
 
-def build(reference="/root/reference", jobs=None, verbose=True):
-    if not os.path.isdir(os.path.join(reference, "src", "cuda")):
+def build(reference=None, jobs=None, verbose=True):
+    reference = reference or reference_dir()
+    if not reference or not os.path.isdir(os.path.join(reference, "src", "cuda")):
         return None
     nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
     if not os.path.exists(nvcc):
@@ -96,7 +128,8 @@ def load():
 
 if __name__ == "__main__":
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=None)
     ap.add_argument("--jobs", type=int, default=None)
     a = ap.parse_args()
+    print(stage_python(a.reference))
     print(build(a.reference, a.jobs))

@@ -7,6 +7,12 @@
 
 #include "cuda/batch/batch_ops.h"
 #include "cuda/fusion/column_row_slicing.h"
+#include "cuda/fusion/fused_coo_e_div_u_sum.h"
+#include "cuda/fusion/fused_coo_e_square_sum.h"
+#include "cuda/fusion/fused_coo_u_op_v.h"
+#include "cuda/fusion/fused_csc_e_div_u_sum.h"
+#include "cuda/fusion/fused_csc_e_square_sum.h"
+#include "cuda/fusion/fused_csc_u_op_v.h"
 #include "cuda/fusion/node2vec.h"
 #include "cuda/fusion/random_walk.h"
 #include "cuda/fusion/slice_sampling.h"
@@ -39,6 +45,45 @@ static void sddmm_coo(const std::string& op, torch::Tensor row, torch::Tensor co
   ri::SDDMMCOO(op, gs::CalcBcastOff(op, lhs, rhs), coo, lhs, rhs, out, (int)lhs_target, (int)rhs_target);
 }
 
+// The fused edge operators as Graph::FusedUOPV / FusedESquareSum / FusedEDivUSum call them
+// (src/graph.cc:341-356,457-503).
+static void fused_u_op_v_coo(const std::string& op, torch::Tensor row, torch::Tensor col, torch::Tensor lhs1,
+                             torch::Tensor rhs1, torch::Tensor out1, torch::Tensor lhs2, torch::Tensor rhs2,
+                             torch::Tensor out2) {
+  auto coo = std::make_shared<gs::COO>(gs::COO{row, col, torch::nullopt, false, false});
+  ri::fusion::FUSED_COO_U_OP_V(op, gs::CalcBcastOff(op, lhs1, rhs1), coo, lhs1, rhs1, out1, lhs2, rhs2, out2);
+}
+static void fused_u_op_v_csc(const std::string& op, torch::Tensor indptr, torch::Tensor indices,
+                             torch::Tensor lhs1, torch::Tensor rhs1, torch::Tensor out1, torch::Tensor lhs2,
+                             torch::Tensor rhs2, torch::Tensor out2) {
+  auto csc = std::make_shared<gs::CSC>(gs::CSC{indptr, indices, torch::nullopt});
+  ri::fusion::FUSED_CSC_U_OP_V(op, gs::CalcBcastOff(op, lhs1, rhs1), csc, lhs1, rhs1, out1, lhs2, rhs2, out2);
+}
+static void e_square_sum_csc(const std::string& op, const std::string& reduce, torch::Tensor indptr,
+                             torch::Tensor indices, torch::Tensor ufeat, torch::Tensor efeat, torch::Tensor out,
+                             torch::Tensor argu, torch::Tensor arge) {
+  auto csc = std::make_shared<gs::CSC>(gs::CSC{indptr, indices, torch::nullopt});
+  ri::fusion::ESquareSumCSC(op, reduce, gs::CalcBcastOff(op, ufeat, efeat), csc, ufeat, efeat, out, {argu, arge});
+}
+static void e_square_sum_coo(const std::string& op, const std::string& reduce, torch::Tensor row,
+                             torch::Tensor col, torch::Tensor ufeat, torch::Tensor efeat, torch::Tensor out,
+                             torch::Tensor argu, torch::Tensor arge) {
+  auto coo = std::make_shared<gs::COO>(gs::COO{row, col, torch::nullopt, false, false});
+  ri::fusion::ESquareSumCOO(op, reduce, gs::CalcBcastOff(op, ufeat, efeat), coo, ufeat, efeat, out, {argu, arge});
+}
+static void e_div_u_sum_csc(const std::string& op, const std::string& reduce, torch::Tensor indptr,
+                            torch::Tensor indices, torch::Tensor ufeat, torch::Tensor efeat, torch::Tensor out,
+                            torch::Tensor argu, torch::Tensor arge) {
+  auto csc = std::make_shared<gs::CSC>(gs::CSC{indptr, indices, torch::nullopt});
+  ri::fusion::EDivUSumCSC(op, reduce, gs::CalcBcastOff(op, ufeat, efeat), csc, ufeat, efeat, out, {argu, arge});
+}
+static void e_div_u_sum_coo(const std::string& op, const std::string& reduce, torch::Tensor row,
+                            torch::Tensor col, torch::Tensor ufeat, torch::Tensor efeat, torch::Tensor out,
+                            torch::Tensor argu, torch::Tensor arge) {
+  auto coo = std::make_shared<gs::COO>(gs::COO{row, col, torch::nullopt, false, false});
+  ri::fusion::EDivUSumCOO(op, reduce, gs::CalcBcastOff(op, ufeat, efeat), coo, ufeat, efeat, out, {argu, arge});
+}
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("slice_cols", &ri::OnIndptrSlicingCUDA);                         // src/cuda/slicing.cu:100-181
   m.def("slice_rows_on_indices", &ri::OnIndicesSlicingCUDA);             // src/cuda/slicing.cu:184-308
@@ -59,4 +104,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("spmm_csc", &spmm_csc);                                           // src/cuda/spmm.cu:253-348
   m.def("spmm_coo", &spmm_coo);                                           // src/cuda/spmm.cu:170-250
   m.def("sddmm_coo", &sddmm_coo);                                         // src/cuda/sddmm.cu:120-200
+  m.def("sort_indices", &ri::SortIndicesCUDA);                            // src/cuda/sort_indices.cu:11-37
+  m.def("fused_u_op_v_coo", &fused_u_op_v_coo);                           // src/cuda/fusion/fused_coo_u_op_v.cu:21-137
+  m.def("fused_u_op_v_csc", &fused_u_op_v_csc);                           // src/cuda/fusion/fused_csc_u_op_v.cu:21-150
+  m.def("e_square_sum_csc", &e_square_sum_csc);                           // src/cuda/fusion/fused_csc_e_square_sum.cu
+  m.def("e_square_sum_coo", &e_square_sum_coo);                           // src/cuda/fusion/fused_coo_e_square_sum.cu
+  m.def("e_div_u_sum_csc", &e_div_u_sum_csc);                             // src/cuda/fusion/fused_csc_e_div_u_sum.cu
+  m.def("e_div_u_sum_coo", &e_div_u_sum_coo);                             // src/cuda/fusion/fused_coo_e_div_u_sum.cu
 }

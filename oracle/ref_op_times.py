@@ -2,7 +2,7 @@
 tier-2 oracle ``oracle/_ref/gs_ref.so``, the reference's kernel files compiled unmodified for
 sm_100a by ``oracle/build_ref.py``) on one GPU and the same inputs.
 
-    python tests/reference_op_times.py [--reps 5] > table.json
+    python oracle/ref_op_times.py [--reps 5] > table.json
 
 Both sides run with device-resident inputs, allocate their own outputs and include their own size
 read-backs; time is CUDA-event time per call, mean of `reps` calls after 2 warm-up calls.  This

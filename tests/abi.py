@@ -57,10 +57,11 @@ def check(rc, what):
 
 # ------------------------------------------------------------------ thin call helpers
 def sample_cols(indptr, indices, seeds, K, replace, seed, stream, S=None, d_S=None, E_cap=None,
-                probs=None):
+                probs=None, num_cols=None):
     import torch
 
     dev = indptr.device
+    ncols = indptr.numel() - 1 if num_cols is None else num_cols
     S_max = int(seeds.numel() if seeds is not None else indptr.numel() - 1) if S is None else S
     E_cap = S_max * K if E_cap is None else E_cap
     o = dict(dtype=torch.int64, device=dev)
@@ -74,14 +75,14 @@ def sample_cols(indptr, indices, seeds, K, replace, seed, stream, S=None, d_S=No
     if probs is None:
         nb = L.gsb_sample_cols_workspace_bytes(i64(S_max), i64(K))
         ws = torch.empty(nb + 256, dtype=torch.uint8, device=dev)
-        rc = L.gsb_sample_cols(ptr(indptr), ptr(indices), dt, ptr(seeds), i64(S_max), ptr(d_S),
+        rc = L.gsb_sample_cols(ptr(indptr), ptr(indices), dt, i64(ncols), ptr(seeds), i64(S_max), ptr(d_S),
                                i64(K), int(replace), C.c_uint64(seed), C.c_uint32(stream), ptr(sub),
                                ptr(rows), ptr(cols), ptr(sel), i64(E_cap), ptr(scal), ptr(ws),
                                C.c_size_t(ws.numel()), ptr(err), st)
     else:
         nb = L.gsb_sample_cols_probs_workspace_bytes(i64(S_max), i64(K))
         ws = torch.empty(nb + 256, dtype=torch.uint8, device=dev)
-        rc = L.gsb_sample_cols_probs(ptr(indptr), ptr(indices), dt, ptr(probs), ptr(seeds),
+        rc = L.gsb_sample_cols_probs(ptr(indptr), ptr(indices), dt, i64(ncols), ptr(probs), ptr(seeds),
                                      i64(S_max), ptr(d_S), i64(K), int(replace), C.c_uint64(seed),
                                      C.c_uint32(stream), ptr(sub), ptr(rows), ptr(cols), ptr(sel),
                                      i64(E_cap), ptr(scal), ptr(ws), C.c_size_t(ws.numel()),
@@ -103,7 +104,7 @@ def slice_cols(indptr, indices, seeds, col_bptr=None, encoding_size=0):
     L = lib()
     st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
     ws = torch.empty(L.gsb_slice_cols_workspace_bytes(i64(S)) + 256, dtype=torch.uint8, device=dev)
-    check(L.gsb_slice_cols_count(ptr(indptr), ptr(seeds), i64(S), ptr(sub), ptr(ws),
+    check(L.gsb_slice_cols_count(ptr(indptr), i64(indptr.numel() - 1), ptr(seeds), i64(S), ptr(sub), ptr(ws),
                                  C.c_size_t(ws.numel()), ptr(err), st), "gsb_slice_cols_count")
     E = int(sub[S])
     rows, cols, sel = (torch.empty(E, **o) for _ in range(3))

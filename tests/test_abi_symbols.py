@@ -27,7 +27,7 @@ def test_library_exports_every_declared_symbol():
 def test_argument_validation_without_device():
     lib = abi.lib()
     # null pointers / bad sizes are rejected before any CUDA call
-    rc = lib.gsb_sample_cols(None, None, 1, None, abi.i64(4), None, abi.i64(2), 0,
+    rc = lib.gsb_sample_cols(None, None, 1, abi.i64(4), None, abi.i64(4), None, abi.i64(2), 0,
                              ctypes.c_uint64(0), ctypes.c_uint32(0), None, None, None, None,
                              abi.i64(8), None, None, ctypes.c_size_t(0), None, None)
     assert rc == 1

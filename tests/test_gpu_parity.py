@@ -281,3 +281,106 @@ def test_weighted_sampling_bit_exact_on_every_kernel_path(oracle, K):
     col_of = np.repeat(np.arange(seeds.size), np.diff(sub))
     assert np.all(np.diff(sel)[np.diff(col_of) == 0] > 0)
     assert np.array_equal(sel, want[3][np.lexsort((want[3], col_of))])
+
+
+def test_edge_positions_beyond_2_pow_31(oracle):
+    """A CSC with int32 row ids and more than 2^31 entries (8.8 GB): edge positions are 64-bit
+    all the way.  indices[pos] is a closed-form function of pos written in chunks, so a sampled
+    (position, row id) pair can be checked without a host copy of the graph.  Seeds whose
+    columns start above 2^31 must yield positions above 2^31, row ids equal to f(position),
+    min(deg, K) distinct positions per column, and a relabel that is bit-exact against the
+    oracle on the sampled edges; the same through the torch class and the whole-sampler call."""
+    import gsampler_b200 as gsb
+
+    deg, ncols, K = 1000, 2_200_000, 10
+    nnz = deg * ncols
+    assert nnz > 2 ** 31
+    mul, mod = 2654435761, 2_199_997          # f(pos) = (pos * mul mod 2^40) mod `mod` < ncols
+
+    def f(pos):
+        return ((pos * mul) & ((1 << 40) - 1)) % mod
+
+    indptr = torch.arange(ncols + 1, dtype=torch.int64, device="cuda") * deg
+    indices = torch.empty(nnz, dtype=torch.int32, device="cuda")
+    step = 1 << 27
+    for a in range(0, nnz, step):
+        b = min(a + step, nnz)
+        indices[a:b] = f(torch.arange(a, b, dtype=torch.int64, device="cuda")).to(torch.int32)
+    rng = np.random.default_rng(31)
+    first_high = (2 ** 31) // deg + 1                      # first column that starts above 2^31
+    seeds = np.concatenate([rng.integers(first_high, ncols, 3000), rng.integers(0, first_high, 1000),
+                            [ncols - 1, first_high - 1, first_high]]).astype(np.int64)
+    B = 4
+    sp = np.array([0, 1000, 1000, 3200, seeds.size], dtype=np.int64)
+    sub, rows, cols, sel, err = abi.sample_cols(indptr, indices, dev(seeds), K, False, seed=77, stream=1)
+    assert err == 0
+    sub_h, rows_h, cols_h, sel_h = map(host, (sub, rows, cols, sel))
+    assert np.array_equal(np.diff(sub_h), np.full(seeds.size, K))
+    assert np.array_equal(rows_h, f(sel_h))
+    col_g = seeds[cols_h]
+    assert np.all((sel_h >= col_g * deg) & (sel_h < (col_g + 1) * deg))
+    high = col_g >= first_high
+    assert high.sum() >= 3000 * K and np.all(sel_h[high] >= 2 ** 31)
+    per_col = np.sort(sel_h.reshape(seeds.size, K), axis=1)
+    assert np.all(per_col[:, 1:] != per_col[:, :-1])
+    # the counter-based draws do not depend on where the column lies: same in-column offsets
+    # as the oracle's sampler on a one-column stand-in of the same degree
+    esub, _, _, esel = oracle.sample_spec(np.array([0, deg]), np.arange(deg), np.zeros(seeds.size, np.int64),
+                                          K, False, 77, 1)
+    assert np.array_equal(sel_h - col_g * deg, esel)
+    # relabel of the sampled edges, per minibatch, against the oracle
+    ep = sub_h[sp]
+    uq, up, orow, ocol, err = abi.batch_relabel(dev(seeds), dev(sp), rows, cols, dev(ep), id_bound=ncols)
+    assert err == 0
+    euq, eup, eorow, eocol = oracle.batch_coo_relabel(seeds, sp, col_g, rows_h, ep)
+    assert np.array_equal(host(up), eup) and np.array_equal(host(uq), euq)
+    assert np.array_equal(host(orow), eorow) and np.array_equal(host(ocol), eocol)
+    # the torch class and the whole-sampler call on the same graph
+    A = gsb.Graph(ncols, ncols)
+    A._CAPI_LoadCSC(indptr, indices)
+    A._CAPI_SetSeed(3)
+    out = A._CAPI_BatchGraphSAGE(dev(seeds), dev(sp), [K, 4])
+    cur = dev(seeds)
+    for l in range(2):
+        sub2, rows2, cols2, sel2, eptr2, uq2, up2, brow2, bcol2 = out[9 * l:9 * l + 9]
+        assert torch.equal(rows2, f(sel2))
+        lo = cur[cols2] * deg
+        assert bool(((sel2 >= lo) & (sel2 < lo + deg)).all())
+        assert int((sel2 >= 2 ** 31).sum()) > 0
+        assert torch.equal(uq2[brow2 + up2[torch.bucketize(torch.arange(rows2.numel(), device="cuda"), eptr2[1:], right=True)]], rows2)
+        cur = uq2
+    del A, out, indices, indptr
+    torch.cuda.empty_cache()
+
+
+def test_out_of_range_seeds_are_reported_not_read(oracle, graph):
+    """A seed that is not a column of the graph -- negative, or at or beyond the column count --
+    sets the BAD_INPUT bit and counts as an empty column; the offsets array is not read for it,
+    so nothing faults.  The valid seeds of the same call are sampled as usual."""
+    indptr, indices = graph
+    n = indptr.size - 1
+    rng = np.random.default_rng(77)
+    good = rng.integers(0, n, 500)
+    seeds = good.copy()
+    bad_at = np.array([3, 77, 140, 499])
+    seeds[bad_at] = [n, -1, 2 ** 40, n + 12345]
+    d_ip, d_ix = dev(indptr), dev(indices)
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, dev(seeds), 6, False, seed=5, stream=2)
+    assert err & 16
+    esub, erows, ecols, esel = oracle.sample_spec(indptr, indices, good, 6, False, 5, 2)
+    cnt, ecnt = np.diff(host(sub)), np.diff(esub)
+    assert np.all(cnt[bad_at] == 0)
+    keep = np.ones(seeds.size, bool); keep[bad_at] = False
+    assert np.array_equal(cnt[keep], ecnt[keep])
+    live = ~np.isin(ecols, bad_at)                      # the oracle's edges without the bad columns
+    assert np.array_equal(host(sel), esel[live]) and np.array_equal(host(rows), erows[live])
+    assert np.array_equal(host(cols), ecols[live])
+    # the slicing count pass and the weighted sampler share the check
+    ssub, srows, scols, ssel, err = abi.slice_cols(d_ip, d_ix, dev(seeds))
+    assert err & 16 and np.all(np.diff(host(ssub))[bad_at] == 0)
+    probs = dev(rng.random(indices.size) + 0.1, torch.float32)
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, dev(seeds), 4, False, 5, 0, probs=probs)
+    assert err & 16 and np.all(np.diff(host(sub))[bad_at] == 0)
+    # a graph with fewer columns than rows: a row id that is not a column cannot be a seed
+    sub, rows, cols, sel, err = abi.sample_cols(d_ip, d_ix, dev(good), 6, False, 5, 2, num_cols=n // 2)
+    assert err & 16 and np.all(np.diff(host(sub))[good >= n // 2] == 0)

@@ -218,7 +218,14 @@ def test_spmm_sddmm_against_reference_kernels(gsb, ref, graph):
     assert np.allclose(host(m.sum("w", axis=0)), host(out)[:, 0], **tol)
     out = torch.zeros(n, 1, device="cuda")
     ref.spmm_coo("copy_rhs", "sum", ix, col, dummy, w[:, None], out, 2, aux((n, 1)), aux((n, 1)))
-    assert np.allclose(host(m.sum("w", axis=1)), host(out)[:, 0], rtol=2e-5, atol=1e-5)
+    # atomics in both implementations, so the order of the additions differs: each side is held
+    # to the fp64 sum of the same fp32 terms -- 1e-5 relative, and for rows long enough that
+    # rounding alone can exceed it the statistical bound 4 * sqrt(terms) * 2^-24
+    want64 = np.bincount(indices, weights=host(w).astype(np.float64), minlength=n)
+    terms = np.bincount(indices, minlength=n)
+    bound = np.maximum(1e-5, 4 * np.sqrt(terms) * 2.0 ** -24) * want64 + 1e-7
+    assert np.all(np.abs(host(m.sum("w", axis=1)).astype(np.float64) - want64) <= bound)
+    assert np.all(np.abs(host(out)[:, 0].astype(np.float64) - want64) <= bound)
     # vector features, broadcast, max reducer
     u = cuda(rng.random((n, 4)), torch.float32)
     e = cuda(rng.random((E, 1)), torch.float32)
@@ -307,3 +314,202 @@ def test_weighted_samplers_against_reference(gsb, ref):
     f_ref, f_ours = counts[0][keep] / counts[0].sum(), counts[1][keep] / counts[1].sum()
     tv = 0.5 * np.abs(f_ref - f_ours).sum()      # total variation distance of the two frequency vectors
     assert tv < 0.02, (fit, tv)
+
+
+@pytest.mark.parametrize("p,q", [(2.0, 0.5), (0.25, 4.0)])
+def test_node2vec_second_order_bias_against_reference(gsb, ref, p, q):
+    """The p/q bias of the second step (src/cuda/fusion/node2vec.cu:99-127): 20 000 walkers start
+    at one node v, so the step-2 candidate is judged against previous node v -- a return to v,
+    a neighbour of v, or neither.  The three class counts (overall and per intermediate node)
+    of this library and of the reference's FusedNode2VecCUDA agree (chi-square two-sample,
+    p > 0.01) and show the bias the parameters ask for."""
+    from scipy import stats
+
+    rng = np.random.default_rng(12)
+    n = 300
+    adj = rng.random((n, n)) < 0.06
+    adj = np.triu(adj, 1)
+    adj = adj | adj.T                                       # symmetric, no self-loops: triangles exist
+    deg = adj.sum(0)
+    indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
+    indices = np.concatenate([np.flatnonzero(adj[:, c]) for c in range(n)]).astype(np.int64)  # sorted columns
+    v = int(np.argmax(deg))
+    reps = 20000
+    start = cuda(np.full(reps, v))
+    ours = host(new_graph(gsb, indptr, indices, seed=41)._CAPI_Node2Vec(start, 2, p, q)).reshape(3, reps)
+    theirs = host(ref.node2vec(start, 2, cuda(indices), cuda(indptr), p, q)).reshape(3, reps)
+    nbr_v = adj[:, v]
+    tables = []
+    for tr in (ours, theirs):
+        assert np.all(tr[0] == v) and np.all(adj[tr[1], v])            # step 1 follows an edge into v's list
+        assert np.all(adj[tr[2], tr[1]])                               # and so does step 2
+        cls = np.where(tr[2] == v, 0, np.where(nbr_v[tr[2]], 1, 2))    # return / neighbour of v / other
+        tables.append(np.bincount(cls, minlength=3))
+    chi2, pval, _, _ = stats.chi2_contingency(np.stack(tables))
+    assert pval > 0.01, (tables, pval)
+    # first step: uniform over v's list on both sides
+    firsts = np.stack([np.bincount(np.searchsorted(indices[indptr[v]:indptr[v + 1]], tr[1]), minlength=deg[v])
+                       for tr in (ours, theirs)])
+    assert stats.chi2_contingency(firsts)[1] > 0.01
+    # direction of the bias: the unbiased walk returns with probability mean(1/deg(c)) over c in N(v)
+    unbiased_return = float(np.mean(1.0 / deg[indices[indptr[v]:indptr[v + 1]]]))
+    frac_return = tables[0][0] / reps
+    if p > 1:      # weight p on the return candidate (the reference accepts y < h with h = p)
+        assert frac_return > 1.3 * unbiased_return
+    else:
+        assert frac_return < 0.7 * unbiased_return
+
+
+def test_sampler_chi_square_grid_against_reference_sampler(gsb, ref):
+    """The configurations' fanouts against the reference's FusedCSCColSlicingSamplingCUDA
+    (src/cuda/fusion/slice_sampling.cu:43-96) and the exact inclusion probability K / deg: K in
+    {5, 10, 15, 25} x degree in {K+1, 2K, 50, 500}.  Degree K+1 is where Floyd's "replace by j"
+    branch and the reference's reservoir differ most."""
+    from scipy import stats
+
+    Ks = (5, 10, 15, 25)
+    degs = sorted({d for K in Ks for d in (K + 1, 2 * K, 50, 500)})
+    indptr = np.concatenate([[0], np.cumsum(degs)]).astype(np.int64)
+    indices = np.concatenate([np.arange(d) for d in degs]).astype(np.int64)
+    d_ip, d_ix = cuda(indptr), cuda(indices)
+    rows_per_block, draws = 32, 12000       # the reference repeats one draw over the 32 rows of a block
+    reps = rows_per_block * draws
+    worst = 1.0
+    for K in Ks:
+        for d in (K + 1, 2 * K, 50, 500):
+            c = degs.index(d)
+            many = cuda(np.full(reps, c))
+            _, _, r_rows, r_sel = ref.fused_slice_sample(d_ip, d_ix, K, many, False, True)
+            sub, o_sel = new_graph(gsb, indptr, indices, seed=1000 + 31 * K + d)._CAPI_SlicingSampling(
+                1, many, K, False, gsb._CSC, gsb._CSC + gsb._COO)
+            counts = []
+            for sel, stride in ((host(r_sel), rows_per_block), (host(o_sel), 1)):
+                assert sel.size == reps * K
+                per_col = sel.reshape(reps, K) - indptr[c]
+                assert per_col.min() >= 0 and per_col.max() < d
+                s = np.sort(per_col, axis=1)
+                assert np.all(s[:, 1:] != s[:, :-1])                   # K distinct edges per column
+                counts.append(np.bincount(per_col[::stride].ravel(), minlength=d).astype(float))
+            p_inc = K / d
+            for cnt in counts:                                          # each against the exact K / deg
+                m = cnt.sum() / K
+                chi2 = ((cnt - m * p_inc) ** 2 / (m * p_inc * (1 - p_inc))).sum() * (d - 1) / d
+                pv = stats.chi2.sf(chi2, d - 1)
+                worst = min(worst, pv)
+                assert pv > 0.001, (K, d, pv)
+            pv = stats.chi2_contingency(np.stack(counts))[1]           # and against each other
+            assert pv > 0.01 / 4, (K, d, pv)   # 16 cells: a per-cell bound of 0.0025 keeps the family near 0.04
+    assert worst > 1e-4
+
+
+def test_benchmark_size_super_batch_through_reference_relabel(gsb, ref):
+    """One super-batch of the benchmark's shape (32 x 1024 seeds, fanouts [15, 10, 5], the
+    2.45 M-node / 123.7 M-edge power-law graph; 23 M relabel items in the last layer): every
+    layer's sampled edges through the reference's BatchCOORelabelCUDA
+    (src/cuda/batch/batch_relabel.cu:376-499) reproduce this library's node lists, offsets and
+    relabelled COO bit for bit; the sampling invariants hold at that size."""
+    from gsampler_b200 import synth
+
+    n, nnz = 2449029, 123718280
+    indptr, indices = synth.powerlaw_csc(n, nnz, exponent=2.1, max_degree=20000, seed=2024, device="cuda")
+    g = torch.Generator()
+    g.manual_seed(7)
+    seeds = torch.randperm(n, generator=g)[:32 * 1024].cuda()
+    ptr = (torch.arange(33) * 1024).cuda()
+    A = gsb.Graph(n, n)
+    A._CAPI_LoadCSC(indptr, indices)
+    A._CAPI_SetSeed(5)
+    fanouts = [15, 10, 5]
+    out = A._CAPI_BatchGraphSAGE(seeds, ptr, fanouts)
+    cur_seeds, cur_ptr = seeds, ptr
+    for l, K in enumerate(fanouts):
+        sub, rows, cols, sel, eptr, uq, up, brow, bcol = out[9 * l:9 * l + 9]
+        deg = indptr[cur_seeds + 1] - indptr[cur_seeds]
+        assert torch.equal(sub[1:] - sub[:-1], deg.clamp_max(K))           # min(deg, K) per column
+        assert torch.equal(indices[sel], rows)                              # every edge exists ...
+        col_g = cur_seeds[cols]
+        assert bool(((sel >= indptr[col_g]) & (sel < indptr[col_g + 1])).all())   # ... in its column
+        key = cols * nnz + sel
+        assert bool((key[1:] != key[:-1]).all()) and bool((cols[1:] >= cols[:-1]).all())
+        assert torch.unique(key).numel() == key.numel()                     # no duplicate edge in a column
+        assert torch.equal(eptr, sub[cur_ptr])
+        r_uq, r_up, r_row, r_col, r_eptr = ref.batch_coo_relabel(cur_seeds, cur_ptr, col_g, rows, eptr)
+        assert torch.equal(r_up, up) and torch.equal(r_uq, uq)
+        assert torch.equal(r_row, brow) and torch.equal(r_col, bcol)
+        cur_seeds, cur_ptr = uq, up
+    assert rows.numel() > 15_000_000      # the last layer really has the benchmark's size
+    del out, indptr, indices
+    torch.cuda.empty_cache()
+
+
+@pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
+def test_sort_columns_equals_reference_and_oracle(gsb, ref, oracle, idx_dtype):
+    """Per-column sort (Graph::SortCSCIndices): bit-exact against the reference's SortIndicesCUDA
+    (src/cuda/sort_indices.cu:11-37, a CUB segmented radix sort; int64 only) and against the
+    restated SortIndicesCPU, over every kernel path: empty and one-entry columns, columns of up
+    to 256 entries (warp), up to 4096 (CTA), longer ones (range partition), a long column whose
+    ids crowd into a narrow range (the in-place network), and duplicate ids."""
+    rng = np.random.default_rng(21)
+    n = 60000
+    degs = np.concatenate([rng.integers(0, 80, 3000), [0, 1, 2, 255, 256, 257, 4095, 4096, 4097, 20000, 70000, 9000],
+                           rng.integers(200, 3000, 40)])
+    indptr = np.concatenate([[0], np.cumsum(degs)]).astype(np.int64)
+    indices = rng.integers(0, n, indptr[-1]).astype(np.int64)
+    crowded = int(np.flatnonzero(degs == 9000)[0])
+    indices[indptr[crowded]:indptr[crowded + 1]] = rng.integers(500, 520, 9000)       # 20 distinct values
+    indices[indptr[crowded]] = n - 1                                                 # ... and one far away
+    g = gsb.Graph(n, degs.size)
+    g._CAPI_LoadCSC(cuda(indptr), cuda(indices, idx_dtype))
+    g._CAPI_SortCSCIndices()
+    got = host(g._CAPI_GetCSCIndices()).astype(np.int64)
+    assert np.array_equal(got, oracle.sort_indices(indptr, indices))
+    assert np.array_equal(got, host(ref.sort_indices(cuda(indptr), cuda(indices))))
+    assert g._CAPI_GetCSCIndices().dtype == idx_dtype
+
+
+def test_fused_edge_operators_against_reference_kernels(gsb, ref, graph):
+    """The fused edge operators of the PASS / AS-GCN / LADIES samplers against the reference's own
+    fused kernels: two u-op-v maps in one pass (FUSED_COO_U_OP_V, FUSED_CSC_U_OP_V), sum of e^2
+    and sum of e / u per node (ESquareSum*, EDivUSum*); 1e-5 relative."""
+    indptr, indices = graph
+    n, E = indptr.size - 1, indices.size
+    rng = np.random.default_rng(14)
+    ip, ix = cuda(indptr), cuda(indices)
+    col = torch.repeat_interleave(torch.arange(n, device="cuda"), ip[1:] - ip[:-1])
+    A = new_graph(gsb, indptr, indices)
+    tol = dict(rtol=1e-5, atol=1e-6)
+    for shape in ((n, 1), (n, 6)):
+        u1, v1, u2, v2 = (cuda(rng.random(shape) + 0.5, torch.float32) for _ in range(4))
+        for op in ("mul", "add", "div", "sub"):
+            want1, want2 = (torch.zeros(E, shape[1], device="cuda") for _ in range(2))
+            ref.fused_u_op_v_coo(op, ix, col, u1, v1, want1, u2, v2, want2)
+            for fmt in (gsb._COO, gsb._CSC):
+                got1, got2 = (torch.full((E, shape[1]), -1.0, device="cuda") for _ in range(2))
+                A._CAPI_FusedUOPV(op, u1, v1, got1, u2, v2, got2, fmt)
+                assert np.allclose(host(got1), host(want1), **tol) and np.allclose(host(got2), host(want2), **tol)
+        wc1, wc2 = (torch.zeros(E, shape[1], device="cuda") for _ in range(2))
+        ref.fused_u_op_v_csc("mul", ip, ix, u1, v1, wc1, u2, v2, wc2)
+        g1, g2 = (torch.zeros(E, shape[1], device="cuda") for _ in range(2))
+        A._CAPI_FusedUOPV("mul", u1, v1, g1, u2, v2, g2, gsb._CSC)
+        assert np.allclose(host(g1), host(wc1), **tol) and np.allclose(host(g2), host(wc2), **tol)
+    # fused reductions (scalar edge weights, the samplers' case)
+    w = cuda(rng.random((E, 1)) + 0.05, torch.float32)
+    node = cuda(rng.random((n, 1)) + 0.5, torch.float32)
+    aux = lambda: torch.zeros(n, 1, dtype=torch.int64, device="cuda")  # noqa: E731
+    dummy = torch.zeros(1, 1, device="cuda")
+    # sums of positive fp32 terms in different orders: each side is held to the fp64 sum of the
+    # same terms (1e-5 relative; 4 * sqrt(terms) * 2^-24 where rounding alone can exceed that)
+    terms = np.diff(indptr)
+    bound = np.maximum(1e-5, 4 * np.sqrt(terms) * 2.0 ** -24)
+    col_h, w64, node64 = host(col), host(w)[:, 0].astype(np.float64), host(node)[:, 0].astype(np.float64)
+    cases = (("e_square_sum_csc", "copy_rhs", dummy, "_CAPI_FusedESquareSum", None,
+              np.bincount(col_h, weights=w64 ** 2, minlength=n)),
+             ("e_div_u_sum_csc", "div", node, "_CAPI_FusedEDivUSum", node,
+              np.bincount(col_h, weights=w64 / node64[indices], minlength=n)))
+    for ref_name, op, ref_u, our_name, our_u, want64 in cases:
+        theirs = torch.zeros(n, 1, device="cuda")
+        getattr(ref, ref_name)(op, "sum", ip, ix, ref_u, w, theirs, aux(), aux())
+        ours = torch.zeros(n, 1, device="cuda")
+        getattr(A, our_name)(op, "sum", our_u, w, ours, None, None, 0, gsb._CSC)
+        for side in (ours, theirs):
+            assert np.all(np.abs(host(side)[:, 0].astype(np.float64) - want64) <= bound * want64 + 1e-7), ref_name

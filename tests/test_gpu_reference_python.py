@@ -1,0 +1,193 @@
+"""The reference's own Python layer -- gs.Matrix, gs.BatchMatrix and gs.jit.compile with its fx
+tracer and every optimisation pass (python/gs/jit/module.py:287-304 in gSampler) -- staged
+unmodified under oracle/_ref/python and run over THIS repository's libraries (tests/ref_python.py
+says how it is bound).  The samplers are the reference's examples, restated here because the
+example files import datasets: examples/graphsage/graphsage.py:7-27 and
+examples/ladies/ladies.py:7-21.  What comes back must satisfy the sampling invariants, and the
+deterministic stages (node lists, relabelled blocks, edge weights) must equal the oracle's on the
+edges that were drawn.  Skipped when the package has not been staged."""
+from typing import List
+
+import numpy as np
+import pytest
+import torch
+
+from tests import ref_python
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def gs():
+    mod = ref_python.load()
+    if mod is None:
+        pytest.skip("oracle/_ref/python/gs not staged (python oracle/build_ref.py needs the reference tree)")
+    return mod
+
+
+@pytest.fixture(scope="module")
+def graph():
+    from gsampler_b200 import synth
+
+    return synth.rmat_csc(20000, 300000, seed=42)
+
+
+def cuda(a, dtype=torch.int64):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=dtype).cuda()
+
+
+def host(t):
+    return t.cpu().numpy()
+
+
+# --- the reference's example samplers (see the module docstring) -----------------------------
+def graphsage_sampler(A, seeds: torch.Tensor, fanouts: List):
+    input_node = seeds
+    ret = []
+    for K in fanouts:
+        subA = A[:, seeds]
+        sampleA = subA.individual_sampling(K, None, False)
+        seeds = sampleA.all_nodes()
+        ret.append(sampleA.to_dgl_block())
+    output_node = seeds
+    return input_node, output_node, ret
+
+
+def batch_graphsage_sampler(A, seeds, seeds_ptr, fanouts):
+    ret = []
+    for k in fanouts:
+        subA = A[:, seeds::seeds_ptr]
+        sampleA = subA.individual_sampling(k, None, False)
+        seeds, seeds_ptr = sampleA.all_nodes()
+        ret.append(sampleA.to_dgl_block())
+    return ret
+
+
+def ladies_sampler(A, seeds: torch.Tensor, fanouts: List):
+    input_node = seeds
+    ret = []
+    for K in fanouts:
+        subA = A[:, seeds]
+        subA.edata["p"] = subA.edata["w"]**2
+        prob = subA.sum("p", axis=1)
+        sampleA, select_index = subA.collective_sampling(K, prob, False)
+        sampleA = sampleA.div("w", prob[select_index], axis=1)
+        out = sampleA.sum("w", axis=0)
+        sampleA = sampleA.div("w", out, axis=0)
+        seeds = sampleA.all_nodes()
+        ret.append(sampleA.to_dgl_block(prefetch_edata={"w"}))
+    output_node = seeds
+    return input_node, output_node, ret
+
+
+def check_sampled_block(oracle, indptr, indices, seeds, block, K):
+    """One GraphSAGE block against its seeds: invariants of the draw, then node list and relabelled
+    COO bit-exact against the oracle's first-occurrence unique + relabel of the drawn edges."""
+    uq = host(block.srcdata["_ID"])
+    row, col = (host(t) for t in block.coo())
+    assert block.num_dst_nodes() == seeds.size and block.num_src_nodes() == uq.size
+    g_row, g_col = uq[row], seeds[col]
+    deg = indptr[seeds + 1] - indptr[seeds]
+    assert np.array_equal(np.bincount(col, minlength=seeds.size), np.minimum(deg, K))
+    key = g_col * (indptr.size - 1) + g_row
+    have = np.repeat(np.arange(indptr.size - 1), np.diff(indptr)) * (indptr.size - 1) + indices
+    assert np.all(np.isin(key, have))                                   # every edge exists
+    pair = col.astype(np.int64) * (indptr.size - 1) + g_row
+    assert np.unique(pair).size == pair.size                            # no edge drawn twice in a column
+    e_uq, e_row, e_col = oracle.relabel(seeds, g_row, col)
+    assert np.array_equal(uq, e_uq) and np.array_equal(row, e_row) and np.array_equal(col, e_col)
+    return uq
+
+
+def test_reference_python_graphsage_compile(gs, oracle, graph):
+    indptr, indices = graph
+    n = indptr.size - 1
+    m = gs.Matrix()
+    m.load_graph("CSC", [cuda(indptr), cuda(indices)])
+    seeds = np.random.default_rng(0).permutation(n)[:1024].astype(np.int64)
+    fanouts = [10, 5]
+    # eager, then compiled with the reference's defaults (compact-or-not and format selection
+    # are decided by timing both, module.py:233-262)
+    compiled = gs.jit.compile(func=graphsage_sampler, args=(m, cuda(seeds), fanouts))
+    targets = [str(nd.target) for nd in compiled.gm.graph.nodes]
+    assert "_CAPI_SlicingSampling" in targets and "_CAPI_Sampling" not in targets     # fused by the pass
+    assert "_CAPI_GetValidNodes" not in targets and targets.count("_CAPI_GraphRelabel") == len(fanouts)
+    for fn in (graphsage_sampler, compiled):
+        inp, outp, blocks = fn(m, cuda(seeds), fanouts)
+        assert np.array_equal(host(inp), seeds)
+        cur = seeds
+        for K, block in zip(fanouts, blocks):
+            cur = check_sampled_block(oracle, indptr, indices, cur, block, K)
+        assert np.array_equal(host(outp), cur)
+
+
+def test_reference_python_batch_graphsage_compile(gs, oracle, graph):
+    indptr, indices = graph
+    n = indptr.size - 1
+    m = gs.Matrix()
+    m.load_graph("CSC", [cuda(indptr), cuda(indices)])
+    bm = gs.BatchMatrix()
+    bm.load_from_matrix(m, False)
+    B, bs = 4, 256
+    seeds = np.random.default_rng(1).permutation(n)[:B * bs].astype(np.int64)
+    ptr = np.arange(B + 1, dtype=np.int64) * bs
+    fanouts = [10, 5]
+    compiled = gs.jit.compile(func=batch_graphsage_sampler, args=(bm, cuda(seeds), cuda(ptr), fanouts),
+                              try_compact=False, format_select=False)
+    targets = [str(nd.target) for nd in compiled.gm.graph.nodes]
+    assert targets.count("_CAPI_BatchFusedSlicingSampling") == len(fanouts)
+    assert "_CAPI_BatchColSlicing" not in targets and "_CAPI_BatchRowSampling" not in targets
+    for fn in (batch_graphsage_sampler, compiled):
+        layers = fn(bm, cuda(seeds), cuda(ptr), fanouts)
+        cur = [seeds[ptr[b]:ptr[b + 1]] for b in range(B)]
+        for K, blocks in zip(fanouts, layers):
+            assert len(blocks) == B
+            cur = [check_sampled_block(oracle, indptr, indices, cur[b], blocks[b], K) for b in range(B)]
+
+
+def test_reference_python_ladies_compile(gs, oracle, graph):
+    indptr, indices = graph
+    n, E = indptr.size - 1, indices.size
+    rng = np.random.default_rng(2)
+    w = (rng.random(E) + 0.05).astype(np.float32)
+    m = gs.Matrix()
+    m.load_graph("CSC", [cuda(indptr), cuda(indices)])
+    m.edata["w"] = cuda(w, torch.float32)
+    seeds = rng.permutation(n)[:256].astype(np.int64)
+    fanouts = [400, 300]
+    compiled = gs.jit.compile(func=ladies_sampler, args=(m, cuda(seeds), fanouts))
+    targets = [str(nd.target) for nd in compiled.gm.graph.nodes]
+    assert targets.count("_CAPI_FusedESquareSum") == len(fanouts)                       # the e^2 + sum pass fired
+    col_of_edge = np.repeat(np.arange(n), np.diff(indptr))
+    for fn in (ladies_sampler, compiled):
+        inp, outp, blocks = fn(m, cuda(seeds), fanouts)
+        cur = seeds
+        for K, block in zip(fanouts, blocks):
+            uq = host(block.srcdata["_ID"])
+            row, col = (host(t) for t in block.coo())
+            got_w = host(block.edata["w"])
+            g_row, g_col = uq[row], cur[col]
+            # the column slice and its row weights p = sum of w^2 per row, recomputed on the host
+            pos = np.concatenate([np.arange(indptr[c], indptr[c + 1]) for c in cur])
+            slot = np.repeat(np.arange(cur.size), indptr[cur + 1] - indptr[cur])
+            p = np.bincount(indices[pos], weights=w[pos].astype(np.float64) ** 2, minlength=n)
+            picked = np.unique(g_row)
+            assert picked.size == min(K, np.count_nonzero(p)) and np.all(p[picked] > 0)
+            keep = np.isin(indices[pos], picked)
+            # the kept edges are exactly the slice's edges on the picked rows (as a multiset of
+            # (column slot, row) pairs; the slice has no duplicate pair)
+            want_key = np.sort(slot[keep] * n + indices[pos][keep])
+            got_key = col.astype(np.int64) * n + g_row
+            order = np.argsort(got_key)
+            assert np.array_equal(got_key[order], want_key)
+            w1 = w[pos][keep].astype(np.float64) / p[indices[pos][keep]]
+            colsum = np.bincount(slot[keep], weights=w1, minlength=cur.size)
+            w2 = w1 / colsum[slot[keep]]
+            want_order = np.argsort(slot[keep] * n + indices[pos][keep])
+            # three chained fp32 stages of 1e-5 each
+            assert np.allclose(got_w[order], w2[want_order], rtol=3e-5, atol=1e-9)
+            e_uq, e_row, e_col = oracle.relabel(cur, g_row, col)
+            assert np.array_equal(uq, e_uq) and np.array_equal(row, e_row) and np.array_equal(col, e_col)
+            cur = uq
+        assert np.array_equal(host(outp), cur)
+    del col_of_edge

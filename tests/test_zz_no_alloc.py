@@ -28,8 +28,8 @@ def _noalloc(indptr, indices, seeds, K, replace, seed, stream):
     n_edges = torch.zeros(1, **o)
     err = torch.zeros(1, dtype=torch.int32, device=indptr.device)
     dt = abi.I32 if indices.dtype == torch.int32 else abi.I64
-    rc = L.gsb_sample_cols_noalloc(abi.ptr(indptr), abi.ptr(indices), dt, abi.ptr(seeds), abi.i64(S),
-                                   None, abi.i64(K), int(replace), C.c_uint64(seed),
+    rc = L.gsb_sample_cols_noalloc(abi.ptr(indptr), abi.ptr(indices), dt, abi.i64(indptr.numel() - 1),
+                                   abi.ptr(seeds), abi.i64(S), None, abi.i64(K), int(replace), C.c_uint64(seed),
                                    C.c_uint32(stream), abi.ptr(sub), abi.ptr(rows), abi.ptr(cols),
                                    abi.ptr(sel), abi.i64(S * K), abi.ptr(n_edges), abi.ptr(err),
                                    C.c_void_p(torch.cuda.current_stream().cuda_stream))
@@ -63,7 +63,7 @@ def test_noalloc_rejects_sizes_beyond_its_scratch():
     L.gsb_sample_cols_noalloc_max_columns.restype = C.c_int64
     limit = L.gsb_sample_cols_noalloc_max_columns(abi.i64(15))
     assert limit == 65536 * 256
-    rc = L.gsb_sample_cols_noalloc(None, None, 1, None, abi.i64(limit + 1), None, abi.i64(15), 0,
+    rc = L.gsb_sample_cols_noalloc(None, None, 1, abi.i64(1), None, abi.i64(limit + 1), None, abi.i64(15), 0,
                                    C.c_uint64(0), C.c_uint32(0), None, None, None, None,
                                    abi.i64(0), None, None, None)
     assert rc == 5
