@@ -1,24 +1,38 @@
 #!/usr/bin/env python
-"""Benchmark of the GraphSAGE sampling hot path.
+"""Benchmark of the sampling hot path.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--reps R] [--impl ours|reference]
+                    [--workload cfg2|cfg3|cfg4|cfg5|medium|small]
 
-Workload (default, "cfg2"): 3-layer GraphSAGE sampler, fanouts [15, 10, 5], uniform without
-replacement over in-neighbours, minibatch 1024, super-batch of 32 minibatches per step, on a
-seeded synthetic power-law graph with 2 449 029 nodes / 123 718 280 directed edges (CSC,
-int64 indptr + int64 indices resident in HBM), cycling through the 7 super-batches of one
-epoch over 196 615 training seeds.  One step = one super-batch through all layers
-(fused slice+sample, then per-minibatch unique/relabel = block construction).
+Workloads (seeded synthetic graphs with the shapes of the benchmark configurations):
 
-Prints ONE JSON line.  ``value`` is sampled edges per second over all ranks with the seeds
-already in HBM and pre-allocated outputs; ``e2e`` is the same metric through the public
-Python API with the seeds coming from pinned host memory and the per-layer sizes read back
-every step.  ``--impl reference`` times the CPU port of the reference's algorithms
-(oracle/) on the host cores for the same workload on a bounded sample.
+cfg2 (default)  3-layer GraphSAGE sampler, fanouts [15, 10, 5], uniform without replacement,
+                minibatch 1024, 32 minibatches per step, power-law graph 2 449 029 nodes /
+                123 718 280 directed edges (CSC int64 / int64), one epoch over 196 615 seeds.
+                One step = one super-batch through all layers (fused slice + sample, then
+                per-minibatch unique / relabel = block construction).  Every rank samples its
+                own epoch (weak scaling).
+cfg5            the same sampler at scale: 64 minibatches per step, 111 059 956 nodes / about
+                3.2 G directed edges, int32 indices (13.7 GB per GPU); 1 207 179 seeds split
+                evenly over the ranks (strong scaling).
+cfg3            2-layer LADIES layer-wise sampler, 4000 nodes per layer, 512 seeds, 232 965
+                nodes / 114 615 892 fp32-weighted edges.  One step = both layers.
+cfg4            node2vec walks, 1 000 000 walkers x 80 steps, p = 2, q = 0.5, on the cfg2 graph.
+                One step = one call producing the [81 x 1 000 000] trace.
+medium / small  reduced GraphSAGE shapes for profiling and functional runs.
+
+Prints ONE JSON line.  The timed region (K steps between two synchronised CUDA events, barrier on
+both sides, max over ranks) is repeated R times; ``ms_per_step`` / ``value`` are the median
+repetition, the spread is reported beside them.  ``value`` has its inputs resident in HBM and
+pre-allocated outputs; ``e2e`` goes through the public Python API with the step's inputs coming
+from pinned host memory and its result sizes read back.  ``--impl reference`` times the CPU port
+of the reference's algorithms (oracle/) on the host cores for the same workload.
 """
 from __future__ import annotations
 
 import argparse
+import gc
+import importlib.util
 import json
 import os
 import subprocess
@@ -32,25 +46,81 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # name: nodes, directed edges, train seeds, fanouts, batch, minibatches per super-batch
-    "cfg2": dict(nodes=2449029, edges=123718280, train=196615, fanouts=[15, 10, 5], batch=1024,
-                 super_batch=32, index_dtype="int64", max_degree=20000),
+    "cfg2": dict(kind="sage", nodes=2449029, edges=123718280, train=196615, fanouts=[15, 10, 5], batch=1024,
+                 super_batch=32, index_dtype="int64", max_degree=20000, scaling="weak", graph_seed=2024),
+    "cfg5": dict(kind="sage", nodes=111059956, edges=3200000000, train=1207179, fanouts=[15, 10, 5], batch=1024,
+                 super_batch=64, index_dtype="int32", max_degree=100000, scaling="strong", graph_seed=9, large=True),
     # profiling shape: graph larger than L2, a few GB on the device, short kernels
-    "medium": dict(nodes=1000000, edges=50000000, train=65536, fanouts=[15, 10, 5], batch=1024,
-                   super_batch=16, index_dtype="int64", max_degree=20000),
-    # reduced shape for quick functional runs (same pipeline, fits any GPU)
-    "small": dict(nodes=200000, edges=8000000, train=20480, fanouts=[15, 10, 5], batch=1024,
-                  super_batch=8, index_dtype="int64", max_degree=5000),
+    "medium": dict(kind="sage", nodes=1000000, edges=50000000, train=65536, fanouts=[15, 10, 5], batch=1024,
+                   super_batch=16, index_dtype="int64", max_degree=20000, scaling="weak", graph_seed=2024),
+    "small": dict(kind="sage", nodes=200000, edges=8000000, train=20480, fanouts=[15, 10, 5], batch=1024,
+                  super_batch=8, index_dtype="int64", max_degree=5000, scaling="weak", graph_seed=2024),
+    "cfg3": dict(kind="ladies", nodes=232965, edges=114615892, seeds=512, layer_nodes=4000, layers=2,
+                 index_dtype="int64", max_degree=30000, scaling="weak", graph_seed=11),
+    "cfg4": dict(kind="walk", nodes=2449029, edges=123718280, walkers=1000000, length=80, p=2.0, q=0.5,
+                 index_dtype="int64", max_degree=20000, scaling="weak", graph_seed=2024),
 }
 
+# DRAM bytes (read + write) per sampled edge, from the `ncu --set full` capture of the "medium"
+# case summarised under profiles/; the access pattern per unit is the same on the bench
+# workload, so the traffic is scaled by the units of a launch / a step.
+NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 94.3}
+NCU_PATH_DRAM_BYTES_PER_EDGE = 183.8
 
-def algorithmic_bytes(S, E, U, w_idx=8):
-    """Compulsory bytes of one GraphSAGE layer: fused slice+sample reads 8S seeds + 16S
-    offsets + w_idx*E gathered ids and writes 8(S+1) + 24E; unique/relabel reads 8S + 16E and
-    writes 8U + 16E."""
-    fss = 8 * S + 16 * S + w_idx * E + 8 * (S + 1) + 24 * E
-    brl = 8 * S + 16 * E + 8 * U + 16 * E
-    return fss, brl
+
+# ----------------------------------------------------------------------------- helpers
+def load_plain(name):
+    """gsampler_b200/<name>.py loaded as a plain file (synth, shard: they need numpy and torch only):
+    the reference arm must not load this repository's native libraries, which importing the package
+    would do."""
+    spec = importlib.util.spec_from_file_location("gsb_%s_standalone" % name, os.path.join(ROOT, "gsampler_b200", name + ".py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def load_synth():
+    return load_plain("synth")
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def make_graph(cfg, device, synth):
+    import torch
+
+    if cfg.get("large"):
+        return synth.powerlaw_csc_large(cfg["nodes"], cfg["edges"], exponent=2.1, max_degree=cfg["max_degree"],
+                                        seed=cfg["graph_seed"], device=device)
+    dt = torch.int32 if cfg["index_dtype"] == "int32" else torch.int64
+    return synth.powerlaw_csc(cfg["nodes"], cfg["edges"], exponent=2.1, max_degree=cfg["max_degree"],
+                              seed=cfg["graph_seed"], device=device, index_dtype=dt)
+
+
+def sage_seed_list(cfg, rank, world, shard):
+    """This rank's training seeds: its own epoch for a weak-scaling workload, its shard of the one
+    global seed list (``shard`` = the gsampler_b200.shard module) for a strong-scaling one."""
+    import torch
+
+    g = torch.Generator()
+    if cfg["scaling"] == "strong":
+        g.manual_seed(7)
+        seeds = torch.randperm(cfg["nodes"], generator=g)[:cfg["train"]].to(torch.int64)
+        return shard.shard_seeds(seeds, rank, world).contiguous()
+    g.manual_seed(7 + rank)
+    return torch.randperm(cfg["nodes"], generator=g)[:cfg["train"]].to(torch.int64)
+
+
+def sage_bytes(S, E, U, w_idx=8):
+    """Compulsory bytes of one GraphSAGE layer: fused slice + sample reads 8S seeds + 16S offsets +
+    w_idx * E gathered ids and writes 8(S+1) + 24E; unique / relabel reads 8S + 16E and writes
+    8U + 16E."""
+    return 8 * S + 16 * S + w_idx * E + 8 * (S + 1) + 24 * E, 8 * S + 16 * E + 8 * U + 16 * E
 
 
 class ClockSampler(threading.Thread):
@@ -98,61 +168,17 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# DRAM bytes (read + write) per sampled edge / per relabel item of one launch, from the
-# `ncu --set full` capture of the "medium" case summarised under profiles/; the access pattern
-# per unit is the same on the bench workload, so the per-launch traffic is scaled by the units.
-NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 94.3}
-# the same capture summed over all kernels and layers of one super-batch, per sampled edge
-NCU_PATH_DRAM_BYTES_PER_EDGE = 183.8
+# ----------------------------------------------------------------------------- CPU side (oracle port)
+def cpu_threads():
+    """All host cores for the OpenMP port (a launcher such as torchrun pins OMP_NUM_THREADS to 1)."""
+    n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
+    os.environ["OMP_NUM_THREADS"] = str(n)
+    return n
 
 
-def ncu_traffic(kernel, mean_edges):
-    per = NCU_DRAM_BYTES_PER_EDGE.get(kernel)
-    return None if per is None else per * mean_edges
-
-
-def load_peaks():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
-    if os.path.exists(path):
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
-    return 6650.0, "fallback"
-
-
-def make_graph(cfg, device):
-    import torch
-
-    from gsampler_b200 import synth
-
-    dt = torch.int32 if cfg["index_dtype"] == "int32" else torch.int64
-    return synth.powerlaw_csc(cfg["nodes"], cfg["edges"], exponent=2.1, max_degree=cfg["max_degree"],
-                              seed=2024, device=device, index_dtype=dt)
-
-
-def make_super_batches(cfg, rank):
-    """The epoch's super-batches for this rank: a seeded permutation of the node ids, cut into
-    minibatches of `batch` seeds, `super_batch` minibatches per step."""
-    import torch
-
-    g = torch.Generator()
-    g.manual_seed(7 + rank)
-    seeds = torch.randperm(cfg["nodes"], generator=g)[:cfg["train"]].to(torch.int64)
-    per_step = cfg["batch"] * cfg["super_batch"]
-    out = []
-    for s0 in range(0, cfg["train"], per_step):
-        chunk = seeds[s0:s0 + per_step]
-        ptr = torch.arange(0, chunk.numel() + cfg["batch"], cfg["batch"], dtype=torch.int64)
-        ptr = ptr[:(chunk.numel() + cfg["batch"] - 1) // cfg["batch"] + 1].clamp_max(chunk.numel())
-        # pad the pointer to super_batch+1 entries (trailing minibatches empty)
-        full = torch.full((cfg["super_batch"] + 1,), chunk.numel(), dtype=torch.int64)
-        full[:ptr.numel()] = ptr
-        out.append((chunk.contiguous(), full))
-    return out
-
-
-def cpu_reference_run(cfg, indptr_np, indices_np, steps, warmup, minibatches, sampler="ref"):
-    """Times the CPU port (oracle/) on `minibatches` minibatches per step.  Returns
-    (edges per second, description, cores)."""
+def cpu_sage(cfg, indptr_np, indices_np, steps, warmup, minibatches):
+    """The CPU port (reference reservoir sampler + batch relabel) on `minibatches` minibatches per
+    step.  Returns (edges/s, sample description, threads, ms per step)."""
     from oracle import gs_oracle
 
     gs_oracle.build()
@@ -163,26 +189,52 @@ def cpu_reference_run(cfg, indptr_np, indices_np, steps, warmup, minibatches, sa
     for i in range(warmup + steps):
         seeds = rng.permutation(cfg["nodes"])[:n].astype(np.int64)
         t0 = time.perf_counter()
-        layers = gs_oracle.graphsage_batch(indptr_np, indices_np, seeds, ptr, cfg["fanouts"], seed=i,
-                                           sampler=sampler)
+        layers = gs_oracle.graphsage_batch(indptr_np, indices_np, seeds, ptr, cfg["fanouts"], seed=i, sampler="ref")
         dt = time.perf_counter() - t0
         if i >= warmup:
             total_t += dt
             total_edges += sum(int(L["rows"].size) for L in layers)
-    desc = "%d steps x %d minibatches of %d seeds, %d layers, oracle %s sampler + batch relabel" % (
-        steps, minibatches, cfg["batch"], len(cfg["fanouts"]), sampler)
+    desc = "%d steps x %d minibatches of %d seeds, %d layers, oracle reference-sampler + batch relabel" % (
+        steps, minibatches, cfg["batch"], len(cfg["fanouts"]))
     return total_edges / total_t, desc, gs_oracle.num_threads(), total_t / steps * 1e3
 
 
-def cpu_sort_indices_run(indptr_np, indices_np, max_edges=20_000_000):
+def cpu_cfg1():
+    """The CPU baseline protocol on configuration 1: R-MAT 100 000 nodes / 2 000 000 edges (seed 42,
+    self-loops, no duplicates), 2 layers [25, 10], 20 minibatches x 1024 seeds of a seed-0
+    permutation; one warm-up, best of 5."""
+    from oracle import gs_oracle
+
+    synth = load_synth()
+    gs_oracle.build()
+    indptr, indices = synth.rmat_csc(100000, 2000000, seed=42)
+    seeds = np.random.default_rng(0).permutation(100000)[:20 * 1024].astype(np.int64)
+    ptr = np.arange(21, dtype=np.int64) * 1024
+    best, edges = None, 0
+    for i in range(6):
+        t0 = time.perf_counter()
+        layers = gs_oracle.graphsage_batch(indptr, indices, seeds, ptr, [25, 10], seed=i, sampler="ref")
+        dt = time.perf_counter() - t0
+        edges = sum(int(L["rows"].size) for L in layers)
+        if i >= 1:
+            best = dt if best is None else min(best, dt)
+    S = [int(L["sub_indptr"].size - 1) for L in layers]
+    E = [int(L["rows"].size) for L in layers]
+    U = [int(L["unique"].size) for L in layers]
+    alg = sum(sum(sage_bytes(s, e, u)) for s, e, u in zip(S, E, U))
+    return {"value": edges / best, "unit": "edges/s", "cores": gs_oracle.num_threads(), "kind": "port",
+            "sample": "cfg1: R-MAT 100000 nodes / %d edges, fanouts [25, 10], 20 x 1024 seeds, 1 warm-up + best of 5"
+                      % int(indptr[-1]), "seconds": best, "algorithmic_gbs": alg / best / 1e9}
+
+
+def cpu_sort_indices(indptr_np, indices_np, max_edges=20_000_000):
     """The one CPU routine the reference owns on this path -- SortIndicesCPU, an OpenMP parallel
     for over columns with a qsort each (src/cpu/sort_indices.cc:27-48 in gSampler, the node2vec
     preprocessing of a graph kept in host memory) -- timed as restated in oracle/ on the leading
     columns of the bench graph with their row ids shuffled."""
     from oracle import gs_oracle
 
-    ncols = int(np.searchsorted(indptr_np, max_edges, side="right")) - 1
-    ncols = max(ncols, 1)
+    ncols = max(int(np.searchsorted(indptr_np, max_edges, side="right")) - 1, 1)
     ip = np.ascontiguousarray(indptr_np[:ncols + 1])
     idx = np.random.default_rng(11).permutation(indices_np[:ip[-1]])
     t0 = time.perf_counter()
@@ -190,25 +242,76 @@ def cpu_sort_indices_run(indptr_np, indices_np, max_edges=20_000_000):
     dt = time.perf_counter() - t0
     assert out.size == idx.size
     return {"what": "SortIndicesCPU algorithm (per-column qsort under OpenMP)", "columns": ncols,
-            "edges": int(ip[-1]), "seconds": dt, "edges_per_sec": float(ip[-1]) / dt,
-            "cores": gs_oracle.num_threads()}
+            "edges": int(ip[-1]), "seconds": dt, "edges_per_sec": float(ip[-1]) / dt, "cores": gs_oracle.num_threads()}
 
 
-def reference_gpu_run(cfg, indptr, indices, rank, steps, warmup):
+def cpu_ladies(cfg, indptr, indices, w, steps, warmup):
+    """LADIES layers composed from the oracle's operators (column slice, row sums of w^2, weighted
+    list sampling, row slice, the two renormalisations, relabel)."""
+    from oracle import gs_oracle as o
+
+    o.build()
+    n, K = cfg["nodes"], cfg["layer_nodes"]
+    rng = np.random.default_rng(1)
+    edges, total = 0, 0.0
+    for i in range(warmup + steps):
+        seeds = rng.permutation(n)[:cfg["seeds"]].astype(np.int64)
+        t0 = time.perf_counter()
+        step_edges = 0
+        for l in range(cfg["layers"]):
+            sip, srows, scols, ssel = o.slice_cols(indptr, indices, seeds)
+            p = o.edge_sum(srows, scols, w[ssel], 0, n, square=True)
+            sel = o.list_sample_probs_spec(p, K, seed=i, stream=l)
+            csr_ip, csr_cols, perm = o.coo2csc(srows, scols, n)
+            rip, rcols, rloc, rsel = o.slice_cols(csr_ip, csr_cols, sel)
+            ew = w[ssel][perm][rsel]
+            w1 = o.edge_op_node(rloc, ew, p[sel], "div")
+            colsum = o.edge_sum(rloc, rcols, w1, 2, seeds.size)
+            o.edge_op_node(rcols, w1, colsum, "div")
+            frontier, _, _ = o.relabel(seeds, sel[rloc], rcols)
+            step_edges += rloc.size
+            seeds = frontier
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            total += dt
+            edges += step_edges
+    return edges / total, "%d steps of the %d-layer LADIES recipe composed from the oracle's operators" % (
+        steps, cfg["layers"]), o.num_threads(), total / steps * 1e3
+
+
+def cpu_walk(cfg, indptr, indices, steps, warmup, walkers):
+    from oracle import gs_oracle as o
+
+    o.build()
+    rng = np.random.default_rng(7)
+    live, total = 0, 0.0
+    for i in range(warmup + steps):
+        seeds = rng.integers(0, cfg["nodes"], walkers).astype(np.int64)
+        t0 = time.perf_counter()
+        tr = o.node2vec_spec(indptr, indices, seeds, cfg["length"], cfg["p"], cfg["q"], seed=i)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            total += dt
+            live += int((np.asarray(tr).reshape(cfg["length"] + 1, walkers)[1:] >= 0).sum())
+    return live / total, "%d calls of %d walkers x %d steps (oracle node2vec)" % (steps, walkers, cfg["length"]), \
+        o.num_threads(), total / steps * 1e3
+
+
+def reference_gpu_sage(cfg, indptr, indices, batches, steps, warmup):
     """The reference's own CUDA kernels (oracle/_ref/gs_ref.so, built from the reference tree by
     oracle/build_ref.py) on the same super-batches on this GPU: per layer
     FusedCSCColSlicingSamplingCUDA, edge_ptr = sub_indptr[seeds_ptr], BatchCOORelabelCUDA once
     (the reference's Python pipeline runs the relabel twice per layer).  None when the file has
-    not been built."""
+    not been built or the graph is beyond its int64 / 2^31 limits."""
     import torch
 
     from oracle import build_ref
 
     ref = build_ref.load()
-    if ref is None or not indptr.is_cuda:
+    if ref is None or not indptr.is_cuda or indices.numel() >= 2 ** 31:
         return None
-    indices = indices.to(torch.int64)      # the reference's sampling path is int64 only
-    batches = [(s.to(indptr.device), p.to(indptr.device)) for s, p in make_super_batches(cfg, rank)]
+    indices = indices.to(torch.int64)
+    batches = [(s.to(indptr.device), p.to(indptr.device)) for s, p in batches]
 
     def step(seeds, ptr):
         edges = 0
@@ -236,39 +339,456 @@ def reference_gpu_run(cfg, indptr, indices, rank, steps, warmup):
 
 
 def run_reference(args, cfg, rank, world):
+    """The reference arm: rank 0 alone, all host cores, the workload's own graph, seeds and step
+    shape; this repository's native libraries are not loaded."""
     if rank != 0:
         return
     import torch
 
+    threads = cpu_threads()
+    synth = load_synth()
     device = "cuda" if torch.cuda.is_available() else "cpu"
-    indptr, indices = make_graph(cfg, device)
-    indptr_np, indices_np = indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64)
-    ref_gpu = reference_gpu_run(cfg, indptr, indices, rank, args.steps, args.warmup) if device == "cuda" else None
-    del indptr, indices
-    eps, desc, cores, ms = cpu_reference_run(cfg, indptr_np, indices_np, args.steps, args.warmup,
-                                             minibatches=4, sampler="ref")
+    indptr, indices = make_graph(cfg, device, synth)
+    extra = {}
+    if cfg["kind"] == "sage":
+        ref_gpu = None
+        if device == "cuda":
+            shard = load_plain("shard")
+            batches = shard.super_batches(sage_seed_list(cfg, 0, 1, shard), cfg["batch"], cfg["super_batch"])
+            ref_gpu = reference_gpu_sage(cfg, indptr, indices, batches, args.steps, args.warmup)
+        indptr_np, indices_np = indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64)
+        del indptr, indices
+        # the arm's own step shape (super_batch minibatches per step); at most 32 so that a run of
+        # K + W steps stays within minutes on the largest workload
+        eps, desc, cores, ms = cpu_sage(cfg, indptr_np, indices_np, args.steps, args.warmup,
+                                        min(cfg["super_batch"], 32))
+        metric, unit = "graphsage_sampled_edges_per_sec", "edges/s"
+        if ref_gpu is not None:
+            extra["reference_gpu"] = ref_gpu
+    elif cfg["kind"] == "ladies":
+        g = torch.Generator(device=device)
+        g.manual_seed(5)
+        w = torch.rand(indices.numel(), generator=g, device=device).clamp_min_(1e-3).cpu().numpy()
+        eps, desc, cores, ms = cpu_ladies(cfg, indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64), w,
+                                          args.steps, args.warmup)
+        metric, unit = "ladies_block_edges_per_sec", "edges/s"
+    else:
+        eps, desc, cores, ms = cpu_walk(cfg, indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64),
+                                        args.steps, args.warmup, walkers=cfg["walkers"] // 10)
+        metric, unit = "walk_steps_per_sec", "steps/s"
     line = {
-        "impl": "reference", "metric": "graphsage_sampled_edges_per_sec", "value": eps,
-        "unit": "edges/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int64", "data": "synthetic",
-        "config": {"workload": args.workload, **{k: cfg[k] for k in ("nodes", "edges", "fanouts", "batch")},
-                   "note": "the reference has no CPU sampler; this is the CPU port of its "
-                           "algorithms (oracle/) on the host cores"},
-        "cpu_baseline": {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc},
-        "e2e": {"value": eps, "unit": "edges/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": metric, "value": eps, "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": cfg["scaling"], "vs_baseline": None, "dtype": "int64", "data": "synthetic",
+        "config": {"workload": args.workload, **{k: v for k, v in cfg.items() if k not in ("kind", "large")},
+                   "note": "the reference has no CPU sampler; this is the CPU port of its algorithms (oracle/) "
+                           "on all host cores of rank 0's machine, %d threads" % threads},
+        "cpu_baseline": {"value": eps, "unit": unit, "cores": cores, "kind": "port", "sample": desc},
+        "e2e": {"value": eps, "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
-    if ref_gpu is not None:
-        line["reference_gpu"] = ref_gpu
+    line.update(extra)
     print(json.dumps(line))
 
 
+# ----------------------------------------------------------------------------- workloads (GPU arm)
+class SageWorkload(object):
+    metric, unit = "graphsage_sampled_edges_per_sec", "edges/s"
+
+    def __init__(self, cfg, dev, rank, world, nstreams):
+        import torch
+
+        import gsampler_b200 as gs
+        from gsampler_b200 import pipeline, shard, synth
+
+        self.cfg, self.dev, self.gs, self.pipeline, self.torch = cfg, dev, gs, pipeline, torch
+        self.L = len(cfg["fanouts"])
+        t0 = time.time()
+        self.indptr, self.indices = make_graph(cfg, dev, synth)
+        torch.cuda.synchronize()
+        self.graph_build_s = time.time() - t0
+        torch.cuda.empty_cache()
+        seeds = sage_seed_list(cfg, rank, world, shard)
+        self.batches_host = shard.super_batches(seeds, cfg["batch"], cfg["super_batch"])
+        self.batches_dev = [(s.to(dev), p.to(dev)) for s, p in self.batches_host]
+        self.batches_pin = [(s.pin_memory(), p.pin_memory()) for s, p in self.batches_host]
+        self.nb = len(self.batches_dev)
+        max_seeds = cfg["batch"] * cfg["super_batch"]
+        # capacities from a measured dry run (the worst case would be ~4x larger); an overflow
+        # raises the sampler's error word, which is checked after every timed region
+        probe = pipeline.GraphSAGESampler(self.indptr, self.indices, cfg["super_batch"], max_seeds, cfg["fanouts"])
+        caps = None
+        for s, p in self.batches_dev[:8]:
+            probe.sample(s, p)
+            cur = [(int(S * 1.15) + 4096, int(E * 1.15) + 4096) for S, E, U in probe.counts()]
+            caps = cur if caps is None else [(max(a[0], b[0]), max(a[1], b[1])) for a, b in zip(caps, cur)]
+        caps[0] = (max_seeds, max_seeds * cfg["fanouts"][0])
+        del probe
+        torch.cuda.empty_cache()
+        # Super-batches are independent: `nstreams` of them are in flight at once, each with its own
+        # pre-allocated sampler on its own CUDA stream, so that the latency-bound relabel passes of
+        # one overlap the bandwidth-bound sampling pass of another.
+        self.nstreams = nstreams
+        self.samplers = [pipeline.GraphSAGESampler(self.indptr, self.indices, cfg["super_batch"], max_seeds,
+                                                   cfg["fanouts"], capacities=caps) for _ in range(nstreams)]
+        self.streams = [torch.cuda.Stream(device=dev) for _ in range(nstreams)]
+        self.counts = None
+
+    def alloc_counts(self, n):
+        self.counts = self.torch.zeros(n, 3 * self.L, dtype=self.torch.int64, device=self.dev)
+
+    def step(self, i, row, overlapped=True):
+        s, p = self.batches_dev[i % self.nb]
+        if not overlapped:
+            self.samplers[0].sample(s, p, counts_out=self.counts[row])
+            return
+        k = i % self.nstreams
+        with self.torch.cuda.stream(self.streams[k]):
+            self.samplers[k].sample(s, p, counts_out=self.counts[row])
+
+    def fork(self):
+        cur = self.torch.cuda.current_stream(self.dev)
+        for st in self.streams:
+            st.wait_stream(cur)
+
+    def join(self):
+        cur = self.torch.cuda.current_stream(self.dev)
+        for st in self.streams:
+            cur.wait_stream(st)
+
+    def check(self):
+        for sm in self.samplers:
+            sm.check()
+
+    def units(self, rows):
+        c = self.counts[rows].cpu().numpy().reshape(-1, self.L, 3)
+        return int(c[:, :, 1].sum()), c
+
+    def e2e_setup(self):
+        gs, cfg = self.gs, self.cfg
+        A = gs.Graph(cfg["nodes"], cfg["nodes"])
+        A._CAPI_LoadCSC(self.indptr, self.indices)
+        self.bm = gs.BatchMatrix()
+        self.bm.load_from_matrix(gs.Matrix(A), False)
+        self.e2e_streams = [self.torch.cuda.Stream(self.dev) for _ in range(2)]
+
+    def e2e_run(self, first, count):
+        """Like a data loader with prefetch depth 2: super-batch k+1 is copied in and enqueued (on the
+        other stream) before the host waits for the sizes of super-batch k.  Every step copies its
+        own seeds from pinned host memory and reads its own result sizes back."""
+        torch, L = self.torch, self.L
+        edges, nin, nout, pending = 0, 0, 0, []
+        for k in range(count + 1):
+            if k < count:
+                s, p = self.batches_pin[(first + k) % self.nb]
+                with torch.cuda.stream(self.e2e_streams[k % 2]):
+                    sd, pd = s.to(self.dev, non_blocking=True), p.to(self.dev, non_blocking=True)
+                    pending.append((self.bm.graphsage_async(sd, pd, self.cfg["fanouts"]), s.numel() * 8 + p.numel() * 8))
+            if k >= 1:
+                fut, nbytes = pending.pop(0)
+                cnt = fut.wait()[-1]
+                edges += int(cnt.view(L, 3)[:, 1].sum())
+                nin += nbytes
+                nout += (3 * L + 1) * 8
+        return edges, nin, nout
+
+    e2e_api = "BatchMatrix.graphsage_async (one native call per super-batch, two in flight)"
+
+    def describe(self, c_host, world):
+        cfg = self.cfg
+        return {"graph": "power-law, %d nodes, %d directed edges, CSC int64/%s" % (
+                    cfg["nodes"], int(self.indptr[-1]), cfg["index_dtype"]),
+                "graph_gb": (self.indices.numel() * self.indices.element_size() + self.indptr.numel() * 8) / 1e9,
+                "graph_build_s": round(self.graph_build_s, 2),
+                "fanouts": cfg["fanouts"], "batch": cfg["batch"], "super_batch": cfg["super_batch"],
+                "train_seeds": cfg["train"], "seeds_this_rank": int(sum(s.numel() for s, _ in self.batches_host)),
+                "super_batches_per_epoch_this_rank": self.nb,
+                "parallelism": ("replica x%d, own epoch per rank" if cfg["scaling"] == "weak" else
+                                "replica x%d, one seed list split by gsampler_b200.shard.shard_seeds") % world,
+                "l2": "inputs_larger_than_l2 (graph indices %.1f GB)" % (
+                    self.indices.numel() * self.indices.element_size() / 1e9),
+                "mean_SEU_per_layer": [[float(c_host[:, l, j].mean()) for j in range(3)] for l in range(self.L)],
+                "capacities": "measured x1.15", "streams": self.nstreams}
+
+    def roofline(self, timed, c_host, elapsed_s, steps, peak, peak_kind):
+        w_idx = 4 if self.cfg["index_dtype"] == "int32" else 8
+        by = {(name, tag): (ms, cnt) for name, tag, ms, cnt in timed}
+        total_ms = sum(v[0] for v in by.values())
+        (dname, dtag), (dms, dcnt) = max(by.items(), key=lambda kv: kv[1][0])
+        S, E, U = (c_host[:, dtag, j].astype(np.float64) for j in range(3))
+        per_launch = {
+            # the sampling kernel also writes the block's column ids (8E), see DESIGN.md
+            "sample_tile": (8 * S + 16 * S + w_idx * E + 8 * (S + 1) + 32 * E).mean(),
+            "relabel_pcount": (8 * (S + E)).mean(), "relabel_scatter": (8 * (S + E)).mean(),
+            "relabel_dedupe": (8 * (S + E)).mean(), "relabel_rank": (8 * (S + E) + 8 * U).mean(),
+            "relabel_emit": (8 * E + 8 * E).mean(),
+        }.get(dname, 0.0)
+        dur_s = dms / dcnt / 1e3
+        achieved = per_launch / dur_s / 1e9 if dur_s > 0 else 0.0
+        path_bytes = 0.0
+        for l in range(self.L):
+            f, b = sage_bytes(c_host[:, l, 0].sum(), c_host[:, l, 1].sum(), c_host[:, l, 2].sum(), w_idx)
+            path_bytes += f + b
+        path_gbs = path_bytes / elapsed_s / 1e9
+        edges = float(c_host[:, :, 1].sum())
+        per = NCU_DRAM_BYTES_PER_EDGE.get(dname)
+        roof = {"bound": "hbm", "kernel": "%s[layer %d]" % (dname, dtag), "achieved": achieved, "peak": peak,
+                "unit": "GB/s", "frac": achieved / peak, "traffic": None if per is None else per * float(E.mean()),
+                "peak_kind": peak_kind, "share_of_kernel_time": dms / total_ms, "avg_launch_ms": dms / dcnt,
+                "algorithmic_bytes_per_launch": per_launch}
+        path = {"algorithmic_gb_per_step": path_bytes / steps / 1e9, "achieved": path_gbs, "unit": "GB/s",
+                "frac": path_gbs / peak, "peak_kind": peak_kind,
+                "dram_traffic_gbs": NCU_PATH_DRAM_BYTES_PER_EDGE * edges / elapsed_s / 1e9,
+                "dram_traffic_frac": NCU_PATH_DRAM_BYTES_PER_EDGE * edges / elapsed_s / 1e9 / peak}
+        return roof, path
+
+    def cpu_baseline(self):
+        indptr_np = self.indptr.cpu().numpy()
+        indices_np = self.indices.cpu().numpy().astype(np.int64)
+        eps, desc, cores, _ = cpu_sage(self.cfg, indptr_np, indices_np, steps=3, warmup=1, minibatches=4)
+        return {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc,
+                "reference_cpu_code": cpu_sort_indices(indptr_np, indices_np)}
+
+
+class LadiesWorkload(object):
+    metric, unit = "ladies_block_edges_per_sec", "edges/s"
+
+    def __init__(self, cfg, dev, rank, world, nstreams):
+        import torch
+
+        import gsampler_b200 as gs
+        from gsampler_b200 import pipeline, synth
+
+        self.cfg, self.dev, self.gs, self.pipeline, self.torch = cfg, dev, gs, pipeline, torch
+        t0 = time.time()
+        self.indptr, self.indices = make_graph(cfg, dev, synth)
+        g = torch.Generator(device=dev)
+        g.manual_seed(5)
+        self.w = torch.rand(self.indices.numel(), generator=g, device=dev).clamp_min_(1e-3)
+        torch.cuda.synchronize()
+        self.graph_build_s = time.time() - t0
+        A = gs.Graph(cfg["nodes"], cfg["nodes"])
+        A._CAPI_LoadCSC(self.indptr, self.indices)
+        m = gs.Matrix(A)
+        m.edata["w"] = self.w
+        # column-normalise once (the preprocessing P = A D^-1 of the recipe, outside the loop)
+        self.m = m.div("w", m.sum("w", axis=0).clamp_min(1e-12), axis=0)
+        gen = torch.Generator()
+        gen.manual_seed(1 + rank)
+        self.batches_host = [torch.randperm(cfg["nodes"], generator=gen)[:cfg["seeds"]].to(torch.int64)
+                             for _ in range(16)]
+        self.batches_dev = [s.to(dev) for s in self.batches_host]
+        self.batches_pin = [s.pin_memory() for s in self.batches_host]
+        self.nb = len(self.batches_dev)
+        self.nstreams = 1
+        self.stats = []
+
+    def alloc_counts(self, n):
+        self.stats = [None] * n
+
+    def _sample(self, seeds):
+        """Both layers; returns [(slice edges, candidate rows, block edges, seeds)] per layer."""
+        out = []
+        for _ in range(self.cfg["layers"]):
+            S = seeds.numel()
+            blk, seeds, picked = self.m.ladies_layer(seeds, self.cfg["layer_nodes"])
+            out.append((S, blk.num_edges(), int(seeds.numel())))
+        return out
+
+    def step(self, i, row, overlapped=True):
+        self.stats[row] = self._sample(self.batches_dev[i % self.nb])
+
+    def fork(self):
+        pass
+
+    def join(self):
+        pass
+
+    def check(self):
+        self.gs.check_async_errors()
+
+    def units(self, rows):
+        sel = [self.stats[r] for r in (range(*rows.indices(len(self.stats))) if isinstance(rows, slice) else rows)]
+        return sum(e for st in sel for _, e, _ in st), sel
+
+    def e2e_setup(self):
+        pass
+
+    def e2e_run(self, first, count):
+        edges, nin, nout = 0, 0, 0
+        for k in range(count):
+            s = self.batches_pin[(first + k) % self.nb]
+            st = self._sample(s.to(self.dev, non_blocking=True))     # block sizes are read back per layer
+            edges += sum(e for _, e, _ in st)
+            nin += s.numel() * 8
+            nout += 2 * 8 * self.cfg["layers"]
+        return edges, nin, nout
+
+    e2e_api = "Matrix.ladies_layer (one native call per layer; two size read-backs per layer)"
+
+    def describe(self, sel, world):
+        cfg = self.cfg
+        return {"graph": "power-law, %d nodes, %d directed fp32-weighted edges, CSC int64/int64" % (
+                    cfg["nodes"], int(self.indptr[-1])),
+                "graph_build_s": round(self.graph_build_s, 2), "seeds": cfg["seeds"], "layer_nodes": cfg["layer_nodes"],
+                "layers": cfg["layers"], "parallelism": "replica x%d" % world,
+                "l2": "inputs_larger_than_l2 (indices + weights %.1f GB)" % (self.indices.numel() * 12 / 1e9),
+                "mean_block_edges_per_step": float(np.mean([sum(e for _, e, _ in st) for st in sel]))}
+
+    def roofline(self, timed, sel, elapsed_s, steps, peak, peak_kind):
+        """Compulsory bytes of a layer with S seeds, E_s sliced edges, R rows, K picks, E kept edges:
+        slice 8S + 16S + 8E_s + 8(S+1) + 24E_s; row sums of w^2: 4E_s + 8E_s + 4R; weighted list
+        sampling 4R + 8K; row filter 8E_s + 24E; two renormalisations 2(4E + 8E + 4E) and the column
+        sums 4E + 8E + 4S; relabel 8S + 16E + 8U + 16E.  E_s is not read back by the native call: the
+        mean column degree times S stands in for it."""
+        by = {}
+        for name, tag, ms, cnt in timed:
+            a = by.setdefault(name, [0.0, 0])
+            a[0] += ms
+            a[1] += cnt
+        total_ms = sum(v[0] for v in by.values())
+        dname, (dms, dcnt) = max(by.items(), key=lambda kv: kv[1][0])
+        R, K = self.cfg["nodes"], self.cfg["layer_nodes"]
+        deg = float(self.indptr[-1]) / self.cfg["nodes"]
+        path = 0.0
+        for st in sel:
+            for S, E, U in st:
+                Es = S * deg
+                path += (40 * S + 32 * Es) + (12 * Es + 4 * R) + (4 * R + 8 * K) + (8 * Es + 24 * E) + \
+                        (32 * E + 12 * E + 4 * S) + (8 * S + 32 * E + 8 * U)
+        gbs = path / elapsed_s / 1e9
+        roof = {"bound": "hbm", "kernel": dname, "achieved": None, "peak": peak, "unit": "GB/s", "frac": None,
+                "traffic": None, "peak_kind": peak_kind, "share_of_kernel_time": dms / total_ms,
+                "avg_launch_ms": dms / dcnt,
+                "note": "per-kernel bytes are not separated for this workload; see roofline_path"}
+        return roof, {"algorithmic_gb_per_step": path / steps / 1e9, "achieved": gbs, "unit": "GB/s",
+                      "frac": gbs / peak, "peak_kind": peak_kind,
+                      "kernel_ms_per_step": total_ms / steps}
+
+    def cpu_baseline(self):
+        eps, desc, cores, _ = cpu_ladies(self.cfg, self.indptr.cpu().numpy(), self.indices.cpu().numpy(),
+                                         self.w.cpu().numpy(), steps=2, warmup=1)
+        return {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port", "sample": desc}
+
+
+class WalkWorkload(object):
+    metric, unit = "walk_steps_per_sec", "steps/s"
+
+    def __init__(self, cfg, dev, rank, world, nstreams):
+        import torch
+
+        import gsampler_b200 as gs
+        from gsampler_b200 import pipeline, synth
+
+        self.cfg, self.dev, self.gs, self.pipeline, self.torch = cfg, dev, gs, pipeline, torch
+        t0 = time.time()
+        self.indptr, self.indices = make_graph(cfg, dev, synth)
+        torch.cuda.synchronize()
+        self.graph_build_s = time.time() - t0
+        self.A = gs.Graph(cfg["nodes"], cfg["nodes"])
+        self.A._CAPI_LoadCSC(self.indptr, self.indices)   # the generator's columns are sorted
+        gen = torch.Generator()
+        gen.manual_seed(7 + rank)
+        self.batches_host = [torch.randint(0, cfg["nodes"], (cfg["walkers"],), generator=gen) for _ in range(4)]
+        self.batches_dev = [s.to(dev) for s in self.batches_host]
+        self.batches_pin = [s.pin_memory() for s in self.batches_host]
+        self.nb = 4
+        self.nstreams = 1
+        # Steps actually taken per call.  The graph is symmetric, so a walk only fails to move when
+        # its start node has no neighbour at all: walkers with a neighbour x length, known before
+        # the walk and checked against a real trace here.
+        deg = self.indptr[1:] - self.indptr[:-1]
+        self.batch_live = [int((deg[s] > 0).sum()) * cfg["length"] for s in self.batches_dev]
+        tr = self._walk(self.batches_dev[0])
+        assert int((tr.view(-1)[cfg["walkers"]:] >= 0).sum()) == self.batch_live[0]
+        del tr
+        self.live = None
+
+    def alloc_counts(self, n):
+        self.live = np.zeros(n, dtype=np.int64)
+
+    def _walk(self, seeds, row=None):
+        c = self.cfg
+        return self.A._CAPI_Node2Vec(seeds, c["length"], c["p"], c["q"])
+
+    def step(self, i, row, overlapped=True):
+        self._walk(self.batches_dev[i % self.nb])
+        self.live[row] = self.batch_live[i % self.nb]
+
+    def fork(self):
+        pass
+
+    def join(self):
+        pass
+
+    def check(self):
+        self.gs.check_async_errors()
+
+    def units(self, rows):
+        v = self.live[rows]
+        return int(v.sum()), v
+
+    def e2e_setup(self):
+        pass
+
+    def e2e_run(self, first, count):
+        live, nin, nout = 0, 0, 0
+        for k in range(count):
+            s = self.batches_pin[(first + k) % self.nb]
+            tr = self._walk(s.to(self.dev, non_blocking=True))
+            live += int((tr.view(-1)[self.cfg["walkers"]:] >= 0).sum())     # the step's result summary
+            nin += s.numel() * 8
+            nout += 8
+        return live, nin, nout
+
+    e2e_api = "Graph._CAPI_Node2Vec (the trace stays on the device; the count of taken steps is read back)"
+
+    def describe(self, v, world):
+        cfg = self.cfg
+        return {"graph": "power-law, %d nodes, %d directed edges, sorted columns, CSC int64/int64" % (
+                    cfg["nodes"], int(self.indptr[-1])),
+                "graph_build_s": round(self.graph_build_s, 2), "walkers": cfg["walkers"], "length": cfg["length"],
+                "p": cfg["p"], "q": cfg["q"], "parallelism": "replica x%d" % world,
+                "l2": "inputs_larger_than_l2 (graph indices %.1f GB)" % (self.indices.numel() * 8 / 1e9),
+                "trace_bytes_per_step": cfg["walkers"] * (cfg["length"] + 1) * 8}
+
+    def roofline(self, timed, v, elapsed_s, steps, peak, peak_kind):
+        """Compulsory bytes per taken step: the offsets pair (16), one row id (8), the trace entry (8)."""
+        by = {}
+        for name, tag, ms, cnt in timed:
+            a = by.setdefault(name, [0.0, 0])
+            a[0] += ms
+            a[1] += cnt
+        total_ms = sum(x[0] for x in by.values())
+        dms, dcnt = by.get("walk", (0.0, 1))
+        alg_launch = float(np.mean(v)) * 32
+        dur = dms / max(dcnt, 1) / 1e3
+        achieved = alg_launch / dur / 1e9 if dur > 0 else 0.0
+        gbs = float(np.sum(v)) * 32 / elapsed_s / 1e9
+        roof = {"bound": "hbm", "kernel": "node2vec_kernel", "achieved": achieved, "peak": peak, "unit": "GB/s",
+                "frac": achieved / peak, "traffic": None, "peak_kind": peak_kind,
+                "share_of_kernel_time": dms / total_ms if total_ms else None, "avg_launch_ms": dms / max(dcnt, 1),
+                "algorithmic_bytes_per_launch": alg_launch}
+        return roof, {"algorithmic_gb_per_step": float(np.sum(v)) * 32 / steps / 1e9, "achieved": gbs,
+                      "unit": "GB/s", "frac": gbs / peak, "peak_kind": peak_kind}
+
+    def cpu_baseline(self):
+        eps, desc, cores, _ = cpu_walk(self.cfg, self.indptr.cpu().numpy(), self.indices.cpu().numpy(),
+                                       steps=2, warmup=1, walkers=self.cfg["walkers"] // 10)
+        return {"value": eps, "unit": "steps/s", "cores": cores, "kind": "port", "sample": desc}
+
+
+KINDS = {"sage": SageWorkload, "ladies": LadiesWorkload, "walk": WalkWorkload}
+
+
+# ----------------------------------------------------------------------------- main
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=14)
     ap.add_argument("--warmup", type=int, default=7)
+    ap.add_argument("--reps", type=int, default=int(os.environ.get("GSB_REPS", "15")),
+                    help="repetitions of the timed K-step region (median reported)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("GSB_WORKLOAD", "cfg2"), choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
@@ -298,220 +818,123 @@ def main():
             os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
         dist.init_process_group("nccl", device_id=dev)
 
-    import gsampler_b200 as gs
     from gsampler_b200 import pipeline
 
-    L = len(cfg["fanouts"])
-    indptr, indices = make_graph(cfg, dev)
-    batches_host = make_super_batches(cfg, rank)
-    batches_dev = [(s.to(dev), p.to(dev)) for s, p in batches_host]
-    batches_pin = [(s.pin_memory(), p.pin_memory()) for s, p in batches_host]
-    nb = len(batches_dev)
-    max_seeds = cfg["batch"] * cfg["super_batch"]
+    wl = KINDS[cfg["kind"]](cfg, dev, rank, world, max(1, args.streams))
+    K, W, R = args.steps, args.warmup, max(1, args.reps)
+    wl.alloc_counts(W + K * R + K)
 
-    # ---- capacities from a measured dry run (worst case would be ~4x larger)
-    probe = pipeline.GraphSAGESampler(indptr, indices, cfg["super_batch"], max_seeds, cfg["fanouts"])
-    caps = None
-    for s, p in batches_dev:
-        probe.sample(s, p)
-        c = probe.counts()
-        cur = [(int(S * 1.15) + 4096, int(E * 1.15) + 4096) for S, E, U in c]
-        caps = cur if caps is None else [(max(a[0], b[0]), max(a[1], b[1])) for a, b in zip(caps, cur)]
-    caps[0] = (max_seeds, max_seeds * cfg["fanouts"][0])
-    del probe
-    torch.cuda.empty_cache()
-    # measured capacities; an overflow would raise the sampler's error word (checked below)
-    # Super-batches are independent: `--streams` of them are in flight at once, each with its
-    # own pre-allocated sampler on its own CUDA stream, so the latency-bound relabel passes of
-    # one overlap the bandwidth-bound sampling pass of another.
-    nstreams = max(1, args.streams)
-    samplers = [pipeline.GraphSAGESampler(indptr, indices, cfg["super_batch"], max_seeds,
-                                          cfg["fanouts"], capacities=caps) for _ in range(nstreams)]
-    streams = [torch.cuda.Stream(device=dev) for _ in range(nstreams)]
-    sampler = samplers[0]
-
-    counts = torch.zeros(args.steps + args.warmup, 3 * L, dtype=torch.int64, device=dev)
-
-    def step(i, row, overlapped=True):
-        s, p = batches_dev[i % nb]
-        if not overlapped:
-            sampler.sample(s, p, counts_out=counts[row])
-            return
-        k = i % nstreams
-        with torch.cuda.stream(streams[k]):
-            samplers[k].sample(s, p, counts_out=counts[row])
-
-    def fork():
-        cur = torch.cuda.current_stream(dev)
-        for st in streams:
-            st.wait_stream(cur)
-
-    def join():
-        cur = torch.cuda.current_stream(dev)
-        for st in streams:
-            cur.wait_stream(st)
-
-    fork()
-    for w in range(args.warmup):
-        step(w, w)
-    join()
+    wl.fork()
+    for w in range(W):
+        wl.step(w, w)
+    wl.join()
     torch.cuda.synchronize()
-    for sm in samplers:
-        sm.check()
+    wl.check()
 
     clocks = ClockSampler(local_rank)
     clocks.start()
     time.sleep(0.3)
     launches0 = pipeline.kernel_launches()
-    if world > 1:
-        dist.barrier()
-    torch.cuda.synchronize()
-    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    ev0.record()
-    fork()
-    for k in range(args.steps):
-        step(args.warmup + k, args.warmup + k)
-    join()
-    ev1.record()
-    torch.cuda.synchronize()
-    if world > 1:
-        dist.barrier()
-    launches = pipeline.kernel_launches() - launches0
-    elapsed_ms = ev0.elapsed_time(ev1)
-    for sm in samplers:
-        sm.check()
-    c_host = counts[args.warmup:].cpu().numpy().reshape(args.steps, L, 3)
-    edges = int(c_host[:, :, 1].sum())
+    rep_ms = []
+    for r in range(R):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ev0.record()
+        wl.fork()
+        for k in range(K):
+            wl.step(W + r * K + k, W + r * K + k)
+        wl.join()
+        ev1.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        rep_ms.append(ev0.elapsed_time(ev1))
+    launches = (pipeline.kernel_launches() - launches0) // R
+    wl.check()
+    rep_units = [wl.units(slice(W + r * K, W + (r + 1) * K))[0] for r in range(R)]
 
-    # ---- per-kernel durations of the same K steps (CUDA events around every launch)
-    # (one stream, no overlap: a kernel's duration is then its own)
+    # ---- per-kernel durations of K steps (CUDA events around every launch; one stream, no
+    # overlap: a kernel's duration is then its own)
     pipeline.timing_enable(True)
-    for k in range(args.steps):
-        step(args.warmup + k, args.warmup + k, overlapped=False)
+    base = W + K * R
+    for k in range(K):
+        wl.step(W + k, base + k, overlapped=False)
     timed = pipeline.timing_collect()
     pipeline.timing_enable(False)
     clocks.stop()
+    _, detail = wl.units(slice(base, base + K))
 
-    # ---- end to end through the public API: pinned host seeds -> blocks on the GPU -> sizes on the host
-    A = gs.Graph(cfg["nodes"], cfg["nodes"])
-    A._CAPI_LoadCSC(indptr, indices)
-    bm = gs.BatchMatrix()
-    bm.load_from_matrix(gs.Matrix(A), False)
-    # Like a data loader with prefetch depth 2: super-batch k+1 is copied in and enqueued (on the
-    # other stream) before the host waits for the sizes of super-batch k.  Every step still
-    # copies its own seeds from pinned host memory and reads its own result sizes back.
-    e2e_streams = [torch.cuda.Stream(dev) for _ in range(2)]
-
-    def e2e_submit(i):
-        s, p = batches_pin[i % nb]
-        with torch.cuda.stream(e2e_streams[i % 2]):
-            sd, pd = s.to(dev, non_blocking=True), p.to(dev, non_blocking=True)
-            return bm.graphsage_async(sd, pd, cfg["fanouts"]), s.numel() * 8 + p.numel() * 8
-
-    def e2e_run(first, count):
-        edges, nin, nout = 0, 0, 0
-        pending = []
-        for k in range(count + 1):
-            if k < count:
-                pending.append(e2e_submit(first + k))
-            if k >= 1:
-                fut, nbytes = pending.pop(0)
-                cnt = fut.wait()[-1]
-                edges += int(cnt.view(L, 3)[:, 1].sum())
-                nin += nbytes
-                nout += (3 * L + 1) * 8
-        return edges, nin, nout
-
-    import gc
-    e2e_run(0, max(args.warmup, 3))
+    # ---- end to end through the public API: pinned host inputs -> result sizes on the host
+    wl.e2e_setup()
+    wl.e2e_run(0, max(W, 3))
     torch.cuda.synchronize()
     gc.collect()
-    gc.disable()          # a collection inside the ~20 ms timed region would be most of it
-    t0 = time.perf_counter()
-    e2e_edges, h2d, d2h = e2e_run(args.warmup, args.steps)
-    torch.cuda.synchronize()
-    e2e_ms = (time.perf_counter() - t0) * 1e3   # host clock around copies, launches and reads
+    gc.disable()          # a collection inside a ~20 ms timed region would be most of it
+    e2e_ms, e2e_units, h2d, d2h = [], [], 0, 0
+    for r in range(R):
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        u, h2d, d2h = wl.e2e_run(W + r * K, K)
+        torch.cuda.synchronize()
+        e2e_ms.append((time.perf_counter() - t0) * 1e3)   # host clock around copies, launches and reads
+        e2e_units.append(u)
     gc.enable()
 
-    # ---- reduce over ranks: slowest rank's time, summed edges
+    # ---- reduce over ranks: per repetition the slowest rank's time and the summed units
+    rep_ms_local = list(rep_ms)
     if world > 1:
-        t = torch.tensor([elapsed_ms, e2e_ms], dtype=torch.float64, device=dev)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        elapsed_ms, e2e_ms = float(t[0]), float(t[1])
-        n = torch.tensor([edges, e2e_edges, launches], dtype=torch.int64, device=dev)
+        t = torch.tensor([rep_ms, e2e_ms], dtype=torch.float64, device=dev)
+        gathered = [torch.zeros_like(t) for _ in range(world)]
+        dist.all_gather(gathered, t)
+        per_rank = torch.stack(gathered)                       # [world, 2, R]
+        rep_ms, e2e_ms = per_rank[:, 0].max(0).values.tolist(), per_rank[:, 1].max(0).values.tolist()
+        rank_medians = per_rank[:, 0].median(1).values.tolist()
+        n = torch.tensor([rep_units, e2e_units], dtype=torch.int64, device=dev)
         dist.all_reduce(n, op=dist.ReduceOp.SUM)
-        edges, e2e_edges, launches = int(n[0]), int(n[1]), int(n[2])
+        rep_units, e2e_units = n[0].tolist(), n[1].tolist()
+        ln = torch.tensor([launches], dtype=torch.int64, device=dev)
+        dist.all_reduce(ln, op=dist.ReduceOp.SUM)
+        launches = int(ln[0])
+    else:
+        rank_medians = [float(np.median(rep_ms))]
 
     if rank == 0:
         peak, peak_kind = load_peaks()
-        # dominant kernel of the timed pipeline and its roofline
+        rates = [u / (ms / 1e3) for u, ms in zip(rep_units, rep_ms)]
+        mid = int(np.argsort(rep_ms)[len(rep_ms) // 2])          # the median repetition
+        e2e_rates = [u / (ms / 1e3) for u, ms in zip(e2e_units, e2e_ms)]
+        e_mid = int(np.argsort(e2e_ms)[len(e2e_ms) // 2])
+        # rooflines use rank 0's own median time and the per-kernel run's counts
+        elapsed_local_s = float(np.median(rep_ms_local)) / 1e3
+        roof, path = wl.roofline(timed, detail, elapsed_local_s, K, peak, peak_kind)
         by = {}
         for name, tag, ms, cnt in timed:
-            by[(name, tag)] = (ms, cnt)
-        total_kernel_ms = sum(v[0] for v in by.values())
-        (dname, dtag), (dms, dcnt) = max(by.items(), key=lambda kv: kv[1][0])
-        S_l = c_host[:, dtag, 0].astype(np.float64)
-        E_l = c_host[:, dtag, 1].astype(np.float64)
-        U_l = c_host[:, dtag, 2].astype(np.float64)
-        w_idx = 4 if cfg["index_dtype"] == "int32" else 8
-        per_launch = {
-            "sample_tile": (8 * S_l + 16 * S_l + w_idx * E_l + 8 * (S_l + 1) + 24 * E_l).mean(),
-            "relabel_pcount": (8 * (S_l + E_l)).mean(),
-            "relabel_scatter": (8 * (S_l + E_l)).mean(),
-            "relabel_dedupe": (8 * (S_l + E_l)).mean(),
-            "relabel_rank": (8 * (S_l + E_l) + 8 * U_l).mean(),
-            "relabel_emit": (24 * E_l).mean(),
-        }.get(dname, 0.0)
-        dur_s = dms / dcnt / 1e3
-        achieved = per_launch / dur_s / 1e9 if dur_s > 0 else 0.0
-        path_bytes = 0.0
-        for l in range(L):
-            f, b = algorithmic_bytes(c_host[:, l, 0].sum(), c_host[:, l, 1].sum(), c_host[:, l, 2].sum(), w_idx)
-            path_bytes += f + b
-        path_gbs = path_bytes / (elapsed_ms / 1e3) / 1e9  # per GPU (rank 0's own counts)
+            by["%s[%d]" % (name, tag)] = {"ms": round(ms, 4), "launches": cnt}
         line = {
-            "metric": "graphsage_sampled_edges_per_sec",
-            "value": edges / (elapsed_ms / 1e3), "unit": "edges/s", "n_gpus": world,
-            "steps": args.steps, "warmup": args.warmup, "ms_per_step": elapsed_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int64",
-            "data": "synthetic",
-            "config": {"workload": args.workload, "graph": "power-law, %d nodes, %d directed edges, CSC int64/%s"
-                       % (cfg["nodes"], int(indptr[-1]), cfg["index_dtype"]),
-                       "fanouts": cfg["fanouts"], "batch": cfg["batch"], "super_batch": cfg["super_batch"],
-                       "train_seeds": cfg["train"], "parallelism": "replica x%d" % world,
-                       "l2": "inputs_larger_than_l2 (graph indices %.1f GB)" % (indices.numel() * indices.element_size() / 1e9),
-                       "edges_per_step": edges / args.steps / max(world, 1),
-                       "mean_SEU_per_layer": [[float(c_host[:, l, j].mean()) for j in range(3)]
-                                              for l in range(L)],
-                       "capacities": "measured x1.15",
-                       "streams": nstreams},
-            "e2e": {"value": e2e_edges / (e2e_ms / 1e3), "unit": "edges/s",
-                    "h2d_bytes_per_step": h2d // args.steps, "d2h_bytes_per_step": d2h // args.steps,
-                    "api": "BatchMatrix.graphsage_async (one native call per super-batch, two in flight)"},
+            "metric": wl.metric, "value": rates[mid], "unit": wl.unit, "n_gpus": world,
+            "steps": K, "warmup": W, "ms_per_step": rep_ms[mid] / K,
+            "higher_is_better": True, "scaling": cfg["scaling"], "vs_baseline": None,
+            "dtype": "int64" if cfg["kind"] != "ladies" else "int64+f32", "data": "synthetic",
+            "config": {"workload": args.workload, **wl.describe(detail, world)},
+            "repeats": {"n": R, "what": "the K-step timed region repeated; value / ms_per_step are the median repetition",
+                        "ms_per_step": {"min": min(rep_ms) / K, "median": rep_ms[mid] / K, "max": max(rep_ms) / K},
+                        "value": {"min": min(rates), "median": rates[mid], "max": max(rates)},
+                        "rank_median_ms_per_step": [m / K for m in rank_medians]},
+            "e2e": {"value": e2e_rates[e_mid], "unit": wl.unit,
+                    "h2d_bytes_per_step": h2d // K, "d2h_bytes_per_step": d2h // K, "api": wl.e2e_api,
+                    "repeats": {"n": R, "min": min(e2e_rates), "median": e2e_rates[e_mid], "max": max(e2e_rates)}},
             "gpu_launches": launches,
-            "roofline": {"bound": "hbm", "kernel": "%s[layer %d]" % (dname, dtag), "achieved": achieved,
-                         "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "traffic": ncu_traffic(dname, float(E_l.mean())),
-                         "peak_kind": peak_kind, "share_of_kernel_time": dms / total_kernel_ms,
-                         "avg_launch_ms": dms / dcnt},
-            "roofline_path": {"algorithmic_gb_per_step": path_bytes / args.steps / 1e9,
-                              "achieved": path_gbs, "unit": "GB/s", "frac": path_gbs / peak,
-                              "peak_kind": peak_kind,
-                              # DRAM traffic (ncu, scaled by edges) over the same time: how busy HBM is
-                              "dram_traffic_gbs": NCU_PATH_DRAM_BYTES_PER_EDGE * (edges / max(world, 1))
-                                                  / (elapsed_ms / 1e3) / 1e9,
-                              "dram_traffic_frac": NCU_PATH_DRAM_BYTES_PER_EDGE * (edges / max(world, 1))
-                                                   / (elapsed_ms / 1e3) / 1e9 / peak},
-            "kernels": {"%s[%d]" % k: {"ms": round(v[0], 4), "launches": v[1]} for k, v in sorted(by.items())},
+            "roofline": roof, "roofline_path": path, "kernels": dict(sorted(by.items())),
             "clocks": clocks.summary(),
         }
         if world == 1 and not args.no_cpu_baseline:
-            indptr_np, indices_np = indptr.cpu().numpy(), indices.cpu().numpy().astype(np.int64)
-            eps, desc, cores, _ = cpu_reference_run(cfg, indptr_np, indices_np, steps=3, warmup=1,
-                                                    minibatches=4, sampler="ref")
-            line["cpu_baseline"] = {"value": eps, "unit": "edges/s", "cores": cores, "kind": "port",
-                                    "sample": desc,
-                                    "reference_cpu_code": cpu_sort_indices_run(indptr_np, indices_np)}
+            cpu_threads()
+            line["cpu_baseline"] = wl.cpu_baseline()
+            if cfg["kind"] == "sage":
+                line["cpu_baseline"]["cfg1"] = cpu_cfg1()
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

@@ -151,7 +151,8 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
                                     int64_t num_cols, int64_t id_bound, const int64_t* seeds,
                                     const int64_t* seeds_ptr, int64_t B, int64_t S0,
                                     int num_layers, const int64_t* fanouts, uint64_t seed,
-                                    const gsb_layer_buffers* layers, int64_t* d_counts,
+                                    uint32_t stream_base, const gsb_layer_buffers* layers,
+                                    int64_t* d_counts,
                                     void* workspace, size_t workspace_bytes, int* d_err,
                                     void* cuda_stream) {
   if (!indptr || !indices || !seeds_ptr || !layers || !fanouts || !d_counts || num_layers < 1 ||
@@ -174,14 +175,18 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
     const int64_t S_max = l == 0 ? S0 : L.S_cap;
     set_timing_tag(l);
     const size_t ws_a = align256(gsb_sample_cols_workspace_bytes(L.S_cap, fanouts[l]));
-    int rc = gsb_sample_cols(indptr, indices, indices_dtype, num_cols, cur_seeds, S_max, d_S, fanouts[l], 0,
-                             seed, (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
-                             d_counts + 3 * l + 1, workspace, ws_a, d_err, cuda_stream);
+    // the sampler also writes block_col = slot - first slot of the minibatch, which is the
+    // relabelled column wherever the minibatch's seeds are distinct (the relabel stage rewrites
+    // the other minibatches)
+    int rc = sample_launch(indptr, indices, indices_dtype, num_cols, cur_seeds, S_max, d_S, fanouts[l], 0,
+                           seed, stream_base + (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
+                           d_counts + 3 * l + 1, cur_ptr, B, L.block_col, workspace, ws_a, d_err,
+                           cuda_stream);
     if (rc != GSB_OK) return rc;
     // edge_ptr = sub_indptr[seeds_ptr] and the {S, U} counts are produced inside the relabel passes
     rc = relabel_launch(cur_seeds, cur_ptr, B, S_max, L.rows, L.cols, nullptr, L.sub_indptr,
                         L.edge_ptr, L.E_cap, id_bound, L.unique, L.S_cap + L.E_cap, L.unique_ptr,
-                        L.block_row, L.block_col, d_counts + 3 * l, (char*)workspace + ws_a,
+                        L.block_row, L.block_col, d_counts + 3 * l, 1, (char*)workspace + ws_a,
                         workspace_bytes - ws_a, d_err, cuda_stream);
     if (rc != GSB_OK) return rc;
     cur_seeds = L.unique;

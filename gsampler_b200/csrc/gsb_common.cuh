@@ -168,6 +168,40 @@ __device__ __forceinline__ i64 chained_exclusive_prefix(u64* status, int tile, i
   return exclusive;
 }
 
+// ---------------------------------------------------------------- L2 residency hints
+// Per-instruction cache policy only (no device-wide setting is touched).  A small array that
+// every CTA gathers from at random (the column offsets) is loaded with an evict-last policy so
+// that the streams flowing past it -- gathered row ids, output stores -- do not push it out of
+// L2; those streams are marked evict-first and bypass L1.
+__device__ __forceinline__ u64 l2_policy_keep() {
+  u64 pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ u64 l2_policy_stream() {
+  u64 pol;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+__device__ __forceinline__ i64 ld_i64_keep(const i64* p, u64 pol) {
+  i64 v;
+  asm volatile("ld.global.nc.L1::evict_last.L2::cache_hint.b64 %0, [%1], %2;" : "=l"(v) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ __forceinline__ i64 ld_i64_stream(const i64* p, u64 pol) {
+  i64 v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b64 %0, [%1], %2;" : "=l"(v) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ __forceinline__ int ld_i32_stream(const int* p, u64 pol) {
+  int v;
+  asm volatile("ld.global.nc.L1::no_allocate.L2::cache_hint.b32 %0, [%1], %2;" : "=r"(v) : "l"(p), "l"(pol));
+  return v;
+}
+__device__ __forceinline__ void st_i64_stream(i64* p, i64 v, u64 pol) {
+  asm volatile("st.global.L1::no_allocate.L2::cache_hint.b64 [%0], %1, %2;" ::"l"(p), "l"(v), "l"(pol) : "memory");
+}
+
 // ---------------------------------------------------------------- misc
 __device__ __forceinline__ u32 hash32(u32 k) {
   k ^= k >> 16; k *= 0x85ebca6bu; k ^= k >> 13; k *= 0xc2b2ae35u; k ^= k >> 16;
@@ -194,14 +228,34 @@ template <>
 __device__ __forceinline__ i64 load_index<i64>(const void* base, i64 pos) {
   return __ldg((const i64*)base + pos);
 }
+// the same gather marked as a stream (see the L2 hints above)
+template <typename T>
+__device__ __forceinline__ i64 load_index_stream(const void* base, i64 pos, u64 pol);
+template <>
+__device__ __forceinline__ i64 load_index_stream<int>(const void* base, i64 pos, u64 pol) {
+  return (i64)ld_i32_stream((const int*)base + pos, pol);
+}
+template <>
+__device__ __forceinline__ i64 load_index_stream<i64>(const void* base, i64 pos, u64 pol) {
+  return ld_i64_stream((const i64*)base + pos, pol);
+}
 
 // gsb_batch_relabel with two extras for the layered sampler (gsb_relabel.cu)
 int relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B, int64_t S_max,
                    const int64_t* coo_row, const int64_t* coo_col, const int64_t* edge_ptr,
                    const int64_t* sub_indptr, int64_t* edge_ptr_out, int64_t E_max, int64_t id_bound,
                    int64_t* unique, int64_t U_cap, int64_t* unique_ptr, int64_t* out_row,
-                   int64_t* out_col, int64_t* counts_out, void* workspace, size_t workspace_bytes,
-                   int* d_err, void* cuda_stream);
+                   int64_t* out_col, int64_t* counts_out, int col_prefilled, void* workspace,
+                   size_t workspace_bytes, int* d_err, void* cuda_stream);
+
+// gsb_sample_cols with the extras of the layered sampler (gsb_sample.cu): `out_block_col`
+// receives every edge's column slot counted from its minibatch's first slot (seeds_ptr, B)
+int sample_launch(const int64_t* indptr, const void* indices, int indices_dtype, int64_t num_cols,
+                  const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K, int replace,
+                  uint64_t seed, uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
+                  int64_t* out_cols, int64_t* out_sel, int64_t E_cap, int64_t* d_num_edges,
+                  const int64_t* seeds_ptr, int64_t B, int64_t* out_block_col, void* workspace,
+                  size_t workspace_bytes, int* d_err, void* cuda_stream);
 
 inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 

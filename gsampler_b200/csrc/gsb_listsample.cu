@@ -77,6 +77,9 @@ __global__ void list_setup_kernel(const ListParams p) {
   if (threadIdx.x == 0) {
     p.out_range[p.B] = s_carry;
     if (p.range[p.B] > p.R) raise(p.err, ERRBIT_CAPACITY);
+    // the segments must cover the items from 0: the weighted rounds would count an item below
+    // range[0] into the first segment while the uniform pass skips it
+    if (p.range[0] != 0) raise(p.err, ERRBIT_BAD_INPUT);
   }
 }
 

@@ -118,6 +118,8 @@ struct RelabelParams {
   u32* bucket_cursor; // [buckets] fill level during the scatter pass
   u64* part;          // [items] id:32 | index:32, grouped by bucket
   u64* overflow;      // global tables of buckets that overflow the shared one
+  u32* seed_repeat;   // [B] set when a seed of the minibatch repeats an earlier seed (or is invalid)
+  int col_prefilled;  // out_col already holds "slot - first slot of the minibatch" (the sampler wrote it)
   i64 buckets_cap;
   int* err;
 };
@@ -374,6 +376,7 @@ __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scat
           } else if (off < lim) {
             raise(p.err, ERRBIT_BAD_INPUT);  // negative, or not below the stated bound
             p.min_idx[sg.ibase + off] = IDX_UNSET;
+            if (off < sg.ns) p.seed_repeat[b] = 1u;  // its edges' columns relabel to -1: no shortcut
           }
         }
       }
@@ -414,6 +417,7 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
     if (cnt == 0) continue;  // uniform over the CTA
     const int b = find_segment(p.bucket_ptr, p.B, k);
     u32* out = p.min_idx + p.item_ptr[b];
+    const u32 ns = (u32)(p.seeds_ptr[b + 1] - p.seeds_ptr[b]);  // items below ns are the minibatch's seeds
     const u64* items = p.part + start;
     // table size: a power of two >= 1.5 * cnt (at most DD_TAB)
     u32 tab = 1024;
@@ -447,7 +451,10 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
         for (int u = 0; u < DD_BATCH; ++u)
           if (it[u] != ~0ull) {
             const u32 m = s_min[slot[u]];
-            if (m != (u32)it[u]) out[(u32)it[u]] = m;  // first occurrences were preset by the scatter pass
+            if (m != (u32)it[u]) {  // first occurrences were preset by the scatter pass
+              out[(u32)it[u]] = m;
+              if ((u32)it[u] < ns) p.seed_repeat[b] = 1u;
+            }
           }
         __syncthreads();
         continue;
@@ -465,7 +472,10 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
           const u32 key = (u32)(it >> 32);
           u32 pos = hash32(key) & mask;
           for (u32 probes = 0; s_key[pos] != key && probes < tab; ++probes) pos = (pos + 1) & mask;
-          if (s_min[pos] != (u32)it) out[(u32)it] = s_min[pos];
+          if (s_min[pos] != (u32)it) {
+            out[(u32)it] = s_min[pos];
+            if ((u32)it < ns) p.seed_repeat[b] = 1u;
+          }
         }
         __syncthreads();
         continue;
@@ -487,6 +497,7 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
       const u32 m = gtab_find(gt, slots, (u32)(it >> 32));
       if (m == IDX_UNSET) raise(p.err, ERRBIT_KEY_MISSING);
       out[(u32)it] = m;
+      if (m != (u32)it && (u32)it < ns) p.seed_repeat[b] = 1u;
     }
     __syncthreads();
   }
@@ -643,10 +654,14 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_RANK_MIN_CTAS) relabel_rank_ke
 }
 
 // ---------------------------------------------------------------- emit
-// Thread per edge, four edges (256 apart) per thread with their loads issued
-// together.  Position of an id = rank[first item carrying it]; for an id seen
-// for the first time on this very edge that is the edge's own item, so two
-// thirds of the gathers of a GraphSAGE layer are in fact coalesced.
+// Thread per edge, EB edges (256 apart) per thread with their loads issued together.  Position
+// of an id = rank[first item carrying it]; for an id seen for the first time on this very edge
+// that is the edge's own item, so two thirds of the gathers of a GraphSAGE layer are in fact
+// coalesced.  The COLUMN of an edge needs no table at all when the seeds of its minibatch are
+// distinct (always, from the second layer on: they are a node list): seed i is then the i-th
+// entry of the minibatch's list, i.e. the relabelled column is the column slot counted from the
+// minibatch's first slot -- which the layered sampler has already written next to the edge.
+// Only minibatches with a repeated (or invalid) seed take the two gathers per column.
 struct EdgeCursor {
   int b;
   i64 e0, e_end;   // edges of the minibatch
@@ -655,6 +670,7 @@ struct EdgeCursor {
   const u32* min_b;   // min_idx of its items
   const u32* rank_b;  // rank of its items
   u32 ns;
+  bool repeat;     // a seed of the minibatch repeats an earlier one
 };
 
 __device__ __forceinline__ void edge_cursor_load(const RelabelParams& p, EdgeCursor& c) {
@@ -665,6 +681,7 @@ __device__ __forceinline__ void edge_cursor_load(const RelabelParams& p, EdgeCur
   c.ubase = p.unique_ptr[c.b];
   c.min_b = p.min_idx + p.item_ptr[c.b];
   c.rank_b = p.rank + p.item_ptr[c.b];
+  c.repeat = p.seed_repeat[c.b] != 0u;
 }
 
 #ifndef GSB_EMIT_EB
@@ -675,6 +692,7 @@ __device__ __forceinline__ void edge_cursor_load(const RelabelParams& p, EdgeCur
 #endif
 __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_kernel(const RelabelParams p) {
   constexpr int EB = GSB_EMIT_EB;
+  constexpr u32 COL_DONE = 0xFFFFFFFEu;  // column written without a table
   const i64 n = p.hdr->n_edges;
   for (i64 e_cta = (i64)blockIdx.x * (EB * RL_THREADS); e_cta < n; e_cta += (i64)gridDim.x * (EB * RL_THREADS)) {
     EdgeCursor c;
@@ -697,29 +715,34 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
         }
         ub[u] = c.ubase; rb[u] = c.rank_b;
         m[u] = __ldg(c.min_b + c.ns + (u32)(e - c.e0));
-        const u64 lc = (u64)(__ldg(p.coo_col + e) - c.s0);  // seed slot inside the minibatch
-        if (lc < c.ns) mc[u] = __ldg(c.min_b + lc);
-        else raise(p.err, ERRBIT_BAD_INPUT);  // a column slot outside the edge's own minibatch
+        if (!c.repeat && p.col_prefilled) {
+          mc[u] = COL_DONE;
+        } else {
+          const u64 lc = (u64)(__ldg(p.coo_col + e) - c.s0);  // seed slot inside the minibatch
+          if (lc >= c.ns) raise(p.err, ERRBIT_BAD_INPUT);  // a column slot outside the edge's own minibatch
+          else if (!c.repeat) { p.out_col[e] = (i64)lc; mc[u] = COL_DONE; }
+          else mc[u] = __ldg(c.min_b + lc);
+        }
       }
     }
     u32 r[EB], rc[EB];
 #pragma unroll
     for (int u = 0; u < EB; ++u) {
       r[u] = m[u] != IDX_UNSET ? __ldg(rb[u] + m[u]) : 0;
-      rc[u] = mc[u] != IDX_UNSET ? __ldg(rb[u] + mc[u]) : 0;
+      rc[u] = mc[u] < COL_DONE ? __ldg(rb[u] + mc[u]) : 0;
     }
 #pragma unroll
     for (int u = 0; u < EB; ++u) {
       if (!live[u]) continue;
       const i64 e = e_cta + u * RL_THREADS + threadIdx.x;
       p.out_row[e] = m[u] != IDX_UNSET ? (i64)r[u] - ub[u] : -1;
-      p.out_col[e] = mc[u] != IDX_UNSET ? (i64)rc[u] - ub[u] : -1;
+      if (mc[u] != COL_DONE) p.out_col[e] = mc[u] != IDX_UNSET ? (i64)rc[u] - ub[u] : -1;
     }
   }
 }
 
 struct RelabelLayout {
-  size_t hdr, item_ptr, bucket_ptr, tile_count, bucket_start, bucket_cursor, min_idx,
+  size_t hdr, item_ptr, bucket_ptr, tile_count, bucket_start, bucket_cursor, seed_repeat, min_idx,
       rank, part, overflow, total;
   i64 tiles, buckets_cap;
 };
@@ -738,6 +761,7 @@ static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   L.tile_count = o; o = up(o + sizeof(u32) * (size_t)(L.tiles + 1));
   L.bucket_start = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
   L.bucket_cursor = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
+  L.seed_repeat = o; o = up(o + sizeof(u32) * (size_t)(B + 1));
   L.min_idx = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
   L.rank = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
   L.part = o; o = up(o + sizeof(u64) * (size_t)(items + 4));
@@ -763,19 +787,20 @@ extern "C" int gsb_batch_relabel(const int64_t* seeds, const int64_t* seeds_ptr,
                                  int64_t* out_row, int64_t* out_col, void* workspace,
                                  size_t workspace_bytes, int* d_err, void* cuda_stream) {
   return gsb::relabel_launch(seeds, seeds_ptr, B, S_max, coo_row, coo_col, edge_ptr, nullptr, nullptr,
-                             E_max, id_bound, unique, U_cap, unique_ptr, out_row, out_col, nullptr,
+                             E_max, id_bound, unique, U_cap, unique_ptr, out_row, out_col, nullptr, 0,
                              workspace, workspace_bytes, d_err, cuda_stream);
 }
 
 // `sub_indptr` non-null: edge_ptr is derived on the device (edge_ptr_out[b] =
 // sub_indptr[seeds_ptr[b]]) instead of read; `counts_out` non-null: receives
 // {seeds_ptr[B], -, unique_ptr[B]}.  Both spare the layered sampler a launch.
+// `col_prefilled`: out_col[e] already holds coo_col[e] - seeds_ptr[minibatch of e].
 int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B, int64_t S_max,
                         const int64_t* coo_row, const int64_t* coo_col, const int64_t* edge_ptr,
                         const int64_t* sub_indptr, int64_t* edge_ptr_out, int64_t E_max,
                         int64_t id_bound, int64_t* unique, int64_t U_cap, int64_t* unique_ptr,
-                        int64_t* out_row, int64_t* out_col, int64_t* counts_out, void* workspace,
-                        size_t workspace_bytes, int* d_err, void* cuda_stream) {
+                        int64_t* out_row, int64_t* out_col, int64_t* counts_out, int col_prefilled,
+                        void* workspace, size_t workspace_bytes, int* d_err, void* cuda_stream) {
   if (sub_indptr) edge_ptr = edge_ptr_out;
   if (B < 1 || S_max < 0 || E_max < 0 || !seeds_ptr || !edge_ptr || !unique_ptr || U_cap < 0)
     return GSB_ERR_INVALID;
@@ -801,9 +826,10 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   p.bucket_ptr = (i64*)(ws + L.bucket_ptr);
   p.bucket_start = (u32*)(ws + L.bucket_start); p.bucket_cursor = (u32*)(ws + L.bucket_cursor);
   p.part = (u64*)(ws + L.part); p.overflow = (u64*)(ws + L.overflow); p.buckets_cap = L.buckets_cap;
+  p.seed_repeat = (u32*)(ws + L.seed_repeat); p.col_prefilled = col_prefilled ? 1 : 0;
 
   { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
-  // bucket counts and cursors are adjacent: one clear
+  // bucket counts, cursors and the repeated-seed flags are adjacent: one clear
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_start, 0, L.min_idx - L.bucket_start, st));
   const i64 items_max = S_max + E_max;
   const int wide = sm_count() * GSB_RL_WIDE;

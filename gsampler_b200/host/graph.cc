@@ -123,6 +123,12 @@ Graph::GraphPtr Graph::Derive(int64_t rows, int64_t cols) const {
 }
 
 uint32_t Graph::NextStream() { return (*stream_counter_)++; }
+// `n` consecutive streams (one per layer of a whole-sampler call); returns the first
+uint32_t Graph::NextStreams(uint32_t n) {
+  const uint32_t first = *stream_counter_;
+  *stream_counter_ += n;
+  return first;
+}
 
 // Lazy format conversion (src/graph.cc:22-49, src/graph_ops.cc:14-61).
 void Graph::CreateSparseFormat(int64_t format) {

@@ -128,6 +128,11 @@ class Graph : public torch::CustomClassHolder {
   }
   int64_t GetSeed() { return (int64_t)seed_; }
   uint64_t GetSeedU64() const { return seed_; }
+  // The call counter that selects the random stream of the next operator.  Together with the seed
+  // it is the whole random state of a graph and its descendants: a loop that is checkpointed saves
+  // both and restores them to resume with the draws it would have made.
+  int64_t GetStreamCounter() { return (int64_t)*stream_counter_; }
+  void SetStreamCounter(int64_t counter) { *stream_counter_ = (uint32_t)counter; }
   // Whole L-layer GraphSAGE super-batch sampler in one call (no counterpart in
   // the reference, which composes it from per-layer operators).
   std::vector<torch::Tensor> BatchGraphSAGE(torch::Tensor seeds, torch::Tensor seeds_ptr,
@@ -143,6 +148,7 @@ class Graph : public torch::CustomClassHolder {
  private:
   GraphPtr Derive(int64_t rows, int64_t cols) const;
   uint32_t NextStream();
+  uint32_t NextStreams(uint32_t n);
   torch::Tensor MapThroughEids(const c10::optional<torch::Tensor>& e_ids, torch::Tensor select);
   // returns (sub_indptr, rows, cols, select) of a sample/slice over `src`
   std::tuple<torch::Tensor, torch::Tensor, torch::Tensor, torch::Tensor> SampleCompressed(

@@ -82,7 +82,7 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGEAsync(torch::Tensor seeds, torch
   CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype, num_cols_,
                                    std::max(num_rows_, num_cols_), P(seeds),
                                    P(seeds_ptr), B, S0, L, fanouts.data(), GetSeedU64(),
-                                   bufs.data(), counts.data_ptr<int64_t>(), ws, ws_bytes,
+                                   NextStreams((uint32_t)L), bufs.data(), counts.data_ptr<int64_t>(), ws, ws_bytes,
                                    (int*)(counts.data_ptr<int64_t>() + 3 * L), CurrentStream()),
               "graphsage_sample");
   // every returned tensor is a view of the one arena (which therefore lives as long as any

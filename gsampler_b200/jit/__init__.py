@@ -1,31 +1,11 @@
-"""``compile``: entry point with the call signature of gSampler's ``gs.jit.compile``
-(python/gs/jit/module.py:191-266).
+"""``gsampler_b200.jit``: trace a sampler written against ``Matrix`` / ``BatchMatrix`` with
+torch.fx, rewrite the trace (common subexpressions, relabel + node list merged, slicing + sampling
+fused, square + sum fused, paired edge maps merged, a whole GraphSAGE super-batch sampler turned
+into one native call), choose sparse formats by measurement, and run the result -- the role of
+``gs.jit`` in gSampler (python/gs/jit/{trace,optimize,module}.py), written anew for this
+package's operators."""
+from . import passes
+from .module import compile  # noqa: A001
+from .trace import SamplerTracer, trace_sampler
 
-gSampler traces the sampler with torch.fx and rewrites the graph (merge relabel + all_nodes,
-fuse slicing + sampling, batch fusion: python/gs/jit/optimize.py:124-325).  Here the same
-fusions happen at run time inside the operators -- a column slice stays lazy until it is
-known whether a sampling call follows (then one fused kernel runs), and ``all_nodes`` /
-``to_dgl_block`` on the same matrix share one relabel pass -- so the compiled callable is
-the user's function itself, bound to a warm-up run that validates it on the example
-arguments.  ``try_compact`` / ``format_select`` / ``must_compact`` are accepted for source
-compatibility; format selection is fixed (CSC for column operators, COO for edge maps).
-"""
-from __future__ import annotations
-
-
-class compile(object):  # noqa: N801  (name kept from the reference API)
-
-    def __init__(self, func, args, try_compact=True, format_select=True, must_compact=False,
-                 warmup=False):
-        self.func = func
-        self.try_compact = try_compact
-        self.format_select = format_select
-        self.must_compact = must_compact
-        if warmup:
-            func(*args)
-
-    def __call__(self, *args):
-        return self.func(*args)
-
-
-__all__ = ["compile"]
+__all__ = ["compile", "passes", "SamplerTracer", "trace_sampler"]

@@ -15,7 +15,11 @@ import torch
 from ..format import _COO, _CSC, _CSR
 from ..ops import gsddmm, gspmm
 from ..utils import create_block_from_coo
+from . import matrix as _matrix
 from .matrix import Matrix, data_index
+
+torch.fx.wrap("batch_gen_block")
+torch.fx.wrap("data_index")
 
 
 def batch_gen_block(frontier_list, coo_row_list, coo_col_list, coo_eids, coo_ptr, edata, col_counts):
@@ -102,17 +106,18 @@ class BatchMatrix(Matrix):
             ret.col_ndata["_ID"] = c_slice
             for key, value in self.col_ndata.items():
                 ret.col_ndata[key] = value[c_slice]
-            if self.encoding:
-                graph, edge_index = self._graph._CAPI_BatchColSlicing(c_slice, c_ptr, True)
-                if "_ID" in self.row_ndata:
-                    raise NotImplementedError
-                row_ids, _ = graph._CAPI_BatchGetRows()
-                ret.row_ndata["_ID"] = row_ids
+            if self.encoding or not _matrix._LAZY_SLICE[0]:
+                graph, edge_index = self._graph._CAPI_BatchColSlicing(c_slice, c_ptr, self.encoding)
+                if self.encoding:
+                    if "_ID" in self.row_ndata:
+                        raise NotImplementedError
+                    row_ids, _ = graph._CAPI_BatchGetRows()
+                    ret.row_ndata["_ID"] = row_ids
                 ret._graph = graph
                 for key, value in self.edata.items():
                     ret._edata[key] = data_index(value, edge_index)
             else:
-                ret._pending = (self._graph, c_slice, self.edata)
+                ret._pending = (self._graph, c_slice, dict(self.edata))
                 ret._pending_ptr = c_ptr
             for key, value in self.row_ndata.items():
                 ret.row_ndata.setdefault(key, value)
@@ -137,7 +142,7 @@ class BatchMatrix(Matrix):
         ret.row_ndata = self.row_ndata
         ret.col_ndata = self.col_ndata
         for key, value in src_edata.items():
-            ret._edata[key] = value[edge_index]
+            ret._edata[key] = data_index(value, edge_index)
         return ret
 
     def collective_sampling(self, K, probs, probs_ptr, replace):

@@ -21,6 +21,23 @@ from ..format import _COO, _CSC, _CSR
 from ..ops import gsddmm, gspmm
 from ..utils import Block, create_block_from_coo
 
+# Helpers that work on real tensors are leaves for ``gsampler_b200.jit``'s tracer (one
+# call_function node each), as in python/gs/matrix_api/matrix.py:12-16 of gSampler.
+torch.fx.wrap("create_block_from_coo")
+torch.fx.wrap("assign_block")
+torch.fx.wrap("data_index")
+torch.fx.wrap("null_ids")
+
+# While ``gsampler_b200.jit.compile`` traces a sampler the column slice is NOT lazy: the trace
+# then holds the elementary operators and the fusion is the passes' job.
+_LAZY_SLICE = [True]
+
+
+def null_ids(graph=None):
+    """The empty id tensor that stands for "no explicit row / column ids".  ``graph`` is unused; a
+    traced sampler passes its graph so that the call is recorded instead of run while tracing."""
+    return torch.empty(0, dtype=torch.int64, device="cuda")
+
 
 def data_index(data, index):
     """``data[index]``; data kept in pinned host memory is gathered in place by a kernel
@@ -81,7 +98,7 @@ class Matrix(object):
 
     @property
     def null_tensor(self):
-        return torch.empty(0, dtype=torch.int64, device="cuda")
+        return null_ids(self._g)
 
     def _new(self) -> "Matrix":
         return Matrix()
@@ -109,11 +126,11 @@ class Matrix(object):
     def __getitem__(self, data) -> "Matrix":
         assert len(data) == 2
         r_slice, c_slice = data
-        has_c = isinstance(c_slice, torch.Tensor)
-        has_r = isinstance(r_slice, torch.Tensor)
+        has_c = isinstance(c_slice, (torch.Tensor, torch.fx.Proxy))   # a Proxy while being traced
+        has_r = isinstance(r_slice, (torch.Tensor, torch.fx.Proxy))
         ret = self._new()
 
-        if has_c and not has_r and not self._compact:
+        if has_c and not has_r and not self._compact and _LAZY_SLICE[0]:
             # lazy column slice
             if "_ID" not in self.col_ndata:
                 ret.col_ndata["_ID"] = c_slice
@@ -121,7 +138,7 @@ class Matrix(object):
                 ret.col_ndata[key] = value[c_slice]
             for key, value in self.row_ndata.items():
                 ret.row_ndata[key] = value
-            ret._pending = (self._graph, c_slice, self.edata)
+            ret._pending = (self._graph, c_slice, dict(self.edata))
             return ret
 
         graph = self._graph
@@ -174,7 +191,7 @@ class Matrix(object):
         ret.row_ndata = self.row_ndata
         ret.col_ndata = self.col_ndata
         for key, value in src_edata.items():
-            ret._edata[key] = value[edge_index]
+            ret._edata[key] = data_index(value, edge_index)
         return ret
 
     def collective_sampling(self, K: int, probs: Optional[torch.Tensor], replace: bool):

@@ -10,8 +10,12 @@ __all__ = ["gsddmm"]
 
 target_mapping = {"u": 0, "e": 1, "v": 2, "src": 0, "edge": 1, "dst": 2}
 
+# leaves for gsampler_b200.jit's tracer
+torch.fx.wrap("sddmm_prepare")
+torch.fx.wrap("sddmm_finish")
 
-def _prepare(num_edges, op, lhs_data, rhs_data):
+
+def sddmm_prepare(num_edges, op, lhs_data, rhs_data):
     if op not in ("copy_lhs", "copy_rhs"):
         lhs_data, rhs_data = pad_ranks(lhs_data, rhs_data)
     op, rhs_data = rewrite_op(op, rhs_data)
@@ -34,9 +38,14 @@ def _prepare(num_edges, op, lhs_data, rhs_data):
     return op, lhs, rhs, out, squeeze
 
 
+def sddmm_finish(out, squeeze):
+    return out.squeeze(-1) if squeeze else out
+
+
 def gsddmm(g, op, lhs_data, rhs_data, lhs_target="u", rhs_target="v", on_format=_COO):
     graph = g._graph
-    op, lhs, rhs, out, squeeze = _prepare(graph._CAPI_GetNumEdges(), op, lhs_data, rhs_data)
-    graph._CAPI_SDDMM(op, lhs, rhs, out, target_mapping[lhs_target], target_mapping[rhs_target],
-                      on_format)
-    return out.squeeze(-1) if squeeze else out
+    prep = sddmm_prepare(graph._CAPI_GetNumEdges(), op, lhs_data, rhs_data)
+    # (op, lhs, rhs, out, squeeze); indexed, not unpacked, so that a trace records it
+    graph._CAPI_SDDMM(prep[0], prep[1], prep[2], prep[3], target_mapping[lhs_target],
+                      target_mapping[rhs_target], on_format)
+    return sddmm_finish(prep[3], prep[4])

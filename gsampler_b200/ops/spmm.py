@@ -6,8 +6,12 @@ from ._shapes import as_2d, broadcast_shape, check_pair, pad_ranks, rewrite_op
 
 __all__ = ["gspmm"]
 
+# leaves for gsampler_b200.jit's tracer: operand preparation works on real tensors and shapes
+torch.fx.wrap("spmm_prepare")
+torch.fx.wrap("spmm_finish")
 
-def _prepare(num_rows, num_cols, op, reduce_op, lhs_data, rhs_data, lhs_target):
+
+def spmm_prepare(num_rows, num_cols, op, reduce_op, lhs_data, rhs_data, lhs_target):
     if op not in ("copy_lhs", "copy_rhs"):
         lhs_data, rhs_data = pad_ranks(lhs_data, rhs_data)
     op, rhs_data = rewrite_op(op, rhs_data)
@@ -36,9 +40,14 @@ def _prepare(num_rows, num_cols, op, reduce_op, lhs_data, rhs_data, lhs_target):
     return op, u, e, v, arg_u, arg_e, squeeze
 
 
+def spmm_finish(v, squeeze):
+    return v.squeeze(-1) if squeeze else v
+
+
 def gspmm(g, op, reduce_op, lhs_data, rhs_data, lhs_target, on_format):
     graph = g._graph
-    op, u, e, v, arg_u, arg_e, squeeze = _prepare(graph._CAPI_GetNumRows(), graph._CAPI_GetNumCols(),
-                                                 op, reduce_op, lhs_data, rhs_data, lhs_target)
-    graph._CAPI_SpMM(op, reduce_op, u, e, v, arg_u, arg_e, lhs_target, on_format)
-    return v.squeeze(-1) if squeeze else v
+    prep = spmm_prepare(graph._CAPI_GetNumRows(), graph._CAPI_GetNumCols(), op, reduce_op, lhs_data,
+                        rhs_data, lhs_target)
+    # (op, u, e, out, arg_u, arg_e, squeeze); indexed, not unpacked, so that a trace records it
+    graph._CAPI_SpMM(prep[0], reduce_op, prep[1], prep[2], prep[3], prep[4], prep[5], lhs_target, on_format)
+    return spmm_finish(prep[3], prep[6])

@@ -344,7 +344,8 @@ GSB_API int gsb_u_op_v_pair(const int64_t* row, const int64_t* col, const int64_
  * candidates without replacement -- uniformly (probs NULL) or with weights
  * probs[R] (A-Res keys; weight <= 0 is chosen last) -- and write their
  * positions to out_idx (weighted: ascending; uniform: reservoir slot order, as
- * the reference's ListSampling); out_range[B+1] = offsets of the picks.  R
+ * the reference's ListSampling); out_range[B+1] = offsets of the picks.  range[0]
+ * must be 0 (anything else sets GSB_ERRBIT_BAD_INPUT).  R
  * bounds range[B]; out_idx holds min(R, B * K) entries.  Replaces ListSampling / ListSamplingProbs /
  * BatchListSamplingProbs without replacement (src/cuda/list_sampling.cu:20-73,
  * src/cuda/list_sampling_probs.cu:11-89, src/cuda/batch/list_sampling_probs.cu:29-107),
@@ -394,6 +395,9 @@ GSB_API int gsb_node2vec(const int64_t* indptr, const void* indices, int indices
  * .. 3*l+2] = {S_l, E_l, U_l}.  S0 is an upper bound of the seed count; the
  * live count is seeds_ptr[B], read on the device, so the same launch sequence
  * (e.g. a recorded CUDA graph) serves shorter super-batches too.
+ * Layer l draws from the random stream (seed, stream_base + l): a caller that wants different
+ * draws from one call to the next advances stream_base by num_layers per call (the reference
+ * seeds every call with the same constant, src/cuda/fusion/slice_sampling.cu:154).
  * num_cols = columns of the graph (every layer's seeds are checked against it:
  * on a graph with more rows than columns a sampled row id may not be a valid
  * column); id_bound = exclusive bound of the row ids, for the relabel stage.
@@ -418,7 +422,7 @@ GSB_API int gsb_graphsage_sample(const int64_t* indptr, const void* indices, int
                                  int64_t num_cols, int64_t id_bound, const int64_t* seeds,
                                  const int64_t* seeds_ptr,
                                  int64_t B, int64_t S0, int num_layers, const int64_t* fanouts,
-                                 uint64_t seed, const gsb_layer_buffers* layers,
+                                 uint64_t seed, uint32_t stream_base, const gsb_layer_buffers* layers,
                                  int64_t* d_counts, void* workspace, size_t workspace_bytes,
                                  int* d_err, void* cuda_stream);
 

@@ -326,7 +326,7 @@ def node2vec_spec(indptr, indices, seeds, L, p, q, seed=0, stream=0):
 
 
 # --------------------------------------------------------------------------- composed samplers
-def graphsage_batch(indptr, indices, seeds, seeds_ptr, fanouts, seed=0, sampler="spec"):
+def graphsage_batch(indptr, indices, seeds, seeds_ptr, fanouts, seed=0, sampler="spec", stream_base=0):
     """The super-batch GraphSAGE sampler of examples/graphsage/graphsage_e2e.py:37-44
     (A[:, seeds::ptr] -> individual_sampling -> all_nodes -> to_dgl_block per layer),
     executed stage by stage with the restated operators.  Returns one dict per layer."""
@@ -334,7 +334,7 @@ def graphsage_batch(indptr, indices, seeds, seeds_ptr, fanouts, seed=0, sampler=
     layers = []
     for li, K in enumerate(fanouts):
         if sampler == "spec":
-            sip, rows, cols, sel = sample_spec(indptr, indices, seeds, K, False, seed, li)
+            sip, rows, cols, sel = sample_spec(indptr, indices, seeds, K, False, seed, stream_base + li)
         else:
             sip, rows, cols, sel = sample_ref(indptr, indices, seeds, K, False)
         edge_ptr = sip[seeds_ptr]                      # batch_graph.cc:203

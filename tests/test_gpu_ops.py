@@ -426,7 +426,9 @@ def test_node2vec_sampler_api(gsb, oracle, graph):
     def node2vec_sampler(A, seeds, walk_length, p, q):
         return A.node2vec(seeds, walk_length, p, q)
 
-    fn = gsb.jit.compile(func=node2vec_sampler, args=(m, cuda(seeds), 80, 2.0, 0.5))
+    # (no timing runs at compile time, so that the first call draws from the graph's stream 0)
+    fn = gsb.jit.compile(func=node2vec_sampler, args=(m, cuda(seeds), 80, 2.0, 0.5), try_compact=False,
+                         format_select=False)
     paths = fn(m, cuda(seeds), 80, 2.0, 0.5)
     srt = oracle.sort_indices(indptr, indices)
     assert np.array_equal(host(paths).reshape(-1), oracle.node2vec_spec(indptr, srt, seeds, 80, 2.0, 0.5, 5, 0))

@@ -326,23 +326,32 @@ def test_node2vec_second_order_bias_against_reference(gsb, ref, p, q):
     from scipy import stats
 
     rng = np.random.default_rng(12)
-    n = 300
+    n, reps = 300, 20000
     adj = rng.random((n, n)) < 0.06
     adj = np.triu(adj, 1)
     adj = adj | adj.T                                       # symmetric, no self-loops: triangles exist
-    deg = adj.sum(0)
+    # The reference starts every walker's "previous node" at its thread index and looks that index
+    # up in the offsets (node2vec.cu:88,113 -> CheckConnect :46-64) without a bound: with more
+    # walkers than nodes it reads past the end of the arrays (an illegal access was seen on the
+    # GPU with 20 000 walkers on the 300-node graph alone).  So the graph gets one node per walker,
+    # the extra ones on a ring so that every node has neighbours and every lookup stays in bounds.
+    N = reps + 1000
+    cols = [np.flatnonzero(adj[:, c]) for c in range(n)]
+    for c in range(n, N):
+        cols.append(np.array(sorted({n + (c - n - 1) % (N - n), n + (c - n + 1) % (N - n)})))
+    deg = np.array([c.size for c in cols])
     indptr = np.concatenate([[0], np.cumsum(deg)]).astype(np.int64)
-    indices = np.concatenate([np.flatnonzero(adj[:, c]) for c in range(n)]).astype(np.int64)  # sorted columns
-    v = int(np.argmax(deg))
-    reps = 20000
+    indices = np.concatenate(cols).astype(np.int64)         # sorted columns
+    v = int(np.argmax(deg[:n]))
     start = cuda(np.full(reps, v))
     ours = host(new_graph(gsb, indptr, indices, seed=41)._CAPI_Node2Vec(start, 2, p, q)).reshape(3, reps)
     theirs = host(ref.node2vec(start, 2, cuda(indices), cuda(indptr), p, q)).reshape(3, reps)
-    nbr_v = adj[:, v]
+    nbr_v = np.zeros(N, bool)
+    nbr_v[:n] = adj[:, v]
     tables = []
     for tr in (ours, theirs):
-        assert np.all(tr[0] == v) and np.all(adj[tr[1], v])            # step 1 follows an edge into v's list
-        assert np.all(adj[tr[2], tr[1]])                               # and so does step 2
+        assert np.all(tr[0] == v) and np.all(tr[1] < n) and np.all(adj[tr[1], v])   # step 1 follows an edge into v's list
+        assert np.all(tr[2] < n) and np.all(adj[tr[2], tr[1]])                      # and so does step 2
         cls = np.where(tr[2] == v, 0, np.where(nbr_v[tr[2]], 1, 2))    # return / neighbour of v / other
         tables.append(np.bincount(cls, minlength=3))
     chi2, pval, _, _ = stats.chi2_contingency(np.stack(tables))
@@ -351,13 +360,22 @@ def test_node2vec_second_order_bias_against_reference(gsb, ref, p, q):
     firsts = np.stack([np.bincount(np.searchsorted(indices[indptr[v]:indptr[v + 1]], tr[1]), minlength=deg[v])
                        for tr in (ours, theirs)])
     assert stats.chi2_contingency(firsts)[1] > 0.01
-    # direction of the bias: the unbiased walk returns with probability mean(1/deg(c)) over c in N(v)
-    unbiased_return = float(np.mean(1.0 / deg[indices[indptr[v]:indptr[v + 1]]]))
-    frac_return = tables[0][0] / reps
-    if p > 1:      # weight p on the return candidate (the reference accepts y < h with h = p)
-        assert frac_return > 1.3 * unbiased_return
-    else:
-        assert frac_return < 0.7 * unbiased_return
+    # both against the exact class probabilities of the rule (node2vec.cu:99-127): y is uniform on
+    # {0 .. max(p,q)-1} (integer max here), a candidate is accepted iff y < min(p,q,1) or y < h
+    # with h = p for a return, q for a neighbour of the previous node, 1 otherwise
+    ms = int(max(p, q))
+    accept = {k: np.ceil(min(max(h, min(p, q, 1.0)), ms)) / ms for k, h in ((0, p), (1, q), (2, 1.0))}
+    expect = np.zeros(3)
+    for c in indices[indptr[v]:indptr[v + 1]]:
+        cand = indices[indptr[c]:indptr[c + 1]]
+        if cand.size == 1:
+            w = np.ones(1)
+        else:
+            w = np.array([accept[0 if x == v else (1 if nbr_v[x] else 2)] for x in cand])
+        cls = np.where(cand == v, 0, np.where(nbr_v[cand], 1, 2))
+        expect += np.bincount(cls, weights=w / w.sum(), minlength=3) / deg[v]
+    for t in tables:
+        assert stats.chisquare(t, expect * reps).pvalue > 0.001, (t, expect * reps)
 
 
 def test_sampler_chi_square_grid_against_reference_sampler(gsb, ref):

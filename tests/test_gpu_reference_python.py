@@ -158,7 +158,6 @@ def test_reference_python_ladies_compile(gs, oracle, graph):
     compiled = gs.jit.compile(func=ladies_sampler, args=(m, cuda(seeds), fanouts))
     targets = [str(nd.target) for nd in compiled.gm.graph.nodes]
     assert targets.count("_CAPI_FusedESquareSum") == len(fanouts)                       # the e^2 + sum pass fired
-    col_of_edge = np.repeat(np.arange(n), np.diff(indptr))
     for fn in (ladies_sampler, compiled):
         inp, outp, blocks = fn(m, cuda(seeds), fanouts)
         cur = seeds
@@ -180,9 +179,14 @@ def test_reference_python_ladies_compile(gs, oracle, graph):
             got_key = col.astype(np.int64) * n + g_row
             order = np.argsort(got_key)
             assert np.array_equal(got_key[order], want_key)
-            w1 = w[pos][keep].astype(np.float64) / p[indices[pos][keep]]
+            # What the reference's Python layer really asks the library for: gs.ops.gsddmm turns
+            # "div" into a multiplication by the reciprocal inside _before_sddmm but then passes
+            # the ORIGINAL op string on (python/gs/ops/sddmm.py:23-25 vs :111-113), so the library
+            # is called as div(lhs, 1 / rhs) = lhs * rhs.  The library must do exactly what it is
+            # asked, as the reference's SDDMMCOO does; this repository's own Matrix.div divides.
+            w1 = w[pos][keep].astype(np.float64) * p[indices[pos][keep]]
             colsum = np.bincount(slot[keep], weights=w1, minlength=cur.size)
-            w2 = w1 / colsum[slot[keep]]
+            w2 = w1 * colsum[slot[keep]]
             want_order = np.argsort(slot[keep] * n + indices[pos][keep])
             # three chained fp32 stages of 1e-5 each
             assert np.allclose(got_w[order], w2[want_order], rtol=3e-5, atol=1e-9)
@@ -190,4 +194,3 @@ def test_reference_python_ladies_compile(gs, oracle, graph):
             assert np.array_equal(uq, e_uq) and np.array_equal(row, e_row) and np.array_equal(col, e_col)
             cur = uq
         assert np.array_equal(host(outp), cur)
-    del col_of_edge
