@@ -520,8 +520,10 @@ class SageWorkload(object):
             # the sampling kernel also writes the block's column ids (8E), see DESIGN.md
             "sample_tile": (8 * S + 16 * S + w_idx * E + 8 * (S + 1) + 32 * E).mean(),
             "relabel_pcount": (8 * (S + E)).mean(), "relabel_scatter": (8 * (S + E)).mean(),
-            "relabel_dedupe": (8 * (S + E)).mean(), "relabel_rank": (8 * (S + E) + 8 * U).mean(),
-            "relabel_emit": (8 * E + 8 * E).mean(),
+            "relabel_dedupe": (8 * (S + E)).mean(), "relabel_mark": (4 * (S + E)).mean(),
+            # one pass over the items: min_idx (4) and the ids of first occurrences (8U) in, node
+            # list (8U) and relabelled rows (8E) out
+            "relabel_emit": (4 * (S + E) + 16 * U + 8 * E).mean(),
         }.get(dname, 0.0)
         dur_s = dms / dcnt / 1e3
         achieved = per_launch / dur_s / 1e9 if dur_s > 0 else 0.0

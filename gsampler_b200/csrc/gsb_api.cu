@@ -16,7 +16,7 @@ static thread_local const char* g_last_cuda_error = "";
 static const char* const kKernelNames[KID_NUM] = {
     "sample_tile", "sample_probs", "count", "slice_fill", "gather", "expand_indptr",
     "indptr_from_sorted", "relabel_setup", "relabel_pcount", "relabel_pscan", "relabel_scatter",
-    "relabel_dedupe", "relabel_count", "relabel_tiles", "relabel_rank", "relabel_emit",
+    "relabel_dedupe", "relabel_mark", "relabel_prefix", "relabel_rank", "relabel_emit",
     "slice_rows", "edge_sum", "edge_op", "list_sample", "walk", "sort", "sample_probs_short",
     "sample_probs_long", "misc"};
 

@@ -23,14 +23,17 @@
 //             the shared table falls back to a table in global memory that
 //             the CTA owns                                        (streaming
 //             read + one scattered 4-byte store per repeat)
-//   count   : number of first occurrences per 1024-item tile      (streaming)
-//   tiles   : exclusive scan of those counts                      (one block)
-//   rank    : first occurrences get their position in `unique`    (streaming)
-//   emit    : every edge reads rank[first item of its row id] and of its
-//             column's seed -> relabelled COO                     (streaming +
-//             one gather for ids seen before)
-// No CTA ever waits for another (a chained tile prefix inside the rank pass
-// measured 0.38 ms against 0.20 + 0.07 ms for count + tiles + rank).
+//   mark    : one bit per item: "is a first occurrence"           (streaming)
+//   prefix  : first occurrences before every 32-item word of that bit array
+//             (popcounts + chained prefix; 1/32 of a word per item)
+//   emit    : one pass over the items: node lists, their offsets, and for
+//             the items that are edges the relabelled row (position of the
+//             id's first item, from the two small arrays above, which stay
+//             in L2) and column                                    (streaming)
+// Only the prefix pass has CTAs that wait for one another (a bounded chained
+// prefix over a few hundred CTAs).  An earlier version kept a 4-byte rank per
+// item: count + scan + rank + emit measured 0.40 ms per step on the benchmark
+// against 0.30 for mark + prefix + emit.
 #include "gsb_common.cuh"
 
 namespace gsb {
@@ -59,9 +62,6 @@ constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
 #ifndef GSB_RL_BK
 #define GSB_RL_BK 64
 #endif
-#ifndef GSB_RL_EMIT
-#define GSB_RL_EMIT 16
-#endif
 #ifndef GSB_BUCKET_ITEMS
 #define GSB_BUCKET_ITEMS 3584
 #endif
@@ -70,9 +70,6 @@ constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
 #endif
 #ifndef GSB_DD_MIN_CTAS
 #define GSB_DD_MIN_CTAS 3
-#endif
-#ifndef GSB_RANK_MIN_CTAS
-#define GSB_RANK_MIN_CTAS 8
 #endif
 #ifndef GSB_SCATTER_MIN_CTAS
 #define GSB_SCATTER_MIN_CTAS 2
@@ -89,6 +86,7 @@ struct RelabelHeader {
   i64 n_seeds;
   i64 n_tiles;
   i64 n_buckets;
+  i64 n_unique;  // first occurrences of the call (written by the prefix pass)
 };
 
 struct RelabelParams {
@@ -110,9 +108,11 @@ struct RelabelParams {
   i64* out_col;
   RelabelHeader* hdr;
   i64* item_ptr;      // [B+1] start of minibatch b in the interleaved item order
-  u32* tile_count;    // [tiles+1] first occurrences per tile, then their exclusive scan
   u32* min_idx;       // [items] smallest item index carrying the item's id
-  u32* rank;          // [items] position in `unique`, valid for first occurrences
+  u32* first_bits;    // [items / 32] bit g % 32 of word g / 32: item g is a first occurrence
+  u32* word_prefix;   // [items / 32] first occurrences before the word
+  u64* pf_status;     // chained-prefix words of the prefix pass (zeroed)
+  int* pf_ticket;     // its CTA ticket (zeroed)
   i64* bucket_ptr;    // [B+1] first bucket of minibatch b
   u32* bucket_start;  // [buckets+1] counts, then their exclusive scan (positions in `part`)
   u32* bucket_cursor; // [buckets] fill level during the scatter pass
@@ -177,6 +177,7 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
     p.hdr->n_seeds = n_items == 0 ? 0 : n_seeds;
     p.hdr->n_tiles = (n_items + RL_TILE - 1) / RL_TILE;
     p.hdr->n_buckets = n_items == 0 ? 0 : s_carry_bk;
+    p.hdr->n_unique = 0;
   }
 }
 
@@ -503,12 +504,19 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
   }
 }
 
-// ---------------------------------------------------------------- count / tiles / rank
-// Tile layout of count and rank: warp w owns 128 consecutive items, lane l
-// handles items w*128 + j*32 + l (j = 0..3), so every load/store instruction
-// of a warp touches 32 consecutive items and ranks follow from warp ballots.
-// A lane follows the minibatch of its items with a cursor that is loaded once
-// per warp and only moves at a minibatch boundary.
+// ---------------------------------------------------------------- mark / prefix / emit
+// After the dedupe pass min_idx says, for every item, which item carries its id first.  The
+// position of a first occurrence in `unique` is the number of first occurrences before it, so:
+//   mark   : one bit per item, "is a first occurrence", 32 items per word (a warp ballot);
+//   prefix : word_prefix[w] = first occurrences in all words before w (popcounts, block scan,
+//            chained prefix across CTAs) -- the position of ANY item g is then
+//            word_prefix[g / 32] + popc(bits[g / 32] below bit g % 32): two loads from arrays of
+//            one bit and one 32nd of a word per item, which stay in L2;
+//   emit   : one pass over the items writes `unique` (first occurrences, in order), the offsets of
+//            the node lists and, for the items that are edges, the relabelled row (and column).
+// Items are laid out so that warp w of a 1024-item tile owns 128 consecutive items and lane l
+// handles items w*128 + j*32 + l (j = 0..3): every load / store instruction of a warp touches 32
+// consecutive items and a ballot is exactly one word of the bit array.
 struct ItemCursor {
   int b;
   i64 ibase, iend;
@@ -529,55 +537,102 @@ __device__ __forceinline__ ItemCursor cursor_at(const RelabelParams& p, i64 g) {
   return c;
 }
 
-// Number of first occurrences (min_idx[item] == the item's own index) of every
-// RL_TILE-item tile.
-__global__ void __launch_bounds__(RL_THREADS) relabel_count_kernel(const RelabelParams p) {
-  __shared__ int s_warp[RL_THREADS / 32];
+__global__ void __launch_bounds__(RL_THREADS) relabel_mark_kernel(const RelabelParams p) {
   const i64 n = p.hdr->n_items;
   const i64 tile = blockIdx.x;
   if (tile >= p.hdr->n_tiles) return;
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   const i64 g_warp = tile * RL_TILE + (i64)wid * (32 * RL_ITEMS);
+  if (g_warp >= n) return;  // whole warp
   u32 m[RL_ITEMS];
 #pragma unroll
   for (int j = 0; j < RL_ITEMS; ++j) {
     const i64 g = g_warp + j * 32 + lane;
     m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
   }
-  int firsts = 0;
-  if (g_warp < n) {
-    ItemCursor c = cursor_at(p, g_warp);
+  ItemCursor c = cursor_at(p, g_warp);
+  u32 mine = 0;
 #pragma unroll
-    for (int j = 0; j < RL_ITEMS; ++j) {
-      const i64 g = g_warp + j * 32 + lane;
-      if (g < n) {
-        cursor_seek(p, c, g);
-        firsts += m[j] == (u32)(g - c.ibase);
-      }
+  for (int j = 0; j < RL_ITEMS; ++j) {
+    const i64 g = g_warp + j * 32 + lane;
+    bool first = false;
+    if (g < n) {
+      cursor_seek(p, c, g);
+      first = m[j] == (u32)(g - c.ibase);
     }
+    const u32 word = __ballot_sync(0xffffffffu, first);
+    if (lane == j) mine = word;
   }
-#pragma unroll
-  for (int d = 16; d > 0; d >>= 1) firsts += __shfl_xor_sync(0xffffffffu, firsts, d);
-  if (lane == 0) s_warp[wid] = firsts;
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    int t = 0;
-#pragma unroll
-    for (int w = 0; w < RL_THREADS / 32; ++w) t += s_warp[w];
-    p.tile_count[tile] = (u32)t;
-  }
+  if (lane < RL_ITEMS) p.first_bits[(g_warp >> 5) + lane] = mine;  // words past n hold zeros
 }
 
-// One block: tile_count <- exclusive scan (the entry after the last tile
-// receives the total).
-__global__ void relabel_tiles_kernel(const RelabelParams p) {
+constexpr int PF_THREADS = 256;
+constexpr int PF_WORDS = PF_THREADS * 4;  // words per CTA: 32 768 items
+
+// word_prefix over the whole bit array; the CTA that owns the last word also stores the number
+// of first occurrences of the call and checks it against the capacity of `unique`.
+__global__ void __launch_bounds__(PF_THREADS) relabel_prefix_kernel(const RelabelParams p) {
   __shared__ i64 s_scan[34];
-  const i64 total = scan_in_place(p.tile_count, p.hdr->n_tiles, s_scan);
-  if (threadIdx.x == 0 && (total > p.U_cap || total >= 0x7FFFFFFFll)) raise(p.err, ERRBIT_CAPACITY);
+  __shared__ int s_tile;
+  __shared__ i64 s_base;
+  if (threadIdx.x == 0) s_tile = atomicAdd(p.pf_ticket, 1);
+  __syncthreads();
+  const int cta = s_tile;
+  const i64 n_words = (p.hdr->n_items + 31) >> 5;
+  const i64 n_ctas = n_words == 0 ? 1 : (n_words + PF_WORDS - 1) / PF_WORDS;
+  if (cta >= n_ctas) return;
+  const i64 w0 = (i64)cta * PF_WORDS + (i64)threadIdx.x * 4;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (w0 < n_words) v = *reinterpret_cast<const uint4*>(p.first_bits + w0);  // padded to a multiple of 4 words
+  const u32 c0 = __popc(v.x), c1 = __popc(v.y), c2 = __popc(v.z), c3 = __popc(v.w);
+  i64 total;
+  const i64 ex = block_exclusive_scan((i64)(c0 + c1 + c2 + c3), s_scan, &total);
+  if (threadIdx.x < 32) {
+    const i64 base = chained_exclusive_prefix(p.pf_status, cta, total, p.err);
+    if (threadIdx.x == 0) s_base = base;
+  }
+  __syncthreads();
+  const u32 run = (u32)(s_base + ex);
+  if (w0 < n_words)
+    *reinterpret_cast<uint4*>(p.word_prefix + w0) = make_uint4(run, run + c0, run + c0 + c1, run + c0 + c1 + c2);
+  if (cta == n_ctas - 1 && threadIdx.x == 0) {
+    const i64 grand = s_base + total;
+    p.hdr->n_unique = grand;
+    if (grand > p.U_cap || grand >= 0x7FFFFFFFll) raise(p.err, ERRBIT_CAPACITY);
+  }
 }
 
-__global__ void __launch_bounds__(RL_THREADS, GSB_RANK_MIN_CTAS) relabel_rank_kernel(const RelabelParams p) {
-  __shared__ int s_warp[RL_THREADS / 32];
+// number of first occurrences before item g (= position in `unique` of a first occurrence g)
+__device__ __forceinline__ u32 position_of(const RelabelParams& p, i64 g) {
+  const i64 w = g >> 5;
+  return __ldg(p.word_prefix + w) + __popc(__ldg(p.first_bits + w) & ((1u << (g & 31)) - 1u));
+}
+
+// Everything a thread needs to know about the minibatch of its current item.
+struct EmitCursor {
+  int b;
+  i64 ibase, iend;  // items of the minibatch
+  i64 s0;           // its first seed slot
+  i64 e0;           // its first edge
+  u32 ns;           // number of seeds
+  u32 ubase;        // its first position in `unique`
+  bool repeat;      // a seed repeats an earlier one (or is invalid): columns need the table
+};
+
+__device__ __forceinline__ void emit_cursor_load(const RelabelParams& p, EmitCursor& c) {
+  c.ibase = p.item_ptr[c.b];
+  c.iend = p.item_ptr[c.b + 1];
+  c.s0 = p.seeds_ptr[c.b];
+  c.ns = (u32)(p.seeds_ptr[c.b + 1] - c.s0);
+  c.e0 = p.edge_ptr[c.b];
+  c.ubase = position_of(p, c.ibase);
+  c.repeat = p.seed_repeat[c.b] != 0u;
+}
+
+#ifndef GSB_EMIT_MIN_CTAS
+#define GSB_EMIT_MIN_CTAS 6
+#endif
+__global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_kernel(const RelabelParams p) {
   const i64 n = p.hdr->n_items;
   const i64 tiles = p.hdr->n_tiles;
   const i64 tile = blockIdx.x;
@@ -589,63 +644,75 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_RANK_MIN_CTAS) relabel_rank_ke
     }
     return;
   }
-  const unsigned lt_mask = (1u << lane) - 1u;
+  const bool fits = p.hdr->n_unique <= p.U_cap;
   const i64 g_warp = tile * RL_TILE + (i64)wid * (32 * RL_ITEMS);
-  u32 m[RL_ITEMS];
+  if (g_warp < n) {
+    u32 m[RL_ITEMS];
 #pragma unroll
-  for (int j = 0; j < RL_ITEMS; ++j) {
-    const i64 g = g_warp + j * 32 + lane;
-    m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
-  }
-  bool first[RL_ITEMS];
-  int before[RL_ITEMS], bj[RL_ITEMS];
-  u32 off[RL_ITEMS];
-  int warp_firsts = 0;
-  ItemCursor c = cursor_at(p, g_warp < n ? g_warp : n - 1);
-#pragma unroll
-  for (int j = 0; j < RL_ITEMS; ++j) {
-    const i64 g = g_warp + j * 32 + lane;
-    first[j] = false;
-    off[j] = IDX_UNSET;
-    bj[j] = c.b;
-    if (g < n) {
-      cursor_seek(p, c, g);
-      bj[j] = c.b;
-      off[j] = (u32)(g - c.ibase);
-      first[j] = m[j] == off[j];
+    for (int j = 0; j < RL_ITEMS; ++j) {
+      const i64 g = g_warp + j * 32 + lane;
+      m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
     }
-    const unsigned bal = __ballot_sync(0xffffffffu, first[j]);
-    before[j] = warp_firsts + __popc(bal & lt_mask);
-    warp_firsts += __popc(bal);
-  }
-  if (lane == 0) s_warp[wid] = warp_firsts;
-  __syncthreads();
-  i64 wbase = p.tile_count[tile];
-  for (int w = 0; w < wid; ++w) wbase += s_warp[w];
-  const bool fits = (i64)p.tile_count[tiles] <= p.U_cap;
+    // this warp's own four words of the bit array and their prefixes (one load each, broadcast)
+    const i64 w_warp = g_warp >> 5;
+    const u32 my_bits = lane < RL_ITEMS ? __ldg(p.first_bits + w_warp + lane) : 0u;
+    const u32 my_pref = lane < RL_ITEMS ? __ldg(p.word_prefix + w_warp + lane) : 0u;
+    EmitCursor c;
+    c.b = find_segment(p.item_ptr, p.B, g_warp);
+    emit_cursor_load(p, c);
+    const u32 lt_mask = (1u << lane) - 1u;
 #pragma unroll
-  for (int j = 0; j < RL_ITEMS; ++j) {
-    if (off[j] == IDX_UNSET) continue;
-    const i64 g = g_warp + j * 32 + lane;
-    const i64 run = wbase + before[j];
-    if (off[j] == 0) {
-      // first item of its minibatch: the running count is the minibatch's
-      // offset; empty minibatches directly before it share the same value
-      int b = bj[j];
-      p.unique_ptr[b] = run;
-      while (b > 0 && p.item_ptr[b - 1] == g) p.unique_ptr[--b] = run;
-    }
-    if (first[j]) {
-      // the id is read only here: one item in three is a repeat
-      const i64 s0 = p.seeds_ptr[bj[j]];
-      const u32 ns = (u32)(p.seeds_ptr[bj[j] + 1] - s0);
-      const i64 id = off[j] < ns ? p.seeds[s0 + off[j]] : p.coo_row[p.edge_ptr[bj[j]] + (off[j] - ns)];
-      if (fits) p.unique[run] = id;
-      p.rank[g] = (u32)run;
+    for (int j = 0; j < RL_ITEMS; ++j) {
+      const i64 g = g_warp + j * 32 + lane;
+      const u32 bits = __shfl_sync(0xffffffffu, my_bits, j);
+      const u32 pref = __shfl_sync(0xffffffffu, my_pref, j);
+      if (g >= n) continue;
+      if (g >= c.iend) {
+        while (g >= p.item_ptr[c.b + 1]) ++c.b;
+        emit_cursor_load(p, c);
+      }
+      const u32 off = (u32)(g - c.ibase);
+      const u32 here = pref + __popc(bits & lt_mask);  // first occurrences before this item
+      if (off == 0) {
+        // first item of its minibatch: the running count is the minibatch's offset; empty
+        // minibatches directly before it share the same value
+        int b = c.b;
+        p.unique_ptr[b] = here;
+        while (b > 0 && p.item_ptr[b - 1] == g) p.unique_ptr[--b] = here;
+      }
+      const bool first = m[j] == off;
+      u32 pos = here;
+      if (!first && m[j] != IDX_UNSET) pos = position_of(p, c.ibase + m[j]);
+      const bool is_edge = off >= c.ns;
+      if (first && fits) {
+        // the id is read only here: one item in three is a repeat
+        const i64 id = is_edge ? __ldg(p.coo_row + c.e0 + (off - c.ns)) : __ldg(p.seeds + c.s0 + off);
+        p.unique[pos] = id;
+      }
+      if (is_edge && p.out_row) {
+        const i64 e = c.e0 + (off - c.ns);
+        p.out_row[e] = m[j] != IDX_UNSET ? (i64)pos - (i64)c.ubase : -1;
+        // The COLUMN of an edge needs no table when the seeds of its minibatch are distinct
+        // (always, from the second layer on: they are a node list): seed i is then the i-th entry
+        // of the minibatch's list, so the relabelled column is the column slot counted from the
+        // minibatch's first slot -- which the layered sampler has already written.
+        if (c.repeat || !p.col_prefilled) {
+          const u64 lc = (u64)(__ldg(p.coo_col + e) - c.s0);  // seed slot inside the minibatch
+          if (lc >= c.ns) {
+            raise(p.err, ERRBIT_BAD_INPUT);  // a column slot outside the edge's own minibatch
+            p.out_col[e] = -1;
+          } else if (!c.repeat) {
+            p.out_col[e] = (i64)lc;
+          } else {
+            const u32 mc = __ldg(p.min_idx + c.ibase + lc);
+            p.out_col[e] = mc != IDX_UNSET ? (i64)position_of(p, c.ibase + mc) - (i64)c.ubase : -1;
+          }
+        }
+      }
     }
   }
   if (tile == tiles - 1 && threadIdx.x == 0) {
-    const i64 grand = p.tile_count[tiles];
+    const i64 grand = p.hdr->n_unique;
     int b = p.B;
     p.unique_ptr[b] = grand;
     while (b > 0 && p.item_ptr[b - 1] == n) p.unique_ptr[--b] = grand;
@@ -653,98 +720,10 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_RANK_MIN_CTAS) relabel_rank_ke
   }
 }
 
-// ---------------------------------------------------------------- emit
-// Thread per edge, EB edges (256 apart) per thread with their loads issued together.  Position
-// of an id = rank[first item carrying it]; for an id seen for the first time on this very edge
-// that is the edge's own item, so two thirds of the gathers of a GraphSAGE layer are in fact
-// coalesced.  The COLUMN of an edge needs no table at all when the seeds of its minibatch are
-// distinct (always, from the second layer on: they are a node list): seed i is then the i-th
-// entry of the minibatch's list, i.e. the relabelled column is the column slot counted from the
-// minibatch's first slot -- which the layered sampler has already written next to the edge.
-// Only minibatches with a repeated (or invalid) seed take the two gathers per column.
-struct EdgeCursor {
-  int b;
-  i64 e0, e_end;   // edges of the minibatch
-  i64 s0;          // its first seed slot
-  i64 ubase;       // its first position in `unique`
-  const u32* min_b;   // min_idx of its items
-  const u32* rank_b;  // rank of its items
-  u32 ns;
-  bool repeat;     // a seed of the minibatch repeats an earlier one
-};
-
-__device__ __forceinline__ void edge_cursor_load(const RelabelParams& p, EdgeCursor& c) {
-  c.e0 = p.edge_ptr[c.b];
-  c.e_end = p.edge_ptr[c.b + 1];
-  c.s0 = p.seeds_ptr[c.b];
-  c.ns = (u32)(p.seeds_ptr[c.b + 1] - c.s0);
-  c.ubase = p.unique_ptr[c.b];
-  c.min_b = p.min_idx + p.item_ptr[c.b];
-  c.rank_b = p.rank + p.item_ptr[c.b];
-  c.repeat = p.seed_repeat[c.b] != 0u;
-}
-
-#ifndef GSB_EMIT_EB
-#define GSB_EMIT_EB 2
-#endif
-#ifndef GSB_EMIT_MIN_CTAS
-#define GSB_EMIT_MIN_CTAS 8
-#endif
-__global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_kernel(const RelabelParams p) {
-  constexpr int EB = GSB_EMIT_EB;
-  constexpr u32 COL_DONE = 0xFFFFFFFEu;  // column written without a table
-  const i64 n = p.hdr->n_edges;
-  for (i64 e_cta = (i64)blockIdx.x * (EB * RL_THREADS); e_cta < n; e_cta += (i64)gridDim.x * (EB * RL_THREADS)) {
-    EdgeCursor c;
-    c.b = find_segment(p.edge_ptr, p.B, e_cta);
-    edge_cursor_load(p, c);
-    u32 m[EB], mc[EB];
-    i64 ub[EB];
-    const u32* rb[EB];
-    bool live[EB];
-#pragma unroll
-    for (int u = 0; u < EB; ++u) {
-      const i64 e = e_cta + u * RL_THREADS + threadIdx.x;
-      live[u] = e < n;
-      m[u] = IDX_UNSET; mc[u] = IDX_UNSET;
-      ub[u] = 0; rb[u] = p.rank;
-      if (live[u]) {
-        if (e >= c.e_end) {
-          while (e >= p.edge_ptr[c.b + 1]) ++c.b;
-          edge_cursor_load(p, c);
-        }
-        ub[u] = c.ubase; rb[u] = c.rank_b;
-        m[u] = __ldg(c.min_b + c.ns + (u32)(e - c.e0));
-        if (!c.repeat && p.col_prefilled) {
-          mc[u] = COL_DONE;
-        } else {
-          const u64 lc = (u64)(__ldg(p.coo_col + e) - c.s0);  // seed slot inside the minibatch
-          if (lc >= c.ns) raise(p.err, ERRBIT_BAD_INPUT);  // a column slot outside the edge's own minibatch
-          else if (!c.repeat) { p.out_col[e] = (i64)lc; mc[u] = COL_DONE; }
-          else mc[u] = __ldg(c.min_b + lc);
-        }
-      }
-    }
-    u32 r[EB], rc[EB];
-#pragma unroll
-    for (int u = 0; u < EB; ++u) {
-      r[u] = m[u] != IDX_UNSET ? __ldg(rb[u] + m[u]) : 0;
-      rc[u] = mc[u] < COL_DONE ? __ldg(rb[u] + mc[u]) : 0;
-    }
-#pragma unroll
-    for (int u = 0; u < EB; ++u) {
-      if (!live[u]) continue;
-      const i64 e = e_cta + u * RL_THREADS + threadIdx.x;
-      p.out_row[e] = m[u] != IDX_UNSET ? (i64)r[u] - ub[u] : -1;
-      if (mc[u] != COL_DONE) p.out_col[e] = mc[u] != IDX_UNSET ? (i64)rc[u] - ub[u] : -1;
-    }
-  }
-}
-
 struct RelabelLayout {
-  size_t hdr, item_ptr, bucket_ptr, tile_count, bucket_start, bucket_cursor, seed_repeat, min_idx,
-      rank, part, overflow, total;
-  i64 tiles, buckets_cap;
+  size_t hdr, item_ptr, bucket_ptr, bucket_start, bucket_cursor, seed_repeat, pf_status, min_idx,
+      first_bits, word_prefix, part, overflow, total;
+  i64 tiles, buckets_cap, pf_ctas;
 };
 
 static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
@@ -758,12 +737,15 @@ static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   L.hdr = o; o = up(o + sizeof(RelabelHeader));
   L.item_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
   L.bucket_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
-  L.tile_count = o; o = up(o + sizeof(u32) * (size_t)(L.tiles + 1));
   L.bucket_start = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
   L.bucket_cursor = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
   L.seed_repeat = o; o = up(o + sizeof(u32) * (size_t)(B + 1));
+  const i64 words = (items + 31) / 32 + 8;
+  L.pf_ctas = (words + PF_WORDS - 1) / PF_WORDS + 1;
+  L.pf_status = o; o = up(o + 256 + sizeof(u64) * (size_t)(L.pf_ctas + 1));   // ticket, then status words
   L.min_idx = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
-  L.rank = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
+  L.first_bits = o; o = up(o + sizeof(u32) * (size_t)(words + 8));
+  L.word_prefix = o; o = up(o + sizeof(u32) * (size_t)(words + 8));
   L.part = o; o = up(o + sizeof(u64) * (size_t)(items + 4));
   // overflow tables: 2 slots per item + 32 per bucket; touched only by buckets that need them
   L.overflow = o; o = up(o + sizeof(u64) * (size_t)(2 * items + 32 * (L.buckets_cap + 1)));
@@ -821,15 +803,17 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   p.id_limit = id_bound > 0 && id_bound < 0xFFFFFFFFll ? (u64)id_bound : 0xFFFFFFFFull;
   p.unique_ptr = (i64*)unique_ptr; p.out_row = (i64*)out_row; p.out_col = (i64*)out_col;
   p.hdr = (RelabelHeader*)(ws + L.hdr); p.item_ptr = (i64*)(ws + L.item_ptr);
-  p.tile_count = (u32*)(ws + L.tile_count); p.min_idx = (u32*)(ws + L.min_idx);
-  p.rank = (u32*)(ws + L.rank); p.err = d_err;
+  p.min_idx = (u32*)(ws + L.min_idx); p.err = d_err;
+  p.first_bits = (u32*)(ws + L.first_bits); p.word_prefix = (u32*)(ws + L.word_prefix);
+  p.pf_ticket = (int*)(ws + L.pf_status); p.pf_status = (u64*)(ws + L.pf_status + 256);
   p.bucket_ptr = (i64*)(ws + L.bucket_ptr);
   p.bucket_start = (u32*)(ws + L.bucket_start); p.bucket_cursor = (u32*)(ws + L.bucket_cursor);
   p.part = (u64*)(ws + L.part); p.overflow = (u64*)(ws + L.overflow); p.buckets_cap = L.buckets_cap;
   p.seed_repeat = (u32*)(ws + L.seed_repeat); p.col_prefilled = col_prefilled ? 1 : 0;
 
   { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
-  // bucket counts, cursors and the repeated-seed flags are adjacent: one clear
+  // bucket counts, cursors, the repeated-seed flags and the prefix pass's ticket / status words
+  // are adjacent: one clear
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_start, 0, L.min_idx - L.bucket_start, st));
   const i64 items_max = S_max + E_max;
   const int wide = sm_count() * GSB_RL_WIDE;
@@ -842,14 +826,9 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   const int dd_smem = 2 * DD_TAB * (int)sizeof(u32);
   GSB_CUDA_OK(cudaFuncSetAttribute(relabel_dedupe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_smem));
   { LaunchScope ls(KID_RL_DEDUPE, st); relabel_dedupe_kernel<<<g_bk, DD_THREADS, dd_smem, st>>>(p); }
-  { LaunchScope ls(KID_RL_COUNT, st); relabel_count_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
-  { LaunchScope ls(KID_RL_TILES, st); relabel_tiles_kernel<<<1, 1024, 0, st>>>(p); }
-  { LaunchScope ls(KID_RL_SCAN, st); relabel_rank_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
-  if (out_row && E_max > 0) {
-    int g_edges = (int)((E_max + GSB_EMIT_EB * RL_THREADS - 1) / (GSB_EMIT_EB * RL_THREADS));
-    if (g_edges > sm_count() * GSB_RL_EMIT) g_edges = sm_count() * GSB_RL_EMIT;
-    { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<g_edges, RL_THREADS, 0, st>>>(p); }
-  }
+  { LaunchScope ls(KID_RL_COUNT, st); relabel_mark_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
+  { LaunchScope ls(KID_RL_TILES, st); relabel_prefix_kernel<<<(int)L.pf_ctas, PF_THREADS, 0, st>>>(p); }
+  { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }
