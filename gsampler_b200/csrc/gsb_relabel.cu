@@ -12,20 +12,18 @@
 // most a few thousand items, and every bucket is deduplicated by one CTA in a
 // SHARED-memory table:
 //   setup   : item / bucket geometry of every minibatch           (one block)
-//   pcount  : per-bucket item counts (shared histograms per 8192-item tile,
-//             one global atomic per tile and non-empty bucket)    (streaming)
-//   pscan   : bucket offsets                                      (one block)
-//   scatter : (id, index) pairs grouped by bucket; every tile reserves a run
-//             per bucket, its 8-byte stores meet in L2            (streaming)
+//   scatter : (id, index) pairs grouped by bucket.  A bucket owns a region of
+//             fixed capacity, so nothing is counted first: every 8192-item
+//             tile reserves a run per bucket with one global atomic; what
+//             finds its region full goes to one overflow list     (streaming)
 //   dedupe  : CTA per bucket: shared table id -> smallest index, then
-//             min_idx[item] for every REPEATED item of the bucket (the scatter
-//             pass preset min_idx[item] = item); a bucket whose ids do not fit
-//             the shared table falls back to a table in global memory that
-//             the CTA owns                                        (streaming
-//             read + one scattered 4-byte store per repeat)
-//   mark    : one bit per item: "is a first occurrence"           (streaming)
-//   prefix  : first occurrences before every 32-item word of that bit array
-//             (popcounts + chained prefix; 1/32 of a word per item)
+//             min_idx[item] for every REPEATED item of the bucket; a bucket
+//             whose ids do not fit the shared table falls back to a table in
+//             global memory that the CTA owns                     (streaming
+//             read + for a repeat one scattered 4-byte store and one bit set
+//             in a bit array with one bit per item)
+//   prefix  : first occurrences (clear bits) before every 32-item word of that
+//             bit array (popcounts + chained prefix; 1/32 of a word per item)
 //   emit    : one pass over the items: node lists, their offsets, and for
 //             the items that are edges the relabelled row (position of the
 //             id's first item, from the two small arrays above, which stay
@@ -75,6 +73,7 @@ constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
 #define GSB_SCATTER_MIN_CTAS 2
 #endif
 constexpr int PT_BUCKET_ITEMS = GSB_BUCKET_ITEMS;  // a minibatch gets ceil(items / this) buckets
+constexpr i64 BK_CAP = 4096;                       // entries of a bucket's region in `part`
 constexpr int DD_THREADS = 512;
 constexpr int DD_BATCH = 8;            // items a dedupe thread keeps in registers
 constexpr int DD_TAB = GSB_DD_TAB;           // shared-table slots of the dedupe CTA
@@ -108,16 +107,19 @@ struct RelabelParams {
   i64* out_col;
   RelabelHeader* hdr;
   i64* item_ptr;      // [B+1] start of minibatch b in the interleaved item order
-  u32* min_idx;       // [items] smallest item index carrying the item's id
-  u32* first_bits;    // [items / 32] bit g % 32 of word g / 32: item g is a first occurrence
+  u32* min_idx;       // [items] for a repeat: offset of the first item carrying its id
+  u32* repeat_bits;   // [items / 32] bit g % 32 of word g / 32: item g repeats an earlier item (zeroed)
   u32* word_prefix;   // [items / 32] first occurrences before the word
   u64* pf_status;     // chained-prefix words of the prefix pass (zeroed)
   int* pf_ticket;     // its CTA ticket (zeroed)
   i64* bucket_ptr;    // [B+1] first bucket of minibatch b
-  u32* bucket_start;  // [buckets+1] counts, then their exclusive scan (positions in `part`)
-  u32* bucket_cursor; // [buckets] fill level during the scatter pass
-  u64* part;          // [items] id:32 | index:32, grouped by bucket
-  u64* overflow;      // global tables of buckets that overflow the shared one
+  u32* bucket_fill;   // [buckets] items of the bucket (zeroed; may exceed BK_CAP: the rest is on the overflow list)
+  u64* part;          // [buckets * BK_CAP] id:32 | index:32, bucket k owns entries k * BK_CAP ...
+  u64* ovf_item;      // [items] items that found their bucket's region full
+  u32* ovf_bucket;    // [items] ... and the bucket each belongs to
+  u32* ovf_count;     // length of that list (zeroed)
+  u64* overflow;      // global tables of buckets whose distinct ids overflow the shared table
+  u64* gt_cursor;     // bump pointer into `overflow` (zeroed)
   u32* seed_repeat;   // [B] set when a seed of the minibatch repeats an earlier seed (or is invalid)
   int col_prefilled;  // out_col already holds "slot - first slot of the minibatch" (the sampler wrote it)
   i64 buckets_cap;
@@ -266,80 +268,27 @@ __device__ __forceinline__ u32 bucket_of(u32 key, int nbk) {
     if (off < (lim)) id[u] = segment_id(sg, off);                    \
   }
 
-// Per-bucket item counts.  A CTA walks tiles of PT_TILE consecutive items; the
-// part of a tile that belongs to one minibatch is histogrammed in shared
-// memory and flushed with one global atomic per non-empty bucket.
-__global__ void __launch_bounds__(PT_THREADS) relabel_pcount_kernel(const RelabelParams p) {
-  __shared__ u32 s_hist[PT_MAX_BUCKETS];
-  const i64 n = p.hdr->n_items;
-  for (i64 lo = (i64)blockIdx.x * PT_TILE; lo < n; lo += (i64)gridDim.x * PT_TILE) {
-    const i64 hi = lo + PT_TILE < n ? lo + PT_TILE : n;
-    int b = find_segment(p.item_ptr, p.B, lo);
-    i64 at = lo;
-    while (at < hi) {
-      while (p.item_ptr[b + 1] <= at) ++b;  // minibatch of item `at` (skips empty ones)
-      const Segment sg = load_segment(p, b);
-      const i64 seg_hi = hi < sg.iend ? hi : sg.iend;
-      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) s_hist[k] = 0;
-      __syncthreads();
-      const u32 lim = (u32)(seg_hi - sg.ibase);
-      for (u32 off0 = (u32)(at - sg.ibase) + threadIdx.x; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
-        GSB_LOAD_ID_BATCH(off0, lim)
-#pragma unroll
-        for (int u = 0; u < PT_BATCH; ++u)
-          if ((u64)id[u] < p.id_limit) atomicAdd(&s_hist[bucket_of((u32)id[u], sg.nbk)], 1u);
-      }
-      __syncthreads();
-      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS)
-        if (s_hist[k]) atomicAdd(p.bucket_start + sg.bk0 + k, s_hist[k]);
-      __syncthreads();
-      at = seg_hi;
-    }
-  }
+// An item that is not a first occurrence: min_idx[g] = offset of the first item carrying its id
+// inside the minibatch (IDX_UNSET for an invalid id), and its bit in the array that the prefix
+// and emit passes read.  First occurrences are never written: their bit stays clear.
+__device__ __forceinline__ void mark_repeat(const RelabelParams& p, i64 g, u32 first_off) {
+  p.min_idx[g] = first_off;
+  atomicOr(p.repeat_bits + (g >> 5), 1u << (g & 31));
 }
 
-// One block: a[0..n] <- exclusive scan of a[0..n), a[n] <- the total.  The
-// array (16-byte aligned) is walked in chunks of four words per thread, so the
-// loads and stores of a warp are contiguous.
-__device__ __forceinline__ i64 scan_in_place(u32* a, i64 n, i64* s_scan) {
-  __shared__ i64 s_carry;
-  if (threadIdx.x == 0) s_carry = 0;
-  __syncthreads();
-  uint4* a4 = reinterpret_cast<uint4*>(a);
-  const i64 chunk = (i64)blockDim.x * 4;
-  for (i64 c0 = 0; c0 < n; c0 += chunk) {
-    const i64 i = c0 + (i64)threadIdx.x * 4;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (i + 3 < n) v = a4[i >> 2];
-    else if (i < n) { v.x = a[i]; if (i + 1 < n) v.y = a[i + 1]; if (i + 2 < n) v.z = a[i + 2]; }
-    i64 total;
-    const i64 run = s_carry + block_exclusive_scan((i64)v.x + v.y + v.z + v.w, s_scan, &total);
-    const uint4 o = make_uint4((u32)run, (u32)(run + v.x), (u32)(run + v.x + v.y), (u32)(run + v.x + v.y + v.z));
-    if (i + 3 < n) a4[i >> 2] = o;
-    else if (i < n) { a[i] = o.x; if (i + 1 < n) a[i + 1] = o.y; if (i + 2 < n) a[i + 2] = o.z; }
-    __syncthreads();
-    if (threadIdx.x == 0) s_carry += total;
-    __syncthreads();
-  }
-  if (threadIdx.x == 0) a[n] = (u32)s_carry;
-  return s_carry;
-}
-
-__global__ void relabel_pscan_kernel(const RelabelParams p) {
-  __shared__ i64 s_scan[34];
-  scan_in_place(p.bucket_start, p.hdr->n_buckets, s_scan);
-}
-
-// Writes (id, index) of every item into its bucket's range of `part`.  Per tile
-// and minibatch: shared histogram, one global atomic per non-empty bucket to
-// reserve the tile's run inside the bucket, then every item takes the next
-// free word of its bucket's run.  The ids are read twice (the second read hits
-// L1/L2); the 8-byte stores of a run meet in L2 before they reach DRAM.
-// (Sorting the tile in shared memory first, to write whole runs, measured the
-// same 0.23 ms per 23 M items.)
+// Writes (id, index) of every item into its bucket's region of `part`.  A bucket owns a region of
+// BK_CAP entries at a fixed place (bucket k: part[k * BK_CAP ...)), so no counting pass and no
+// scan come first: per tile and minibatch a shared histogram, ONE global atomic per non-empty
+// bucket reserves the tile's run inside the bucket's region, then every item takes the next free
+// entry of its bucket's run.  A minibatch of n items has ceil(n / PT_BUCKET_ITEMS) buckets, so a
+// bucket holds PT_BUCKET_ITEMS items on average and its size scatters by a few tens around that;
+// items that do not fit the region any more (an id repeated thousands of times, a minibatch so
+// large that its 1024 buckets exceed the mean) go to one overflow list, tagged with their
+// bucket, which the bucket's dedupe CTA reads after its region.  The ids are read twice (the
+// second read hits L1/L2); the 8-byte stores of a run meet in L2 before they reach DRAM.
 __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scatter_kernel(const RelabelParams p) {
   __shared__ u32 s_hist[PT_MAX_BUCKETS];  // items of the bucket in this tile
-  __shared__ u32 s_next[PT_MAX_BUCKETS];  // next free position of the bucket's run in `part`
+  __shared__ u32 s_next[PT_MAX_BUCKETS];  // next free entry of the bucket's run (may pass BK_CAP)
   const i64 n = p.hdr->n_items;
   for (i64 lo = (i64)blockIdx.x * PT_TILE; lo < n; lo += (i64)gridDim.x * PT_TILE) {
     const i64 hi = lo + PT_TILE < n ? lo + PT_TILE : n;
@@ -362,7 +311,7 @@ __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scat
       __syncthreads();
       for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) {
         const u32 h = s_hist[k];
-        if (h) s_next[k] = p.bucket_start[sg.bk0 + k] + atomicAdd(p.bucket_cursor + sg.bk0 + k, h);
+        if (h) s_next[k] = atomicAdd(p.bucket_fill + sg.bk0 + k, h);
       }
       __syncthreads();
       for (u32 off0 = first; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
@@ -371,12 +320,19 @@ __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scat
         for (int u = 0; u < PT_BATCH; ++u) {
           const u32 off = off0 + (u32)(u * PT_THREADS);
           if ((u64)id[u] < p.id_limit) {
-            const u32 dst = atomicAdd(&s_next[bucket_of((u32)id[u], sg.nbk)], 1u);
-            p.part[dst] = ((u64)(u32)id[u] << 32) | off;
-            p.min_idx[sg.ibase + off] = off;  // "first occurrence" until the dedupe pass says otherwise
+            const u32 k = bucket_of((u32)id[u], sg.nbk);
+            const u32 dst = atomicAdd(&s_next[k], 1u);
+            const u64 item = ((u64)(u32)id[u] << 32) | off;
+            if (dst < (u32)BK_CAP) {
+              p.part[(sg.bk0 + k) * BK_CAP + dst] = item;
+            } else {
+              const u32 q = atomicAdd(p.ovf_count, 1u);  // < number of items, which the list holds
+              p.ovf_item[q] = item;
+              p.ovf_bucket[q] = (u32)(sg.bk0 + k);
+            }
           } else if (off < lim) {
             raise(p.err, ERRBIT_BAD_INPUT);  // negative, or not below the stated bound
-            p.min_idx[sg.ibase + off] = IDX_UNSET;
+            mark_repeat(p, sg.ibase + off, IDX_UNSET);  // in no node list; relabels to -1
             if (off < sg.ns) p.seed_repeat[b] = 1u;  // its edges' columns relabel to -1: no shortcut
           }
         }
@@ -401,25 +357,45 @@ __device__ __forceinline__ u32 stab_insert(u32* s_key, u32* s_min, u32 tab, u32 
   return tab;
 }
 
-// CTA per bucket: shared table id -> smallest index, then min_idx for every
-// item of the bucket.  Only the distinct ids have to fit the table, so a hub
-// id repeated thousands of times costs nothing extra.  A bucket of at most
-// DD_BATCH * DD_THREADS items (the normal case) stays in registers between the
-// two phases together with the table slot each item found.
+// CTA per bucket: shared table id -> smallest index, then min_idx + the repeat bit for every
+// repeated item of the bucket.  Only the distinct ids have to fit the table, so a hub id repeated
+// thousands of times costs nothing extra.  A bucket whose items all lie in its own region (the
+// normal case: at most BK_CAP = DD_BATCH * DD_THREADS of them) stays in registers between the two
+// phases together with the table slot each item found; a bucket with items on the overflow list
+// streams its region and then the list (every entry of the list is looked at, the bucket's own
+// are used).
+template <typename Fn>
+__device__ __forceinline__ void for_each_bucket_item(const RelabelParams& p, i64 k, u32 in_region, u32 n_ovf,
+                                                     Fn fn) {
+  const u64* items = p.part + k * BK_CAP;
+  for (u32 i = threadIdx.x; i < in_region; i += DD_THREADS) fn(__ldg(items + i));
+  for (u32 j = threadIdx.x; j < n_ovf; j += DD_THREADS)
+    if (__ldg(p.ovf_bucket + j) == (u32)k) fn(__ldg(p.ovf_item + j));
+}
+
 __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_kernel(const RelabelParams p) {
   extern __shared__ __align__(16) unsigned char dd_smem[];
   u32* s_key = reinterpret_cast<u32*>(dd_smem);
   u32* s_min = s_key + DD_TAB;
   __shared__ int s_over;
+  __shared__ u64 s_gt_off;
   const i64 nb = p.hdr->n_buckets;
   for (i64 k = blockIdx.x; k < nb; k += gridDim.x) {
-    const u32 start = p.bucket_start[k];
-    const u32 cnt = p.bucket_start[k + 1] - start;
+    const u32 cnt = p.bucket_fill[k];
     if (cnt == 0) continue;  // uniform over the CTA
+    const bool spilled = cnt > (u32)BK_CAP;
+    const u32 in_region = spilled ? (u32)BK_CAP : cnt;
+    const u32 n_ovf = spilled ? *p.ovf_count : 0u;
     const int b = find_segment(p.bucket_ptr, p.B, k);
-    u32* out = p.min_idx + p.item_ptr[b];
+    const i64 gbase = p.item_ptr[b];
     const u32 ns = (u32)(p.seeds_ptr[b + 1] - p.seeds_ptr[b]);  // items below ns are the minibatch's seeds
-    const u64* items = p.part + start;
+    const u64* items = p.part + k * BK_CAP;
+    auto repeat = [&](u64 it, u32 m) {
+      if (m != (u32)it) {
+        mark_repeat(p, gbase + (u32)it, m);
+        if ((u32)it < ns) p.seed_repeat[b] = 1u;
+      }
+    };
     // table size: a power of two >= 1.5 * cnt (at most DD_TAB)
     u32 tab = 1024;
     while (tab < DD_TAB && 2 * tab < 3 * cnt) tab <<= 1;
@@ -431,7 +407,7 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
     }
     if (threadIdx.x == 0) s_over = 0;
     __syncthreads();
-    if (cnt <= DD_BATCH * DD_THREADS) {
+    if (!spilled) {
       u64 it[DD_BATCH];
       u32 slot[DD_BATCH];
 #pragma unroll
@@ -450,73 +426,61 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
       if (!s_over) {
 #pragma unroll
         for (int u = 0; u < DD_BATCH; ++u)
-          if (it[u] != ~0ull) {
-            const u32 m = s_min[slot[u]];
-            if (m != (u32)it[u]) {  // first occurrences were preset by the scatter pass
-              out[(u32)it[u]] = m;
-              if ((u32)it[u] < ns) p.seed_repeat[b] = 1u;
-            }
-          }
+          if (it[u] != ~0ull) repeat(it[u], s_min[slot[u]]);
         __syncthreads();
         continue;
       }
     } else {
-      for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
-        const u64 it = __ldg(items + i);
+      for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
         if (stab_insert(s_key, s_min, tab, (u32)(it >> 32), (u32)it) == tab) s_over = 1;
-      }
+      });
       __syncthreads();
       if (!s_over) {
         const u32 mask = tab - 1;
-        for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
-          const u64 it = __ldg(items + i);
+        for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
           const u32 key = (u32)(it >> 32);
           u32 pos = hash32(key) & mask;
           for (u32 probes = 0; s_key[pos] != key && probes < tab; ++probes) pos = (pos + 1) & mask;
-          if (s_min[pos] != (u32)it) {
-            out[(u32)it] = s_min[pos];
-            if ((u32)it < ns) p.seed_repeat[b] = 1u;
-          }
-        }
+          repeat(it, s_min[pos]);
+        });
         __syncthreads();
         continue;
       }
     }
-    // more distinct ids than the shared table holds: a table in global memory,
-    // owned by this CTA (2 slots per item of the bucket)
-    u64* gt = p.overflow + 2 * (i64)start + 32 * k;
+    // more distinct ids than the shared table holds: a table in global memory, owned by this
+    // CTA (2 slots per item of the bucket, taken off a bump pointer)
     const u32 slots = 2 * cnt + 32;
+    if (threadIdx.x == 0) s_gt_off = atomicAdd(p.gt_cursor, (u64)slots);
+    __syncthreads();
+    u64* gt = p.overflow + s_gt_off;
     for (u32 i = threadIdx.x; i < slots; i += DD_THREADS) gt[i] = SLOT_EMPTY;
     __syncthreads();
-    for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
-      const u64 it = items[i];
+    for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
       if (!gtab_insert(gt, slots, (u32)(it >> 32), (u32)it)) raise(p.err, ERRBIT_TABLE_FULL);
-    }
+    });
     __syncthreads();
-    for (u32 i = threadIdx.x; i < cnt; i += DD_THREADS) {
-      const u64 it = items[i];
+    for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
       const u32 m = gtab_find(gt, slots, (u32)(it >> 32));
       if (m == IDX_UNSET) raise(p.err, ERRBIT_KEY_MISSING);
-      out[(u32)it] = m;
-      if (m != (u32)it && (u32)it < ns) p.seed_repeat[b] = 1u;
-    }
+      else repeat(it, m);
+    });
     __syncthreads();
   }
 }
 
 // ---------------------------------------------------------------- mark / prefix / emit
-// After the dedupe pass min_idx says, for every item, which item carries its id first.  The
-// position of a first occurrence in `unique` is the number of first occurrences before it, so:
-//   mark   : one bit per item, "is a first occurrence", 32 items per word (a warp ballot);
-//   prefix : word_prefix[w] = first occurrences in all words before w (popcounts, block scan,
-//            chained prefix across CTAs) -- the position of ANY item g is then
-//            word_prefix[g / 32] + popc(bits[g / 32] below bit g % 32): two loads from arrays of
-//            one bit and one 32nd of a word per item, which stay in L2;
+// The dedupe pass leaves one bit per item, 32 items per word: set = the item repeats an earlier
+// one (min_idx then says which).  The position of a first occurrence in `unique` is the number of
+// first occurrences before it, so:
+//   prefix : word_prefix[w] = first occurrences (clear bits) in all words before w (popcounts,
+//            block scan, chained prefix across CTAs) -- the position of ANY item g is then
+//            word_prefix[g / 32] + popc(clear bits of word g / 32 below bit g % 32): two loads
+//            from arrays of one bit and one 32nd of a word per item, which stay in L2;
 //   emit   : one pass over the items writes `unique` (first occurrences, in order), the offsets of
 //            the node lists and, for the items that are edges, the relabelled row (and column).
 // Items are laid out so that warp w of a 1024-item tile owns 128 consecutive items and lane l
 // handles items w*128 + j*32 + l (j = 0..3): every load / store instruction of a warp touches 32
-// consecutive items and a ballot is exactly one word of the bit array.
+// consecutive items, which are exactly one word of the bit array.
 struct ItemCursor {
   int b;
   i64 ibase, iend;
@@ -537,35 +501,6 @@ __device__ __forceinline__ ItemCursor cursor_at(const RelabelParams& p, i64 g) {
   return c;
 }
 
-__global__ void __launch_bounds__(RL_THREADS) relabel_mark_kernel(const RelabelParams p) {
-  const i64 n = p.hdr->n_items;
-  const i64 tile = blockIdx.x;
-  if (tile >= p.hdr->n_tiles) return;
-  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const i64 g_warp = tile * RL_TILE + (i64)wid * (32 * RL_ITEMS);
-  if (g_warp >= n) return;  // whole warp
-  u32 m[RL_ITEMS];
-#pragma unroll
-  for (int j = 0; j < RL_ITEMS; ++j) {
-    const i64 g = g_warp + j * 32 + lane;
-    m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
-  }
-  ItemCursor c = cursor_at(p, g_warp);
-  u32 mine = 0;
-#pragma unroll
-  for (int j = 0; j < RL_ITEMS; ++j) {
-    const i64 g = g_warp + j * 32 + lane;
-    bool first = false;
-    if (g < n) {
-      cursor_seek(p, c, g);
-      first = m[j] == (u32)(g - c.ibase);
-    }
-    const u32 word = __ballot_sync(0xffffffffu, first);
-    if (lane == j) mine = word;
-  }
-  if (lane < RL_ITEMS) p.first_bits[(g_warp >> 5) + lane] = mine;  // words past n hold zeros
-}
-
 constexpr int PF_THREADS = 256;
 constexpr int PF_WORDS = PF_THREADS * 4;  // words per CTA: 32 768 items
 
@@ -582,9 +517,16 @@ __global__ void __launch_bounds__(PF_THREADS) relabel_prefix_kernel(const Relabe
   const i64 n_ctas = n_words == 0 ? 1 : (n_words + PF_WORDS - 1) / PF_WORDS;
   if (cta >= n_ctas) return;
   const i64 w0 = (i64)cta * PF_WORDS + (i64)threadIdx.x * 4;
-  uint4 v = make_uint4(0, 0, 0, 0);
-  if (w0 < n_words) v = *reinterpret_cast<const uint4*>(p.first_bits + w0);  // padded to a multiple of 4 words
-  const u32 c0 = __popc(v.x), c1 = __popc(v.y), c2 = __popc(v.z), c3 = __popc(v.w);
+  uint4 v = make_uint4(~0u, ~0u, ~0u, ~0u);
+  if (w0 < n_words) v = *reinterpret_cast<const uint4*>(p.repeat_bits + w0);  // padded to a multiple of 4 words
+  const i64 n = p.hdr->n_items;
+  // first occurrences of a word: its clear bits among the items that exist
+  auto firsts = [n](u32 bits, i64 w) -> u32 {
+    const i64 left = n - (w << 5);
+    const u32 valid = left >= 32 ? ~0u : (left <= 0 ? 0u : ((1u << left) - 1u));
+    return (u32)__popc(~bits & valid);
+  };
+  const u32 c0 = firsts(v.x, w0), c1 = firsts(v.y, w0 + 1), c2 = firsts(v.z, w0 + 2), c3 = firsts(v.w, w0 + 3);
   i64 total;
   const i64 ex = block_exclusive_scan((i64)(c0 + c1 + c2 + c3), s_scan, &total);
   if (threadIdx.x < 32) {
@@ -605,7 +547,7 @@ __global__ void __launch_bounds__(PF_THREADS) relabel_prefix_kernel(const Relabe
 // number of first occurrences before item g (= position in `unique` of a first occurrence g)
 __device__ __forceinline__ u32 position_of(const RelabelParams& p, i64 g) {
   const i64 w = g >> 5;
-  return __ldg(p.word_prefix + w) + __popc(__ldg(p.first_bits + w) & ((1u << (g & 31)) - 1u));
+  return __ldg(p.word_prefix + w) + __popc(~__ldg(p.repeat_bits + w) & ((1u << (g & 31)) - 1u));
 }
 
 // Everything a thread needs to know about the minibatch of its current item.
@@ -647,16 +589,18 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
   const bool fits = p.hdr->n_unique <= p.U_cap;
   const i64 g_warp = tile * RL_TILE + (i64)wid * (32 * RL_ITEMS);
   if (g_warp < n) {
+    // this warp's own four words of the bit array and their prefixes (one load each, broadcast)
+    const i64 w_warp = g_warp >> 5;
+    const u32 my_bits = lane < RL_ITEMS ? __ldg(p.repeat_bits + w_warp + lane) : ~0u;
+    const u32 my_pref = lane < RL_ITEMS ? __ldg(p.word_prefix + w_warp + lane) : 0u;
+    // min_idx is defined for repeats only
     u32 m[RL_ITEMS];
 #pragma unroll
     for (int j = 0; j < RL_ITEMS; ++j) {
       const i64 g = g_warp + j * 32 + lane;
-      m[j] = g < n ? __ldg(p.min_idx + g) : IDX_UNSET;
+      const u32 bits = __shfl_sync(0xffffffffu, my_bits, j);
+      m[j] = (g < n && ((bits >> lane) & 1u)) ? __ldg(p.min_idx + g) : IDX_UNSET;
     }
-    // this warp's own four words of the bit array and their prefixes (one load each, broadcast)
-    const i64 w_warp = g_warp >> 5;
-    const u32 my_bits = lane < RL_ITEMS ? __ldg(p.first_bits + w_warp + lane) : 0u;
-    const u32 my_pref = lane < RL_ITEMS ? __ldg(p.word_prefix + w_warp + lane) : 0u;
     EmitCursor c;
     c.b = find_segment(p.item_ptr, p.B, g_warp);
     emit_cursor_load(p, c);
@@ -672,7 +616,7 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
         emit_cursor_load(p, c);
       }
       const u32 off = (u32)(g - c.ibase);
-      const u32 here = pref + __popc(bits & lt_mask);  // first occurrences before this item
+      const u32 here = pref + __popc(~bits & lt_mask);  // first occurrences before this item
       if (off == 0) {
         // first item of its minibatch: the running count is the minibatch's offset; empty
         // minibatches directly before it share the same value
@@ -680,9 +624,10 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
         p.unique_ptr[b] = here;
         while (b > 0 && p.item_ptr[b - 1] == g) p.unique_ptr[--b] = here;
       }
-      const bool first = m[j] == off;
+      const bool first = ((bits >> lane) & 1u) == 0u;
+      const bool valid_id = first || m[j] != IDX_UNSET;
       u32 pos = here;
-      if (!first && m[j] != IDX_UNSET) pos = position_of(p, c.ibase + m[j]);
+      if (!first && valid_id) pos = position_of(p, c.ibase + m[j]);
       const bool is_edge = off >= c.ns;
       if (first && fits) {
         // the id is read only here: one item in three is a repeat
@@ -691,7 +636,7 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
       }
       if (is_edge && p.out_row) {
         const i64 e = c.e0 + (off - c.ns);
-        p.out_row[e] = m[j] != IDX_UNSET ? (i64)pos - (i64)c.ubase : -1;
+        p.out_row[e] = valid_id ? (i64)pos - (i64)c.ubase : -1;
         // The COLUMN of an edge needs no table when the seeds of its minibatch are distinct
         // (always, from the second layer on: they are a node list): seed i is then the i-th entry
         // of the minibatch's list, so the relabelled column is the column slot counted from the
@@ -704,7 +649,10 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
           } else if (!c.repeat) {
             p.out_col[e] = (i64)lc;
           } else {
-            const u32 mc = __ldg(p.min_idx + c.ibase + lc);
+            // the seed's own item: a first occurrence, or a repeat of an earlier seed
+            const i64 gs = c.ibase + (i64)lc;
+            const bool seed_first = ((__ldg(p.repeat_bits + (gs >> 5)) >> (gs & 31)) & 1u) == 0u;
+            const u32 mc = seed_first ? (u32)lc : __ldg(p.min_idx + gs);
             p.out_col[e] = mc != IDX_UNSET ? (i64)position_of(p, c.ibase + mc) - (i64)c.ubase : -1;
           }
         }
@@ -721,8 +669,8 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
 }
 
 struct RelabelLayout {
-  size_t hdr, item_ptr, bucket_ptr, bucket_start, bucket_cursor, seed_repeat, pf_status, min_idx,
-      first_bits, word_prefix, part, overflow, total;
+  size_t hdr, item_ptr, bucket_ptr, bucket_fill, seed_repeat, pf_status, repeat_bits,
+      min_idx, word_prefix, part, ovf_item, ovf_bucket, overflow, total;
   i64 tiles, buckets_cap, pf_ctas;
 };
 
@@ -737,16 +685,19 @@ static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   L.hdr = o; o = up(o + sizeof(RelabelHeader));
   L.item_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
   L.bucket_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
-  L.bucket_start = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
-  L.bucket_cursor = o; o = up(o + sizeof(u32) * (size_t)(L.buckets_cap + 1));
+  // zeroed block: overflow-list length and table bump pointer (first 256 bytes), bucket fill
+  // levels, repeated-seed flags, prefix-pass ticket / status, repeat bits
+  L.bucket_fill = o; o = up(o + 256 + sizeof(u32) * (size_t)(L.buckets_cap + 1));
   L.seed_repeat = o; o = up(o + sizeof(u32) * (size_t)(B + 1));
   const i64 words = (items + 31) / 32 + 8;
   L.pf_ctas = (words + PF_WORDS - 1) / PF_WORDS + 1;
   L.pf_status = o; o = up(o + 256 + sizeof(u64) * (size_t)(L.pf_ctas + 1));   // ticket, then status words
+  L.repeat_bits = o; o = up(o + sizeof(u32) * (size_t)(words + 8));
   L.min_idx = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
-  L.first_bits = o; o = up(o + sizeof(u32) * (size_t)(words + 8));
   L.word_prefix = o; o = up(o + sizeof(u32) * (size_t)(words + 8));
-  L.part = o; o = up(o + sizeof(u64) * (size_t)(items + 4));
+  L.part = o; o = up(o + sizeof(u64) * (size_t)(L.buckets_cap + 1) * (size_t)BK_CAP);
+  L.ovf_item = o; o = up(o + sizeof(u64) * (size_t)(items + 4));
+  L.ovf_bucket = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
   // overflow tables: 2 slots per item + 32 per bucket; touched only by buckets that need them
   L.overflow = o; o = up(o + sizeof(u64) * (size_t)(2 * items + 32 * (L.buckets_cap + 1)));
   L.total = o;
@@ -804,29 +755,28 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   p.unique_ptr = (i64*)unique_ptr; p.out_row = (i64*)out_row; p.out_col = (i64*)out_col;
   p.hdr = (RelabelHeader*)(ws + L.hdr); p.item_ptr = (i64*)(ws + L.item_ptr);
   p.min_idx = (u32*)(ws + L.min_idx); p.err = d_err;
-  p.first_bits = (u32*)(ws + L.first_bits); p.word_prefix = (u32*)(ws + L.word_prefix);
+  p.repeat_bits = (u32*)(ws + L.repeat_bits); p.word_prefix = (u32*)(ws + L.word_prefix);
   p.pf_ticket = (int*)(ws + L.pf_status); p.pf_status = (u64*)(ws + L.pf_status + 256);
   p.bucket_ptr = (i64*)(ws + L.bucket_ptr);
-  p.bucket_start = (u32*)(ws + L.bucket_start); p.bucket_cursor = (u32*)(ws + L.bucket_cursor);
+  p.ovf_count = (u32*)(ws + L.bucket_fill); p.gt_cursor = (u64*)(ws + L.bucket_fill + 64);
+  p.bucket_fill = (u32*)(ws + L.bucket_fill + 256);
+  p.ovf_item = (u64*)(ws + L.ovf_item); p.ovf_bucket = (u32*)(ws + L.ovf_bucket);
   p.part = (u64*)(ws + L.part); p.overflow = (u64*)(ws + L.overflow); p.buckets_cap = L.buckets_cap;
   p.seed_repeat = (u32*)(ws + L.seed_repeat); p.col_prefilled = col_prefilled ? 1 : 0;
 
   { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
-  // bucket counts, cursors, the repeated-seed flags and the prefix pass's ticket / status words
-  // are adjacent: one clear
-  GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_start, 0, L.min_idx - L.bucket_start, st));
+  // overflow-list length, bucket fill levels, the repeated-seed flags, the prefix pass's ticket /
+  // status words and the repeat bits are adjacent: one clear
+  GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_fill, 0, L.min_idx - L.bucket_fill, st));
   const i64 items_max = S_max + E_max;
   const int wide = sm_count() * GSB_RL_WIDE;
   int g_tiles = (int)((items_max + PT_TILE - 1) / PT_TILE); if (g_tiles < 1) g_tiles = 1;
   if (g_tiles > wide) g_tiles = wide;
-  { LaunchScope ls(KID_RL_PCOUNT, st); relabel_pcount_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
-  { LaunchScope ls(KID_RL_PSCAN, st); relabel_pscan_kernel<<<1, 1024, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_SCATTER, st); relabel_scatter_kernel<<<g_tiles, PT_THREADS, 0, st>>>(p); }
   const int g_bk = (int)(L.buckets_cap < sm_count() * GSB_RL_BK ? L.buckets_cap : sm_count() * GSB_RL_BK);
   const int dd_smem = 2 * DD_TAB * (int)sizeof(u32);
   GSB_CUDA_OK(cudaFuncSetAttribute(relabel_dedupe_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dd_smem));
   { LaunchScope ls(KID_RL_DEDUPE, st); relabel_dedupe_kernel<<<g_bk, DD_THREADS, dd_smem, st>>>(p); }
-  { LaunchScope ls(KID_RL_COUNT, st); relabel_mark_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_TILES, st); relabel_prefix_kernel<<<(int)L.pf_ctas, PF_THREADS, 0, st>>>(p); }
   { LaunchScope ls(KID_RL_EDGES, st); relabel_emit_kernel<<<(int)L.tiles, RL_THREADS, 0, st>>>(p); }
   GSB_CUDA_OK(cudaGetLastError());
