@@ -180,7 +180,7 @@ extern "C" int gsb_graphsage_sample(const int64_t* indptr, const void* indices, 
     // the other minibatches)
     int rc = sample_launch(indptr, indices, indices_dtype, num_cols, cur_seeds, S_max, d_S, fanouts[l], 0,
                            seed, stream_base + (uint32_t)l, L.sub_indptr, L.rows, L.cols, L.sel, L.E_cap,
-                           d_counts + 3 * l + 1, cur_ptr, B, L.block_col, workspace, ws_a, d_err,
+                           d_counts + 3 * l + 1, cur_ptr, B, L.block_col, L.S_cap, workspace, ws_a, d_err,
                            cuda_stream);
     if (rc != GSB_OK) return rc;
     // edge_ptr = sub_indptr[seeds_ptr] and the {S, U} counts are produced inside the relabel passes

@@ -249,13 +249,14 @@ int relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t B, in
                    size_t workspace_bytes, int* d_err, void* cuda_stream);
 
 // gsb_sample_cols with the extras of the layered sampler (gsb_sample.cu): `out_block_col`
-// receives every edge's column slot counted from its minibatch's first slot (seeds_ptr, B)
+// receives every edge's column slot counted from its minibatch's first slot (seeds_ptr, B);
+// S_geom (>= S_max) is the slot count the workspace was sized for
 int sample_launch(const int64_t* indptr, const void* indices, int indices_dtype, int64_t num_cols,
                   const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K, int replace,
                   uint64_t seed, uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
                   int64_t* out_cols, int64_t* out_sel, int64_t E_cap, int64_t* d_num_edges,
-                  const int64_t* seeds_ptr, int64_t B, int64_t* out_block_col, void* workspace,
-                  size_t workspace_bytes, int* d_err, void* cuda_stream);
+                  const int64_t* seeds_ptr, int64_t B, int64_t* out_block_col, int64_t S_geom,
+                  void* workspace, size_t workspace_bytes, int* d_err, void* cuda_stream);
 
 inline int ceil_div_i(i64 a, i64 b) { return (int)((a + b - 1) / b); }
 

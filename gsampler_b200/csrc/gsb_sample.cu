@@ -189,10 +189,17 @@ sample_tile_kernel(const SampleParams p) {
   }
 }
 
-static int sample_tile_cols(i64 K) {
+// Column slots per tile (CTA).  `S_geom` = the number of slots the launch is laid out for: with
+// few of them the tiles shrink (down to 64 slots) so that every SM still gets several CTAs --
+// the first layer of a 32 x 1024-seed super-batch is 128 tiles of 256 slots otherwise, fewer
+// CTAs than the GPU has SMs.  Results do not depend on the tile size (the random streams are
+// keyed by slot).
+static int sample_tile_cols(i64 K, i64 S_geom = -1) {
   i64 tc = SAMPLE_MAX_TILE_EDGES / K;
   if (tc > SAMPLE_THREADS) tc = SAMPLE_THREADS;
   if (tc < 1) tc = 1;
+  if (S_geom >= 0)
+    while (tc > 64 && (S_geom + tc - 1) / tc < 4 * (i64)sm_count()) tc >>= 1;
   return (int)tc;
 }
 
@@ -206,7 +213,7 @@ using namespace gsb;
 
 extern "C" size_t gsb_sample_cols_workspace_bytes(int64_t S_max, int64_t K) {
   if (S_max < 0 || K < 1) return 0;
-  int tc = sample_tile_cols(K);
+  int tc = sample_tile_cols(K, S_max);
   size_t tiles = (size_t)((S_max + tc - 1) / tc) + 1;
   return 256 + tiles * sizeof(u64);
 }
@@ -234,18 +241,19 @@ int sample_launch(const int64_t* indptr, const void* indices, int indices_dtype,
                   const int64_t* seeds, int64_t S_max, const int64_t* d_S, int64_t K, int replace,
                   uint64_t seed, uint32_t stream, int64_t* sub_indptr, int64_t* out_rows,
                   int64_t* out_cols, int64_t* out_sel, int64_t E_cap, int64_t* d_num_edges,
-                  const int64_t* seeds_ptr, int64_t B, int64_t* out_block_col, void* workspace,
-                  size_t workspace_bytes, int* d_err, void* cuda_stream) {
+                  const int64_t* seeds_ptr, int64_t B, int64_t* out_block_col, int64_t S_geom,
+                  void* workspace, size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (S_geom < S_max) S_geom = S_max;
   if (!indptr || !indices || !sub_indptr || S_max < 0 || E_cap < 0 || num_cols < 0) return GSB_ERR_INVALID;
   if (E_cap > 0 && (!out_rows || !out_sel)) return GSB_ERR_INVALID;
   if (indices_dtype != GSB_I32 && indices_dtype != GSB_I64) return GSB_ERR_INVALID;
   if (K < 1) return GSB_ERR_INVALID;
   if (K > SAMPLE_MAX_TILE_EDGES) return GSB_ERR_UNSUPPORTED;
   if (out_block_col && (!seeds_ptr || B < 1)) return GSB_ERR_INVALID;
-  if (workspace_bytes < gsb_sample_cols_workspace_bytes(S_max, K) || !workspace)
+  if (workspace_bytes < gsb_sample_cols_workspace_bytes(S_geom, K) || !workspace)
     return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
-  const int tc = sample_tile_cols(K);
+  const int tc = sample_tile_cols(K, S_geom);
   const int tiles = S_max == 0 ? 1 : ceil_div_i(S_max, tc);
   GSB_CUDA_OK(cudaMemsetAsync(workspace, 0, 256 + (size_t)(tiles + 1) * sizeof(u64), st));
   SampleParams p;
@@ -277,7 +285,7 @@ extern "C" int gsb_sample_cols(const int64_t* indptr, const void* indices, int i
                                size_t workspace_bytes, int* d_err, void* cuda_stream) {
   return gsb::sample_launch(indptr, indices, indices_dtype, num_cols, seeds, S_max, d_S, K, replace, seed,
                             stream, sub_indptr, out_rows, out_cols, out_sel, E_cap, d_num_edges, nullptr,
-                            0, nullptr, workspace, workspace_bytes, d_err, cuda_stream);
+                            0, nullptr, S_max, workspace, workspace_bytes, d_err, cuda_stream);
 }
 
 // ---------------------------------------------------------------- fixed-scratch variant

@@ -14,7 +14,7 @@ import torch
 
 from ..format import _COO, _CSC, _CSR
 from ..ops import gsddmm, gspmm
-from ..utils import create_block_from_coo
+from ..utils import create_block_from_coo, create_block_from_csc
 from . import matrix as _matrix
 from .matrix import Matrix, data_index
 
@@ -37,6 +37,28 @@ def batch_gen_block(frontier_list, coo_row_list, coo_col_list, coo_eids, coo_ptr
             block.edata[key] = value[i]
         block_list.append(block)
     return block_list
+
+
+def batch_gen_block_csc(frontier_list, indptr_list, row_list, coo_eids, coo_ptr, edata, col_counts):
+    """The same blocks in compressed form: block b = (indptr over its seed slots, relabelled row ids),
+    what gSampler's ``_BatchCSCRelabelByKey`` prepares (src/cuda/batch/batch_relabel.cu:215-321,
+    not bound in its Python layer)."""
+    edata_list = {}
+    if coo_eids is not None:
+        edata_list["_ID"] = torch.ops.gs_ops._CAPI_BatchSplitByOffset(coo_eids, coo_ptr)
+    for key, value in edata.items():
+        edata_list[key] = torch.ops.gs_ops._CAPI_BatchSplitByOffset(value, coo_ptr)
+    block_list = []
+    for i in range(len(frontier_list)):
+        block = create_block_from_csc(indptr_list[i], row_list[i], None, frontier_list[i].numel(), col_counts[i])
+        block.srcdata["_ID"] = frontier_list[i]
+        for key, value in edata_list.items():
+            block.edata[key] = value[i]
+        block_list.append(block)
+    return block_list
+
+
+torch.fx.wrap("batch_gen_block_csc")
 
 
 class BatchMatrix(Matrix):
@@ -152,16 +174,24 @@ class BatchMatrix(Matrix):
             probs, K, replace, probs_ptr)
         return self[selected_index::index_ptr, :], selected_index
 
-    def to_dgl_block(self, prefetch_edata={}):
+    def to_dgl_block(self, prefetch_edata={}, block_format="coo"):
+        """One block per minibatch.  ``block_format="csc"`` gives the compressed form instead of
+        the COO: the offsets of the minibatch's seed slots (one column per slot, also where a seed
+        repeats an earlier one) and the relabelled row ids."""
         (frontiers, frontiers_ptr, coo_row, coo_col, coo_eids,
          coo_bptr) = self._graph._CAPI_BatchGraphRelabel(
              self.col_ndata.get("_ID", self.null_tensor), self.row_ndata.get("_ID", self.null_tensor))
         split = torch.ops.gs_ops._CAPI_BatchSplitByOffset
         frontier_list = split(frontiers, frontiers_ptr)
         coo_row_list = split(coo_row, coo_bptr)
-        coo_col_list = split(coo_col, coo_bptr)
         col_counts = self._graph._CAPI_BatchGetColCounts()
         assign_edata = {key: self.edata[key] for key in prefetch_edata}
+        if block_format == "csc":
+            indptr_list = torch.ops.gs_ops._CAPI_BatchIndptrSplitByOffset(
+                self._graph._CAPI_GetCSCIndptr(), self._graph._CAPI_GetColBptr())
+            return batch_gen_block_csc(frontier_list, indptr_list, coo_row_list, coo_eids, coo_bptr,
+                                       assign_edata, col_counts)
+        coo_col_list = split(coo_col, coo_bptr)
         return batch_gen_block(frontier_list, coo_row_list, coo_col_list, coo_eids, coo_bptr,
                                assign_edata, col_counts)
 

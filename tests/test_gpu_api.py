@@ -180,6 +180,40 @@ def test_batchmatrix_sampler_matches_oracle(gsb, oracle, rmat):
             assert blk.num_dst_nodes() == layer["seeds_ptr"][b + 1] - layer["seeds_ptr"][b]
 
 
+def test_batch_blocks_in_csc_form(gsb, oracle, rmat):
+    """to_dgl_block(block_format="csc"): per minibatch the offsets over its seed slots and the
+    relabelled row ids -- the CSC block build (src/cuda/batch/batch_relabel.cu:215-321 in gSampler
+    prepares the same arrays).  Expanding the offsets gives back the COO block, and both equal the
+    oracle's relabel of the sampled edges."""
+    indptr, indices = rmat
+    seeds, ptr = _seeds(indptr.size - 1, nb=4, bs=300, seed=9)
+    ptr[2] = ptr[1]                                             # an empty minibatch
+    m = gsb.Matrix(new_graph(gsb, indptr, indices))
+    bm = gsb.BatchMatrix()
+    bm.load_from_matrix(m, False)
+    d_seeds, d_ptr = torch.as_tensor(seeds).cuda(), torch.as_tensor(ptr).cuda()
+    cur_seeds, cur_ptr = seeds, ptr
+    for K in (7, 3):
+        sample = bm[:, d_seeds::d_ptr].individual_sampling(K, None, False)
+        coo = sample.to_dgl_block()
+        csc = sample.to_dgl_block(block_format="csc")
+        sub = sample._graph
+        rows_g, cols = host(sub._CAPI_GetCOORows()), host(sub._CAPI_GetCOOCols())
+        eptr = host(sub._CAPI_GetEdgeBptr())
+        euq, eup, erow, ecol = oracle.batch_coo_relabel(cur_seeds, cur_ptr, cur_seeds[cols], rows_g, eptr)
+        assert len(coo) == len(csc) == ptr.size - 1
+        for b, (a, c) in enumerate(zip(coo, csc)):
+            ns = int(cur_ptr[b + 1] - cur_ptr[b])
+            ip = host(c.indptr)
+            assert ip.size == ns + 1 and ip[0] == 0 and c.num_dst_nodes() == ns
+            assert np.array_equal(np.repeat(np.arange(ns), np.diff(ip)), host(a.col))   # seeds are distinct here
+            assert np.array_equal(host(c.row), host(a.row)) and c.col is None
+            assert np.array_equal(host(c.row), erow[eptr[b]:eptr[b + 1]])
+            assert np.array_equal(host(c.srcdata["_ID"]), euq[eup[b]:eup[b + 1]])
+        d_seeds, d_ptr = sample.all_nodes()
+        cur_seeds, cur_ptr = host(d_seeds), host(d_ptr)
+
+
 def test_matrix_sampler_matches_oracle(gsb, oracle, rmat):
     """Single-minibatch graphsage_sampler (examples/graphsage/graphsage.py:7-17): slice, sample,
     all_nodes, to_dgl_block -- both the fused (lazy slice) and the unfused order of calls."""

@@ -507,3 +507,31 @@ def test_graph_in_pinned_host_memory(gsb, oracle, graph, idx_dtype):
         assert (S, E, U) == (ref[l]["seeds"].size, ref[l]["rows"].size, ref[l]["unique"].size)
         assert np.array_equal(host(smp.layers[l]["unique"][:U]), ref[l]["unique"])
         assert np.array_equal(host(smp.layers[l]["block_row"][:E]), ref[l]["block_row"])
+
+
+def test_lazy_slice_with_edge_data_in_pinned_host_memory(gsb, graph):
+    """``A[:, seeds].individual_sampling(...)`` runs as one fused kernel (the slice is lazy) and then
+    gathers the PARENT's edge data with the fused edge index: the same values as slicing first and
+    sampling the slice, also when the edge data lives in pinned host memory, and also when the
+    parent's edge data is edited between the slice and the sampling."""
+    indptr, indices = graph
+    n, E = indptr.size - 1, indices.size
+    rng = np.random.default_rng(21)
+    w = torch.from_numpy(rng.random(E).astype(np.float32))
+    seeds = cuda(rng.permutation(n)[:500])
+    results = []
+    for where in ("device", "pinned"):
+        for lazy in (True, False):
+            m = gsb.Matrix(new_graph(gsb, indptr, indices, seed=8))
+            m.edata["w"] = w.cuda() if where == "device" else w.clone().pin_memory()
+            sub = m[:, seeds]
+            if not lazy:
+                sub.num_edges()                      # any other use materialises the slice first
+            else:
+                m.edata["extra"] = m.edata["w"]      # an edit of the parent after the slice: not seen by it
+            s = sub.individual_sampling(6, None, False)
+            assert "extra" not in s.edata
+            assert s.edata["w"].is_cuda
+            results.append((s.edata["w"], s._graph._CAPI_GetCOORows(), s._graph._CAPI_GetCOOCols()))
+    for r in results[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(results[0], r))
