@@ -226,6 +226,15 @@ Graph::GraphAndIndex Graph::Compact(int64_t axis) {
 
 static torch::Tensor& AsyncErrorWord(const torch::Device& dev);
 
+// 32-bit copy of a compressed format's offsets, made on first use and kept with the format, for
+// the kernels that gather offsets at random (walks); null when the graph has 2^32 entries or more
+// or does not live on the GPU.
+static const uint32_t* Offsets32(Compressed& c) {
+  if (!c.indptr.is_cuda() || c.indices.numel() >= (int64_t)0xFFFFFFFFll) return nullptr;
+  if (!c.indptr32.defined()) c.indptr32 = c.indptr.to(torch::kInt32);  // wraps modulo 2^32: read back as unsigned
+  return reinterpret_cast<const uint32_t*>(c.indptr32.data_ptr<int32_t>());
+}
+
 // ------------------------------------------------------------------ walks
 // src/graph.cc:310-317.  The buffer is step-major [(L+1), N]; like the
 // reference it is returned REINTERPRETED as [N, L+1] (a reshape, no transpose).
@@ -238,7 +247,7 @@ torch::Tensor Graph::RandomWalk(torch::Tensor seeds, int64_t walk_length) {
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  CheckStatus(gsb_random_walk(P(csc_->indptr), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
+  CheckStatus(gsb_random_walk(P(csc_->indptr), Offsets32(*csc_), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
                               num_cols_, P(seeds), N, walk_length, seed_, NextStream(), PM(out),
                               AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "random_walk");
@@ -251,7 +260,7 @@ torch::Tensor Graph::Node2Vec(torch::Tensor seeds, int64_t walk_length, double p
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  CheckStatus(gsb_node2vec(P(csc_->indptr), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
+  CheckStatus(gsb_node2vec(P(csc_->indptr), Offsets32(*csc_), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
                            num_cols_, P(seeds), N, walk_length, p, q, seed_, NextStream(), PM(out),
                            AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "node2vec");

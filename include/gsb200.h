@@ -367,15 +367,20 @@ GSB_API int gsb_list_sample_replace(const float* probs, int64_t n, int64_t K, ui
  * w consumes the draws (seed, stream, w, 0..) in order.  Replaces
  * FusedRandomWalkCUDA (src/cuda/fusion/random_walk.cu:10-70) and
  * FusedNode2VecCUDA (src/cuda/fusion/node2vec.cu:67-162; needs sorted
- * columns).  Unlike the reference, a draw equal to 1.0 is clamped to the last
+ * columns).  indptr32 (optional, may be NULL): the same offsets as 32-bit
+ * unsigned values, usable when the graph has fewer than 2^32 entries -- every
+ * walker gathers two offsets at every step, and the half-size array stays in
+ * L2 where the 64-bit one does not; when given, `indptr` is not read.
+ * Unlike the reference, a draw equal to 1.0 is clamped to the last
  * neighbour and a "previous node" outside [0, num_nodes) counts as unconnected
  * instead of reading out of bounds. */
-GSB_API int gsb_random_walk(const int64_t* indptr, const void* indices, int indices_dtype,
-                            int64_t num_nodes, const int64_t* seeds, int64_t N,
+GSB_API int gsb_random_walk(const int64_t* indptr, const uint32_t* indptr32, const void* indices,
+                            int indices_dtype, int64_t num_nodes, const int64_t* seeds, int64_t N,
                             int64_t walk_length, uint64_t seed, uint32_t stream, int64_t* out,
                             int* d_err, void* cuda_stream);
-GSB_API int gsb_node2vec(const int64_t* indptr, const void* indices, int indices_dtype,
-                         int64_t num_nodes, const int64_t* seeds, int64_t N, int64_t walk_length,
+GSB_API int gsb_node2vec(const int64_t* indptr, const uint32_t* indptr32, const void* indices,
+                         int indices_dtype, int64_t num_nodes, const int64_t* seeds, int64_t N,
+                         int64_t walk_length,
                          double p, double q, uint64_t seed, uint32_t stream, int64_t* out,
                          int* d_err, void* cuda_stream);
 
