@@ -53,7 +53,8 @@ constexpr u32 IDX_UNSET = 0xFFFFFFFFu;
 constexpr int PT_TILE = GSB_PT_TILE;   // items per CTA tile of pcount / scatter
 constexpr int PT_THREADS = 512;
 constexpr int PT_BATCH = GSB_PT_BATCH; // loads in flight per thread
-constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch
+constexpr int OVF_LANES = 512;         // the overflow list is kept in this many lanes (see relabel_scatter_kernel)
+constexpr int PT_MAX_BUCKETS = 1024;   // buckets per minibatch that the scatter pass's shared histogram holds
 // grid caps in CTAs per SM: tile kernels (pcount, scatter), the bucket kernel (dedupe) and emit.  One
 // CTA per tile / bucket up to 64 per SM lets the hardware scheduler even out the tail (layer 3 of
 // cfg2: 2800 tiles, 6400 buckets; caps of 8 and 12 left CTAs with 2 or 3 tiles each): -1.2 % per step.
@@ -118,9 +119,10 @@ struct RelabelParams {
   i64* bucket_ptr;    // [B+1] first bucket of minibatch b
   u32* bucket_fill;   // [buckets] items of the bucket (zeroed; may exceed BK_CAP: the rest is on the overflow list)
   u64* part;          // [buckets * BK_CAP] id:32 | index:32, bucket k owns entries k * BK_CAP ...
-  u64* ovf_item;      // [items] items that found their bucket's region full
-  u32* ovf_bucket;    // [items] ... and the bucket each belongs to
-  u32* ovf_count;     // length of that list (zeroed)
+  u64* ovf_item;      // [OVF_LANES * ovf_lane_cap] items that found their bucket's region full
+  u32* ovf_bucket;    // ... and the bucket each belongs to
+  u32* ovf_count;     // [OVF_LANES] entries pushed to each lane (zeroed; above ovf_lane_cap: the lane is full)
+  u32 ovf_lane_cap;
   u64* overflow;      // global tables of buckets whose distinct ids overflow the shared table
   u64* gt_cursor;     // bump pointer into `overflow` (zeroed)
   u32* seed_repeat;   // [B] set when a seed of the minibatch repeats an earlier seed (or is invalid)
@@ -152,7 +154,7 @@ __global__ void relabel_setup_kernel(const RelabelParams p) {
       if (ns < 0 || ne < 0) { raise(p.err, ERRBIT_BAD_INPUT); ns = ns < 0 ? 0 : ns; ne = ne < 0 ? 0 : ne; }
       items = ns + ne;
       const i64 need = (items + PT_BUCKET_ITEMS - 1) / PT_BUCKET_ITEMS;
-      nbk = need < 1 ? 1 : (need > PT_MAX_BUCKETS ? PT_MAX_BUCKETS : need);
+      nbk = need < 1 ? 1 : need;
     }
     i64 tot_items, tot_bk;
     i64 ei = block_exclusive_scan(items, s_scan, &tot_items);
@@ -285,9 +287,11 @@ __device__ __forceinline__ void mark_repeat(const RelabelParams& p, i64 g, u32 f
 // bucket reserves the tile's run inside the bucket's region, then every item takes the next free
 // entry of its bucket's run.  A minibatch of n items has ceil(n / PT_BUCKET_ITEMS) buckets, so a
 // bucket holds PT_BUCKET_ITEMS items on average and its size scatters by a few tens around that;
-// items that do not fit the region any more (an id repeated thousands of times, a minibatch so
-// large that its 1024 buckets exceed the mean) go to one overflow list, tagged with their
-// bucket, which the bucket's dedupe CTA reads after its region.  The ids are read twice (the
+// items that do not fit the region any more (an id repeated thousands of times) go to the
+// overflow list, tagged with their bucket, which the bucket's dedupe CTA reads after its region.
+// The list is kept in OVF_LANES lanes of equal capacity so that a bucket does not have to look
+// at all of it: bucket k pushes to lane k % OVF_LANES, and to the next lane (and so on, around)
+// when that one is full.  The ids are read twice (the
 // second read hits L1/L2); the 8-byte stores of a run meet in L2 before they reach DRAM.
 __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scatter_kernel(const RelabelParams p) {
   __shared__ u32 s_hist[PT_MAX_BUCKETS];  // items of the bucket in this tile
@@ -301,10 +305,56 @@ __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scat
       while (p.item_ptr[b + 1] <= at) ++b;
       const Segment sg = load_segment(p, b);
       const i64 seg_hi = hi < sg.iend ? hi : sg.iend;
-      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) s_hist[k] = 0;
-      __syncthreads();
       const u32 lim = (u32)(seg_hi - sg.ibase);
       const u32 first = (u32)(at - sg.ibase) + threadIdx.x;
+      // entry `dst` of bucket k's items: inside the bucket's region, or on the overflow list
+      auto place = [&](i64 id, u32 off, u32 k, u32 dst) {
+        const u64 item = ((u64)(u32)id << 32) | off;
+        if (dst < (u32)BK_CAP) {
+          p.part[(sg.bk0 + k) * BK_CAP + dst] = item;
+        } else {
+          u32 lane = (u32)((sg.bk0 + k) % OVF_LANES);
+          int tries = 0;
+          for (; tries < OVF_LANES; ++tries) {
+            const u32 q = atomicAdd(p.ovf_count + lane, 1u);
+            if (q < p.ovf_lane_cap) {
+              const size_t at = (size_t)lane * p.ovf_lane_cap + q;
+              p.ovf_item[at] = item;
+              p.ovf_bucket[at] = (u32)(sg.bk0 + k);
+              break;
+            }
+            lane = (lane + 1) % OVF_LANES;
+          }
+          if (tries == OVF_LANES) raise(p.err, ERRBIT_CAPACITY);  // cannot happen: the lanes hold every item
+        }
+      };
+      auto reject = [&](u32 off) {
+        raise(p.err, ERRBIT_BAD_INPUT);  // negative, or not below the stated bound
+        mark_repeat(p, sg.ibase + off, IDX_UNSET);  // in no node list; relabels to -1
+        if (off < sg.ns) p.seed_repeat[b] = 1u;  // its edges' columns relabel to -1: no shortcut
+      };
+      if (sg.nbk > PT_MAX_BUCKETS) {
+        // a minibatch of more than PT_MAX_BUCKETS * PT_BUCKET_ITEMS items (one relabel call over
+        // a whole layer): more buckets than the shared histogram holds, so every item takes its
+        // entry with a global atomic of its own (thousands of addresses, all in L2)
+        for (u32 off0 = first; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
+          GSB_LOAD_ID_BATCH(off0, lim)
+#pragma unroll
+          for (int u = 0; u < PT_BATCH; ++u) {
+            const u32 off = off0 + (u32)(u * PT_THREADS);
+            if ((u64)id[u] < p.id_limit) {
+              const u32 k = bucket_of((u32)id[u], sg.nbk);
+              place(id[u], off, k, atomicAdd(p.bucket_fill + sg.bk0 + k, 1u));
+            } else if (off < lim) {
+              reject(off);
+            }
+          }
+        }
+        at = seg_hi;
+        continue;
+      }
+      for (int k = threadIdx.x; k < sg.nbk; k += PT_THREADS) s_hist[k] = 0;
+      __syncthreads();
       for (u32 off0 = first; off0 < lim; off0 += PT_BATCH * PT_THREADS) {
         GSB_LOAD_ID_BATCH(off0, lim)
 #pragma unroll
@@ -324,19 +374,9 @@ __global__ void __launch_bounds__(PT_THREADS, GSB_SCATTER_MIN_CTAS) relabel_scat
           const u32 off = off0 + (u32)(u * PT_THREADS);
           if ((u64)id[u] < p.id_limit) {
             const u32 k = bucket_of((u32)id[u], sg.nbk);
-            const u32 dst = atomicAdd(&s_next[k], 1u);
-            const u64 item = ((u64)(u32)id[u] << 32) | off;
-            if (dst < (u32)BK_CAP) {
-              p.part[(sg.bk0 + k) * BK_CAP + dst] = item;
-            } else {
-              const u32 q = atomicAdd(p.ovf_count, 1u);  // < number of items, which the list holds
-              p.ovf_item[q] = item;
-              p.ovf_bucket[q] = (u32)(sg.bk0 + k);
-            }
+            place(id[u], off, k, atomicAdd(&s_next[k], 1u));
           } else if (off < lim) {
-            raise(p.err, ERRBIT_BAD_INPUT);  // negative, or not below the stated bound
-            mark_repeat(p, sg.ibase + off, IDX_UNSET);  // in no node list; relabels to -1
-            if (off < sg.ns) p.seed_repeat[b] = 1u;  // its edges' columns relabel to -1: no shortcut
+            reject(off);
           }
         }
       }
@@ -365,15 +405,26 @@ __device__ __forceinline__ u32 stab_insert(u32* s_key, u32* s_min, u32 tab, u32 
 // thousands of times costs nothing extra.  A bucket whose items all lie in its own region (the
 // normal case: at most BK_CAP = DD_BATCH * DD_THREADS of them) stays in registers between the two
 // phases together with the table slot each item found; a bucket with items on the overflow list
-// streams its region and then the list (every entry of the list is looked at, the bucket's own
-// are used).
+// streams its region and then its lane of the list (every entry of the lane is looked at, the
+// bucket's own are used).
 template <typename Fn>
-__device__ __forceinline__ void for_each_bucket_item(const RelabelParams& p, i64 k, u32 in_region, u32 n_ovf,
+__device__ __forceinline__ void for_each_bucket_item(const RelabelParams& p, i64 k, u32 in_region, bool spilled,
                                                      Fn fn) {
   const u64* items = p.part + k * BK_CAP;
   for (u32 i = threadIdx.x; i < in_region; i += DD_THREADS) fn(__ldg(items + i));
-  for (u32 j = threadIdx.x; j < n_ovf; j += DD_THREADS)
-    if (__ldg(p.ovf_bucket + j) == (u32)k) fn(__ldg(p.ovf_item + j));
+  if (!spilled) return;
+  // the bucket's lane, and the lanes after it for as long as each was filled to the brim (only
+  // then can an entry of this bucket have moved on to the next)
+  u32 lane = (u32)(k % OVF_LANES);
+  for (int t = 0; t < OVF_LANES; ++t) {
+    const u32 pushed = p.ovf_count[lane];
+    const u32 n = pushed < p.ovf_lane_cap ? pushed : p.ovf_lane_cap;
+    const size_t base = (size_t)lane * p.ovf_lane_cap;
+    for (u32 j = threadIdx.x; j < n; j += DD_THREADS)
+      if (__ldg(p.ovf_bucket + base + j) == (u32)k) fn(__ldg(p.ovf_item + base + j));
+    if (pushed < p.ovf_lane_cap) break;
+    lane = (lane + 1) % OVF_LANES;
+  }
 }
 
 __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_kernel(const RelabelParams p) {
@@ -388,7 +439,6 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
     if (cnt == 0) continue;  // uniform over the CTA
     const bool spilled = cnt > (u32)BK_CAP;
     const u32 in_region = spilled ? (u32)BK_CAP : cnt;
-    const u32 n_ovf = spilled ? *p.ovf_count : 0u;
     const int b = find_segment(p.bucket_ptr, p.B, k);
     const i64 gbase = p.item_ptr[b];
     const u32 ns = (u32)(p.seeds_ptr[b + 1] - p.seeds_ptr[b]);  // items below ns are the minibatch's seeds
@@ -434,13 +484,13 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
         continue;
       }
     } else {
-      for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
+      for_each_bucket_item(p, k, in_region, spilled, [&](u64 it) {
         if (stab_insert(s_key, s_min, tab, (u32)(it >> 32), (u32)it) == tab) s_over = 1;
       });
       __syncthreads();
       if (!s_over) {
         const u32 mask = tab - 1;
-        for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
+        for_each_bucket_item(p, k, in_region, spilled, [&](u64 it) {
           const u32 key = (u32)(it >> 32);
           u32 pos = hash32(key) & mask;
           for (u32 probes = 0; s_key[pos] != key && probes < tab; ++probes) pos = (pos + 1) & mask;
@@ -458,11 +508,11 @@ __global__ void __launch_bounds__(DD_THREADS, GSB_DD_MIN_CTAS) relabel_dedupe_ke
     u64* gt = p.overflow + s_gt_off;
     for (u32 i = threadIdx.x; i < slots; i += DD_THREADS) gt[i] = SLOT_EMPTY;
     __syncthreads();
-    for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
+    for_each_bucket_item(p, k, in_region, spilled, [&](u64 it) {
       if (!gtab_insert(gt, slots, (u32)(it >> 32), (u32)it)) raise(p.err, ERRBIT_TABLE_FULL);
     });
     __syncthreads();
-    for_each_bucket_item(p, k, in_region, n_ovf, [&](u64 it) {
+    for_each_bucket_item(p, k, in_region, spilled, [&](u64 it) {
       const u32 m = gtab_find(gt, slots, (u32)(it >> 32));
       if (m == IDX_UNSET) raise(p.err, ERRBIT_KEY_MISSING);
       else repeat(it, m);
@@ -700,10 +750,14 @@ __global__ void __launch_bounds__(RL_THREADS, GSB_EMIT_MIN_CTAS) relabel_emit_ke
   }
 }
 
+// offsets inside the zeroed block
+constexpr size_t ZB_GT_CURSOR = 0, ZB_OVF_COUNT = 256, ZB_BUCKET_FILL = 256 + sizeof(u32) * OVF_LANES;
+static_assert(ZB_BUCKET_FILL % 256 == 0, "bucket fill levels start on a 256-byte boundary");
+
 struct RelabelLayout {
   size_t hdr, item_ptr, bucket_ptr, bucket_fill, seed_repeat, pf_status, repeat_bits,
       min_idx, word_prefix, part, ovf_item, ovf_bucket, overflow, total;
-  i64 tiles, buckets_cap, pf_ctas;
+  i64 tiles, buckets_cap, pf_ctas, ovf_lane_cap;
 };
 
 static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
@@ -717,9 +771,9 @@ static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   L.hdr = o; o = up(o + sizeof(RelabelHeader));
   L.item_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
   L.bucket_ptr = o; o = up(o + sizeof(i64) * (size_t)(B + 1));
-  // zeroed block: overflow-list length and table bump pointer (first 256 bytes), bucket fill
+  // zeroed block: table bump pointer (first 256 bytes), overflow-lane fill levels, bucket fill
   // levels, repeated-seed flags, prefix-pass ticket / status, repeat bits
-  L.bucket_fill = o; o = up(o + 256 + sizeof(u32) * (size_t)(L.buckets_cap + 1));
+  L.bucket_fill = o; o = up(o + ZB_BUCKET_FILL + sizeof(u32) * (size_t)(L.buckets_cap + 1));
   L.seed_repeat = o; o = up(o + sizeof(u32) * (size_t)(B + 1));
   const i64 words = (items + 31) / 32 + 8;
   L.pf_ctas = (words + PF_WORDS - 1) / PF_WORDS + 1;
@@ -728,8 +782,10 @@ static RelabelLayout relabel_layout(i64 S_max, i64 E_max, i64 B) {
   L.min_idx = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
   L.word_prefix = o; o = up(o + sizeof(u32) * (size_t)(words + 8));
   L.part = o; o = up(o + sizeof(u64) * (size_t)(L.buckets_cap + 1) * (size_t)BK_CAP);
-  L.ovf_item = o; o = up(o + sizeof(u64) * (size_t)(items + 4));
-  L.ovf_bucket = o; o = up(o + sizeof(u32) * (size_t)(items + 4));
+  // together the lanes hold every item, whichever lanes they crowd into
+  L.ovf_lane_cap = (items + OVF_LANES - 1) / OVF_LANES + 64;
+  L.ovf_item = o; o = up(o + sizeof(u64) * (size_t)(L.ovf_lane_cap * OVF_LANES));
+  L.ovf_bucket = o; o = up(o + sizeof(u32) * (size_t)(L.ovf_lane_cap * OVF_LANES));
   // overflow tables: 2 slots per item + 32 per bucket; touched only by buckets that need them
   L.overflow = o; o = up(o + sizeof(u64) * (size_t)(2 * items + 32 * (L.buckets_cap + 1)));
   L.total = o;
@@ -790,14 +846,14 @@ int gsb::relabel_launch(const int64_t* seeds, const int64_t* seeds_ptr, int64_t 
   p.repeat_bits = (u32*)(ws + L.repeat_bits); p.word_prefix = (u32*)(ws + L.word_prefix);
   p.pf_ticket = (int*)(ws + L.pf_status); p.pf_status = (u64*)(ws + L.pf_status + 256);
   p.bucket_ptr = (i64*)(ws + L.bucket_ptr);
-  p.ovf_count = (u32*)(ws + L.bucket_fill); p.gt_cursor = (u64*)(ws + L.bucket_fill + 64);
-  p.bucket_fill = (u32*)(ws + L.bucket_fill + 256);
+  p.gt_cursor = (u64*)(ws + L.bucket_fill + ZB_GT_CURSOR); p.ovf_count = (u32*)(ws + L.bucket_fill + ZB_OVF_COUNT);
+  p.bucket_fill = (u32*)(ws + L.bucket_fill + ZB_BUCKET_FILL); p.ovf_lane_cap = (u32)L.ovf_lane_cap;
   p.ovf_item = (u64*)(ws + L.ovf_item); p.ovf_bucket = (u32*)(ws + L.ovf_bucket);
   p.part = (u64*)(ws + L.part); p.overflow = (u64*)(ws + L.overflow); p.buckets_cap = L.buckets_cap;
   p.seed_repeat = (u32*)(ws + L.seed_repeat); p.col_prefilled = col_prefilled ? 1 : 0;
 
   { LaunchScope ls(KID_RL_SETUP, st); relabel_setup_kernel<<<1, 1024, 0, st>>>(p); }
-  // overflow-list length, bucket fill levels, the repeated-seed flags, the prefix pass's ticket /
+  // table bump pointer, overflow-lane and bucket fill levels, the repeated-seed flags, the prefix pass's ticket /
   // status words and the repeat bits are adjacent: one clear
   GSB_CUDA_OK(cudaMemsetAsync(ws + L.bucket_fill, 0, L.min_idx - L.bucket_fill, st));
   const i64 items_max = S_max + E_max;

@@ -23,7 +23,8 @@ constexpr int64_t kCOO = 1, kCSC = 2, kCSR = 4;  // format bits (src/graph_stora
 struct Compressed {  // CSC (offsets over columns) or CSR (offsets over rows)
   torch::Tensor indptr, indices;
   c10::optional<torch::Tensor> e_ids;
-  torch::Tensor indptr32;  // lazily built 32-bit copy of the offsets (see Offsets32)
+  torch::Tensor indptr32;   // lazily built 32-bit copy of the offsets (walks)
+  torch::Tensor indices32;  // lazily built 32-bit copy of 64-bit indices (walks)
 };
 
 struct Coordinate {

@@ -235,6 +235,17 @@ static const uint32_t* Offsets32(Compressed& c) {
   return reinterpret_cast<const uint32_t*>(c.indptr32.data_ptr<int32_t>());
 }
 
+// 32-bit copy of 64-bit row ids, made on first use and kept with the format, for the walks: every
+// step is one gather at a random place of this array, and the rate of such gathers grows with the
+// share of the array that L2 holds.  Costs half the array's size again in device memory.
+struct WalkIndices { const void* ptr; int dtype; };
+static WalkIndices NarrowIndices(Compressed& c, int64_t num_rows) {
+  if (c.indices.scalar_type() == torch::kInt32 || !c.indices.is_cuda() || num_rows > (int64_t)0x7FFFFFFF)
+    return {c.indices.data_ptr(), IdxDtype(c.indices)};
+  if (!c.indices32.defined()) c.indices32 = c.indices.to(torch::kInt32);
+  return {c.indices32.data_ptr(), GSB_I32};
+}
+
 // ------------------------------------------------------------------ walks
 // src/graph.cc:310-317.  The buffer is step-major [(L+1), N]; like the
 // reference it is returned REINTERPRETED as [N, L+1] (a reshape, no transpose).
@@ -247,8 +258,8 @@ torch::Tensor Graph::RandomWalk(torch::Tensor seeds, int64_t walk_length) {
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  CheckStatus(gsb_random_walk(P(csc_->indptr), Offsets32(*csc_), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
-                              num_cols_, P(seeds), N, walk_length, seed_, NextStream(), PM(out),
+  const WalkIndices ix = NarrowIndices(*csc_, num_rows_);
+  CheckStatus(gsb_random_walk(P(csc_->indptr), Offsets32(*csc_), ix.ptr, ix.dtype, num_cols_, P(seeds), N, walk_length, seed_, NextStream(), PM(out),
                               AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "random_walk");
   return out.reshape({N, -1});
@@ -260,8 +271,8 @@ torch::Tensor Graph::Node2Vec(torch::Tensor seeds, int64_t walk_length, double p
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  CheckStatus(gsb_node2vec(P(csc_->indptr), Offsets32(*csc_), csc_->indices.data_ptr(), IdxDtype(csc_->indices),
-                           num_cols_, P(seeds), N, walk_length, p, q, seed_, NextStream(), PM(out),
+  const WalkIndices ix = NarrowIndices(*csc_, num_rows_);
+  CheckStatus(gsb_node2vec(P(csc_->indptr), Offsets32(*csc_), ix.ptr, ix.dtype, num_cols_, P(seeds), N, walk_length, p, q, seed_, NextStream(), PM(out),
                            AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "node2vec");
   return out.reshape({N, -1});
@@ -282,6 +293,7 @@ void Graph::SortCSCIndices() {
   auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(csc_->indices.device()));
   // a graph loaded from the caller's tensors shares them: sort a private copy
   csc_->indices = csc_->indices.clone();
+  csc_->indices32 = torch::Tensor();
   CheckStatus(gsb_sort_segments(P(csc_->indptr), csc_->indices.data_ptr(), dt, num_cols_, nnz,
                                 ws.data_ptr(), (size_t)ws.numel(), err.data_ptr<int>(), CurrentStream()),
               "sort_segments");

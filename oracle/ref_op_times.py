@@ -24,6 +24,7 @@ sys.path.insert(0, ROOT)
 
 import bench  # noqa: E402
 import gsampler_b200 as gsb  # noqa: E402
+from gsampler_b200 import synth  # noqa: E402
 from oracle import build_ref  # noqa: E402
 
 
@@ -50,7 +51,7 @@ def main():
         return
     dev = torch.device("cuda")
     cfg = bench.WORKLOADS["cfg2"]
-    indptr, indices = bench.make_graph(cfg, dev)
+    indptr, indices = bench.make_graph(cfg, dev, synth)
     n, E = cfg["nodes"], int(indptr[-1])
     gen = torch.Generator(device=dev)
     gen.manual_seed(11)
@@ -212,6 +213,49 @@ def main():
     row("N2V", "1 M node2vec walks x 80 steps, p=2, q=0.5 (sorted columns)",
         lambda: A._CAPI_Node2Vec(walkers, 80, 2.0, 0.5),
         lambda: ref.node2vec(walkers, 80, indices, indptr, 2.0, 0.5))
+
+    # ---- fused edge operators of the PASS / AS-GCN / LADIES samplers (scalar per-node values)
+    u1, v1, u2, v2 = (torch.rand(n, 1, generator=gen, device=dev) + 0.5 for _ in range(4))
+    o1, o2 = torch.empty(E, 1, device=dev), torch.empty(E, 1, device=dev)
+    row("FUSED_U_OP_V", "two u-mul-v maps over 123.7 M edges in one pass (COO)",
+        lambda: A._CAPI_FusedUOPV("mul", u1, v1, o1, u2, v2, o2, COO),
+        lambda: ref.fused_u_op_v_coo("mul", indices, col_of_edge, u1, v1, o1, u2, v2, o2))
+
+    def ours_e2():
+        out = torch.zeros(n, 1, device=dev)
+        A._CAPI_FusedESquareSum("copy_rhs", "sum", None, w2, out, None, None, 0, CSC)
+        return out
+
+    def ref_e2():
+        out = torch.zeros(n, 1, device=dev)
+        ref.e_square_sum_csc("copy_rhs", "sum", indptr, indices, dummy, w2, out, aux, aux)
+        return out
+
+    row("E_SQUARE_SUM", "per-column sum of squared edge weights, 123.7 M edges (CSC)", ours_e2, ref_e2)
+
+    def ours_edu():
+        out = torch.zeros(n, 1, device=dev)
+        A._CAPI_FusedEDivUSum("div", "sum", node, w2, out, None, None, 0, CSC)
+        return out
+
+    def ref_edu():
+        out = torch.zeros(n, 1, device=dev)
+        ref.e_div_u_sum_csc("div", "sum", indptr, indices, node, w2, out, aux, aux)
+        return out
+
+    row("E_DIV_U_SUM", "per-column sum of edge weight / value of the row node (CSC)", ours_edu, ref_edu)
+
+    # ---- SORT: per-column sort of the whole graph (once-per-graph preprocessing), shuffled columns
+    shuffled = indices[torch.randperm(E, generator=gen, device=dev)]  # columns keep their lengths, not their order
+
+    def ours_sort():
+        g = gsb.Graph(n, n)
+        g._CAPI_LoadCSC(indptr, shuffled)
+        g._CAPI_SortCSCIndices()
+        return g
+
+    row("SORT", "every column of 123.7 M randomly ordered row ids sorted (copy included on both sides)",
+        ours_sort, lambda: ref.sort_indices(indptr, shuffled))
     print(json.dumps({"graph": "cfg2: %d nodes / %d edges, int64" % (n, E), "reps": args.reps,
                       "rows": len(rows_out)}))
 

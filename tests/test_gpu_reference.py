@@ -460,6 +460,30 @@ def test_benchmark_size_super_batch_through_reference_relabel(gsb, ref):
     torch.cuda.empty_cache()
 
 
+def test_one_large_minibatch_relabel_equals_reference(gsb, ref):
+    """Unique / relabel of ONE minibatch of 6.5 M items (a whole layer relabelled at once, as the
+    non-batch samplers do): more buckets than the scatter pass's shared histogram holds, so its
+    per-item atomic path runs; a few ids repeated tens of thousands of times fill their buckets'
+    regions and go through the overflow list.  Bit-exact against the reference's
+    TensorUniqueCUDA / TensorRelabelCUDA (src/cuda/unique_reindex.cu:174-199)."""
+    g = torch.Generator(device="cuda")
+    g.manual_seed(31)
+    n = 3_000_000
+    seeds = torch.randint(0, n, (1_500_000,), generator=g, device="cuda")
+    rows = torch.randint(0, n, (5_000_000,), generator=g, device="cuda")
+    hubs = torch.randint(0, n, (12,), generator=g, device="cuda")
+    at = torch.randint(0, rows.numel(), (400_000,), generator=g, device="cuda")
+    rows[at] = hubs[torch.randint(0, 12, (at.numel(),), generator=g, device="cuda")]
+    cols = torch.sort(torch.randint(0, seeds.numel(), (rows.numel(),), generator=g, device="cuda")).values
+    A = gsb.Graph(n, seeds.numel())
+    A._CAPI_LoadCOO(rows, cols, False, True)
+    no_map = torch.empty(0, dtype=torch.int64, device="cuda")
+    assert torch.equal(A._CAPI_GetValidNodes(seeds, no_map), ref.tensor_unique(torch.cat([seeds, rows])))
+    r_uq, (r_col, r_row) = ref.tensor_relabel([seeds, rows], [seeds[cols], rows])
+    uq, new_row, new_col, _ = A._CAPI_GraphRelabel(seeds, no_map)
+    assert torch.equal(uq, r_uq) and torch.equal(new_row, r_row) and torch.equal(new_col, r_col)
+
+
 @pytest.mark.parametrize("idx_dtype", [torch.int64, torch.int32])
 def test_sort_columns_equals_reference_and_oracle(gsb, ref, oracle, idx_dtype):
     """Per-column sort (Graph::SortCSCIndices): bit-exact against the reference's SortIndicesCUDA
