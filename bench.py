@@ -173,6 +173,7 @@ def cpu_threads():
     """All host cores for the OpenMP port (a launcher such as torchrun pins OMP_NUM_THREADS to 1)."""
     n = len(os.sched_getaffinity(0)) if hasattr(os, "sched_getaffinity") else (os.cpu_count() or 1)
     os.environ["OMP_NUM_THREADS"] = str(n)
+    os.environ["GS_ORACLE_THREADS"] = str(n)  # read by the oracle when it loads: OpenMP may be initialised already
     return n
 
 
@@ -816,8 +817,9 @@ def main():
     dev = torch.device("cuda", local_rank)
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        if os.environ.get("NCCL_DEBUG", "").upper() in ("", "VERSION"):
-            os.environ["NCCL_DEBUG"] = "WARN"  # keep stdout to the one JSON line
+        # NCCL writes its version banner and warnings to stdout: send them to stderr, stdout
+        # carries the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=dev)
 
     from gsampler_b200 import pipeline

@@ -5,6 +5,8 @@ repository root holds the headline one):
                                                   # 232 965 nodes / 114.6 M weighted edges
     python -m gsampler_b200.benchmarks node2vec   # 1 M walkers x 80 steps, p=2, q=0.5,
                                                   # 2 449 029 nodes / 123.7 M edges
+    python -m gsampler_b200.benchmarks limits     # uniform walks, COO row sums, uniform list sampling on
+                                                  # a 1 M-node / 50 M-edge graph (a profiling shape)
     python -m gsampler_b200.benchmarks gather     # feature fetch: 4 M rows of 100 fp32 out of 2 449 029
     python -m gsampler_b200.benchmarks cfg5       # the same on the full 111 M nodes / 3.2 G edges (14 GB)
     python -m gsampler_b200.benchmarks cfg5s      # GraphSAGE [15,10,5] on an int32-index R-MAT-like
@@ -153,6 +155,40 @@ def node2vec(steps=3, warmup=1, walkers=1000000, length=80):
                                  % (walkers, length, n, int(indptr[-1]))}, **out}))
 
 
+def limits(steps=3, warmup=2, n=1000000, e=50000000):
+    """The three operators whose rate is set by one hardware unit rather than by DRAM bandwidth:
+    uniform walks (random 32-byte gathers), row sums over a COO in column order (one L2 reduction
+    per edge) and a uniform choice from one list (one Philox block per candidate).  Small enough
+    for a profiler capture, larger than L2."""
+    dev = torch.device("cuda")
+    indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=20000, seed=2024, device=dev)
+    nnz = int(indptr[-1])
+    A = gs.Graph(n, n)
+    A._CAPI_LoadCSC(indptr, indices)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(7)
+    walkers = torch.randint(0, n, (400000,), generator=gen, device=dev)
+    M = gs.Matrix(A)
+    M.edata["w"] = torch.rand(nnz, generator=gen, device=dev)
+    M.sum("w", axis=1)   # builds the COO outside the timed calls
+    out = {}
+    for name, fn, units in (("random_walk", lambda: A._CAPI_RandomWalk(walkers, 80), 400000 * 80),
+                            ("coo_row_sums", lambda: M.sum("w", axis=1), nnz),
+                            ("list_sampling_uniform", lambda: torch.ops.gs_ops._CAPI_ListSampling(n, 4000, False), n)):
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out[name] = {"ms_per_call": ms, "units_per_sec": units / (ms / 1e3)}
+    print(json.dumps({"metric": "operator_ms", "config": {"workload": "%d nodes / %d edges" % (n, nnz)}, **out}))
+
+
 def gather(steps=10, warmup=3, rows=4000000, width=100):
     """Feature fetch for a sampled frontier: random rows of a [2 449 029, 100] fp32 table."""
     dev = torch.device("cuda")
@@ -239,5 +275,6 @@ def cfg5s(steps=6, warmup=3, n=11105996, e=320000000, large=False):
 if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "node2vec"
     t0 = time.time()
-    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s, "cfg5": cfg5, "gather": gather}[which]()
+    {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s, "cfg5": cfg5, "gather": gather,
+     "limits": limits}[which]()
     print("# %s finished in %.1f s" % (which, time.time() - t0), file=sys.stderr)

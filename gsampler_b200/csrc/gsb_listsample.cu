@@ -280,8 +280,9 @@ __global__ void __launch_bounds__(LS_THREADS) list_emit_kernel(const ListParams 
 // i.e. the largest index: an atomic max, whatever the order of execution.  `out_idx` must be zero
 // before the launch; picks come out in slot order.
 __global__ void __launch_bounds__(LS_THREADS) list_reservoir_kernel(const ListParams p) {
-  const i64 n = p.range[p.B] < p.R ? p.range[p.B] : p.R;
-  if (p.B == 1 && blockIdx.x == 0 && threadIdx.x == 0) {  // a single list has no set-up launch
+  const bool whole = p.range == nullptr;  // one list [0, R), stated by the caller: no offsets to read or write
+  const i64 n = whole ? p.R : (p.range[p.B] < p.R ? p.range[p.B] : p.R);
+  if (!whole && p.B == 1 && blockIdx.x == 0 && threadIdx.x == 0) {  // a single list has no set-up launch
     i64 len = p.range[1] - p.range[0];
     if (len < 0) { raise(p.err, ERRBIT_BAD_INPUT); len = 0; }
     if (p.range[1] > p.R) raise(p.err, ERRBIT_CAPACITY);
@@ -290,7 +291,7 @@ __global__ void __launch_bounds__(LS_THREADS) list_reservoir_kernel(const ListPa
   }
   for (i64 i = (i64)blockIdx.x * LS_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * LS_THREADS) {
     const int b = p.B == 1 ? 0 : find_segment(p.range, p.B, i);
-    const i64 r0 = p.range[b], j = i - r0, len = p.range[b + 1] - r0;
+    const i64 r0 = whole ? 0 : p.range[b], j = i - r0, len = whole ? p.R : p.range[b + 1] - r0;
     if (j < 0) continue;  // an item before the first segment
     long long* out = reinterpret_cast<long long*>(p.out_idx) + (p.B == 1 ? 0 : p.out_range[b]);
     if (len <= p.K) { out[j] = i; continue; }
@@ -378,7 +379,8 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
                                int64_t K, uint64_t seed, uint32_t stream, int64_t* out_idx,
                                int64_t* out_range, void* workspace, size_t workspace_bytes,
                                int* d_err, void* cuda_stream) {
-  if (!range || !out_range || B < 1 || R < 0 || K < 0 || (R > 0 && K > 0 && !out_idx))
+  const bool whole = !range && !probs && B == 1;  // uniform choice from the one list [0, R)
+  if ((!whole && (!range || !out_range)) || B < 1 || R < 0 || K < 0 || (R > 0 && K > 0 && !out_idx))
     return GSB_ERR_INVALID;
   if (R >= (1ll << 31) || B >= (1ll << 22)) return GSB_ERR_UNSUPPORTED;
   const ListLayout L = list_layout(R, B);
@@ -397,7 +399,7 @@ extern "C" int gsb_list_sample(const float* probs, const int64_t* range, int64_t
     p.status = nullptr; p.ticket = nullptr; p.done = nullptr;
     const i64 cap = R < B * K ? R : B * K;  // most picks there can be
     if (cap > 0) GSB_CUDA_OK(cudaMemsetAsync(out_idx, 0, sizeof(i64) * (size_t)cap, st));
-    if (B > 1 || R == 0 || K == 0) { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
+    if (!whole && (B > 1 || R == 0 || K == 0)) { LaunchScope ls(KID_LIST_SAMPLE, st); list_setup_kernel<<<1, 1024, 0, st>>>(p); }
     if (R > 0 && K > 0) {
       i64 gr = (R + LS_THREADS - 1) / LS_THREADS; if (gr > sm_count() * 16) gr = sm_count() * 16;
       LaunchScope ls(KID_LIST_SAMPLE, st);

@@ -40,6 +40,7 @@ struct ProbParams {
   i64 E_cap;
   int* err;
   int thread_path;       // columns of at most WT_MAX_DEG entries are handled by the thread kernel
+  int short_rounds;      // ... which orders groups of this many tiles by column length
   const i64* slot_start;  // [S] first entry of the slot's column   } by-products of
   const u32* slot_deg;    // [S] its length                          } the count pass
   const i64* list;        // slots the warp kernel has to process (unordered)
@@ -75,16 +76,81 @@ constexpr int WT_THREADS = 128;
 #endif
 constexpr int WT_MAX_DEG = GSB_WT_MAX_DEG;
 constexpr int WT_MAX_K = 32;
+#ifndef GSB_WT_BATCH
+#define GSB_WT_BATCH 8
+#endif
+// Tiles of WT_THREADS columns ordered together (at most; fewer on small inputs).  Ordering by
+// length makes the lanes of a warp agree, but neighbouring lanes then read weights from places
+// far apart instead of from one contiguous stretch of the slice, and the wider the group the
+// further apart: 3.7 M columns at K = 5 take 1.08 ms with groups of 1 tile, 0.95 with 2,
+// 1.07 with 4, 1.26 with 8.
+#ifndef GSB_WT_ROUNDS
+#define GSB_WT_ROUNDS 2
+#endif
+constexpr int WT_ROUNDS = GSB_WT_ROUNDS;
+constexpr int WT_BATCH = GSB_WT_BATCH;  // keys computed together: 8 (two Philox blocks) or 4 (one)
+static_assert(WT_BATCH == 4 || WT_BATCH == 8, "whole Philox blocks");
 
+// No minimum number of CTAs per SM is stated on purpose: left alone the compiler settles on 64
+// registers (8 CTAs per SM, 1.08 ms for 3.7 M columns at K = 5); a stated minimum of 1 lets it
+// take 83 (6 CTAs, 1.49 ms), one of 10 forces 48 with spills (1.43 ms).
+#ifdef GSB_WT_MIN_CTAS
+#define GSB_WT_BOUNDS __launch_bounds__(WT_THREADS, GSB_WT_MIN_CTAS)
+#else
+#define GSB_WT_BOUNDS __launch_bounds__(WT_THREADS)
+#endif
 template <typename IndexT>
-__global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const ProbParams p) {
+__global__ void GSB_WT_BOUNDS sample_probs_thread_kernel(const ProbParams p) {
   extern __shared__ u32 s_top[];  // keys[K][WT_THREADS], then positions[K][WT_THREADS]
+  __shared__ u32 s_hist[WT_MAX_DEG + 2];  // columns of each length in the tile, then first place of the length
+  __shared__ unsigned short s_order[WT_THREADS * WT_ROUNDS];  // the group's columns by ascending length
+  __shared__ i64 s_scan[34];
   const int K = p.K;
   u32* tkey = s_top + threadIdx.x;
   u32* tpos = s_top + K * WT_THREADS + threadIdx.x;
   i64 S = p.S_max;
   if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
-  for (i64 slot = (i64)blockIdx.x * WT_THREADS + threadIdx.x; slot < S; slot += (i64)gridDim.x * WT_THREADS) {
+  const int rounds = p.short_rounds;  // 1 .. WT_ROUNDS
+  const i64 group = (i64)WT_THREADS * rounds;
+  for (i64 g0 = (i64)blockIdx.x * group; g0 < S; g0 += (i64)gridDim.x * group) {
+    // The trip count of the selection loop is the column's length, and a warp runs as long as
+    // its longest column.  The CTA therefore takes a group of `rounds` x WT_THREADS consecutive
+    // columns, orders them by length (a counting sort in shared memory) and goes through the
+    // order in `rounds` rounds of WT_THREADS neighbours: the lanes of a warp finish together,
+    // and the warps of a round get columns of similar lengths.
+    for (int i = threadIdx.x; i < WT_MAX_DEG + 2; i += WT_THREADS) s_hist[i] = 0;
+    __syncthreads();
+    u32 len_sub[WT_ROUNDS];  // per round: length (low 8 bits; 0 = not selected from by this kernel) | place among equals
+#pragma unroll
+    for (int r = 0; r < WT_ROUNDS; ++r) {
+      len_sub[r] = 0;
+      if (r < rounds) {
+        const i64 slot0 = g0 + (i64)r * WT_THREADS + threadIdx.x;
+        u32 len = 0;
+        if (slot0 < S) {
+          const u32 dg = p.slot_deg[slot0];
+          if ((i64)dg > K && dg <= (u32)WT_MAX_DEG) len = dg;
+        }
+        len_sub[r] = len | (atomicAdd(&s_hist[len], 1u) << 8);
+      }
+    }
+    __syncthreads();
+    {  // exclusive running sum over the lengths 0 .. WT_MAX_DEG (at most WT_THREADS + 1 values: two per thread)
+      const int i0 = 2 * threadIdx.x, i1 = i0 + 1;
+      const u32 h0 = i0 <= WT_MAX_DEG ? s_hist[i0] : 0u, h1 = i1 <= WT_MAX_DEG ? s_hist[i1] : 0u;
+      i64 total;
+      const i64 ex = block_exclusive_scan((i64)(h0 + h1), s_scan, &total);
+      if (i0 <= WT_MAX_DEG) s_hist[i0] = (u32)ex;
+      if (i1 <= WT_MAX_DEG) s_hist[i1] = (u32)ex + h0;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < WT_ROUNDS; ++r)
+      if (r < rounds) s_order[s_hist[len_sub[r] & 0xFFu] + (len_sub[r] >> 8)] = (unsigned short)(r * WT_THREADS + threadIdx.x);
+    __syncthreads();
+    for (int r = 0; r < rounds; ++r) {
+    const i64 slot = g0 + s_order[r * WT_THREADS + threadIdx.x];
+    if (slot >= S) continue;
     const i64 in_start = p.slot_start[slot];
     const i64 deg = (i64)p.slot_deg[slot];
     if (deg == 0 || deg > WT_MAX_DEG) continue;  // nothing to do / the warp kernel's column
@@ -103,17 +169,27 @@ __global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const P
     u32 kmin = 0, pmin = 0;
     int imin = 0;
     // eight keys at a time: the two Philox blocks and the eight log2/divide chains are independent
-    // of each other, so they overlap; the top-K update below stays in entry order
-    for (int e0 = 0; e0 < d; e0 += 8) {
+    // of each other, so they overlap; the top-K update below stays in entry order.  The weights
+    // of the next eight entries are requested before this batch's keys are computed, so that
+    // their latency hides behind the arithmetic.
+    float w[WT_BATCH];
+#pragma unroll
+    for (int j = 0; j < WT_BATCH; ++j) w[j] = j < d ? __ldg(pr + j) : 0.f;
+    for (int e0 = 0; e0 < d; e0 += WT_BATCH) {
+      float wn[WT_BATCH];
+#pragma unroll
+      for (int j = 0; j < WT_BATCH; ++j) wn[j] = e0 + WT_BATCH + j < d ? __ldg(pr + e0 + WT_BATCH + j) : 0.f;
       const Philox4 b0 = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
       Philox4 b1 = b0;
-      if (e0 + 4 < d) b1 = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2) + 1u);
-      u32 keys[8];
+      if (WT_BATCH > 4 && e0 + 4 < d) b1 = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2) + 1u);
+      u32 keys[WT_BATCH];
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        keys[j] = e0 + j < d ? ares_key(pick_word(j < 4 ? b0 : b1, j & 3), __ldg(pr + e0 + j)) : 0u;
+      for (int j = 0; j < WT_BATCH; ++j)
+        keys[j] = e0 + j < d ? ares_key(pick_word(j < 4 ? b0 : b1, j & 3), w[j]) : 0u;
 #pragma unroll
-      for (int j = 0; j < 8; ++j) {
+      for (int j = 0; j < WT_BATCH; ++j) w[j] = wn[j];
+#pragma unroll
+      for (int j = 0; j < WT_BATCH; ++j) {
       const int e = e0 + j;
       if (e >= d) break;
       const u32 key = keys[j];
@@ -133,7 +209,8 @@ __global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const P
       }
       }
     }
-    // winners in column order: repeatedly take the smallest remaining position
+    // winners in column order: repeatedly take the smallest remaining position (the ordered
+    // positions go where the keys were) ...
     u32 last = 0;
     for (int k = 0; k < K; ++k) {
       u32 best = 0xFFFFFFFFu;
@@ -142,11 +219,27 @@ __global__ void __launch_bounds__(WT_THREADS) sample_probs_thread_kernel(const P
         if (pj < best && (k == 0 || pj > last)) best = pj;
       }
       last = best;
-      const i64 e = in_start + best;
-      p.out_rows[out_start + k] = load_index<IndexT>(p.indices, e);
-      p.out_sel[out_start + k] = e;
-      if (p.out_cols) p.out_cols[out_start + k] = slot;
+      tkey[k * WT_THREADS] = best;
     }
+    // ... then the gathers of the winners' row ids, four in flight at a time
+    for (int k0 = 0; k0 < K; k0 += 4) {
+      i64 e[4], r[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        e[j] = in_start + (k0 + j < K ? tkey[(k0 + j) * WT_THREADS] : 0u);
+        r[j] = k0 + j < K ? load_index<IndexT>(p.indices, e[j]) : 0;
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (k0 + j < K) {
+          p.out_rows[out_start + k0 + j] = r[j];
+          p.out_sel[out_start + k0 + j] = e[j];
+          if (p.out_cols) p.out_cols[out_start + k0 + j] = slot;
+        }
+      }
+    }
+    }
+    __syncthreads();  // the next group rewrites the order
   }
 }
 
@@ -694,12 +787,24 @@ extern "C" int gsb_sample_cols_probs(const int64_t* indptr, const void* indices,
   p.out_rows = (i64*)out_rows; p.out_cols = (i64*)out_cols; p.out_sel = (i64*)out_sel;
   p.E_cap = E_cap; p.err = d_err;
   p.thread_path = thread_path ? 1 : 0;
+  p.short_rounds = 1;
   p.slot_start = extra.start; p.slot_deg = extra.deg; p.list = extra.list; p.list_n = extra.list_n;
   p.long_list = (i64*)(ws + L.long_list); p.long_n = (int*)(ws + L.list_n) + 16;
   if (p.thread_path) {
     i64 tb = (S_max + WT_THREADS - 1) / WT_THREADS;
-    if (tb > sm_count() * 16) tb = sm_count() * 16;
     const size_t tsmem = sizeof(u32) * 2 * (size_t)K * WT_THREADS;
+    int resident = 0;  // CTAs an SM holds at this K: whole waves only
+    if (indices_dtype == GSB_I32)
+      GSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, sample_probs_thread_kernel<int>, WT_THREADS, tsmem));
+    else
+      GSB_CUDA_OK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&resident, sample_probs_thread_kernel<i64>, WT_THREADS, tsmem));
+    if (resident < 1) resident = 1;
+    // as many tiles per group as still leave every resident CTA a group
+    i64 rounds = tb / ((i64)sm_count() * resident);
+    rounds = rounds < 1 ? 1 : (rounds > WT_ROUNDS ? WT_ROUNDS : rounds);
+    p.short_rounds = (int)rounds;
+    tb = (tb + rounds - 1) / rounds;
+    if (tb > (i64)sm_count() * resident) tb = (i64)sm_count() * resident;
     LaunchScope ls(KID_SAMPLE_PROBS_SHORT, st);
     if (indices_dtype == GSB_I32)
       sample_probs_thread_kernel<int><<<(int)tb, WT_THREADS, tsmem, st>>>(p);

@@ -759,8 +759,15 @@ static torch::Device CurrentCudaDevice() { return torch::Device(torch::kCUDA, c1
 torch::Tensor ListSampling(int64_t num_items, int64_t num_picks, bool replace) {
   const auto dev = CurrentCudaDevice();
   if (replace) return ListReplaceImpl(c10::nullopt, num_items, num_picks, dev);
-  return std::get<0>(ListSampleImpl(c10::nullopt, Range2(num_items, dev), num_items, num_picks, dev,
-                                    /*single_list=*/true));
+  // one list whose length the host knows: no offsets go to the device, none come back
+  TORCH_CHECK(num_items >= 0 && num_picks >= 0, "ListSampling: negative size");
+  c10::cuda::CUDAGuard guard(dev);
+  auto out = torch::empty({std::min(num_picks, num_items)}, torch::dtype(torch::kInt64).device(dev));
+  CheckStatus(gsb_list_sample(nullptr, nullptr, 1, num_items, num_picks, ListSamplingSeed(), NextListStream(),
+                              PM(out), nullptr, nullptr, 0, AsyncErrorWord(dev).data_ptr<int>(),
+                              CurrentStream()),
+              "list_sample");
+  return out;
 }
 
 // src/tensor_ops.cc:10-13

@@ -346,7 +346,10 @@ GSB_API int gsb_u_op_v_pair(const int64_t* row, const int64_t* col, const int64_
  * positions to out_idx (weighted: ascending; uniform: reservoir slot order, as
  * the reference's ListSampling); out_range[B+1] = offsets of the picks.  range[0]
  * must be 0 (anything else sets GSB_ERRBIT_BAD_INPUT).  R
- * bounds range[B]; out_idx holds min(R, B * K) entries.  Replaces ListSampling / ListSamplingProbs /
+ * bounds range[B]; out_idx holds min(R, B * K) entries.  For a uniform choice
+ * from ONE list (probs NULL, B == 1) range may be NULL: the list is [0, R),
+ * min(K, R) picks are written and out_range is not touched (may be NULL);
+ * the uniform choice needs no workspace.  Replaces ListSampling / ListSamplingProbs /
  * BatchListSamplingProbs without replacement (src/cuda/list_sampling.cu:20-73,
  * src/cuda/list_sampling_probs.cu:11-89, src/cuda/batch/list_sampling_probs.cu:29-107),
  * which return the same set in descending-key order.

@@ -38,6 +38,14 @@ typedef uint32_t u32;
 
 #define GO_API __attribute__((visibility("default")))
 
+GO_API void go_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 GO_API int go_num_threads(void) {
 #ifdef _OPENMP
   return omp_get_max_threads();

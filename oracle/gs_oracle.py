@@ -44,6 +44,10 @@ def lib():
         _lib.go_list_sample_replace_spec.restype = C.c_int64
         _lib.go_spec_draw.restype = C.c_uint32
         _lib.go_num_threads.restype = C.c_int
+        # a launcher may have pinned OMP_NUM_THREADS to 1 and an OpenMP runtime loaded before this
+        # library has read it already: GS_ORACLE_THREADS states the thread count explicitly
+        if os.environ.get("GS_ORACLE_THREADS", "").isdigit():
+            _lib.go_set_num_threads(int(os.environ["GS_ORACLE_THREADS"]))
     return _lib
 
 
@@ -61,6 +65,12 @@ def _p(a):
 
 def num_threads() -> int:
     return int(lib().go_num_threads())
+
+
+def set_num_threads(n: int) -> None:
+    """OpenMP threads of the following calls (a launcher may have pinned OMP_NUM_THREADS to 1
+    before this process could say otherwise)."""
+    lib().go_set_num_threads(int(n))
 
 
 def philox4x32_10(ctr, key):
