@@ -156,10 +156,10 @@ def node2vec(steps=3, warmup=1, walkers=1000000, length=80):
 
 
 def limits(steps=3, warmup=2, n=1000000, e=50000000):
-    """The three operators whose rate is set by one hardware unit rather than by DRAM bandwidth:
-    uniform walks (random 32-byte gathers), row sums over a COO in column order (one L2 reduction
-    per edge) and a uniform choice from one list (one Philox block per candidate).  Small enough
-    for a profiler capture, larger than L2."""
+    """Operators whose rate is set by one hardware unit rather than by the algorithm: uniform
+    walks (random 32-byte gathers), row sums over a COO in column order (one L2 reduction per
+    edge), the fused pair of u-op-v maps (a streaming pass) and a uniform choice from one list
+    (one Philox block per candidate).  Small enough for a profiler capture, larger than L2."""
     dev = torch.device("cuda")
     indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=20000, seed=2024, device=dev)
     nnz = int(indptr[-1])
@@ -171,9 +171,16 @@ def limits(steps=3, warmup=2, n=1000000, e=50000000):
     M = gs.Matrix(A)
     M.edata["w"] = torch.rand(nnz, generator=gen, device=dev)
     M.sum("w", axis=1)   # builds the COO outside the timed calls
+    u1, v1, u2, v2 = (torch.rand(n, 1, generator=gen, device=dev) + 0.5 for _ in range(4))
+    o1, o2 = torch.empty(nnz, 1, device=dev), torch.empty(nnz, 1, device=dev)
+    # the yardstick for a walk step: as many 8-byte gathers from random places of the row-id array
+    # as the walks take steps, by the tensor library (it also reads the positions and writes the result)
+    where = torch.randint(0, nnz, (400000 * 80,), generator=gen, device=dev)
     out = {}
     for name, fn, units in (("random_walk", lambda: A._CAPI_RandomWalk(walkers, 80), 400000 * 80),
+                            ("library_gather_of_as_many_row_ids", lambda: torch.index_select(indices, 0, where), 400000 * 80),
                             ("coo_row_sums", lambda: M.sum("w", axis=1), nnz),
+                            ("fused_u_op_v", lambda: A._CAPI_FusedUOPV("mul", u1, v1, o1, u2, v2, o2, gs._COO), nnz),
                             ("list_sampling_uniform", lambda: torch.ops.gs_ops._CAPI_ListSampling(n, 4000, False), n)):
         for _ in range(warmup):
             fn()
