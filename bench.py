@@ -509,7 +509,9 @@ class SageWorkload(object):
                 "l2": "inputs_larger_than_l2 (graph indices %.1f GB)" % (
                     self.indices.numel() * self.indices.element_size() / 1e9),
                 "mean_SEU_per_layer": [[float(c_host[:, l, j].mean()) for j in range(3)] for l in range(self.L)],
-                "capacities": "measured x1.15", "streams": self.nstreams}
+                "capacities": "measured x1.15", "streams": self.nstreams,
+                "row_ids_read_from": ("a 32-bit copy made when the sampler is built (inputs and outputs stay int64)"
+                                      if cfg["index_dtype"] == "int64" else "the int32 array itself")}
 
     def roofline(self, timed, c_host, elapsed_s, steps, peak, peak_kind):
         w_idx = 4 if self.cfg["index_dtype"] == "int32" else 8

@@ -16,6 +16,20 @@ namespace gsb_host {
 
 static const int64_t* P(const torch::Tensor& t) { return t.data_ptr<int64_t>(); }
 
+// 32-bit copy of a CSC's 64-bit row ids, made on first use and kept with the format, for the
+// kernels that gather row ids from random places (the sampler's picks, the walks' steps): the
+// number of DRAM bursts such gathers cost falls with the bytes a column spans, and the share of the
+// array that L2 holds doubles.  Costs half the array's size again in device memory; graphs with
+// 2^31 rows or more, or kept in host memory, are read as they are.
+struct IdArray { const void* ptr; int dtype; };
+static IdArray NarrowIndices(Compressed& c, int64_t num_rows) {
+  const int dt = c.indices.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
+  if (dt == GSB_I32 || !c.indices.is_cuda() || num_rows > (int64_t)0x7FFFFFFF)
+    return {c.indices.data_ptr(), dt};
+  if (!c.indices32.defined()) c.indices32 = c.indices.to(torch::kInt32);
+  return {c.indices32.data_ptr(), GSB_I32};
+}
+
 // L-layer GraphSAGE super-batch sampler in ONE call: the operator sequence
 // A[:, seeds::ptr] -> individual_sampling(K) -> all_nodes -> to_dgl_block per
 // layer (examples/graphsage/graphsage_e2e.py:37-44 in gSampler) with every
@@ -78,8 +92,8 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGEAsync(torch::Tensor seeds, torch
   auto counts = keep.back();
   counts.zero_();
   void* ws = arena.data_ptr<int64_t>() + total_words;
-  const int dtype = csc_->indices.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
-  CheckStatus(gsb_graphsage_sample(P(csc_->indptr), csc_->indices.data_ptr(), dtype, num_cols_,
+  const IdArray ids = NarrowIndices(*csc_, num_rows_);
+  CheckStatus(gsb_graphsage_sample(P(csc_->indptr), ids.ptr, ids.dtype, num_cols_,
                                    std::max(num_rows_, num_cols_), P(seeds),
                                    P(seeds_ptr), B, S0, L, fanouts.data(), GetSeedU64(),
                                    NextStreams((uint32_t)L), bufs.data(), counts.data_ptr<int64_t>(), ws, ws_bytes,
@@ -235,17 +249,6 @@ static const uint32_t* Offsets32(Compressed& c) {
   return reinterpret_cast<const uint32_t*>(c.indptr32.data_ptr<int32_t>());
 }
 
-// 32-bit copy of 64-bit row ids, made on first use and kept with the format, for the walks: every
-// step is one gather at a random place of this array, and the rate of such gathers grows with the
-// share of the array that L2 holds.  Costs half the array's size again in device memory.
-struct WalkIndices { const void* ptr; int dtype; };
-static WalkIndices NarrowIndices(Compressed& c, int64_t num_rows) {
-  if (c.indices.scalar_type() == torch::kInt32 || !c.indices.is_cuda() || num_rows > (int64_t)0x7FFFFFFF)
-    return {c.indices.data_ptr(), IdxDtype(c.indices)};
-  if (!c.indices32.defined()) c.indices32 = c.indices.to(torch::kInt32);
-  return {c.indices32.data_ptr(), GSB_I32};
-}
-
 // ------------------------------------------------------------------ walks
 // src/graph.cc:310-317.  The buffer is step-major [(L+1), N]; like the
 // reference it is returned REINTERPRETED as [N, L+1] (a reshape, no transpose).
@@ -258,7 +261,7 @@ torch::Tensor Graph::RandomWalk(torch::Tensor seeds, int64_t walk_length) {
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  const WalkIndices ix = NarrowIndices(*csc_, num_rows_);
+  const IdArray ix = NarrowIndices(*csc_, num_rows_);
   CheckStatus(gsb_random_walk(P(csc_->indptr), Offsets32(*csc_), ix.ptr, ix.dtype, num_cols_, P(seeds), N, walk_length, seed_, NextStream(), PM(out),
                               AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "random_walk");
@@ -271,7 +274,7 @@ torch::Tensor Graph::Node2Vec(torch::Tensor seeds, int64_t walk_length, double p
   CheckIds(seeds, "seeds");
   const int64_t N = seeds.numel();
   auto out = torch::empty({N * (walk_length + 1)}, I64(seeds));
-  const WalkIndices ix = NarrowIndices(*csc_, num_rows_);
+  const IdArray ix = NarrowIndices(*csc_, num_rows_);
   CheckStatus(gsb_node2vec(P(csc_->indptr), Offsets32(*csc_), ix.ptr, ix.dtype, num_cols_, P(seeds), N, walk_length, p, q, seed_, NextStream(), PM(out),
                            AsyncErrorWord(seeds.device()).data_ptr<int>(), CurrentStream()),
               "node2vec");
