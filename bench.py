@@ -64,8 +64,8 @@ WORKLOADS = {
 # DRAM bytes (read + write) per sampled edge, from the `ncu --set full` capture of the "medium"
 # case summarised under profiles/; the access pattern per unit is the same on the bench
 # workload, so the traffic is scaled by the units of a launch / a step.
-NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 97.6}
-NCU_PATH_DRAM_BYTES_PER_EDGE = 140.5
+NCU_DRAM_BYTES_PER_EDGE = {"sample_tile": 75.6}
+NCU_PATH_DRAM_BYTES_PER_EDGE = 119.3
 
 
 # ----------------------------------------------------------------------------- helpers
