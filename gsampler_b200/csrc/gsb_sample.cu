@@ -14,7 +14,10 @@
 
 namespace gsb {
 
-constexpr int SAMPLE_THREADS = 256;
+#ifndef GSB_SAMPLE_THREADS
+#define GSB_SAMPLE_THREADS 256
+#endif
+constexpr int SAMPLE_THREADS = GSB_SAMPLE_THREADS;
 #ifndef GSB_SAMPLE_MIN_CTAS
 #define GSB_SAMPLE_MIN_CTAS 8  // 32 registers/thread: eight resident CTAs (2048 threads) per SM.
                                // Measured on the layer-3 launch: 72 regs 0.55 ms, 40 regs 0.41 ms,

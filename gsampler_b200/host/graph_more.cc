@@ -26,6 +26,8 @@ static IdArray NarrowIndices(Compressed& c, int64_t num_rows) {
   const int dt = c.indices.scalar_type() == torch::kInt32 ? GSB_I32 : GSB_I64;
   if (dt == GSB_I32 || !c.indices.is_cuda() || num_rows > (int64_t)0x7FFFFFFF)
     return {c.indices.data_ptr(), dt};
+  static std::mutex mu;  // two host threads asking for the first time make one copy
+  std::lock_guard<std::mutex> lock(mu);
   if (!c.indices32.defined()) c.indices32 = c.indices.to(torch::kInt32);
   return {c.indices32.data_ptr(), GSB_I32};
 }
@@ -245,6 +247,8 @@ static torch::Tensor& AsyncErrorWord(const torch::Device& dev);
 // or does not live on the GPU.
 static const uint32_t* Offsets32(Compressed& c) {
   if (!c.indptr.is_cuda() || c.indices.numel() >= (int64_t)0xFFFFFFFFll) return nullptr;
+  static std::mutex mu;
+  std::lock_guard<std::mutex> lock(mu);
   if (!c.indptr32.defined()) c.indptr32 = c.indptr.to(torch::kInt32);  // wraps modulo 2^32: read back as unsigned
   return reinterpret_cast<const uint32_t*>(c.indptr32.data_ptr<int32_t>());
 }
