@@ -141,3 +141,36 @@ def batch_relabel(seeds, seeds_ptr, coo_row, coo_col, edge_ptr, want_edges=True,
     torch.cuda.synchronize()
     U = int(uptr[B])
     return unique[:max(U, 0)], uptr, orow, ocol, int(err[0])
+
+
+def random_walk(indptr, indices, seeds, length, seed, stream, indptr32=None, node2vec=None):
+    """gsb_random_walk / gsb_node2vec (``node2vec`` = (p, q)); returns (trace [(L+1) * N], error word)."""
+    import torch
+
+    N = seeds.numel()
+    out = torch.empty(N * (length + 1), dtype=torch.int64, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    dt = I32 if indices.dtype == torch.int32 else I64
+    num_nodes = (indptr if indptr is not None else indptr32).numel() - 1
+    st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    if node2vec is None:
+        check(lib().gsb_random_walk(ptr(indptr), ptr(indptr32), ptr(indices), dt, i64(num_nodes), ptr(seeds),
+                                    i64(N), i64(length), C.c_uint64(seed), C.c_uint32(stream), ptr(out),
+                                    ptr(err), st), "gsb_random_walk")
+    else:
+        check(lib().gsb_node2vec(ptr(indptr), ptr(indptr32), ptr(indices), dt, i64(num_nodes), ptr(seeds),
+                                 i64(N), i64(length), C.c_double(node2vec[0]), C.c_double(node2vec[1]),
+                                 C.c_uint64(seed), C.c_uint32(stream), ptr(out), ptr(err), st), "gsb_node2vec")
+    return out, int(err.item())
+
+
+def list_sample_whole(n, K, seed, stream):
+    """gsb_list_sample on ONE list [0, n) stated by the caller: no offsets in, none out, no workspace."""
+    import torch
+
+    out = torch.empty(min(n, K), dtype=torch.int64, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    check(lib().gsb_list_sample(None, None, i64(1), i64(n), i64(K), C.c_uint64(seed), C.c_uint32(stream),
+                                ptr(out), None, None, C.c_size_t(0), ptr(err),
+                                C.c_void_p(torch.cuda.current_stream().cuda_stream)), "gsb_list_sample")
+    return out, int(err.item())

@@ -282,6 +282,38 @@ def test_list_sampling(gsb, oracle):
     assert stats.chisquare(np.bincount(idx % 12, minlength=12)).pvalue > 0.01
 
 
+def test_walk_entry_points_all_widths(oracle, graph):
+    """gsb_random_walk / gsb_node2vec through the C ABI with 64-bit or 32-bit offsets and 64-bit or
+    32-bit row ids (the host layer always hands a small graph the 32-bit copies): the four
+    combinations give the oracle's traces bit for bit."""
+    from tests import abi
+
+    indptr, indices = graph
+    srt = oracle.sort_indices(indptr, indices)
+    rng = np.random.default_rng(16)
+    seeds = cuda(rng.integers(0, 3000, 4000).astype(np.int64))
+    want_rw = oracle.random_walk_spec(indptr, srt, host(seeds), 9, 5, 3)
+    want_n2v = oracle.node2vec_spec(indptr, srt, host(seeds), 9, 0.5, 2.0, 5, 4)
+    ip64, ip32 = cuda(indptr), cuda(indptr).to(torch.int32)
+    for ids in (cuda(srt), cuda(srt, torch.int32)):
+        for a, b in ((ip64, None), (None, ip32), (ip64, ip32)):
+            tr, err = abi.random_walk(a, ids, seeds, 9, 5, 3, indptr32=b)
+            assert err == 0 and np.array_equal(host(tr), want_rw)
+            tr, err = abi.random_walk(a, ids, seeds, 9, 5, 4, indptr32=b, node2vec=(0.5, 2.0))
+            assert err == 0 and np.array_equal(host(tr), want_n2v)
+
+
+def test_list_sampling_whole_list_without_offsets(oracle):
+    """gsb_list_sample with range == NULL (one list [0, n), uniform): the reservoir spec's picks,
+    nothing read or written besides them; K >= n returns the whole list."""
+    from tests import abi
+
+    for n, K in ((100000, 500), (5000, 4999), (300, 300), (300, 1000)):
+        got, err = abi.list_sample_whole(n, K, 11, 2)
+        assert err == 0
+        assert np.array_equal(host(got), oracle.list_sample_spec(n, K, seed=11, stream=2))
+
+
 def test_walks_bit_exact(gsb, oracle, graph):
     indptr, indices = graph
     srt = oracle.sort_indices(indptr, indices)
