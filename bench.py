@@ -817,11 +817,15 @@ def main():
                          "(use --impl reference for the CPU port)")
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
+    json_fd = None
     if world > 1:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # NCCL writes its version banner and warnings to stdout: send them to stderr, stdout
-        # carries the one JSON line
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        # NCCL writes its version banner to stdout when the first communicator is made: until the
+        # result line is printed, file descriptor 1 points at stderr, so that stdout carries the
+        # one JSON line and nothing else
+        sys.stdout.flush()
+        json_fd = os.dup(1)
+        os.dup2(2, 1)
         dist.init_process_group("nccl", device_id=dev)
 
     from gsampler_b200 import pipeline
@@ -941,7 +945,11 @@ def main():
             line["cpu_baseline"] = wl.cpu_baseline()
             if cfg["kind"] == "sage":
                 line["cpu_baseline"]["cfg1"] = cpu_cfg1()
-        print(json.dumps(line))
+        if json_fd is None:
+            print(json.dumps(line))
+        else:
+            sys.stdout.flush()
+            os.write(json_fd, (json.dumps(line) + "\n").encode())
     if world > 1:
         dist.destroy_process_group()
 

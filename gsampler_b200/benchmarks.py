@@ -7,6 +7,8 @@ repository root holds the headline one):
                                                   # 2 449 029 nodes / 123.7 M edges
     python -m gsampler_b200.benchmarks limits     # uniform walks, COO row sums, uniform list sampling on
                                                   # a 1 M-node / 50 M-edge graph (a profiling shape)
+    python -m gsampler_b200.benchmarks weighted   # weighted per-column sampling of a column slice, same
+                                                  # 1 M-node graph: 400 000 columns, K = 10 and K = 5
     python -m gsampler_b200.benchmarks gather     # feature fetch: 4 M rows of 100 fp32 out of 2 449 029
     python -m gsampler_b200.benchmarks cfg5       # the same on the full 111 M nodes / 3.2 G edges (14 GB)
     python -m gsampler_b200.benchmarks cfg5s      # GraphSAGE [15,10,5] on an int32-index R-MAT-like
@@ -196,6 +198,43 @@ def limits(steps=3, warmup=2, n=1000000, e=50000000):
     print(json.dumps({"metric": "operator_ms", "config": {"workload": "%d nodes / %d edges" % (n, nnz)}, **out}))
 
 
+def weighted(steps=3, warmup=2, n=1000000, e=50000000, columns=400000):
+    """Weighted per-column sampling (`_CAPI_SamplingProbs` on a column slice with fp32 weights),
+    with the per-kernel times of the library's launch accounting.  A profiling shape."""
+    dev = torch.device("cuda")
+    indptr, indices = synth.powerlaw_csc(n, e, exponent=2.1, max_degree=20000, seed=2024, device=dev)
+    nnz = int(indptr[-1])
+    A = gs.Graph(n, n)
+    A._CAPI_LoadCSC(indptr, indices)
+    gen = torch.Generator(device=dev)
+    gen.manual_seed(11)
+    probs = torch.rand(nnz, generator=gen, device=dev) + 0.01
+    seeds = torch.randint(0, n, (columns,), generator=gen, device=dev)
+    sub, sel = A._CAPI_Slicing(seeds, 1, gs._CSC, gs._CSC)
+    w = probs[sel]
+    out = {}
+    for K in (10, 5):
+        fn = lambda: sub._CAPI_SamplingProbs(1, w, K, False, gs._CSC, gs._COO)  # noqa: E731
+        for _ in range(warmup):
+            fn()
+        torch.cuda.synchronize()
+        e0, e1 = _events()
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        pipeline.timing_enable(True)
+        for _ in range(steps):
+            fn()
+        timed = pipeline.timing_collect()
+        pipeline.timing_enable(False)
+        out["K=%d" % K] = {"ms_per_call": e0.elapsed_time(e1) / steps,
+                           "kernels_ms": {name: round(ms / cnt, 4) for name, _, ms, cnt in timed}}
+    print(json.dumps({"metric": "weighted_sampling_ms", "config": {"workload": "%d columns of %d nodes / %d edges"
+                                                                   % (columns, n, nnz)}, **out}))
+
+
 def gather(steps=10, warmup=3, rows=4000000, width=100):
     """Feature fetch for a sampled frontier: random rows of a [2 449 029, 100] fp32 table."""
     dev = torch.device("cuda")
@@ -283,5 +322,5 @@ if __name__ == "__main__":
     which = sys.argv[1] if len(sys.argv) > 1 else "node2vec"
     t0 = time.time()
     {"ladies": ladies, "node2vec": node2vec, "cfg5s": cfg5s, "cfg5": cfg5, "gather": gather,
-     "limits": limits}[which]()
+     "limits": limits, "weighted": weighted}[which]()
     print("# %s finished in %.1f s" % (which, time.time() - t0), file=sys.stderr)
