@@ -1,0 +1,158 @@
+// Unsorted COO -> CSC / CSR: group the entries by key (column for a CSC, row for a CSR), keeping
+// the entries of a key in their original order, and report where every entry came from.
+//
+// The reference sorts (key, position) pairs with a device-wide radix sort
+// (src/cuda/format_transform.cu:66-86, 108-142).  Here the keys are node ids of a graph, i.e. a
+// dense range, so the grouping is a counting sort:
+//   histogram : entries per key (one L2 reduction per entry)
+//   scan      : offsets = exclusive running sum (tiles of 4096 keys, chained prefix)
+//   scatter   : every entry takes the next free place of its key's segment (one L2 atomic) and
+//               leaves `position:32 | value:32` there -- in whatever order the atomics land
+//   sort      : every segment sorted by the packed word, i.e. by original position: the per-segment
+//               sort of gsb_sort.cu (segments are columns: tens of entries, a warp each)
+//   unpack    : values and positions apart
+// which makes the result the stable grouping, bit for bit what a stable sort by key gives.
+// Limits (checked): fewer than 2^31 entries, values in [0, 2^32).
+#include "gsb_common.cuh"
+
+namespace gsb {
+
+constexpr int FM_THREADS = 256;
+constexpr int SC_THREADS = 1024;
+constexpr int SC_ITEMS = 4;
+constexpr int SC_TILE = SC_THREADS * SC_ITEMS;
+
+__global__ void __launch_bounds__(FM_THREADS) group_hist_kernel(const i64* __restrict__ keys, i64 nnz, i64 nkeys,
+                                                               unsigned long long* __restrict__ count, int* err) {
+  for (i64 e = (i64)blockIdx.x * FM_THREADS + threadIdx.x; e < nnz; e += (i64)gridDim.x * FM_THREADS) {
+    const i64 k = __ldg(keys + e);
+    if ((u64)k < (u64)nkeys) atomicAdd(count + k, 1ull);
+    else raise(err, ERRBIT_BAD_INPUT);  // not a segment: the entry is left out
+  }
+}
+
+// out[i] = sum of in[0 .. i), i in [0, n]; in and out may be the same array
+__global__ void __launch_bounds__(SC_THREADS) scan_i64_kernel(const i64* in, i64 n, i64* out, u64* status,
+                                                             int* ticket, int* err) {
+  __shared__ i64 s_scan[34];
+  __shared__ int s_tile;
+  __shared__ i64 s_base;
+  if (threadIdx.x == 0) s_tile = atomicAdd(ticket, 1);
+  __syncthreads();
+  const int tile = s_tile;
+  const i64 n_tiles = (n + SC_TILE) / SC_TILE;  // covers index n as well
+  if (tile >= n_tiles) return;
+  const i64 i0 = (i64)tile * SC_TILE + (i64)threadIdx.x * SC_ITEMS;
+  i64 v[SC_ITEMS], sum = 0;
+#pragma unroll
+  for (int j = 0; j < SC_ITEMS; ++j) {
+    v[j] = i0 + j < n ? in[i0 + j] : 0;
+    sum += v[j];
+  }
+  i64 total;
+  const i64 ex = block_exclusive_scan(sum, s_scan, &total);
+  if (threadIdx.x < 32) {
+    const i64 base = chained_exclusive_prefix(status, tile, total, err);
+    if (threadIdx.x == 0) s_base = base;
+  }
+  __syncthreads();
+  i64 run = s_base + ex;
+#pragma unroll
+  for (int j = 0; j < SC_ITEMS; ++j) {
+    if (i0 + j <= n) out[i0 + j] = run;
+    run += v[j];
+  }
+}
+
+__global__ void __launch_bounds__(FM_THREADS) group_scatter_kernel(const i64* __restrict__ keys,
+                                                                  const i64* __restrict__ vals, i64 nnz, i64 nkeys,
+                                                                  unsigned long long* __restrict__ cursor,
+                                                                  u64* __restrict__ packed, int* err) {
+  for (i64 e = (i64)blockIdx.x * FM_THREADS + threadIdx.x; e < nnz; e += (i64)gridDim.x * FM_THREADS) {
+    const i64 k = __ldg(keys + e);
+    if ((u64)k >= (u64)nkeys) continue;  // reported by the histogram pass
+    i64 v = __ldg(vals + e);
+    if ((u64)v > 0xFFFFFFFFull) { raise(err, ERRBIT_BAD_INPUT); v = 0xFFFFFFFFll; }
+    const unsigned long long at = atomicAdd(cursor + k, 1ull);
+    packed[at] = ((u64)e << 32) | (u64)v;
+  }
+}
+
+__global__ void __launch_bounds__(FM_THREADS) group_unpack_kernel(const u64* __restrict__ packed, i64 n,
+                                                                 i64* __restrict__ vals, i64* __restrict__ pos) {
+  for (i64 i = (i64)blockIdx.x * FM_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * FM_THREADS) {
+    const u64 w = packed[i];
+    vals[i] = (i64)(w & 0xFFFFFFFFull);
+    pos[i] = (i64)(w >> 32);
+  }
+}
+
+struct GroupLayout {
+  size_t status, cursor, packed, sort, total;
+  i64 scan_tiles;
+};
+
+static GroupLayout group_layout(i64 nnz, i64 nkeys) {
+  GroupLayout L;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  L.scan_tiles = (nkeys + SC_TILE) / SC_TILE;
+  size_t o = 0;
+  L.status = o; o = up(o + 256 + sizeof(u64) * (size_t)(L.scan_tiles + 1));  // ticket, then status words
+  L.cursor = o; o = up(o + sizeof(i64) * (size_t)(nkeys + 1));
+  L.packed = o; o = up(o + sizeof(u64) * (size_t)(nnz + 1));
+  L.sort = o; o = up(o + gsb_sort_segments_workspace_bytes(nkeys, nnz, GSB_I64));
+  L.total = o;
+  return L;
+}
+
+static int wide_grid_fm(i64 n) {
+  i64 g = (n + FM_THREADS - 1) / FM_THREADS;
+  const i64 cap = (i64)sm_count() * 16;
+  if (g > cap) g = cap;
+  return (int)(g < 1 ? 1 : g);
+}
+
+}  // namespace gsb
+
+using namespace gsb;
+
+extern "C" size_t gsb_group_by_key_workspace_bytes(int64_t nnz, int64_t nkeys) {
+  if (nnz < 0 || nkeys < 0) return 0;
+  return group_layout(nnz, nkeys).total;
+}
+
+extern "C" int gsb_group_by_key(const int64_t* keys, const int64_t* vals, int64_t nnz, int64_t nkeys,
+                                int64_t* indptr, int64_t* out_vals, int64_t* out_pos, void* workspace,
+                                size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (nnz < 0 || nkeys < 0 || !indptr || (nnz > 0 && (!keys || !vals || !out_vals || !out_pos)))
+    return GSB_ERR_INVALID;
+  if (nnz >= (1ll << 31) || nkeys >= (1ll << 40)) return GSB_ERR_UNSUPPORTED;
+  const GroupLayout L = group_layout(nnz, nkeys);
+  if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  char* ws = (char*)workspace;
+  int* ticket = (int*)(ws + L.status);
+  u64* status = (u64*)(ws + L.status + 256);
+  i64* cursor = (i64*)(ws + L.cursor);
+  u64* packed = (u64*)(ws + L.packed);
+  GSB_CUDA_OK(cudaMemsetAsync(ws + L.status, 0, L.cursor - L.status, st));
+  GSB_CUDA_OK(cudaMemsetAsync(indptr, 0, sizeof(i64) * (size_t)(nkeys + 1), st));
+  LaunchScope ls(KID_INDPTR_SORTED, st);
+  if (nnz > 0)
+    group_hist_kernel<<<wide_grid_fm(nnz), FM_THREADS, 0, st>>>((const i64*)keys, nnz, nkeys,
+                                                                 (unsigned long long*)indptr, d_err);
+  scan_i64_kernel<<<(int)L.scan_tiles, SC_THREADS, 0, st>>>((const i64*)indptr, nkeys, (i64*)indptr, status,
+                                                            ticket, d_err);
+  if (nnz > 0) {
+    GSB_CUDA_OK(cudaMemcpyAsync(cursor, indptr, sizeof(i64) * (size_t)(nkeys + 1), cudaMemcpyDeviceToDevice, st));
+    group_scatter_kernel<<<wide_grid_fm(nnz), FM_THREADS, 0, st>>>((const i64*)keys, (const i64*)vals, nnz, nkeys,
+                                                                    (unsigned long long*)cursor, packed, d_err);
+    // entries with a key that is no segment were left out: the segments cover indptr[nkeys] <= nnz entries
+    const int rc = gsb_sort_segments(indptr, packed, GSB_I64, nkeys, nnz, ws + L.sort, workspace_bytes - L.sort,
+                                     d_err, cuda_stream);
+    if (rc != GSB_OK) return rc;
+    group_unpack_kernel<<<wide_grid_fm(nnz), FM_THREADS, 0, st>>>(packed, nnz, (i64*)out_vals, (i64*)out_pos);
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}

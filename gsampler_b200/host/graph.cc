@@ -142,6 +142,22 @@ void Graph::CreateSparseFormat(int64_t format) {
                            int64_t nkeys) {
     torch::Tensor k = key, v = val;
     c10::optional<torch::Tensor> e_ids = coo_->e_ids;
+    if (!sorted && key.is_cuda() && key.numel() < (int64_t(1) << 31) &&
+        std::max(num_rows_, num_cols_) <= (int64_t)0xFFFFFFFFll) {
+      // unsorted COO on the GPU: this library's counting sort by key, stable in the entries' order
+      // (the reference: a device-wide radix sort, src/cuda/format_transform.cu:66-86)
+      c10::cuda::CUDAGuard guard(key.device());
+      const int64_t nnz = key.numel();
+      auto indptr = torch::empty({nkeys + 1}, I64(key));
+      auto vals = torch::empty({nnz}, I64(key)), perm = torch::empty({nnz}, I64(key));
+      auto ws = NewWorkspace(gsb_group_by_key_workspace_bytes(nnz, nkeys), key.device());
+      CheckStatus(gsb_group_by_key(P(key), P(val), nnz, nkeys, PM(indptr), PM(vals), PM(perm), ws.data_ptr(),
+                                   (size_t)ws.numel(), AsyncErrorWord(key.device()).data_ptr<int>(),
+                                   CurrentStream()),
+                  "group_by_key");
+      e_ids = coo_->e_ids.has_value() ? coo_->e_ids.value().index_select(0, perm) : perm;
+      return std::make_shared<Compressed>(Compressed{indptr, vals, e_ids});
+    }
     if (!sorted) {
       // unsorted COO: stable sort by the key (src/cuda/format_transform.cu:66-86)
       auto perm = std::get<1>(key.sort(/*stable=*/true, /*dim=*/0, /*descending=*/false));

@@ -194,6 +194,8 @@ class Graph : public torch::CustomClassHolder {
 void CheckStatus(int status, const char* what);
 void CheckDeviceError(int err, const char* what);
 torch::Tensor NewWorkspace(size_t bytes, const torch::Device& dev);
+// per-device error word of the calls that do not synchronise (read by _CAPI_CheckAsyncErrors)
+torch::Tensor& AsyncErrorWord(const torch::Device& dev);
 void* CurrentStream();
 void CheckIds(const torch::Tensor& t, const char* name);
 torch::Device ComputeDevice(const torch::Tensor& t);

@@ -240,7 +240,7 @@ Graph::GraphAndIndex Graph::Compact(int64_t axis) {
   return {ret, frontiers};
 }
 
-static torch::Tensor& AsyncErrorWord(const torch::Device& dev);
+torch::Tensor& AsyncErrorWord(const torch::Device& dev);  // per-device error word of the calls that do not synchronise
 
 // 32-bit copy of a compressed format's offsets, made on first use and kept with the format, for
 // the kernels that gather offsets at random (walks); null when the graph has 2^32 entries or more
@@ -823,7 +823,7 @@ torch::Tensor IndexSearch(torch::Tensor origin_data, torch::Tensor keys) {
 // One error word per device that the sync-free operators raise bits in; it is
 // read (and cleared) by CheckAsyncErrors, the way CUDA reports kernel faults
 // at the next synchronising call rather than at the launch.
-static torch::Tensor& AsyncErrorWord(const torch::Device& dev) {
+torch::Tensor& AsyncErrorWord(const torch::Device& dev) {
   static std::mutex mu;
   // never destroyed: a static destructor would free device memory after the CUDA context is gone
   static auto* words = new std::map<int, torch::Tensor>();

@@ -224,6 +224,17 @@ GSB_API int gsb_expand_indptr(const int64_t* indptr, int64_t nseg, int64_t nnz, 
  * col_sorted branch of COO2CSCCUDA (src/cuda/format_transform.cu:121-142). */
 GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nkeys,
                                    int64_t* indptr, void* cuda_stream);
+/* Unsorted COO -> CSC / CSR: entries grouped by key (in [0, nkeys)), the entries of a key in
+ * their original order.  indptr[nkeys+1] = offsets of the groups, out_vals[nnz] = the values in
+ * grouped order, out_pos[nnz] = the position each came from (the edge-id permutation).  A
+ * counting sort: histogram, scan, scatter, per-segment sort by original position.  nnz < 2^31,
+ * values in [0, 2^32); a key outside [0, nkeys) or a value outside that range sets
+ * GSB_ERRBIT_BAD_INPUT.  Replaces the unsorted branches of COO2CSCCUDA / COO2CSRCUDA
+ * (src/cuda/format_transform.cu:66-86, 108-120: a device-wide radix sort of (key, position)). */
+GSB_API size_t gsb_group_by_key_workspace_bytes(int64_t nnz, int64_t nkeys);
+GSB_API int gsb_group_by_key(const int64_t* keys, const int64_t* vals, int64_t nnz, int64_t nkeys,
+                             int64_t* indptr, int64_t* out_vals, int64_t* out_pos, void* workspace,
+                             size_t workspace_bytes, int* d_err, void* cuda_stream);
 
 /* ------------------------------------------------------------------ per-segment sort
  * Sorts the ids of every segment of a CSC / CSR ascending, in place (node2vec's membership

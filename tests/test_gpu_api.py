@@ -16,6 +16,10 @@ def host(t):
     return t.cpu().numpy()
 
 
+def cuda(a):
+    return torch.as_tensor(np.ascontiguousarray(a), dtype=torch.int64).cuda()
+
+
 @pytest.fixture(scope="module")
 def rmat():
     from gsampler_b200 import synth
@@ -268,6 +272,31 @@ def test_graph_accessors_and_formats(gsb, oracle):
     assert np.array_equal(host(sub._CAPI_GetCSCIndices()), cp)
     counts = sub._CAPI_BatchGetColCounts()
     assert counts == [10, 30]
+
+
+def test_unsorted_coo_to_csc_and_csr_is_the_stable_grouping(gsb):
+    """An unsorted COO turned into CSC and CSR by the library's counting sort (histogram, scan,
+    scatter, per-segment sort by original position): offsets, ids and the edge-id permutation equal
+    a stable sort by key (what the reference's radix sort of (key, position) pairs gives,
+    src/cuda/format_transform.cu:66-86, 108-142).  Empty segments, a segment of 40 000 entries
+    (the long-column sort path) and segments of a few thousand are present."""
+    rng = np.random.default_rng(12)
+    n, nnz = 50000, 1_500_000
+    row = rng.integers(0, n, nnz)
+    col = rng.integers(0, n, nnz)
+    col[rng.choice(nnz, 40000, replace=False)] = 7          # one hub column
+    col[col == 11] = 12                                      # an empty column
+    row[rng.choice(nnz, 3000, replace=False)] = 123          # a mid-size row
+    g = gsb.Graph(n, n)
+    g._CAPI_LoadCOO(cuda(row), cuda(col), False, False)
+    for key, val, ip_fn, id_fn, e_fn in ((col, row, g._CAPI_GetCSCIndptr, g._CAPI_GetCSCIndices, g._CAPI_GetCSCEids),
+                                         (row, col, g._CAPI_GetCSRIndptr, g._CAPI_GetCSRIndices, g._CAPI_GetCSREids)):
+        perm = np.argsort(key, kind="stable")
+        want_ip = np.concatenate([[0], np.cumsum(np.bincount(key, minlength=n))])
+        assert np.array_equal(host(ip_fn()), want_ip)
+        assert np.array_equal(host(id_fn()), val[perm])
+        assert np.array_equal(host(e_fn()), perm)
+    gsb.check_async_errors()
 
 
 def test_short_row_id_map_is_an_exception(gsb, rmat):
