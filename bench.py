@@ -520,7 +520,7 @@ class SageWorkload(object):
         (dname, dtag), (dms, dcnt) = max(by.items(), key=lambda kv: kv[1][0])
         S, E, U = (c_host[:, dtag, j].astype(np.float64) for j in range(3))
         per_launch = {
-            # the sampling kernel also writes the block's column ids (8E), see DESIGN.md
+            # the sampling kernel also writes the block's column ids (8E): 32E written, not 24E
             "sample_tile": (8 * S + 16 * S + w_idx * E + 8 * (S + 1) + 32 * E).mean(),
             "relabel_pcount": (8 * (S + E)).mean(), "relabel_scatter": (8 * (S + E)).mean(),
             "relabel_dedupe": (8 * (S + E)).mean(), "relabel_mark": (4 * (S + E)).mean(),
