@@ -158,15 +158,47 @@ def test_relabel_reports_bad_ids():
     assert host(ocol).tolist() == [0, 0, 1, 2, 2]
 
 
+def _bucket_of(ids, nbk):
+    """The relabel stage's bucket of an id (csrc/gsb_relabel.cu: hash32, then scaled to [0, nbk))."""
+    k = np.asarray(ids, dtype=np.uint64) & np.uint64(0xFFFFFFFF)
+    m = np.uint64(0xFFFFFFFF)
+    k ^= k >> np.uint64(16); k = (k * np.uint64(0x85ebca6b)) & m
+    k ^= k >> np.uint64(13); k = (k * np.uint64(0xc2b2ae35)) & m
+    k ^= k >> np.uint64(16)
+    return (k * np.uint64(nbk)) >> np.uint64(32)
+
+
+def test_batch_relabel_ids_crowding_into_one_bucket(oracle):
+    """Ids chosen so that all of them hash into ONE of the minibatch's three buckets: 10 300
+    mostly distinct ids in a bucket whose region holds 4096 entries and whose shared table holds
+    8192 -- the rest goes through the overflow list, and the CTA falls back to its table in global
+    memory.  A second minibatch of ordinary ids follows."""
+    rng = np.random.default_rng(77)
+    pool = rng.integers(0, 2 ** 31 - 5, 200_000)
+    crowd = pool[_bucket_of(pool, 3) == 0]
+    assert crowd.size >= 11_000
+    ns = np.array([100, 300]); ne = np.array([10_300, 5_000])       # 10 400 items -> 3 buckets
+    sp = np.concatenate([[0], np.cumsum(ns)]); ep = np.concatenate([[0], np.cumsum(ne)])
+    seeds = np.concatenate([crowd[:100], rng.integers(0, 50_000, 300)])
+    rows = np.concatenate([rng.permutation(crowd[50:10_350]), rng.integers(0, 50_000, 5_000)])   # 10 300 distinct
+    col_local = np.sort(np.concatenate([rng.integers(0, 100, 10_300), rng.integers(100, 400, 5_000)])).astype(np.int64)
+    uq, up, orow, ocol, err = abi.batch_relabel(dev(seeds), dev(sp), dev(rows), dev(col_local), dev(ep))
+    assert err == 0
+    euq, eup, eorow, eocol = oracle.batch_coo_relabel(seeds, sp, seeds[col_local], rows, ep)
+    assert np.array_equal(host(up), eup) and np.array_equal(host(uq), euq)
+    assert np.array_equal(host(orow), eorow) and np.array_equal(host(ocol), eocol)
+    assert eup[1] > 8192      # more distinct ids than the shared table has slots
+
+
 @pytest.mark.parametrize("case", ["streamed_buckets", "table_overflow", "hub", "two_big"])
 def test_batch_relabel_large_minibatches(oracle, case):
-    """Minibatches far larger than a sampler produces: buckets too large for the register path
-    (streamed twice), more distinct ids than the shared table holds (CTA-owned table in global
-    memory), and one id repeated hundreds of thousands of times."""
+    """Minibatches far larger than a sampler produces: several thousand buckets per minibatch
+    (more than the scatter pass's shared histogram holds: its per-item path), and one id
+    repeated hundreds of thousands of times (overflow list)."""
     rng = np.random.default_rng(len(case))
-    if case == "streamed_buckets":      # 1024 buckets of ~5 000 items
+    if case == "streamed_buckets":      # 1452 buckets, ids repeat about twice
         sizes, nid = [(1000, 5_200_000)], 3_000_000
-    elif case == "table_overflow":      # 1024 buckets of ~9 300 mostly distinct ids
+    elif case == "table_overflow":      # 2665 buckets of mostly distinct ids
         sizes, nid = [(50_000, 9_500_000)], 2 ** 31 - 5
     elif case == "hub":
         sizes, nid = [(100, 400_000), (50, 30_000)], 50_000
