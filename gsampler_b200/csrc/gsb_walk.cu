@@ -9,10 +9,13 @@
 // trace[s * N + w], which makes every step's store coalesced across walkers.
 //
 // A step is two dependent random accesses: the offsets pair of the current node, then one row
-// id.  The offsets array is small (8 bytes per node) and every walker reads it at random at
-// every step, so it is loaded with an evict-last policy while the row-id gathers and the trace
-// stores -- both streams that are never read again -- are marked evict-first: the offsets then
-// stay in L2 and a step costs one DRAM access instead of two.
+// id.  The offsets array is small (4 or 8 bytes per node) and every walker reads it at random
+// at every step, so it is loaded with an evict-last policy and the trace stores -- never read
+// again -- are marked evict-first: the offsets then stay in L2 and a step costs one DRAM access
+// instead of two.  What is left is the rate at which the memory system serves random 32-byte
+// gathers from the row-id array, which grows with the share of that array L2 holds: hence the
+// 32-bit copies of offsets and row ids the caller may pass, and the normal (not evict-first)
+// policy on the gathers.
 #include "gsb_common.cuh"
 
 namespace gsb {
