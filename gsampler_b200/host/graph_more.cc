@@ -28,7 +28,13 @@ static IdArray NarrowIndices(Compressed& c, int64_t num_rows) {
     return {c.indices.data_ptr(), dt};
   static std::mutex mu;  // two host threads asking for the first time make one copy
   std::lock_guard<std::mutex> lock(mu);
-  if (!c.indices32.defined()) c.indices32 = c.indices.to(torch::kInt32);
+  if (!c.indices32.defined()) {
+    try {
+      c.indices32 = c.indices.to(torch::kInt32);
+    } catch (const c10::Error&) {  // no room for the copy: the 64-bit array serves as it is
+      return {c.indices.data_ptr(), dt};
+    }
+  }
   return {c.indices32.data_ptr(), GSB_I32};
 }
 

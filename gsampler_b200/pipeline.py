@@ -133,7 +133,10 @@ class GraphSAGESampler(object):
         self._err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._ids = self.indices
         if narrow_ids and on_gpu and indices.dtype == torch.int64 and self.num_nodes <= 0x7FFFFFFF:
-            self._ids = self.indices.to(torch.int32)
+            try:
+                self._ids = self.indices.to(torch.int32)
+            except torch.cuda.OutOfMemoryError:   # no room for the copy: sample from the 64-bit array
+                self._ids = self.indices
         self._dtype = 0 if self._ids.dtype == torch.int32 else 1
         # every call draws from fresh random streams: call c, layer l uses stream c * L + l
         # (``stream_base`` can be saved and restored to resume a run)
