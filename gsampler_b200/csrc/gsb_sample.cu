@@ -193,16 +193,23 @@ sample_tile_kernel(const SampleParams p) {
 }
 
 // Column slots per tile (CTA).  `S_geom` = the number of slots the launch is laid out for: with
-// few of them the tiles shrink (down to 64 slots) so that every SM still gets several CTAs --
-// the first layer of a 32 x 1024-seed super-batch is 128 tiles of 256 slots otherwise, fewer
-// CTAs than the GPU has SMs.  Results do not depend on the tile size (the random streams are
+// few of them the tiles shrink (down to 64 slots) so that every SM still gets several rounds
+// of CTAs -- the first layer of a 32 x 1024-seed super-batch is 128 tiles of 256 slots
+// otherwise, fewer CTAs than the GPU has SMs.  Results do not depend on the tile size (the random streams are
 // keyed by slot).
+// Tiles per SM below which the tiles shrink: 16 = two rounds of the 8 CTAs an SM holds.  The
+// second layer of the benchmark (410 k slots) is 1600 tiles of 256 slots -- one full round of
+// resident CTAs and a second one a third full -- or 3200 tiles of 128: 1.007 -> 0.986 ms per
+// step (threshold 4 -> 16; 32 halves the tiles once more and loses: 1.017 ms).
+#ifndef GSB_SAMPLE_MIN_TILES_PER_SM
+#define GSB_SAMPLE_MIN_TILES_PER_SM 16
+#endif
 static int sample_tile_cols(i64 K, i64 S_geom = -1) {
   i64 tc = SAMPLE_MAX_TILE_EDGES / K;
   if (tc > SAMPLE_THREADS) tc = SAMPLE_THREADS;
   if (tc < 1) tc = 1;
   if (S_geom >= 0)
-    while (tc > 64 && (S_geom + tc - 1) / tc < 4 * (i64)sm_count()) tc >>= 1;
+    while (tc > 64 && (S_geom + tc - 1) / tc < GSB_SAMPLE_MIN_TILES_PER_SM * (i64)sm_count()) tc >>= 1;
   return (int)tc;
 }
 
