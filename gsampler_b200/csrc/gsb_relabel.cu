@@ -15,7 +15,8 @@
 //   scatter : (id, index) pairs grouped by bucket.  A bucket owns a region of
 //             fixed capacity, so nothing is counted first: every 8192-item
 //             tile reserves a run per bucket with one global atomic; what
-//             finds its region full goes to one overflow list     (streaming)
+//             finds its region full goes to an overflow list kept
+//             in lanes, so that a bucket rereads only its lane     (streaming)
 //   dedupe  : CTA per bucket: shared table id -> smallest index, then
 //             min_idx[item] for every REPEATED item of the bucket; a bucket
 //             whose ids do not fit the shared table falls back to a table in
