@@ -928,7 +928,10 @@ def main():
             "steps": K, "warmup": W, "ms_per_step": rep_ms[mid] / K,
             "higher_is_better": True, "scaling": cfg["scaling"], "vs_baseline": None,
             "dtype": "int64" if cfg["kind"] != "ladies" else "int64+f32", "data": "synthetic",
-            "config": {"workload": args.workload, **wl.describe(detail, world)},
+            # the workload's defining keys first (the reference arm prints the same ones), then what
+            # this arm measured about it
+            "config": {"workload": args.workload, **{k: v for k, v in cfg.items() if k not in ("kind", "large")},
+                       **wl.describe(detail, world)},
             "repeats": {"n": R, "what": "the K-step timed region repeated; value / ms_per_step are the median repetition",
                         "ms_per_step": {"min": min(rep_ms) / K, "median": rep_ms[mid] / K, "max": max(rep_ms) / K},
                         "value": {"min": min(rates), "median": rates[mid], "max": max(rates)},
