@@ -87,6 +87,55 @@ __global__ void __launch_bounds__(FM_THREADS) group_unpack_kernel(const u64* __r
   }
 }
 
+// ---------------------------------------------------------------- compaction of an id axis
+// Sorted unique of node ids + the map id -> position in it (Graph::Compact).  The ids are below
+// the graph's number of rows / columns, so "sorted unique" is a presence table over that range:
+// mark, running sum (the rank of every present id), then gather.  The reference sorts
+// (src/cuda/compact.cu:10-30, torch::_unique2).
+template <typename IndexT>
+__global__ void __launch_bounds__(FM_THREADS) compact_mark_kernel(const IndexT* __restrict__ ids, i64 n, i64 bound,
+                                                                 i64* __restrict__ present, int* err) {
+  for (i64 i = (i64)blockIdx.x * FM_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * FM_THREADS) {
+    const i64 v = (i64)ids[i];
+    if ((u64)v < (u64)bound) present[v] = 1;  // every writer stores the same value
+    else raise(err, ERRBIT_BAD_INPUT);
+  }
+}
+
+// rank[v] = present ids below v (rank has bound + 1 entries; v is present iff rank[v+1] > rank[v])
+__global__ void __launch_bounds__(FM_THREADS) compact_unique_kernel(const i64* __restrict__ rank, i64 bound,
+                                                                   i64* __restrict__ unique) {
+  for (i64 v = (i64)blockIdx.x * FM_THREADS + threadIdx.x; v < bound; v += (i64)gridDim.x * FM_THREADS) {
+    const i64 r = rank[v];
+    if (rank[v + 1] != r) unique[r] = v;
+  }
+}
+
+template <typename IndexT>
+__global__ void __launch_bounds__(FM_THREADS) compact_map_kernel(const IndexT* __restrict__ ids, i64 n, i64 bound,
+                                                                const i64* __restrict__ rank, i64* __restrict__ out) {
+  for (i64 i = (i64)blockIdx.x * FM_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * FM_THREADS) {
+    const i64 v = (i64)ids[i];
+    out[i] = (u64)v < (u64)bound ? __ldg(rank + v) : -1;
+  }
+}
+
+struct CompactLayout {
+  size_t status, rank, total;
+  i64 scan_tiles;
+};
+
+static CompactLayout compact_layout(i64 bound) {
+  CompactLayout L;
+  auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
+  L.scan_tiles = (bound + SC_TILE) / SC_TILE;
+  size_t o = 0;
+  L.status = o; o = up(o + 256 + sizeof(u64) * (size_t)(L.scan_tiles + 1));
+  L.rank = o; o = up(o + sizeof(i64) * (size_t)(bound + 1));
+  L.total = o;
+  return L;
+}
+
 struct GroupLayout {
   size_t status, cursor, packed, sort, total;
   i64 scan_tiles;
@@ -152,6 +201,56 @@ extern "C" int gsb_group_by_key(const int64_t* keys, const int64_t* vals, int64_
                                      d_err, cuda_stream);
     if (rc != GSB_OK) return rc;
     group_unpack_kernel<<<wide_grid_fm(nnz), FM_THREADS, 0, st>>>(packed, nnz, (i64*)out_vals, (i64*)out_pos);
+  }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" size_t gsb_compact_workspace_bytes(int64_t bound) {
+  if (bound < 0) return 0;
+  return compact_layout(bound).total;
+}
+
+extern "C" int gsb_compact_rank(const void* ids, int ids_dtype, int64_t n, int64_t bound, void* workspace,
+                                size_t workspace_bytes, int64_t* d_count, int* d_err, void* cuda_stream) {
+  if (n < 0 || bound < 0 || (n > 0 && !ids)) return GSB_ERR_INVALID;
+  if (ids_dtype != GSB_I32 && ids_dtype != GSB_I64) return GSB_ERR_INVALID;
+  if (bound >= (1ll << 40)) return GSB_ERR_UNSUPPORTED;
+  const CompactLayout L = compact_layout(bound);
+  if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  char* ws = (char*)workspace;
+  i64* rank = (i64*)(ws + L.rank);
+  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.total, st));  // ticket, status words, presence table
+  LaunchScope ls(KID_MISC, st);
+  if (n > 0) {
+    if (ids_dtype == GSB_I32)
+      compact_mark_kernel<int><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const int*)ids, n, bound, rank, d_err);
+    else
+      compact_mark_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, rank, d_err);
+  }
+  scan_i64_kernel<<<(int)L.scan_tiles, SC_THREADS, 0, st>>>(rank, bound, rank, (u64*)(ws + L.status + 256),
+                                                            (int*)(ws + L.status), d_err);
+  if (d_count)
+    GSB_CUDA_OK(cudaMemcpyAsync(d_count, rank + bound, sizeof(i64), cudaMemcpyDeviceToDevice, st));
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" int gsb_compact_apply(const void* workspace, int64_t bound, int64_t* unique, const void* ids,
+                                 int ids_dtype, int64_t n, int64_t* out, void* cuda_stream) {
+  if (!workspace || bound < 0 || n < 0 || (n > 0 && (!ids || !out))) return GSB_ERR_INVALID;
+  if (n > 0 && ids_dtype != GSB_I32 && ids_dtype != GSB_I64) return GSB_ERR_INVALID;
+  const CompactLayout L = compact_layout(bound);
+  const i64* rank = (const i64*)((const char*)workspace + L.rank);
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  LaunchScope ls(KID_MISC, st);
+  if (unique && bound > 0) compact_unique_kernel<<<wide_grid_fm(bound), FM_THREADS, 0, st>>>(rank, bound, (i64*)unique);
+  if (n > 0) {
+    if (ids_dtype == GSB_I32)
+      compact_map_kernel<int><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const int*)ids, n, bound, rank, (i64*)out);
+    else
+      compact_map_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, rank, (i64*)out);
   }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;

@@ -205,43 +205,62 @@ std::tuple<torch::Tensor, torch::Tensor, torch::Tensor> Graph::SliceCoo(torch::T
 }
 
 // src/graph.cc:508-575 (sorted unique of one axis + remap, src/cuda/compact.cu:10-30).
-// Secondary path: the sorted unique is torch's library routine.
+// The ids of an axis lie below the graph's number of rows / columns, so the sorted unique is a
+// presence table over that range (gsb_compact_rank / gsb_compact_apply): the rank table is built
+// once from one of the formats' id arrays and every format's array is mapped through it.
 Graph::GraphAndIndex Graph::Compact(int64_t axis) {
   TORCH_CHECK(axis == 0 || axis == 1, "Compact: axis must be 0 or 1");
   auto ret = Derive(num_rows_, num_cols_);
-  torch::Tensor frontiers;
-  auto compact = [&](const torch::Tensor& ids) {
-    auto uq = torch::_unique2(ids.to(torch::kInt64), true, true, false);
-    frontiers = std::get<0>(uq);
-    return std::get<1>(uq);
+  const int64_t bound = axis == 0 ? num_rows_ : num_cols_;
+  const torch::Tensor* first = nullptr;  // any array holding the axis' ids (they all hold the same set)
+  if (coo_) first = axis == 0 ? &coo_->row : &coo_->col;
+  else if (axis == 0 && csc_) first = &csc_->indices;
+  else if (axis == 1 && csr_) first = &csr_->indices;
+  TORCH_CHECK(first != nullptr, axis == 0 ? "Compact(0) needs a COO or CSC format" : "Compact(1) needs a COO or CSR format");
+  TORCH_CHECK(first->is_cuda(), "Compact: the graph must be on the GPU");
+  c10::cuda::CUDAGuard guard(first->device());
+  const auto dev = first->device();
+  auto ws = NewWorkspace(gsb_compact_workspace_bytes(bound), dev);
+  auto count = torch::empty({1}, torch::dtype(torch::kInt64).device(dev));
+  auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(dev));
+  auto ids_of = [](const torch::Tensor& t) { return t.contiguous(); };
+  {
+    auto ids = ids_of(*first);
+    CheckStatus(gsb_compact_rank(ids.data_ptr(), IdxDtype(ids), ids.numel(), bound, ws.data_ptr(),
+                                 (size_t)ws.numel(), PM(count), err.data_ptr<int>(), CurrentStream()),
+                "compact_rank");
+  }
+  const int64_t U = count.item<int64_t>();  // sizes the frontier list
+  CheckDeviceError(err.item<int>(), "Compact");
+  auto frontiers = torch::empty({U}, torch::dtype(torch::kInt64).device(dev));
+  bool listed = false;
+  auto compact = [&](const torch::Tensor& t) {
+    auto ids = ids_of(t);
+    auto mapped = torch::empty({ids.numel()}, torch::dtype(torch::kInt64).device(dev));
+    CheckStatus(gsb_compact_apply(ws.data_ptr(), bound, listed ? nullptr : PM(frontiers), ids.data_ptr(),
+                                  IdxDtype(ids), ids.numel(), PM(mapped), CurrentStream()),
+                "compact_apply");
+    listed = true;
+    return mapped;
   };
   if (axis == 0) {
-    torch::Tensor mapped;
-    if (coo_) {
-      mapped = compact(coo_->row);
+    if (coo_)
       ret->coo_ = std::make_shared<Coordinate>(
-          Coordinate{mapped, coo_->col, coo_->e_ids, coo_->row_sorted, coo_->col_sorted});
-    }
-    if (csc_) {
-      if (!mapped.defined()) mapped = compact(csc_->indices);
-      ret->csc_ = std::make_shared<Compressed>(Compressed{csc_->indptr, mapped, csc_->e_ids});
-    }
-    TORCH_CHECK(frontiers.defined(), "Compact(0) needs a COO or CSC format");
-    ret->num_rows_ = frontiers.numel();
+          Coordinate{compact(coo_->row), coo_->col, coo_->e_ids, coo_->row_sorted, coo_->col_sorted});
+    if (csc_)
+      ret->csc_ = std::make_shared<Compressed>(Compressed{csc_->indptr, compact(csc_->indices), csc_->e_ids});
+    ret->num_rows_ = U;
   } else {
-    torch::Tensor mapped;
-    if (coo_) {
-      mapped = compact(coo_->col);
+    if (coo_)
       ret->coo_ = std::make_shared<Coordinate>(
-          Coordinate{coo_->row, mapped, coo_->e_ids, coo_->row_sorted, coo_->col_sorted});
-    }
-    if (csr_) {
-      if (!mapped.defined()) mapped = compact(csr_->indices);
-      ret->csr_ = std::make_shared<Compressed>(Compressed{csr_->indptr, mapped, csr_->e_ids});
-    }
-    TORCH_CHECK(frontiers.defined(), "Compact(1) needs a COO or CSR format");
-    ret->num_cols_ = frontiers.numel();
+          Coordinate{coo_->row, compact(coo_->col), coo_->e_ids, coo_->row_sorted, coo_->col_sorted});
+    if (csr_)
+      ret->csr_ = std::make_shared<Compressed>(Compressed{csr_->indptr, compact(csr_->indices), csr_->e_ids});
+    ret->num_cols_ = U;
   }
+  if (!listed)  // U == 0 and no array: nothing to map
+    CheckStatus(gsb_compact_apply(ws.data_ptr(), bound, PM(frontiers), nullptr, GSB_I64, 0, nullptr, CurrentStream()),
+                "compact_apply");
   ret->num_edges_ = num_edges_;
   return {ret, frontiers};
 }

@@ -231,6 +231,18 @@ GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nke
  * values in [0, 2^32); a key outside [0, nkeys) or a value outside that range sets
  * GSB_ERRBIT_BAD_INPUT.  Replaces the unsorted branches of COO2CSCCUDA / COO2CSRCUDA
  * (src/cuda/format_transform.cu:66-86, 108-120: a device-wide radix sort of (key, position)). */
+/* Compaction of an id axis (Graph::Compact): the sorted distinct ids among ids[n] (all below
+ * `bound`, the graph's number of rows or columns) and the map id -> position among them.
+ * gsb_compact_rank builds the rank table in the workspace (presence marks, running sum) and
+ * writes the number of distinct ids to d_count (device); gsb_compact_apply then writes the sorted
+ * distinct ids (unique[count], may be NULL) and / or maps an id array of the same id set
+ * (out[i] = position of ids[i]; -1 for an id that is not below bound).  Replaces
+ * TensorCompactCUDA (src/cuda/compact.cu:10-30: a library sort + unique). */
+GSB_API size_t gsb_compact_workspace_bytes(int64_t bound);
+GSB_API int gsb_compact_rank(const void* ids, int ids_dtype, int64_t n, int64_t bound, void* workspace,
+                             size_t workspace_bytes, int64_t* d_count, int* d_err, void* cuda_stream);
+GSB_API int gsb_compact_apply(const void* workspace, int64_t bound, int64_t* unique, const void* ids,
+                              int ids_dtype, int64_t n, int64_t* out, void* cuda_stream);
 GSB_API size_t gsb_group_by_key_workspace_bytes(int64_t nnz, int64_t nkeys);
 GSB_API int gsb_group_by_key(const int64_t* keys, const int64_t* vals, int64_t nnz, int64_t nkeys,
                              int64_t* indptr, int64_t* out_vals, int64_t* out_pos, void* workspace,

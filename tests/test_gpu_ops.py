@@ -356,6 +356,23 @@ def test_compact_and_index_search(gsb, oracle, graph):
     uq, cp = oracle.compact(host(sub._CAPI_GetCSCIndices()))
     assert np.array_equal(host(frontier), uq) and np.array_equal(host(g2._CAPI_GetCSCIndices()), cp)
     assert g2._CAPI_GetNumRows() == uq.size
+    # the COO and the CSC of one graph in different edge orders: each is mapped in its own order
+    rng = np.random.default_rng(2)
+    n, nnz = 5000, 60000
+    row, col = rng.integers(0, n, nnz) * 3 % n, rng.integers(0, 700, nnz)
+    g = gsb.Graph(n, 700)
+    g._CAPI_LoadCOO(cuda(row), cuda(col), False, False)
+    csc_rows = host(g._CAPI_GetCSCIndices())                 # grouped by column: another order than `row`
+    assert not np.array_equal(csc_rows, row)
+    for axis, ids in ((0, row), (1, col)):
+        g3, fr = g._CAPI_Compact(axis)
+        uq = np.unique(ids)
+        assert np.array_equal(host(fr), uq)
+        got = host(g3._CAPI_GetCOORows() if axis == 0 else g3._CAPI_GetCOOCols())
+        assert np.array_equal(got, np.searchsorted(uq, ids))
+        assert (g3._CAPI_GetNumRows() if axis == 0 else g3._CAPI_GetNumCols()) == uq.size
+        if axis == 0:
+            assert np.array_equal(host(g3._CAPI_GetCSCIndices()), np.searchsorted(uq, csc_rows))
     data = cuda(np.array([7, 3, 9, 11]))
     keys = cuda(np.array([9, 4, 7, 11, 3]))
     assert host(torch.ops.gs_ops._CAPI_IndexSearch(data, keys)).tolist() == [2, -1, 0, 3, 1]
