@@ -136,6 +136,66 @@ static CompactLayout compact_layout(i64 bound) {
   return L;
 }
 
+// ---------------------------------------------------------------- position lookup (IndexSearch)
+// out[j] = the smallest i with data[i] == keys[j], or -1.  An open-addressing table in global
+// memory, twice as many slots as entries (a power of two): slot key claimed by compare-and-swap,
+// slot value lowered by atomicMin, so that the result does not depend on the order of execution
+// (the reference's table keeps whichever duplicate wrote last, src/cuda/index_search.cu:46-57).
+// -1 is the empty key, as in the reference: it cannot be looked up.  Every probe loop ends after
+// `slots` probes.
+constexpr i64 IS_EMPTY = -1;
+__device__ __forceinline__ u64 mix64(u64 k) {
+  k ^= k >> 30; k *= 0xBF58476D1CE4E5B9ull; k ^= k >> 27; k *= 0x94D049BB133111EBull; k ^= k >> 31;
+  return k;
+}
+
+__global__ void __launch_bounds__(FM_THREADS) index_insert_kernel(const i64* __restrict__ data, i64 n,
+                                                                 long long* tab_k, long long* tab_v, u64 slots,
+                                                                 int* err) {
+  const u64 mask = slots - 1;
+  for (i64 i = (i64)blockIdx.x * FM_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * FM_THREADS) {
+    const i64 key = __ldg(data + i);
+    if (key == IS_EMPTY) { raise(err, ERRBIT_BAD_INPUT); continue; }
+    u64 pos = mix64((u64)key) & mask;
+    u64 probes = 0;
+    for (; probes < slots; ++probes) {
+      long long cur = tab_k[pos];
+      if (cur == IS_EMPTY) cur = (long long)atomicCAS((unsigned long long*)(tab_k + pos), (unsigned long long)IS_EMPTY,
+                                                      (unsigned long long)key);
+      if (cur == IS_EMPTY || cur == key) { atomicMin(tab_v + pos, (long long)i); break; }
+      pos = (pos + 1) & mask;
+    }
+    if (probes == slots) raise(err, ERRBIT_TABLE_FULL);
+  }
+}
+
+__global__ void __launch_bounds__(FM_THREADS) index_query_kernel(const i64* __restrict__ keys, i64 m,
+                                                                const long long* __restrict__ tab_k,
+                                                                const long long* __restrict__ tab_v, u64 slots,
+                                                                i64* __restrict__ out) {
+  const u64 mask = slots - 1;
+  for (i64 j = (i64)blockIdx.x * FM_THREADS + threadIdx.x; j < m; j += (i64)gridDim.x * FM_THREADS) {
+    const i64 key = __ldg(keys + j);
+    i64 found = -1;
+    if (key != IS_EMPTY) {
+      u64 pos = mix64((u64)key) & mask;
+      for (u64 probes = 0; probes < slots; ++probes) {
+        const long long cur = tab_k[pos];
+        if (cur == key) { found = tab_v[pos]; break; }
+        if (cur == IS_EMPTY) break;
+        pos = (pos + 1) & mask;
+      }
+    }
+    out[j] = found;
+  }
+}
+
+static u64 index_slots(i64 n) {
+  u64 s = 64;
+  while (s < 2 * (u64)n) s <<= 1;
+  return s;
+}
+
 struct GroupLayout {
   size_t status, cursor, packed, sort, total;
   i64 scan_tiles;
@@ -252,6 +312,31 @@ extern "C" int gsb_compact_apply(const void* workspace, int64_t bound, int64_t* 
     else
       compact_map_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, rank, (i64*)out);
   }
+  GSB_CUDA_OK(cudaGetLastError());
+  return GSB_OK;
+}
+
+extern "C" size_t gsb_index_search_workspace_bytes(int64_t n) {
+  if (n < 0) return 0;
+  return (size_t)index_slots(n) * 16;
+}
+
+extern "C" int gsb_index_search(const int64_t* data, int64_t n, const int64_t* keys, int64_t m, int64_t* out,
+                                void* workspace, size_t workspace_bytes, int* d_err, void* cuda_stream) {
+  if (n < 0 || m < 0 || (n > 0 && !data) || (m > 0 && (!keys || !out))) return GSB_ERR_INVALID;
+  if (n >= (1ll << 40)) return GSB_ERR_UNSUPPORTED;
+  const u64 slots = index_slots(n);
+  if (!workspace || workspace_bytes < slots * 16) return GSB_ERR_WORKSPACE;
+  cudaStream_t st = (cudaStream_t)cuda_stream;
+  long long* tab_k = (long long*)workspace;
+  long long* tab_v = tab_k + slots;
+  GSB_CUDA_OK(cudaMemsetAsync(tab_k, 0xFF, slots * 8, st));  // every key -1 = empty
+  GSB_CUDA_OK(cudaMemsetAsync(tab_v, 0x7F, slots * 8, st));  // every value above any position
+  LaunchScope ls(KID_MISC, st);
+  if (n > 0)
+    index_insert_kernel<<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)data, n, tab_k, tab_v, slots, d_err);
+  if (m > 0)
+    index_query_kernel<<<wide_grid_fm(m), FM_THREADS, 0, st>>>((const i64*)keys, m, tab_k, tab_v, slots, (i64*)out);
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }

@@ -551,9 +551,31 @@ Graph::GraphAndIndex Graph::BatchColSlicing(torch::Tensor seeds, torch::Tensor c
   if (encoding) {
     // sorted unique of the encoded ids + remap (src/cuda/compact.cu:10-30), then
     // split the unique list per minibatch (src/cuda/batch/encoding_decoding.cu:99-122)
-    auto uq = torch::_unique2(ids, /*sorted=*/true, /*return_inverse=*/true, false);
-    auto enc = std::get<0>(uq);
-    ids = std::get<1>(uq);
+    torch::Tensor enc;
+    const int64_t bound = num_rows_ * B;  // the encoded ids lie below it
+    if (ids.is_cuda() && num_rows_ > 0 && bound / num_rows_ == B && bound <= (int64_t(1) << 29)) {
+      // presence table over the encoded range (gsb_compact_*): 8 bytes per possible id
+      c10::cuda::CUDAGuard guard(ids.device());
+      ids = ids.to(torch::kInt64).contiguous();
+      auto ws = NewWorkspace(gsb_compact_workspace_bytes(bound), ids.device());
+      auto count = torch::empty({1}, I64(ids));
+      auto err = torch::zeros({1}, torch::dtype(torch::kInt32).device(ids.device()));
+      CheckStatus(gsb_compact_rank(ids.data_ptr(), GSB_I64, ids.numel(), bound, ws.data_ptr(), (size_t)ws.numel(),
+                                   PM(count), err.data_ptr<int>(), CurrentStream()),
+                  "compact_rank");
+      const int64_t U = count.item<int64_t>();  // sizes the list of distinct ids
+      CheckDeviceError(err.item<int>(), "BatchColSlicing");
+      enc = torch::empty({U}, I64(ids));
+      auto mapped = torch::empty({ids.numel()}, I64(ids));
+      CheckStatus(gsb_compact_apply(ws.data_ptr(), bound, PM(enc), ids.data_ptr(), GSB_I64, ids.numel(),
+                                    PM(mapped), CurrentStream()),
+                  "compact_apply");
+      ids = mapped;
+    } else {  // an encoded range too wide for a table: the library's sorted unique
+      auto uq = torch::_unique2(ids, /*sorted=*/true, /*return_inverse=*/true, false);
+      enc = std::get<0>(uq);
+      ids = std::get<1>(uq);
+    }
     auto batch_of = torch::floor_divide(enc, num_rows_);
     orig_row_ids = enc - batch_of * num_rows_;
     row_bptr = torch::empty({B + 1}, I64(enc));

@@ -831,17 +831,22 @@ std::tuple<torch::Tensor, torch::Tensor> BatchListSampling(int64_t num_picks, bo
   return ListSampleImpl(c10::nullopt, range, R, num_picks, range.device());
 }
 
-// src/tensor_ops.cc:30-38: position of every key in `origin_data`, -1 if absent.
-// Utility operator outside the sampling path: a library sort + binary search.
+// src/tensor_ops.cc:30-38: position of every key in `origin_data`, -1 if absent (the smallest
+// position when `origin_data` holds a value more than once).  Does not synchronise: a -1 inside
+// `origin_data` (the table's empty key, as in the reference) is reported by CheckAsyncErrors.
 torch::Tensor IndexSearch(torch::Tensor origin_data, torch::Tensor keys) {
-  auto sorted = origin_data.sort();
-  const auto& vals = std::get<0>(sorted);
-  const auto& perm = std::get<1>(sorted);
-  if (vals.numel() == 0) return torch::full_like(keys, -1);
-  auto pos = torch::searchsorted(vals, keys).clamp_max(vals.numel() - 1);
-  auto hit = vals.index_select(0, pos.reshape({-1})).reshape(keys.sizes()) == keys;
-  return torch::where(hit, perm.index_select(0, pos.reshape({-1})).reshape(keys.sizes()),
-                      torch::full_like(keys, -1));
+  TORCH_CHECK(origin_data.is_cuda() && keys.is_cuda(), "IndexSearch: tensors must be on the GPU");
+  TORCH_CHECK(origin_data.scalar_type() == torch::kInt64 && keys.scalar_type() == torch::kInt64,
+              "IndexSearch: int64 tensors");
+  c10::cuda::CUDAGuard guard(keys.device());
+  auto data = origin_data.contiguous().reshape({-1});
+  auto flat = keys.contiguous().reshape({-1});
+  auto out = torch::empty_like(flat);
+  auto ws = NewWorkspace(gsb_index_search_workspace_bytes(data.numel()), keys.device());
+  CheckStatus(gsb_index_search(P(data), data.numel(), P(flat), flat.numel(), PM(out), ws.data_ptr(),
+                               (size_t)ws.numel(), AsyncErrorWord(keys.device()).data_ptr<int>(), CurrentStream()),
+              "index_search");
+  return out.reshape(keys.sizes());
 }
 
 // ------------------------------------------------------------------ row gather

@@ -243,6 +243,14 @@ GSB_API int gsb_compact_rank(const void* ids, int ids_dtype, int64_t n, int64_t 
                              size_t workspace_bytes, int64_t* d_count, int* d_err, void* cuda_stream);
 GSB_API int gsb_compact_apply(const void* workspace, int64_t bound, int64_t* unique, const void* ids,
                               int ids_dtype, int64_t n, int64_t* out, void* cuda_stream);
+/* Position lookup: out[j] = the smallest i with data[i] == keys[j], or -1 when there is none
+ * (an open-addressing table in the workspace; the key -1 stands for "empty" and cannot be looked
+ * up: in `data` it sets GSB_ERRBIT_BAD_INPUT, in `keys` it gives -1).  Replaces
+ * IndexHashMapInsertCUDA + IndexHashMapSearchCUDA (src/cuda/index_search.cu:101-157), whose
+ * table keeps whichever of several equal entries wrote last. */
+GSB_API size_t gsb_index_search_workspace_bytes(int64_t n);
+GSB_API int gsb_index_search(const int64_t* data, int64_t n, const int64_t* keys, int64_t m, int64_t* out,
+                             void* workspace, size_t workspace_bytes, int* d_err, void* cuda_stream);
 GSB_API size_t gsb_group_by_key_workspace_bytes(int64_t nnz, int64_t nkeys);
 GSB_API int gsb_group_by_key(const int64_t* keys, const int64_t* vals, int64_t nnz, int64_t nkeys,
                              int64_t* indptr, int64_t* out_vals, int64_t* out_pos, void* workspace,

@@ -376,6 +376,17 @@ def test_compact_and_index_search(gsb, oracle, graph):
     data = cuda(np.array([7, 3, 9, 11]))
     keys = cuda(np.array([9, 4, 7, 11, 3]))
     assert host(torch.ops.gs_ops._CAPI_IndexSearch(data, keys)).tolist() == [2, -1, 0, 3, 1]
+    # a large table with repeated values (the smallest position wins), absent keys, ids beyond 2^32, shaped keys
+    big = rng.integers(0, 2 ** 40, 300_000)
+    big[rng.integers(0, big.size, 50_000)] = big[rng.integers(0, 1000, 50_000)]
+    look = np.concatenate([big[rng.integers(0, big.size, 100_000)], rng.integers(2 ** 41, 2 ** 42, 20_000)]).reshape(400, 300)
+    first = {}
+    for i, v in enumerate(big.tolist()):
+        first.setdefault(v, i)
+    want = np.array([first.get(v, -1) for v in look.reshape(-1).tolist()]).reshape(look.shape)
+    assert np.array_equal(host(torch.ops.gs_ops._CAPI_IndexSearch(cuda(big), cuda(look))), want)
+    assert host(torch.ops.gs_ops._CAPI_IndexSearch(cuda(np.empty(0, np.int64)), keys)).tolist() == [-1] * 5
+    gsb.check_async_errors()
 
 
 def test_ladies_sampler_layer(gsb, oracle):
