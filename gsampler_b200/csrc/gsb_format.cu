@@ -88,50 +88,75 @@ __global__ void __launch_bounds__(FM_THREADS) group_unpack_kernel(const u64* __r
 }
 
 // ---------------------------------------------------------------- compaction of an id axis
-// Sorted unique of node ids + the map id -> position in it (Graph::Compact).  The ids are below
-// the graph's number of rows / columns, so "sorted unique" is a presence table over that range:
-// mark, running sum (the rank of every present id), then gather.  The reference sorts
-// (src/cuda/compact.cu:10-30, torch::_unique2).
+// Sorted unique of node ids + the map id -> position in it (Graph::Compact, the encoding of batch
+// column slicing).  The ids lie below a known bound (rows / columns of the graph, times the
+// number of minibatches for encoded ids), so "sorted unique" is a presence table over that
+// range: one BIT per possible id, a running sum of the set bits per 32-bit word, and
+// rank(v) = prefix[v / 32] + popc(bits[v / 32] below bit v % 32).  3/8 of a byte per possible id.
+// The reference sorts (src/cuda/compact.cu:10-30, torch::_unique2).
 template <typename IndexT>
 __global__ void __launch_bounds__(FM_THREADS) compact_mark_kernel(const IndexT* __restrict__ ids, i64 n, i64 bound,
-                                                                 i64* __restrict__ present, int* err) {
+                                                                 u32* __restrict__ bits, int* err) {
   for (i64 i = (i64)blockIdx.x * FM_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * FM_THREADS) {
     const i64 v = (i64)ids[i];
-    if ((u64)v < (u64)bound) present[v] = 1;  // every writer stores the same value
-    else raise(err, ERRBIT_BAD_INPUT);
+    if ((u64)v < (u64)bound) {
+      const u32 bit = 1u << (v & 31);
+      if (!(bits[v >> 5] & bit)) atomicOr(bits + (v >> 5), bit);  // most ids repeat: skip the atomic then
+    } else {
+      raise(err, ERRBIT_BAD_INPUT);
+    }
   }
 }
 
-// rank[v] = present ids below v (rank has bound + 1 entries; v is present iff rank[v+1] > rank[v])
-__global__ void __launch_bounds__(FM_THREADS) compact_unique_kernel(const i64* __restrict__ rank, i64 bound,
+__global__ void __launch_bounds__(FM_THREADS) compact_popc_kernel(const u32* __restrict__ bits, i64 words,
+                                                                 i64* __restrict__ count) {
+  for (i64 w = (i64)blockIdx.x * FM_THREADS + threadIdx.x; w < words; w += (i64)gridDim.x * FM_THREADS)
+    count[w] = __popc(bits[w]);
+}
+
+__device__ __forceinline__ i64 compact_rank_of(const u32* __restrict__ bits, const i64* __restrict__ prefix, i64 v) {
+  return __ldg(prefix + (v >> 5)) + __popc(__ldg(bits + (v >> 5)) & ((1u << (v & 31)) - 1u));
+}
+
+// the distinct ids in ascending order: every set bit writes its id at its rank
+__global__ void __launch_bounds__(FM_THREADS) compact_unique_kernel(const u32* __restrict__ bits,
+                                                                   const i64* __restrict__ prefix, i64 words,
                                                                    i64* __restrict__ unique) {
-  for (i64 v = (i64)blockIdx.x * FM_THREADS + threadIdx.x; v < bound; v += (i64)gridDim.x * FM_THREADS) {
-    const i64 r = rank[v];
-    if (rank[v + 1] != r) unique[r] = v;
+  for (i64 w = (i64)blockIdx.x * FM_THREADS + threadIdx.x; w < words; w += (i64)gridDim.x * FM_THREADS) {
+    u32 b = bits[w];
+    i64 r = prefix[w];
+    while (b) {
+      const int k = __ffs(b) - 1;
+      unique[r++] = (w << 5) + k;
+      b &= b - 1;
+    }
   }
 }
 
 template <typename IndexT>
 __global__ void __launch_bounds__(FM_THREADS) compact_map_kernel(const IndexT* __restrict__ ids, i64 n, i64 bound,
-                                                                const i64* __restrict__ rank, i64* __restrict__ out) {
+                                                                const u32* __restrict__ bits,
+                                                                const i64* __restrict__ prefix, i64* __restrict__ out) {
   for (i64 i = (i64)blockIdx.x * FM_THREADS + threadIdx.x; i < n; i += (i64)gridDim.x * FM_THREADS) {
     const i64 v = (i64)ids[i];
-    out[i] = (u64)v < (u64)bound ? __ldg(rank + v) : -1;
+    out[i] = (u64)v < (u64)bound ? compact_rank_of(bits, prefix, v) : -1;
   }
 }
 
 struct CompactLayout {
-  size_t status, rank, total;
-  i64 scan_tiles;
+  size_t status, bits, prefix, total;
+  i64 words, scan_tiles;
 };
 
 static CompactLayout compact_layout(i64 bound) {
   CompactLayout L;
   auto up = [](size_t x) { return (x + 255) & ~(size_t)255; };
-  L.scan_tiles = (bound + SC_TILE) / SC_TILE;
+  L.words = (bound + 31) / 32;
+  L.scan_tiles = (L.words + SC_TILE) / SC_TILE;
   size_t o = 0;
   L.status = o; o = up(o + 256 + sizeof(u64) * (size_t)(L.scan_tiles + 1));
-  L.rank = o; o = up(o + sizeof(i64) * (size_t)(bound + 1));
+  L.bits = o; o = up(o + sizeof(u32) * (size_t)(L.words + 1));
+  L.prefix = o; o = up(o + sizeof(i64) * (size_t)(L.words + 1));
   L.total = o;
   return L;
 }
@@ -275,24 +300,26 @@ extern "C" int gsb_compact_rank(const void* ids, int ids_dtype, int64_t n, int64
                                 size_t workspace_bytes, int64_t* d_count, int* d_err, void* cuda_stream) {
   if (n < 0 || bound < 0 || (n > 0 && !ids)) return GSB_ERR_INVALID;
   if (ids_dtype != GSB_I32 && ids_dtype != GSB_I64) return GSB_ERR_INVALID;
-  if (bound >= (1ll << 40)) return GSB_ERR_UNSUPPORTED;
+  if (bound >= (1ll << 44)) return GSB_ERR_UNSUPPORTED;
   const CompactLayout L = compact_layout(bound);
   if (!workspace || workspace_bytes < L.total) return GSB_ERR_WORKSPACE;
   cudaStream_t st = (cudaStream_t)cuda_stream;
   char* ws = (char*)workspace;
-  i64* rank = (i64*)(ws + L.rank);
-  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.total, st));  // ticket, status words, presence table
+  u32* bits = (u32*)(ws + L.bits);
+  i64* prefix = (i64*)(ws + L.prefix);
+  GSB_CUDA_OK(cudaMemsetAsync(ws, 0, L.prefix, st));  // ticket, status words, presence bits
   LaunchScope ls(KID_MISC, st);
   if (n > 0) {
     if (ids_dtype == GSB_I32)
-      compact_mark_kernel<int><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const int*)ids, n, bound, rank, d_err);
+      compact_mark_kernel<int><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const int*)ids, n, bound, bits, d_err);
     else
-      compact_mark_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, rank, d_err);
+      compact_mark_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, bits, d_err);
   }
-  scan_i64_kernel<<<(int)L.scan_tiles, SC_THREADS, 0, st>>>(rank, bound, rank, (u64*)(ws + L.status + 256),
+  compact_popc_kernel<<<wide_grid_fm(L.words + 1), FM_THREADS, 0, st>>>(bits, L.words, prefix);
+  scan_i64_kernel<<<(int)L.scan_tiles, SC_THREADS, 0, st>>>(prefix, L.words, prefix, (u64*)(ws + L.status + 256),
                                                             (int*)(ws + L.status), d_err);
   if (d_count)
-    GSB_CUDA_OK(cudaMemcpyAsync(d_count, rank + bound, sizeof(i64), cudaMemcpyDeviceToDevice, st));
+    GSB_CUDA_OK(cudaMemcpyAsync(d_count, prefix + L.words, sizeof(i64), cudaMemcpyDeviceToDevice, st));
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;
 }
@@ -302,15 +329,17 @@ extern "C" int gsb_compact_apply(const void* workspace, int64_t bound, int64_t* 
   if (!workspace || bound < 0 || n < 0 || (n > 0 && (!ids || !out))) return GSB_ERR_INVALID;
   if (n > 0 && ids_dtype != GSB_I32 && ids_dtype != GSB_I64) return GSB_ERR_INVALID;
   const CompactLayout L = compact_layout(bound);
-  const i64* rank = (const i64*)((const char*)workspace + L.rank);
+  const u32* bits = (const u32*)((const char*)workspace + L.bits);
+  const i64* prefix = (const i64*)((const char*)workspace + L.prefix);
   cudaStream_t st = (cudaStream_t)cuda_stream;
   LaunchScope ls(KID_MISC, st);
-  if (unique && bound > 0) compact_unique_kernel<<<wide_grid_fm(bound), FM_THREADS, 0, st>>>(rank, bound, (i64*)unique);
+  if (unique && L.words > 0)
+    compact_unique_kernel<<<wide_grid_fm(L.words), FM_THREADS, 0, st>>>(bits, prefix, L.words, (i64*)unique);
   if (n > 0) {
     if (ids_dtype == GSB_I32)
-      compact_map_kernel<int><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const int*)ids, n, bound, rank, (i64*)out);
+      compact_map_kernel<int><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const int*)ids, n, bound, bits, prefix, (i64*)out);
     else
-      compact_map_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, rank, (i64*)out);
+      compact_map_kernel<i64><<<wide_grid_fm(n), FM_THREADS, 0, st>>>((const i64*)ids, n, bound, bits, prefix, (i64*)out);
   }
   GSB_CUDA_OK(cudaGetLastError());
   return GSB_OK;

@@ -553,8 +553,8 @@ Graph::GraphAndIndex Graph::BatchColSlicing(torch::Tensor seeds, torch::Tensor c
     // split the unique list per minibatch (src/cuda/batch/encoding_decoding.cu:99-122)
     torch::Tensor enc;
     const int64_t bound = num_rows_ * B;  // the encoded ids lie below it
-    if (ids.is_cuda() && num_rows_ > 0 && bound / num_rows_ == B && bound <= (int64_t(1) << 29)) {
-      // presence table over the encoded range (gsb_compact_*): 8 bytes per possible id
+    if (ids.is_cuda() && num_rows_ > 0 && bound / num_rows_ == B && bound < (int64_t(1) << 40)) {
+      // presence table over the encoded range (gsb_compact_*): 3/8 of a byte per possible id
       c10::cuda::CUDAGuard guard(ids.device());
       ids = ids.to(torch::kInt64).contiguous();
       auto ws = NewWorkspace(gsb_compact_workspace_bytes(bound), ids.device());
@@ -571,7 +571,7 @@ Graph::GraphAndIndex Graph::BatchColSlicing(torch::Tensor seeds, torch::Tensor c
                                     PM(mapped), CurrentStream()),
                   "compact_apply");
       ids = mapped;
-    } else {  // an encoded range too wide for a table: the library's sorted unique
+    } else {  // not on the GPU, or an encoded range of 2^40 and more: the library's sorted unique
       auto uq = torch::_unique2(ids, /*sorted=*/true, /*return_inverse=*/true, false);
       enc = std::get<0>(uq);
       ids = std::get<1>(uq);

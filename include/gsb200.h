@@ -233,7 +233,8 @@ GSB_API int gsb_indptr_from_sorted(const int64_t* keys, int64_t nnz, int64_t nke
  * (src/cuda/format_transform.cu:66-86, 108-120: a device-wide radix sort of (key, position)). */
 /* Compaction of an id axis (Graph::Compact): the sorted distinct ids among ids[n] (all below
  * `bound`, the graph's number of rows or columns) and the map id -> position among them.
- * gsb_compact_rank builds the rank table in the workspace (presence marks, running sum) and
+ * gsb_compact_rank builds the rank table in the workspace (one presence bit per possible id and
+ * a running sum per 32-bit word: 3/8 of a byte per possible id) and
  * writes the number of distinct ids to d_count (device); gsb_compact_apply then writes the sorted
  * distinct ids (unique[count], may be NULL) and / or maps an id array of the same id set
  * (out[i] = position of ids[i]; -1 for an id that is not below bound).  Replaces
