@@ -289,7 +289,8 @@ __global__ void __launch_bounds__(WB_THREADS) sample_probs_block_kernel(const Pr
   __shared__ u32 s_digit, s_above;
   __shared__ u32 s_top[WB_THREADS];
   __shared__ u64 s_cand[WB_CAND];
-  __shared__ int s_ncand;
+  __shared__ int s_ncand, s_nhit;
+  __shared__ int s_hits[WB_THREADS];  // threads whose largest key reaches the bound
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
   i64 S = p.S_max;
   if (p.d_S) { i64 live = *p.d_S; S = live < S ? (live < 0 ? 0 : live) : S; }
@@ -318,12 +319,21 @@ __global__ void __launch_bounds__(WB_THREADS) sample_probs_block_kernel(const Pr
       }
       __syncthreads();  // the previous column's readers of s_top / s_cand
       s_top[threadIdx.x] = mine;
-      if (threadIdx.x == 0) s_ncand = 0;
+      if (threadIdx.x == 0) { s_ncand = 0; s_nhit = 0; }
       __syncthreads();
       cta_sort_desc(s_top, WB_THREADS);
       const u32 bound = s_top[K - 1];
       if (bound > 0u) {  // pass B: the entries that can still win (0 = weights <= 0 are in play)
-        for (i64 e0 = (i64)threadIdx.x * 4; e0 < deg; e0 += WB_THREADS * 4) {
+        // Only a thread whose own largest key reaches the bound has such entries (about K of the
+        // WB_THREADS threads): the strides of those threads are rescanned, by all threads together
+        // -- one Philox block of four entries per thread and step -- instead of the whole column.
+        if (mine >= bound) s_hits[atomicAdd(&s_nhit, 1)] = threadIdx.x;
+        __syncthreads();
+        const i64 per_thread = (deg + WB_THREADS * 4 - 1) / (WB_THREADS * 4);  // Philox blocks of one thread's stride
+        const i64 todo = (i64)s_nhit * per_thread;
+        for (i64 q = threadIdx.x; q < todo; q += WB_THREADS) {
+          const i64 e0 = (i64)s_hits[q / per_thread] * 4 + (q % per_thread) * (WB_THREADS * 4);
+          if (e0 >= deg) continue;
           const Philox4 blk = stream_block(p.seed, p.stream, (u64)slot, (u32)(e0 >> 2));
 #pragma unroll
           for (int j = 0; j < 4; ++j) {
