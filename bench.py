@@ -47,7 +47,7 @@ sys.path.insert(0, ROOT)
 
 WORKLOADS = {
     "cfg2": dict(kind="sage", nodes=2449029, edges=123718280, train=196615, fanouts=[15, 10, 5], batch=1024,
-                 super_batch=32, index_dtype="int64", max_degree=20000, scaling="weak", graph_seed=2024),
+                 super_batch=32, index_dtype="int64", max_degree=20000, scaling="weak", graph_seed=2024, streams=4),
     "cfg5": dict(kind="sage", nodes=111059956, edges=3200000000, train=1207179, fanouts=[15, 10, 5], batch=1024,
                  super_batch=64, index_dtype="int32", max_degree=100000, scaling="strong", graph_seed=9, large=True),
     # profiling shape: graph larger than L2, a few GB on the device, short kernels
@@ -471,21 +471,23 @@ class SageWorkload(object):
         A._CAPI_LoadCSC(self.indptr, self.indices)
         self.bm = gs.BatchMatrix()
         self.bm.load_from_matrix(gs.Matrix(A), False)
-        self.e2e_streams = [self.torch.cuda.Stream(self.dev) for _ in range(2)]
+        self.e2e_streams = [self.torch.cuda.Stream(self.dev) for _ in range(self.nstreams)]
 
     def e2e_run(self, first, count):
-        """Like a data loader with prefetch depth 2: super-batch k+1 is copied in and enqueued (on the
-        other stream) before the host waits for the sizes of super-batch k.  Every step copies its
-        own seeds from pinned host memory and reads its own result sizes back."""
+        """Like a data loader with a prefetch depth of `streams`: the next super-batches are copied in
+        and enqueued (each on its own stream) before the host waits for the sizes of the oldest one
+        in flight.  Every step copies its own seeds from pinned host memory and reads its own result
+        sizes back."""
         torch, L = self.torch, self.L
+        depth = len(self.e2e_streams)
         edges, nin, nout, pending = 0, 0, 0, []
-        for k in range(count + 1):
+        for k in range(count + depth - 1):
             if k < count:
                 s, p = self.batches_pin[(first + k) % self.nb]
-                with torch.cuda.stream(self.e2e_streams[k % 2]):
+                with torch.cuda.stream(self.e2e_streams[k % depth]):
                     sd, pd = s.to(self.dev, non_blocking=True), p.to(self.dev, non_blocking=True)
                     pending.append((self.bm.graphsage_async(sd, pd, self.cfg["fanouts"]), s.numel() * 8 + p.numel() * 8))
-            if k >= 1:
+            if k >= depth - 1 and pending:
                 fut, nbytes = pending.pop(0)
                 cnt = fut.wait()[-1]
                 edges += int(cnt.view(L, 3)[:, 1].sum())
@@ -493,7 +495,7 @@ class SageWorkload(object):
                 nout += (3 * L + 1) * 8
         return edges, nin, nout
 
-    e2e_api = "BatchMatrix.graphsage_async (one native call per super-batch, two in flight)"
+    e2e_api = "BatchMatrix.graphsage_async (one native call per super-batch, as many in flight as `streams`)"
 
     def describe(self, c_host, world):
         cfg = self.cfg
@@ -797,8 +799,10 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=os.environ.get("GSB_WORKLOAD", "cfg2"), choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--streams", type=int, default=int(os.environ.get("GSB_STREAMS", "2")),
-                    help="independent super-batches in flight (each on its own CUDA stream)")
+    ap.add_argument("--streams", type=int, default=int(os.environ.get("GSB_STREAMS", "0")),
+                    help="independent super-batches in flight, each on its own CUDA stream (default: the "
+                         "workload's own setting -- 4 for cfg2, 2 elsewhere: the 64-minibatch super-batches "
+                         "of cfg5 run slower with 4 in flight, 2.75 against 2.58 ms per step)")
     args = ap.parse_args()
     cfg = WORKLOADS[args.workload]
     rank = int(os.environ.get("RANK", "0"))
@@ -830,7 +834,7 @@ def main():
 
     from gsampler_b200 import pipeline
 
-    wl = KINDS[cfg["kind"]](cfg, dev, rank, world, max(1, args.streams))
+    wl = KINDS[cfg["kind"]](cfg, dev, rank, world, args.streams if args.streams > 0 else cfg.get("streams", 2))
     K, W, R = args.steps, args.warmup, max(1, args.reps)
     wl.alloc_counts(W + K * R + K)
 
