@@ -140,7 +140,6 @@ std::vector<torch::Tensor> Graph::BatchGraphSAGE(torch::Tensor seeds, torch::Ten
   return out;
 }
 
-#define GSB_NOT_YET(name) TORCH_CHECK(false, name ": not implemented in this build")
 
 static int64_t* PM(torch::Tensor& t) { return t.data_ptr<int64_t>(); }
 static torch::TensorOptions I64(const torch::Tensor& like) {
